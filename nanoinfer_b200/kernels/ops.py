@@ -1,0 +1,234 @@
+"""Python entry points of the CUDA kernels.
+
+Each function checks its operands (device, dtype, contiguity, sizes the kernel can take),
+launches on torch's current stream and raises on any error.  Nothing here computes: a
+missing CUDA library or a tensor on the CPU is an error, never a fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional
+
+import torch
+
+from . import build
+
+_I, _F, _P, _LL = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
+
+F32, BF16 = 0, 1
+_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+
+_ERRORS = {-1: "bad argument", -2: "size not supported by this kernel",
+           -3: "a wait inside the kernel ran out (device timeout)"}
+
+# module -> {function: argtypes}
+_SIGNATURES = {
+    "elementwise": {
+        "ni_embedding": [_P, _P, _I, _P, _I, _I, _I, _P],
+        "ni_add_rmsnorm": [_P, _P, _I, _P, _F, _P, _I, _P, _I, _I, _P],
+        "ni_residual_add": [_P, _P, _I, _LL, _P],
+        "ni_swiglu": [_P, _P, _I, _I, _I, _P],
+    },
+    "rope_kv": {
+        "ni_rope_kv_write": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    },
+    "attention_generic": {
+        "ni_attention_generic": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P],
+    },
+    "gemm_f32": {
+        "ni_gemm_f32": [_P, _P, _P, _I, _I, _I, _P],
+    },
+}
+
+_libs: Dict[str, ctypes.CDLL] = {}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def require_cuda() -> None:
+    if not torch.cuda.is_available():
+        raise KernelError("nanoinfer_b200 runs on a CUDA device (sm_100a) only; "
+                          "torch.cuda.is_available() is False and there is no CPU path")
+
+
+def load(module: str) -> ctypes.CDLL:
+    lib = _libs.get(module)
+    if lib is None:
+        path = build.ensure_built([module])[module]
+        lib = ctypes.CDLL(path)
+        for fn, argtypes in _SIGNATURES.get(module, {}).items():
+            f = getattr(lib, fn)
+            f.argtypes = argtypes
+            f.restype = _I
+        _libs[module] = lib
+    return lib
+
+
+def preload(modules) -> None:
+    """Build (in parallel) and load the given modules ahead of their first use."""
+    build.ensure_built(list(modules))
+    for m in modules:
+        load(m)
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{what}: {_ERRORS.get(code, f'error {code}')}")
+    raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dev(t: torch.Tensor, name: str, dtype=None) -> int:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, found {t.dtype}")
+    return t.data_ptr()
+
+
+def _code(t: torch.Tensor, name: str) -> int:
+    if t.dtype not in _DTYPE_CODE:
+        raise KernelError(f"{name}: dtype {t.dtype} is not supported (float32 or bfloat16)")
+    return _DTYPE_CODE[t.dtype]
+
+
+def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, :] = float32(table[tokens[t], :]);  tokens int32 [T], out float32 [T, d]."""
+    n, d = out.shape
+    if tokens.numel() != n or table.shape[1] != d:
+        raise KernelError("embedding: shapes do not agree")
+    _check(load("elementwise").ni_embedding(_dev(tokens, "tokens", torch.int32), _dev(table, "table"),
+                                            _code(table, "table"), _dev(out, "out", torch.float32),
+                                            n, d, table.shape[0], _stream()), "embedding")
+
+
+def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    """Residual add fused with RMSNorm.
+
+    h float32 [T, d]; delta [T, d] or None; gain float32 [d]; out [R, d].
+    rows None: R = T, h += delta in place, out = norm(h) * gain.
+    rows int32 [R]: out[r] = norm(h[rows[r]] + delta[rows[r]]) * gain, h untouched.
+    """
+    d = h.shape[1]
+    n_out = out.shape[0]
+    if out.shape[1] != d or gain.numel() != d:
+        raise KernelError("add_rmsnorm: widths do not agree")
+    if rows is None and n_out != h.shape[0]:
+        raise KernelError("add_rmsnorm: out must have as many rows as h")
+    if rows is not None and rows.numel() != n_out:
+        raise KernelError("add_rmsnorm: rows and out do not agree")
+    if delta is not None and delta.shape != h.shape:
+        raise KernelError("add_rmsnorm: delta must have the shape of h")
+    _check(load("elementwise").ni_add_rmsnorm(
+        _dev(h, "h", torch.float32), _dev(delta, "delta") if delta is not None else None,
+        _code(delta, "delta") if delta is not None else F32, _dev(gain, "gain", torch.float32),
+        float(eps), _dev(out, "out"), _code(out, "out"),
+        _dev(rows, "rows", torch.int32) if rows is not None else None, n_out, d, _stream()),
+        "add_rmsnorm")
+
+
+def residual_add(h: torch.Tensor, delta: torch.Tensor) -> None:
+    if delta.shape != h.shape:
+        raise KernelError("residual_add: shapes do not agree")
+    _check(load("elementwise").ni_residual_add(_dev(h, "h", torch.float32), _dev(delta, "delta"),
+                                               _code(delta, "delta"), h.numel(), _stream()),
+           "residual_add")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    n, inter = out.shape
+    if gate_up.shape != (n, 2 * inter) or gate_up.dtype != out.dtype:
+        raise KernelError("swiglu: gate_up must be [T, 2I] of out's dtype")
+    _check(load("elementwise").ni_swiglu(_dev(gate_up, "gate_up"), _dev(out, "out"),
+                                         _code(out, "out"), n, inter, _stream()), "swiglu")
+
+
+def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, k_pages: Optional[torch.Tensor],
+                  v_pages: Optional[torch.Tensor], positions: torch.Tensor,
+                  seq_of_token: torch.Tensor, block_table: torch.Tensor, inv_freq: torch.Tensor,
+                  n_q_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int,
+                  interleaved: bool, page_size: int) -> None:
+    """Rotate q and k of the fused projection qkv [T, (Hq + 2 Hkv) hd]; q -> q_out
+    [T, Hq hd]; k (rotated) and v -> pages [P, Hkv, page_size, hd] unless k_pages is None."""
+    n = qkv.shape[0]
+    write = k_pages is not None
+    if qkv.shape[1] != (n_q_heads + 2 * n_kv_heads) * head_dim or q_out.shape != (n, n_q_heads * head_dim):
+        raise KernelError("rope_kv_write: widths do not agree with the head counts")
+    if q_out.dtype != qkv.dtype or (write and (k_pages.dtype != qkv.dtype or v_pages.dtype != qkv.dtype)):
+        raise KernelError("rope_kv_write: all operands must share one dtype")
+    if write and tuple(k_pages.shape[1:]) != (n_kv_heads, page_size, head_dim):
+        raise KernelError("rope_kv_write: pages must be [P, Hkv, page_size, head_dim]")
+    if inv_freq.numel() != rotary_dim // 2 and rotary_dim > 0:
+        raise KernelError("rope_kv_write: inv_freq must have rotary_dim / 2 entries")
+    _check(load("rope_kv").ni_rope_kv_write(
+        _dev(qkv, "qkv"), _code(qkv, "qkv"), _dev(q_out, "q_out"),
+        _dev(k_pages, "k_pages") if write else None, _dev(v_pages, "v_pages") if write else None,
+        _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
+        _dev(block_table, "block_table", torch.int32), block_table.shape[1],
+        _dev(inv_freq, "inv_freq", torch.float32), n, n_q_heads, n_kv_heads, head_dim, rotary_dim,
+        1 if interleaved else 0, page_size, 1 if write else 0, _stream()), "rope_kv_write")
+
+
+def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                      out: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                      block_table: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int,
+                      page_size: int, window: Optional[int], scale: float) -> None:
+    n = q.shape[0]
+    if q.shape != (n, n_q_heads * head_dim) or out.shape != q.shape:
+        raise KernelError("attention: q and out must be [T, Hq * head_dim]")
+    if not (q.dtype == out.dtype == k_pages.dtype == v_pages.dtype):
+        raise KernelError("attention: all operands must share one dtype")
+    if head_dim > 256:
+        raise KernelError(f"attention: head_dim {head_dim} > 256 is not supported")
+    _check(load("attention_generic").ni_attention_generic(
+        _dev(q, "q"), _code(q, "q"), _dev(k_pages, "k_pages"), _dev(v_pages, "v_pages"),
+        _dev(out, "out"), _dev(positions, "positions", torch.int32),
+        _dev(seq_of_token, "seq_of_token", torch.int32), _dev(block_table, "block_table", torch.int32),
+        block_table.shape[1], n, n_q_heads, n_kv_heads, head_dim, page_size,
+        int(window) if window else 0, float(scale), _stream()), "attention_generic")
+
+
+def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = x[M, K] . w[N, K]^T, all float32, plain FP32 arithmetic."""
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape != (m, n):
+        raise KernelError("gemm_f32: shapes do not agree")
+    _check(load("gemm_f32").ni_gemm_f32(_dev(x, "x", torch.float32), _dev(w, "w", torch.float32),
+                                        _dev(out, "out", torch.float32), m, n, k, _stream()), "gemm_f32")
+
+
+def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """y = x . w^T for bfloat16 operands with FP32 accumulation.
+
+    The product itself is a library matrix product (cuBLASLt through torch), as the
+    reference's projections are cuBLAS calls (src/op/kernels/cuda/matmul_kernel.cu:76-86).
+    """
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("linear_bf16: operands must be bfloat16")
+    if not x.is_cuda or not w.is_cuda:
+        raise KernelError("linear_bf16: operands must be CUDA tensors")
+    if out_dtype == torch.bfloat16:
+        return torch.matmul(x, w.t())
+    return torch.mm(x, w.t(), out_dtype=torch.float32)
+
+
+def attention(q, k_pages, v_pages, out, ctx, block_table, n_q_heads, n_kv_heads, head_dim,
+              page_size, window, scale) -> None:
+    """Attention of every token of the step over its own request's cache.
+
+    ``ctx`` is the step context (positions, seq_of_token and per-request segments).
+    """
+    attention_generic(q, k_pages, v_pages, out, ctx.positions, ctx.seq_of_token, block_table,
+                      n_q_heads, n_kv_heads, head_dim, page_size, window, scale)

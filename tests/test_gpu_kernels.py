@@ -1,0 +1,178 @@
+"""Each kernel alone against a plain FP32 computation of the same op, at sizes other than
+the engine tests': widths and vocabularies that are no power of two, head sizes in steps of
+16, odd head counts and page sizes."""
+import math
+
+import pytest
+import torch
+
+import plain_llama as plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def _tol(dtype):
+    # float32: rounding in a different order.  bfloat16: the kernels compute in FP32 and round
+    # the result once: one unit in the last place of bfloat16 (2^-8) plus cancellation slack.
+    return dict(rtol=1e-5, atol=1e-6) if dtype == torch.float32 else dict(rtol=4e-3, atol=1e-3)
+
+
+def _randn(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d,vocab", [(64, 100), (120, 1000), (2056, 333)])
+def test_embedding(dtype, d, vocab):
+    from nanoinfer_b200.kernels import ops
+    table = _randn(vocab, d, dtype=dtype)
+    tokens = torch.randint(0, vocab, (37,), generator=torch.Generator().manual_seed(1)).int().to(DEV)
+    out = torch.empty(37, d, dtype=torch.float32, device=DEV)
+    ops.embedding(tokens, table, out)
+    assert torch.equal(out.cpu(), plain.embedding(table.cpu(), tokens.cpu()))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d,eps", [(64, 1e-5), (120, 1e-6), (2056, 1e-5), (8200, 1e-3)])
+def test_add_rmsnorm(dtype, d, eps):
+    from nanoinfer_b200.kernels import ops
+    n = 19
+    h = _randn(n, d, seed=1)
+    delta = _randn(n, d, dtype=dtype, seed=2)
+    gain = _randn(d, seed=3) + 1.0
+    want_h = h.cpu() + delta.cpu().float()
+    want = plain.rms_norm(want_h, gain.cpu(), eps)
+    out = torch.empty(n, d, dtype=dtype, device=DEV)
+    h1 = h.clone()
+    ops.add_rmsnorm(h1, delta, gain, eps, out)
+    torch.testing.assert_close(h1.cpu(), want_h, rtol=0, atol=0)
+    torch.testing.assert_close(out.cpu().float(), want, **_tol(dtype))
+    # without an addition
+    h2 = h.clone()
+    ops.add_rmsnorm(h2, None, gain, eps, out)
+    assert torch.equal(h2, h)
+    torch.testing.assert_close(out.cpu().float(), plain.rms_norm(h.cpu(), gain.cpu(), eps), **_tol(dtype))
+    # selected rows only: h untouched, rows may repeat
+    rows = torch.tensor([18, 0, 7, 7], dtype=torch.int32, device=DEV)
+    out_r = torch.empty(4, d, dtype=dtype, device=DEV)
+    h3 = h.clone()
+    ops.add_rmsnorm(h3, delta, gain, eps, out_r, rows)
+    assert torch.equal(h3, h)
+    torch.testing.assert_close(out_r.cpu().float(), want[rows.cpu().long()], **_tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("inter", [192, 200, 8200])
+def test_swiglu(dtype, inter):
+    from nanoinfer_b200.kernels import ops
+    gu = _randn(11, 2 * inter, dtype=dtype, scale=3.0)
+    out = torch.empty(11, inter, dtype=dtype, device=DEV)
+    ops.swiglu(gu, out)
+    g, u = gu.cpu().float()[:, :inter], gu.cpu().float()[:, inter:]
+    torch.testing.assert_close(out.cpu().float(), (g / (1 + torch.exp(-g))) * u, **_tol(dtype))
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 64, 64), (7, 100, 120), (65, 333, 200), (130, 64, 2056)])
+def test_gemm_f32(m, n, k):
+    from nanoinfer_b200.kernels import ops
+    x, w = _randn(m, k, seed=1), _randn(n, k, seed=2)
+    out = torch.empty(m, n, dtype=torch.float32, device=DEV)
+    ops.gemm_f32(x, w, out)
+    want = (x.cpu().double() @ w.cpu().double().t()).float()
+    torch.testing.assert_close(out.cpu(), want, rtol=1e-5, atol=1e-5 * math.sqrt(k))
+    # a row's result does not depend on the rows beside it
+    out1 = torch.empty(1, n, dtype=torch.float32, device=DEV)
+    ops.gemm_f32(x[m - 1:m].contiguous(), w, out1)
+    assert torch.equal(out1[0], out[m - 1])
+
+
+def _paged_setup(T_per_seq, n_kv, hd, page, dtype, seed):
+    """Random k/v for sequences of the given lengths, scattered over shuffled pages."""
+    g = torch.Generator().manual_seed(seed)
+    n_seq = len(T_per_seq)
+    width = max(-(-t // page) for t in T_per_seq)
+    n_pages = sum(-(-t // page) for t in T_per_seq) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    table = torch.full((n_seq, width), -1, dtype=torch.int32)
+    ks, vs = [], []
+    k_pages = torch.zeros(n_pages, n_kv, page, hd, dtype=dtype)
+    v_pages = torch.zeros_like(k_pages)
+    for s, t in enumerate(T_per_seq):
+        k = (torch.randn(t, n_kv, hd, generator=g)).to(dtype)
+        v = (torch.randn(t, n_kv, hd, generator=g)).to(dtype)
+        ks.append(k); vs.append(v)
+        for j in range(t):
+            if j % page == 0:
+                table[s, j // page] = perm.pop()
+            p = table[s, j // page]
+            k_pages[p, :, j % page] = k[j]
+            v_pages[p, :, j % page] = v[j]
+    return table, k_pages, v_pages, ks, vs
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_q,n_kv,hd,page,window", [(4, 2, 16, 16, None), (3, 1, 32, 8, None),
+                                                      (6, 3, 48, 4, 20), (5, 5, 80, 16, None),
+                                                      (8, 2, 128, 32, 100), (2, 1, 256, 16, None)])
+def test_attention_generic(dtype, n_q, n_kv, hd, page, window):
+    from nanoinfer_b200.kernels import ops
+    lens = [37, 1, 150]
+    table, k_pages, v_pages, ks, vs = _paged_setup(lens, n_kv, hd, page, dtype, seed=hd)
+    # queries: the last 5 tokens of seq 0, the only token of seq 1, tokens 100..149 of seq 2
+    spans = [(32, 37), (0, 1), (100, 150)]
+    g = torch.Generator().manual_seed(5)
+    qs = [torch.randn(t, n_q, hd, generator=g).to(dtype) for t in lens]
+    q = torch.cat([qs[s][a:b] for s, (a, b) in enumerate(spans)]).reshape(-1, n_q * hd)
+    positions = torch.cat([torch.arange(a, b) for a, b in spans]).int()
+    seq_of = torch.cat([torch.full((b - a,), s) for s, (a, b) in enumerate(spans)]).int()
+    out = torch.empty_like(q).to(DEV)
+    scale = 1.0 / math.sqrt(hd)
+    ops.attention_generic(q.to(DEV), k_pages.to(DEV), v_pages.to(DEV), out, positions.to(DEV),
+                          seq_of.to(DEV), table.to(DEV), n_q, n_kv, hd, page, window, scale)
+    want = torch.cat([plain.attention(qs[s], ks[s], vs[s], scale, window)[a:b]
+                      for s, (a, b) in enumerate(spans)]).reshape(-1, n_q * hd)
+    torch.testing.assert_close(out.cpu().float(), want, **_tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("pairing", ["half", "interleaved"])
+@pytest.mark.parametrize("n_q,n_kv,hd,rot,page", [(4, 2, 16, 16, 16), (3, 1, 32, 32, 8), (6, 3, 48, 32, 4),
+                                                  (5, 5, 80, 80, 16)])
+def test_rope_kv_write(dtype, pairing, n_q, n_kv, hd, rot, page):
+    from nanoinfer_b200.kernels import ops
+    lens = [9, 70]
+    starts = [4, 60]          # tokens [start, len) of each sequence are in this step
+    width = max(-(-t // page) for t in lens)
+    n_pages = 2 * width + 2
+    g = torch.Generator().manual_seed(rot)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    table = torch.tensor([[perm.pop() for _ in range(width)] for _ in lens], dtype=torch.int32)
+    positions = torch.cat([torch.arange(s, t) for s, t in zip(starts, lens)]).int()
+    seq_of = torch.cat([torch.full((t - s,), i) for i, (s, t) in enumerate(zip(starts, lens))]).int()
+    T = positions.numel()
+    qkv = torch.randn(T, (n_q + 2 * n_kv) * hd, generator=g).to(dtype)
+    inv_freq = plain.rope_inv_freq(rot, 10000.0, None)
+    q_out = torch.empty(T, n_q * hd, dtype=dtype, device=DEV)
+    k_pages = torch.full((n_pages, n_kv, page, hd), 7.0, dtype=dtype, device=DEV)
+    v_pages = torch.full((n_pages, n_kv, page, hd), 7.0, dtype=dtype, device=DEV)
+    ops.rope_kv_write(qkv.to(DEV), q_out, k_pages, v_pages, positions.to(DEV), seq_of.to(DEV),
+                      table.to(DEV), inv_freq.to(DEV), n_q, n_kv, hd, rot, pairing == "interleaved", page)
+    qf = qkv.float()
+    q = plain.rope(qf[:, :n_q * hd].view(T, n_q, hd), positions, inv_freq, pairing)
+    k = plain.rope(qf[:, n_q * hd:(n_q + n_kv) * hd].view(T, n_kv, hd), positions, inv_freq, pairing)
+    v = qf[:, (n_q + n_kv) * hd:].view(T, n_kv, hd)
+    torch.testing.assert_close(q_out.cpu().float().view(T, n_q, hd), q, **_tol(dtype))
+    touched = torch.zeros(n_pages, page, dtype=torch.bool)
+    kp, vp = k_pages.cpu().float(), v_pages.cpu().float()
+    for t in range(T):
+        p, slot = table[seq_of[t], positions[t] // page], positions[t] % page
+        torch.testing.assert_close(kp[p, :, slot], k[t], **_tol(dtype))
+        torch.testing.assert_close(vp[p, :, slot], v[t].to(dtype).float(), rtol=0, atol=0)
+        touched[p, slot] = True
+    # nothing else was written
+    assert torch.all(kp.permute(0, 2, 1, 3)[~touched] == 7.0)
+    assert torch.all(vp.permute(0, 2, 1, 3)[~touched] == 7.0)

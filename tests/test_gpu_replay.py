@@ -1,0 +1,112 @@
+"""Replay on the GPU against the plain implementation: the same requests whole, with the
+last 32 tokens one by one, in portions of changing size, and mixed with other requests so
+that pages are used again - in 32-bit and in bfloat16."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import replay_util as ru
+from helpers import load_plain, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+# per configuration: page size and request lengths (up to max_position_embeddings)
+SETUP = {
+    "a": (16, [5, 17, 33, 64, 100, 128]),
+    "b": (8, [1, 7, 40, 90, 130, 300, 47]),
+    "c": (16, [3, 48, 250, 611, 97]),
+}
+CUTS = {"whole": ru.whole, "tail": ru.tail_by_token, "ragged": ru.ragged, "mixed": ru.mixed}
+
+
+def _requests(raw, lens, seed):
+    return {f"r{i}": random_tokens(raw["vocab_size"], n, seed * 100 + i) for i, n in enumerate(lens)}
+
+
+@pytest.fixture(scope="module")
+def plain_cache():
+    return {}
+
+
+def _plain(plain_cache, key, model_dir):
+    if key not in plain_cache:
+        raw, w = load_plain(model_dir)
+        page, lens = SETUP[key]
+        reqs = _requests(raw, lens, seed=ord(key))
+        plain_cache[key] = (raw, reqs, ru.plain_logits(raw, w, reqs))
+    return plain_cache[key]
+
+
+def _runner(model_dir, dtype, page, steps):
+    from nanoinfer_b200.config import load_config
+    from nanoinfer_b200.engine import ModelRunner
+    from nanoinfer_b200.weights import load_weights
+    cfg = load_config(model_dir)
+    # exactly as many pages as the trace needs at its fullest (requests rounded up to 64)
+    num_pages = ru.max_live_tokens(steps, 64) // page
+    return ModelRunner(cfg, load_weights(model_dir, cfg), dtype=dtype, page_size=page,
+                       num_pages=num_pages, max_requests=4)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cut", ["whole", "tail", "ragged", "mixed"])
+@pytest.mark.parametrize("key", ["a", "b", "c"])
+def test_replay_matches_plain(model_dirs, plain_cache, key, cut, dtype):
+    raw, reqs, want = _plain(plain_cache, key, model_dirs[key])
+    steps = CUTS[cut](reqs)
+    runner = _runner(model_dirs[key], dtype, SETUP[key][0], steps)
+    got = ru.run_trace(runner, steps)
+    assert len(got) == sum(len(t) for t in reqs.values())
+    ru.compare(got, want, dtype, label=f"{key}/{cut}/{dtype}")
+    runner.cache.check_consistency()
+    assert runner.cache.num_free_pages(0) == runner.cache.pools[0].num_pages
+
+
+@pytest.mark.parametrize("key", ["a", "b"])
+def test_cuts_agree_bitwise_in_float32(model_dirs, plain_cache, key):
+    """The 32-bit path fixes the order of every sum, so the cut cannot change a single bit."""
+    raw, reqs, _ = _plain(plain_cache, key, model_dirs[key])
+    results = {}
+    for cut, fn in CUTS.items():
+        steps = fn(reqs)
+        results[cut] = ru.run_trace(_runner(model_dirs[key], "float32", SETUP[key][0], steps), steps)
+    for cut in ("tail", "ragged", "mixed"):
+        for k, row in results["whole"].items():
+            assert torch.equal(row, results[cut][k]), f"{key}: {cut} differs from whole at {k}"
+
+
+def test_trace_run_program(model_dirs, tmp_path):
+    """bin/trace_run as a user runs it: JSON lines in, <step>.f32 files and 'done' lines out."""
+    raw, w = load_plain(model_dirs["a"])
+    reqs = _requests(raw, [33, 70, 20], seed=7)
+    steps = ru.mixed(reqs, max_live=2)
+    out = tmp_path / "out"
+    proc = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dirs["a"], "--dtype",
+         "float32", "--out", str(out), "--max-tokens", str(ru.max_live_tokens(steps, 64))],
+        input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {s['step']}" for s in steps]
+    want = ru.plain_logits(raw, w, reqs)
+    fed = {}
+    for s in steps:
+        n_want = sum(len(e["want"]) for e in s["entries"])
+        path = out / f"{s['step']}.f32"
+        if n_want == 0:
+            assert not path.exists()
+            continue
+        logits = torch.from_numpy(np.fromfile(path, dtype="<f4").reshape(n_want, raw["vocab_size"]))
+        r = 0
+        for e in s["entries"]:
+            base = fed.get(e["id"], 0)
+            for wpos in e["want"]:
+                torch.testing.assert_close(logits[r], want[e["id"]][base + wpos], rtol=ru.F32_RTOL, atol=ru.F32_ATOL)
+                r += 1
+            fed[e["id"]] = base + len(e["tokens"])

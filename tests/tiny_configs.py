@@ -1,0 +1,34 @@
+"""The tiny Llama configurations of the tests, as config.json dictionaries.
+
+A and B differ in every size and option: layers, width, head counts and grouping, head
+size, feed-forward width, vocabulary, rope theta and scaling, eps, tied or untied output.
+C has sizes that are no power of two and a head size of 48.
+"""
+TINY_A = {
+    "architectures": ["LlamaForCausalLM"],
+    "hidden_size": 64, "intermediate_size": 192, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16,
+    "vocab_size": 256, "max_position_embeddings": 128, "rms_norm_eps": 1e-5,
+    "rope_theta": 10000.0, "rope_scaling": None, "tie_word_embeddings": True,
+    "hidden_act": "silu", "bos_token_id": 1, "eos_token_id": 2,
+}
+TINY_B = {
+    "architectures": ["LlamaForCausalLM"],
+    "hidden_size": 96, "intermediate_size": 256, "num_hidden_layers": 3,
+    "num_attention_heads": 3, "num_key_value_heads": 1, "head_dim": 32,
+    "vocab_size": 384, "max_position_embeddings": 512, "rms_norm_eps": 1e-6,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 64},
+    "tie_word_embeddings": False, "hidden_act": "silu", "eos_token_id": [2, 3],
+}
+TINY_C = {
+    "architectures": ["LlamaForCausalLM"],
+    "hidden_size": 120, "intermediate_size": 200, "num_hidden_layers": 2,
+    "num_attention_heads": 6, "num_key_value_heads": 3, "head_dim": 48,
+    "vocab_size": 1000, "max_position_embeddings": 2048, "rms_norm_eps": 1e-5,
+    "rope_theta": 10000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 256},
+    "tie_word_embeddings": True, "hidden_act": "silu",
+}
