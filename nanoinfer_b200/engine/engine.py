@@ -1,0 +1,169 @@
+"""The engine: requests in, tokens out.  Scheduler -> step function -> sampler, every step.
+
+Same public surface as the reference's Engine (include/nanoinfer/engine/engine.h:23-105):
+EngineConfig with its field names and defaults, add_request / step / run / stop / has_work /
+get_request / get_request_result / get_scheduler_stats.  Requests are given as token ids
+(tokenisation is outside this engine).
+"""
+from __future__ import annotations
+
+import os
+import time
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..sampling import Sampler, SamplingParams
+from .request import InferenceRequest, RequestState
+from .scheduler import ScheduledBatch, Scheduler, SchedulerStats
+from .step import ModelRunner, StepEntry
+
+
+@dataclass
+class EngineConfig:
+    max_batch_size: int = 32            # requests in one step
+    max_sequences: int = 128            # requests running at once
+    prefill_chunk_size: int = 512       # most prompt tokens of one request per step
+    block_size: int = 16                # tokens per cache page
+    num_cache_blocks: int = 1024        # pages in the pool
+    max_num_batched_tokens: int = 2048  # token budget of one step
+    max_model_len: Optional[int] = None  # most tokens a request may hold (default: model limit)
+    dtype: str = "bfloat16"
+    device: str = "cuda:0"
+
+
+@dataclass
+class StepOutput:
+    request_id: int
+    token: int
+    finished: bool
+
+
+class Engine:
+    def __init__(self, runner, sampler=None, config: Optional[EngineConfig] = None,
+                 stop_token_ids: Sequence[int] = ()) -> None:
+        """``runner`` provides .cache (a CacheManager), .step(entries) -> logits, .end(request)
+        and .config.vocab_size; ``sampler`` provides .sample(...).  Use ``from_model_dir`` for
+        the usual construction."""
+        self.config = config or EngineConfig()
+        self.runner = runner
+        self.sampler = sampler
+        self.stop_token_ids = tuple(stop_token_ids)
+        self.scheduler = Scheduler(runner.cache, self.config.max_batch_size, self.config.max_sequences,
+                                   self.config.prefill_chunk_size, self.config.max_num_batched_tokens)
+        self._next_id = 0
+        self._running = False
+        self.num_steps = 0
+
+    @classmethod
+    def from_model_dir(cls, model_dir: str, config: Optional[EngineConfig] = None, **overrides) -> "Engine":
+        from ..config import load_config
+        from ..weights import load_weights
+        cfg = config or EngineConfig()
+        for k, v in overrides.items():
+            if not hasattr(cfg, k):
+                raise TypeError(f"unknown engine option '{k}'")
+            setattr(cfg, k, v)
+        model_config = load_config(model_dir)
+        weights = load_weights(model_dir, model_config)
+        return cls.from_weights(model_config, weights, cfg)
+
+    @classmethod
+    def from_weights(cls, model_config, weights, config: Optional[EngineConfig] = None) -> "Engine":
+        cfg = config or EngineConfig()
+        runner = ModelRunner(model_config, weights, dtype=cfg.dtype, page_size=cfg.block_size,
+                             num_pages=cfg.num_cache_blocks, max_requests=cfg.max_sequences,
+                             max_tokens_per_request=cfg.max_model_len, device=cfg.device)
+        sampler = Sampler(model_config.vocab_size, runner.rt.device)
+        return cls(runner, sampler, cfg, stop_token_ids=model_config.eos_token_ids)
+
+    # ---- requests -------------------------------------------------------------------------
+    def add_request(self, prompt_tokens: Sequence[int], max_new_tokens: int = 128,
+                    sampling_params: Optional[SamplingParams] = None) -> int:
+        """Queue a request; returns its id.  Raises ValueError for a request that can never
+        run (empty, bad token id, longer than the model or the pool allow)."""
+        sp = sampling_params or SamplingParams()
+        sp.validate()
+        prompt = [int(t) for t in prompt_tokens]
+        vocab = self.runner.config.vocab_size
+        if not prompt:
+            raise ValueError("a request needs at least one prompt token")
+        if max_new_tokens <= 0:
+            raise ValueError("max_new_tokens must be positive")
+        bad = [t for t in prompt if not 0 <= t < vocab]
+        if bad:
+            raise ValueError(f"token id {bad[0]} is outside [0, {vocab})")
+        cache = self.runner.cache
+        limit = cache.max_tokens_per_request
+        if len(prompt) + 1 > limit:
+            raise ValueError(f"a prompt of {len(prompt)} tokens leaves no room to generate within the "
+                             f"limit of {limit} tokens per request")
+        pool_tokens = min(p.num_pages for p in cache.pools) * cache.page_size
+        if len(prompt) + 1 > pool_tokens:
+            raise ValueError(f"a prompt of {len(prompt)} tokens does not fit the cache pool of "
+                             f"{pool_tokens} tokens")
+        max_new_tokens = min(max_new_tokens, limit - len(prompt))
+        seed = sp.seed if sp.seed >= 0 else int.from_bytes(os.urandom(7), "little")
+        rid = self._next_id
+        self._next_id += 1
+        self.scheduler.add_request(InferenceRequest(rid, prompt, max_new_tokens, sp, seed, self.stop_token_ids))
+        return rid
+
+    def get_request(self, request_id: int) -> InferenceRequest:
+        return self.scheduler.requests[request_id]
+
+    def get_request_result(self, request_id: int) -> List[int]:
+        """The tokens generated so far for the request."""
+        return list(self.scheduler.requests[request_id].generated_tokens)
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    def get_scheduler_stats(self) -> SchedulerStats:
+        return self.scheduler.stats()
+
+    # ---- stepping -------------------------------------------------------------------------
+    def step(self) -> List[StepOutput]:
+        """One scheduling decision, one forward pass over its batch, one token for every
+        request whose last pending token was in it."""
+        batch = self.scheduler.schedule()
+        if not batch.entries:
+            return []
+        entries, emitting = [], []
+        for req, n in batch.entries:
+            want = [n - 1] if n == req.num_remaining else []
+            entries.append(StepEntry(req.request_id, req.next_tokens(n), want))
+            if want:
+                emitting.append(req)
+        logits = self.runner.step(entries)
+        sampled: Dict[int, int] = {}
+        if emitting:
+            ids = self.sampler.sample(
+                logits, [r.sampling_params for r in emitting], [r.seed for r in emitting],
+                [len(r.generated_tokens) for r in emitting], [r.generated_tokens for r in emitting])
+            for req, tok in zip(emitting, ids.tolist()):
+                sampled[req.request_id] = int(tok)
+        finished = self.scheduler.update_after_step(batch, sampled)
+        self.num_steps += 1
+        done = {r.request_id for r in finished}
+        return [StepOutput(rid, tok, rid in done) for rid, tok in sampled.items()]
+
+    def run(self) -> None:
+        """Step until no request is waiting or running (or stop() is called)."""
+        self._running = True
+        while self._running and self.has_work():
+            self.step()
+        self._running = False
+
+    def stop(self) -> None:
+        self._running = False
+
+    def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 128,
+                 sampling_params: Optional[SamplingParams] = None) -> List[List[int]]:
+        """Generate for a list of token-id prompts; returns the generated ids per prompt."""
+        if sampling_params is None or isinstance(sampling_params, SamplingParams):
+            sampling_params = [sampling_params] * len(prompts)
+        ids = [self.add_request(p, max_new_tokens, sp) for p, sp in zip(prompts, sampling_params)]
+        self.run()
+        return [self.get_request_result(i) for i in ids]

@@ -76,6 +76,38 @@ class StepContext:
     max_kv_len: int = 0
 
 
+def reserve_entries(cache: CacheManager, entries: Sequence[StepEntry], admit) -> List[int]:
+    """Take slots and pages for every entry of a step, all or nothing.
+
+    Every group's pool and the slot count are checked before anything is taken, so a step
+    that does not fit raises OutOfPages (or StepError) and leaves the cache unchanged.
+    ``admit(request)`` is called for requests the cache does not know yet.  Returns each
+    entry's start position (its cached length before this step).
+    """
+    need = [0] * len(cache.groups)
+    new_requests = 0
+    for e in entries:
+        if cache.has(e.request):
+            per_group = cache.pages_needed(e.request, len(e.tokens))
+        else:
+            per_group = cache.pages_for_new_request(len(e.tokens))
+            new_requests += 1
+        need = [a + b for a, b in zip(need, per_group)]
+    if new_requests > cache.num_free_slots:
+        raise StepError(f"{new_requests} new requests but only {cache.num_free_slots} free slots")
+    for g, n in enumerate(need):
+        if n > cache.num_free_pages(g):
+            raise OutOfPages(f"group {g}: the step needs {n} more pages, "
+                             f"{cache.num_free_pages(g)} are free")
+    for e in entries:
+        if not cache.has(e.request):
+            admit(e.request)
+    starts = [cache.length(e.request) for e in entries]
+    for e in entries:
+        cache.append(e.request, len(e.tokens))
+    return starts
+
+
 def _round_up(n: int, m: int) -> int:
     return -(-n // m) * m
 
@@ -183,28 +215,7 @@ class ModelRunner:
     def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
         """Take pages for the entries' tokens and upload the step's metadata."""
         cache = self.cache
-        # all or nothing: check every group's pool and the slots before taking anything
-        need = [0] * len(cache.groups)
-        new_requests = 0
-        for e in entries:
-            if cache.has(e.request):
-                per_group = cache.pages_needed(e.request, len(e.tokens))
-            else:
-                per_group = cache.pages_for_new_request(len(e.tokens))
-                new_requests += 1
-            need = [a + b for a, b in zip(need, per_group)]
-        if new_requests > cache.num_free_slots:
-            raise StepError(f"{new_requests} new requests but only {cache.num_free_slots} free slots")
-        for g, n in enumerate(need):
-            if n > cache.num_free_pages(g):
-                raise OutOfPages(f"group {g}: the step needs {n} more pages, "
-                                 f"{cache.num_free_pages(g)} are free")
-        for e in entries:
-            if not cache.has(e.request):
-                self.admit(e.request)
-        starts = [cache.length(e.request) for e in entries]
-        for e in entries:
-            cache.append(e.request, len(e.tokens))
+        starts = reserve_entries(cache, entries, self.admit)
         q_lens = [len(e.tokens) for e in entries]
         kv_lens = [s + q for s, q in zip(starts, q_lens)]
         slots = [cache.slot(e.request) for e in entries]

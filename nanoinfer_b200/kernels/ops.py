@@ -38,6 +38,11 @@ _SIGNATURES = {
     "gemm_f32": {
         "ni_gemm_f32": [_P, _P, _P, _I, _I, _I, _P],
     },
+    "sampling": {
+        "ni_argmax": [_P, _P, _I, _I, _P],
+        "ni_repetition_penalty": [_P, _P, _P, _I, _I, _I, _P],
+        "ni_sample": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P],
+    },
 }
 
 _libs: Dict[str, ctypes.CDLL] = {}
@@ -232,3 +237,35 @@ def attention(q, k_pages, v_pages, out, ctx, block_table, n_q_heads, n_kv_heads,
     """
     attention_generic(q, k_pages, v_pages, out, ctx.positions, ctx.seq_of_token, block_table,
                       n_q_heads, n_kv_heads, head_dim, page_size, window, scale)
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = index of the largest logit of row r, ties to the lowest index."""
+    n, v = logits.shape
+    _check(load("sampling").ni_argmax(_dev(logits, "logits", torch.float32), _dev(out, "out", torch.int32),
+                                      n, v, _stream()), "argmax")
+
+
+def repetition_penalty(logits: torch.Tensor, ids: torch.Tensor, penalties: torch.Tensor) -> None:
+    """In place: logits[r, id] = l / p if l > 0 else l * p for the ids listed in row r of
+    ``ids`` (int32 [R, W], padded with -1, each id at most once per row)."""
+    n, v = logits.shape
+    if ids.shape[0] != n or penalties.numel() != n:
+        raise KernelError("repetition_penalty: one id list and one penalty per row")
+    _check(load("sampling").ni_repetition_penalty(
+        _dev(logits, "logits", torch.float32), _dev(ids, "ids", torch.int32),
+        _dev(penalties, "penalties", torch.float32), n, v, ids.shape[1], _stream()), "repetition_penalty")
+
+
+def sample(logits, out, temperatures, top_ks, top_ps, seeds, counters) -> None:
+    """One token per row by the row's own parameters; seeds and counters are 64-bit."""
+    n, v = logits.shape
+    for name, t in (("temperatures", temperatures), ("top_ks", top_ks), ("top_ps", top_ps),
+                    ("seeds", seeds), ("counters", counters)):
+        if t.numel() != n:
+            raise KernelError(f"sample: {name} must have one entry per row")
+    _check(load("sampling").ni_sample(
+        _dev(logits, "logits", torch.float32), _dev(out, "out", torch.int32),
+        _dev(temperatures, "temperatures", torch.float32), _dev(top_ks, "top_ks", torch.int32),
+        _dev(top_ps, "top_ps", torch.float32), _dev(seeds, "seeds", torch.int64),
+        _dev(counters, "counters", torch.int64), n, v, _stream()), "sample")

@@ -1,0 +1,122 @@
+"""Generation through the Python entry point and the command line against the plain
+implementation: greedy, temperature sampling, few pages (preemption), first tokens."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_llama as plain
+import plain_sampling as ps
+from helpers import load_plain, random_tokens
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _check_greedy(raw, w, prompt, generated, dtype):
+    """Every generated token is the plain arg-max given the tokens before it - unless the
+    plain top-2 logits are closer than the precision of the engine's dtype can tell apart."""
+    seq = list(prompt)
+    for i, tok in enumerate(generated):
+        logits = plain.forward(raw, w, seq)[-1]
+        top2 = torch.topk(logits, 2).values
+        tol = 1e-4 if dtype == "float32" else 0.05 * logits.abs().max().item()
+        if int(torch.argmax(logits)) != tok:
+            assert (top2[0] - logits[tok]).item() <= tol, f"token {i}: engine {tok}, plain {int(torch.argmax(logits))}"
+        seq.append(tok)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key,page,lens,n_new", [("a", 16, [5, 17, 33], 16), ("b", 8, [1, 7, 40, 90, 130], 24)])
+def test_greedy_generation_matches_plain(model_dirs, key, page, lens, n_new, dtype):
+    from nanoinfer_b200 import Engine, SamplingParams
+    raw, w = load_plain(model_dirs[key])
+    raw = dict(raw, eos_token_id=None)
+    prompts = [random_tokens(raw["vocab_size"], n, 50 + i) for i, n in enumerate(lens)]
+    eng = Engine.from_model_dir(model_dirs[key], dtype=dtype, block_size=page, num_cache_blocks=64,
+                                max_sequences=8, prefill_chunk_size=24)
+    eng.stop_token_ids = ()
+    outs = eng.generate(prompts, max_new_tokens=n_new, sampling_params=SamplingParams.greedy())
+    for p, o in zip(prompts, outs):
+        assert len(o) == n_new
+        _check_greedy(raw, w, p, o, dtype)
+        if dtype == "float32":
+            assert o == plain.greedy_generate(raw, w, p, n_new)
+    eng.runner.cache.check_consistency()
+    assert eng.runner.cache.num_free_pages() == 64
+
+
+def test_temperature_generation_follows_the_plain_stream(model_dirs):
+    from nanoinfer_b200 import Engine, SamplingParams
+    raw, w = load_plain(model_dirs["b"])
+    prompts = [random_tokens(raw["vocab_size"], n, 70 + i) for i, n in enumerate([1, 7, 40, 90, 130])]
+    eng = Engine.from_model_dir(model_dirs["b"], dtype="float32", block_size=8, num_cache_blocks=64,
+                                max_sequences=8, prefill_chunk_size=24)
+    eng.stop_token_ids = ()
+    sp = SamplingParams(temperature=0.7, seed=1)
+    outs = eng.generate(prompts, max_new_tokens=24, sampling_params=sp)
+    for p, o in zip(prompts, outs):
+        seq = list(p)
+        for i, tok in enumerate(o):
+            want, margin = ps.sample(plain.forward(raw, w, seq)[-1], 0.7, seed=1, index=i)
+            assert tok == want or margin < 1e-4, f"token {i}: engine {tok}, plain {want}"
+            seq.append(tok)
+    # the same requests one at a time give the same tokens: the stream does not depend on batching
+    eng2 = Engine.from_model_dir(model_dirs["b"], dtype="float32", block_size=8, num_cache_blocks=64,
+                                 max_sequences=1, prefill_chunk_size=512)
+    eng2.stop_token_ids = ()
+    assert eng2.generate(prompts, max_new_tokens=24, sampling_params=sp) == outs
+
+
+def test_few_pages_force_preemption_and_tokens_stay_the_same(model_dirs):
+    from nanoinfer_b200 import Engine, SamplingParams
+    raw, w = load_plain(model_dirs["a"])
+    prompts = [random_tokens(raw["vocab_size"], n, 90 + i) for i, n in enumerate([30, 28, 25])]
+    eng = Engine.from_model_dir(model_dirs["a"], dtype="float32", block_size=16, num_cache_blocks=7,
+                                max_sequences=4, prefill_chunk_size=16)
+    eng.stop_token_ids = ()
+    outs = eng.generate(prompts, max_new_tokens=40, sampling_params=SamplingParams.greedy())
+    assert eng.get_scheduler_stats().num_preemptions >= 1
+    for p, o in zip(prompts, outs):
+        assert o == plain.greedy_generate(raw, w, p, 40)
+    assert eng.runner.cache.num_free_pages() == 7
+
+
+def test_stop_token_from_config_ends_generation(model_dirs):
+    from nanoinfer_b200 import Engine, SamplingParams
+    raw, w = load_plain(model_dirs["a"])
+    prompt = random_tokens(raw["vocab_size"], 9, 3)
+    free_run = plain.greedy_generate(raw, w, prompt, 12)
+    eng = Engine.from_model_dir(model_dirs["a"], dtype="float32")
+    eng.stop_token_ids = (free_run[4],)
+    first = free_run.index(free_run[4])
+    out = eng.generate([prompt], max_new_tokens=12, sampling_params=SamplingParams.greedy())[0]
+    assert out == free_run[:first + 1]
+    assert eng.get_request(0).finish_reason == "stop"
+
+
+def test_command_line(model_dirs, tmp_path):
+    raw, w = load_plain(model_dirs["a"])
+    prompt = random_tokens(raw["vocab_size"], 11, 4)
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "nanoinfer"), "generate", "--model",
+                           model_dirs["a"], "--dtype", "float32", "--prompt-ids", ",".join(map(str, prompt)),
+                           "--max-new-tokens", "8", "--temperature", "0"], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    rec = json.loads(proc.stdout.splitlines()[0])
+    want = plain.greedy_generate(raw, w, prompt, 8)
+    stop = set([raw["eos_token_id"]]) if isinstance(raw["eos_token_id"], int) else set(raw["eos_token_id"] or [])
+    cut = next((i + 1 for i, t in enumerate(want) if t in stop), len(want))
+    assert rec["generated"] == want[:cut]
+    # random-model writes a folder the loader accepts
+    cfg = tmp_path / "c.json"
+    cfg.write_text(json.dumps(raw))
+    out = tmp_path / "m"
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "nanoinfer"), "random-model", "--config",
+                           str(cfg), "--seed", "0", "--out", str(out)], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    from safetensors.torch import load_file
+    again = load_file(str(out / "model.safetensors"))
+    assert all(torch.equal(again[k].float(), w[k]) for k in w)
