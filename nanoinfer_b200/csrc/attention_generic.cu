@@ -1,7 +1,8 @@
 // Causal grouped-query attention over the paged cache, the plain way: one warp per
 // (token, query head), keys visited one by one in ascending position with an online
 // softmax in FP32.  Prompt portions and single decoded tokens are the same case: a
-// token at position p sees keys [max(0, p - window + 1), p] of its own request.
+// token at position p sees keys [max(0, p - window + 1), p] of its own request.  An optional
+// token list restricts the launch to some of the step's tokens (n_tokens = its length).
 //
 // The result of a token depends only on its own keys and their order, never on how the
 // step was cut or what else is in the batch, so this kernel is the FP32 path's attention
@@ -18,6 +19,7 @@
 template <typename T>
 __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
                                          const T* __restrict__ v_pages, T* __restrict__ out,
+                                         const int* __restrict__ token_list,
                                          const int* __restrict__ positions,
                                          const int* __restrict__ seq_of_token,
                                          const int* __restrict__ block_table, int bt_stride,
@@ -27,8 +29,9 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
     const long long item = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
     if (item >= (long long)n_tokens * n_q_heads) return;
     const int lane = threadIdx.x & 31;
-    const int t = (int)(item / n_q_heads);
-    const int head = (int)(item - (long long)t * n_q_heads);
+    const int t_item = (int)(item / n_q_heads);
+    const int head = (int)(item - (long long)t_item * n_q_heads);
+    const int t = token_list ? token_list[t_item] : t_item;
     const int kvh = head / (n_q_heads / n_kv_heads);
     const int pos = positions[t];
     const int* table = block_table + (size_t)seq_of_token[t] * bt_stride;
@@ -77,8 +80,8 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
 }
 
 NI_EXPORT int ni_attention_generic(const void* q, int dtype, const void* k_pages,
-                                   const void* v_pages, void* out, const int* positions,
-                                   const int* seq_of_token, const int* block_table, int bt_stride,
+                                   const void* v_pages, void* out, const int* token_list,
+                                   const int* positions, const int* seq_of_token, const int* block_table, int bt_stride,
                                    int n_tokens, int n_q_heads, int n_kv_heads, int head_dim,
                                    int page_size, int window, float scale, cudaStream_t stream) {
     if (n_tokens <= 0) return NI_OK;
@@ -91,7 +94,8 @@ NI_EXPORT int ni_attention_generic(const void* q, int dtype, const void* k_pages
     if (blocks > 2147483647LL) return NI_ERR_UNSUPPORTED_SIZE;
 #define LAUNCH(T)                                                                                   \
     attention_generic_kernel<T><<<(int)blocks, warps * 32, 0, stream>>>(                            \
-        (const T*)q, (const T*)k_pages, (const T*)v_pages, (T*)out, positions, seq_of_token,       \
+        (const T*)q, (const T*)k_pages, (const T*)v_pages, (T*)out, token_list, positions,         \
+        seq_of_token,                                                                               \
         block_table, bt_stride, n_tokens, n_q_heads, n_kv_heads, head_dim, page_size, window, scale)
     if (dtype == NI_DTYPE_F32) LAUNCH(float);
     else if (dtype == NI_DTYPE_BF16) LAUNCH(__nv_bfloat16);

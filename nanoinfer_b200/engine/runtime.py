@@ -35,6 +35,8 @@ class Runtime:
     page_size: int
 
     def __post_init__(self) -> None:
+        self._workspaces = {}
+        self._retired = []
         ops.require_cuda()
         if self.device.type != "cuda":
             raise ops.KernelError(f"device {self.device} is not a CUDA device; there is no CPU path")
@@ -50,14 +52,31 @@ class Runtime:
     def empty(self, *shape, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         return torch.empty(shape, device=self.device, dtype=dtype or self.dtype)
 
-    def linear(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None
-               ) -> torch.Tensor:
+    def linear(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+               residual: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """y[M, N] = x[M, K] . w[N, K]^T.  ``out_dtype`` float32 asks for FP32 results
-        (logits); the default is the compute dtype."""
+        (logits); the default is the compute dtype.  With ``residual`` (the FP32 residual
+        stream) the kernel MAY add the product into it and return None; otherwise the product
+        is returned and the caller adds it."""
         m, n = x.shape[0], w.shape[0]
         out_dtype = out_dtype or self.dtype
         if self.dtype == torch.float32:
             out = self.empty(m, n, dtype=torch.float32)
             ops.gemm_f32(x, w, out)
             return out
-        return ops.linear_bf16(x, w, out_dtype)
+        return ops.linear_bf16(x, w, out_dtype, residual)
+
+    def workspace(self, name: str, numel: int, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
+        """A persistent scratch tensor of at least ``numel`` elements, shared by all layers
+        (they run one after the other on one stream).  ``zero``: zero-filled when created;
+        its users leave it zero."""
+        t = self._workspaces.get(name)
+        if t is None or t.numel() < numel or t.dtype != dtype:
+            if torch.cuda.is_current_stream_capturing():
+                raise ops.KernelError(f"workspace '{name}' would have to grow during graph capture")
+            n = max(numel, 2 * t.numel() if t is not None else 0)
+            if t is not None:
+                self._retired.append(t)   # captured graphs may still point at the smaller one
+            t = (torch.zeros if zero else torch.empty)(n, dtype=dtype, device=self.device)
+            self._workspaces[name] = t
+        return t

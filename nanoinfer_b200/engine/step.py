@@ -74,6 +74,22 @@ class StepContext:
     host_slots: List[int] = field(default_factory=list)
     max_q_len: int = 0
     max_kv_len: int = 0
+    # How attention splits the step: requests with at most SHORT_PORTION tokens are handled
+    # token by token (dec_tokens: their token indices), longer portions in tiles of
+    # ATTENTION_TILE query rows (tile_seq / tile_row0, heaviest first; long_tokens: their token
+    # indices).  decode_only: every request has exactly one token (then the lists are unused,
+    # so that a captured step does not depend on them).
+    decode_only: bool = False
+    n_dec: int = 0
+    dec_tokens: Optional[torch.Tensor] = None
+    n_tiles: int = 0
+    tile_seq: Optional[torch.Tensor] = None
+    tile_row0: Optional[torch.Tensor] = None
+    long_tokens: Optional[torch.Tensor] = None
+
+
+SHORT_PORTION = 2
+ATTENTION_TILE = 64
 
 
 def reserve_entries(cache: CacheManager, entries: Sequence[StepEntry], admit) -> List[int]:
@@ -159,6 +175,9 @@ class ModelRunner:
                 src = self.caches[run.cache_of]
                 self.caches[r] = CacheView(group=src.group, k_pages=src.k_pages, v_pages=src.v_pages,
                                            state=src.state, writable=False)
+        self.use_graphs = True
+        self.max_graph_batch = 256
+        self._graphs: Dict[int, "_DecodeGraph"] = {}
         self._pinned: List[torch.Tensor] = []
         self._pinned_events: List[torch.cuda.Event] = []
         self._pinned_next = 0
@@ -228,8 +247,21 @@ class ModelRunner:
         rows = [int(cu_q[i]) + int(w) for i, e in enumerate(entries) for w in e.want]
         width = max(1, -(-max(kv_lens) // cache.page_size))
         tables = [cache.table_rows(g, slots, width).reshape(-1) for g in range(len(cache.groups))]
+        dec, long_tok, tiles = [], [], []
+        for i, ql in enumerate(q_lens):
+            if ql <= SHORT_PORTION:
+                dec.extend(range(int(cu_q[i]), int(cu_q[i]) + ql))
+            else:
+                long_tok.extend(range(int(cu_q[i]), int(cu_q[i]) + ql))
+                tiles.extend((starts[i] + r0, i, r0) for r0 in range(0, ql, ATTENTION_TILE))
+        tiles.sort(key=lambda x: -x[0])      # most keys first
+        n_fixed = 7
         parts = [tokens, positions, seq_of_token, cu_q, np.asarray(kv_lens, dtype=np.int32),
-                 np.asarray(slots, dtype=np.int32), np.asarray(rows, dtype=np.int32)] + tables
+                 np.asarray(slots, dtype=np.int32), np.asarray(rows, dtype=np.int32),
+                 np.asarray(dec, dtype=np.int32), np.asarray(long_tok, dtype=np.int32),
+                 np.asarray([x[1] for x in tiles], dtype=np.int32),
+                 np.asarray([x[2] for x in tiles], dtype=np.int32)] + tables
+        n_fixed = 11
         offsets, total = [], 0
         for p in parts:
             offsets.append(total)
@@ -246,21 +278,157 @@ class ModelRunner:
             n_tokens=n_tokens, n_seqs=n_seqs, n_logit_rows=len(rows), tokens=view(0),
             positions=view(1), seq_of_token=view(2), cu_q=view(3), kv_len=view(4), slots=view(5),
             logit_rows=view(6),
-            block_tables=[view(7 + g).view(n_seqs, width) for g in range(len(cache.groups))],
+            block_tables=[view(n_fixed + g).view(n_seqs, width) for g in range(len(cache.groups))],
             host_q_lens=q_lens, host_kv_lens=kv_lens, host_slots=slots, max_q_len=max(q_lens),
-            max_kv_len=max(kv_lens))
+            max_kv_len=max(kv_lens), decode_only=all(q == 1 for q in q_lens), n_dec=len(dec),
+            dec_tokens=view(7), long_tokens=view(8), n_tiles=len(tiles), tile_seq=view(9),
+            tile_row0=view(10))
 
     # ---- the step -------------------------------------------------------------------------
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run one batch; returns FP32 logits [number of wanted places, vocab] on the device,
-        ordered by entry and then by ``want``."""
+        ordered by entry and then by ``want``.  The tensor is valid until the next step."""
         self._validate(entries)
-        ctx = self.build_context(entries)
-        logits = self.model.forward(ctx, self.caches)
+        if self._graphable(entries):
+            starts = reserve_entries(self.cache, entries, self.admit)
+            logits = self._decode_graph(len(entries)).run(entries, starts)
+        else:
+            ctx = self.build_context(entries)
+            logits = self.model.forward(ctx, self.caches)
         for e in entries:
             self.cache.release_passed(e.request)
         return logits
 
+    # ---- decode steps as CUDA graphs ------------------------------------------------------
+    def _graphable(self, entries: Sequence[StepEntry]) -> bool:
+        """A step of single tokens that all want their logits, for a model whose layers keep
+        nothing but pages between steps (replaying a page write is harmless; replaying a
+        state update is not), can be captured once per batch size and replayed."""
+        return (self.use_graphs and not self._state_runs and len(entries) <= self.max_graph_batch
+                and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries))
+
+    def _decode_graph(self, n: int) -> "_DecodeGraph":
+        g = self._graphs.get(n)
+        if g is None:
+            g = self._graphs[n] = _DecodeGraph(self, n)
+        return g
+
+    def greedy_decode_on_device(self, requests: Sequence[object], last_tokens: Sequence[int],
+                                n_steps: int) -> torch.Tensor:
+        """Decode ``n_steps`` greedy tokens for each request without touching the host between
+        steps: arg-max, token feedback and position advance are part of the replayed graph.
+        ``last_tokens[i]`` is the token of request i that has not been run yet.  Pages for all
+        steps are taken up front.  Returns int32 [n_steps, len(requests)] on the device; the
+        token that the last step samples is returned but not yet run."""
+        if self._state_runs:
+            raise StepError("device-side decoding needs a model without per-request state")
+        for r in requests:
+            self.cache.append(r, n_steps)
+        n = len(requests)
+        g = self._decode_graph(n)
+        starts = [self.cache.length(r) - n_steps for r in requests]
+        entries = [StepEntry(r, [int(t)], [0]) for r, t in zip(requests, last_tokens)]
+        return g.run_greedy(entries, starts, n_steps)
+
     def end(self, request) -> None:
         """The request is finished: give back its pages and its slot."""
         self.cache.free(request)
+
+
+class _DecodeGraph:
+    """The forward pass of ``n`` single-token requests, captured once and replayed.
+
+    All metadata lives in one static device buffer at fixed offsets (block tables at their
+    full width), refreshed by one copy from pinned host memory before each replay; grids do
+    not depend on context lengths.  A second capture adds arg-max, token feedback and the
+    advance of positions, for decoding without the host in the loop.
+    """
+
+    def __init__(self, runner: ModelRunner, n: int) -> None:
+        self.runner, self.n = runner, n
+        cache = runner.cache
+        self.width = cache.table_width
+        n_groups = len(cache.groups)
+        sizes = [n, n, n, n + 1, n, n, n] + [n * self.width] * n_groups
+        self.offsets, total = [], 0
+        for sz in sizes:
+            self.offsets.append(total)
+            total += _round_up(sz, 4)
+        dev = runner.rt.device
+        self.host = torch.zeros(total, dtype=torch.int32, pin_memory=True)
+        self.host_np = self.host.numpy()
+        self.dev = torch.zeros(total, dtype=torch.int32, device=dev)
+        self.copied = torch.cuda.Event()
+        self.copy_pending = False
+        o = self.offsets
+        self.host_np[o[2]:o[2] + n] = np.arange(n)            # seq_of_token
+        self.host_np[o[3]:o[3] + n + 1] = np.arange(n + 1)    # cu_q
+        self.host_np[o[6]:o[6] + n] = np.arange(n)            # logit rows: all
+
+        def view(i, sz):
+            return self.dev[o[i]:o[i] + sz]
+
+        self.ctx = StepContext(
+            n_tokens=n, n_seqs=n, n_logit_rows=n, tokens=view(0, n), positions=view(1, n),
+            seq_of_token=view(2, n), cu_q=view(3, n + 1), kv_len=view(4, n), slots=view(5, n),
+            logit_rows=view(6, n),
+            block_tables=[view(7 + g, n * self.width).view(n, self.width) for g in range(n_groups)],
+            max_q_len=1, max_kv_len=runner.max_tokens_per_request, decode_only=True)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.greedy_graph: Optional[torch.cuda.CUDAGraph] = None
+        self.greedy_out: Optional[torch.Tensor] = None
+
+    def _fill(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> None:
+        n, o, cache = self.n, self.offsets, self.runner.cache
+        if self.copy_pending:
+            self.copied.synchronize()
+        h = self.host_np
+        h[o[0]:o[0] + n] = [int(e.tokens[0]) for e in entries]
+        h[o[1]:o[1] + n] = starts
+        h[o[4]:o[4] + n] = np.asarray(starts, dtype=np.int32) + 1
+        slots = [cache.slot(e.request) for e in entries]
+        h[o[5]:o[5] + n] = slots
+        for g in range(len(cache.groups)):
+            h[o[7 + g]:o[7 + g] + n * self.width] = cache.table_rows(g, slots).reshape(-1)
+        self.dev.copy_(self.host, non_blocking=True)
+        self.copied.record()
+        self.copy_pending = True
+
+    def _capture(self) -> None:
+        runner = self.runner
+        # an eager pass first: compiles and loads what is missing and sizes the workspaces;
+        # it writes the same keys and values that the replay will write again
+        runner.model.forward(self.ctx, runner.caches)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = runner.model.forward(self.ctx, runner.caches)
+
+    def run(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> torch.Tensor:
+        self._fill(entries, starts)
+        if self.graph is None:
+            self._capture()
+        self.graph.replay()
+        return self.logits
+
+    def run_greedy(self, entries: Sequence[StepEntry], starts: Sequence[int], n_steps: int) -> torch.Tensor:
+        from ..kernels import ops
+        runner, ctx = self.runner, self.ctx
+        self._fill(entries, starts)
+        if self.greedy_graph is None:
+            runner.model.forward(ctx, runner.caches)
+            torch.cuda.synchronize()
+            self.greedy_out = torch.zeros(self.n, dtype=torch.int32, device=runner.rt.device)
+            self.greedy_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.greedy_graph):
+                logits = runner.model.forward(ctx, runner.caches)
+                ops.argmax(logits, self.greedy_out)
+                ctx.tokens.copy_(self.greedy_out)
+                ctx.positions.add_(1)
+                ctx.kv_len.add_(1)
+        out = torch.empty(n_steps, self.n, dtype=torch.int32, device=runner.rt.device)
+        for i in range(n_steps):
+            self.greedy_graph.replay()
+            out[i].copy_(self.greedy_out)
+        return out

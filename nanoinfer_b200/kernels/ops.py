@@ -33,10 +33,19 @@ _SIGNATURES = {
         "ni_rope_kv_write": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     },
     "attention_generic": {
-        "ni_attention_generic": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P],
+        "ni_attention_generic": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P],
     },
     "gemm_f32": {
         "ni_gemm_f32": [_P, _P, _P, _I, _I, _I, _P],
+    },
+    "gemv_bf16": {
+        "ni_gemv_bf16": [_P, _P, _P, _I, _I, _I, _I, _P],
+    },
+    "attention_decode": {
+        "ni_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P],
+    },
+    "attention_prefill": {
+        "ni_attention_prefill": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
     },
     "sampling": {
         "ni_argmax": [_P, _P, _I, _I, _P],
@@ -188,7 +197,10 @@ def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, k_pages: Optional[torc
 def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                       out: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
                       block_table: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int,
-                      page_size: int, window: Optional[int], scale: float) -> None:
+                      page_size: int, window: Optional[int], scale: float,
+                      token_list: Optional[torch.Tensor] = None) -> None:
+    """The plain attention kernel (any dtype, any head size up to 256).  ``token_list``
+    int32 [n] restricts it to those tokens of the step."""
     n = q.shape[0]
     if q.shape != (n, n_q_heads * head_dim) or out.shape != q.shape:
         raise KernelError("attention: q and out must be [T, Hq * head_dim]")
@@ -198,9 +210,10 @@ def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         raise KernelError(f"attention: head_dim {head_dim} > 256 is not supported")
     _check(load("attention_generic").ni_attention_generic(
         _dev(q, "q"), _code(q, "q"), _dev(k_pages, "k_pages"), _dev(v_pages, "v_pages"),
-        _dev(out, "out"), _dev(positions, "positions", torch.int32),
+        _dev(out, "out"), _dev(token_list, "token_list", torch.int32) if token_list is not None else None,
+        _dev(positions, "positions", torch.int32),
         _dev(seq_of_token, "seq_of_token", torch.int32), _dev(block_table, "block_table", torch.int32),
-        block_table.shape[1], n, n_q_heads, n_kv_heads, head_dim, page_size,
+        block_table.shape[1], n if token_list is None else token_list.numel(), n_q_heads, n_kv_heads, head_dim, page_size,
         int(window) if window else 0, float(scale), _stream()), "attention_generic")
 
 
@@ -214,29 +227,89 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
                                         _dev(out, "out", torch.float32), m, n, k, _stream()), "gemm_f32")
 
 
-def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+GEMV_MAX_ROWS = 16
+STORE_BF16, STORE_F32, ADD_F32 = 0, 1, 2
+
+
+def gemv_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int) -> None:
+    """out[M, N] (=, or += for mode ADD_F32) x[M, K] . w[N, K]^T for M <= 16, K % 8 == 0."""
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape != (m, n):
+        raise KernelError("gemv_bf16: shapes do not agree")
+    if m > GEMV_MAX_ROWS or k % 8:
+        raise KernelError(f"gemv_bf16: takes at most {GEMV_MAX_ROWS} rows and K a multiple of 8 "
+                          f"(got M={m}, K={k})")
+    want = torch.bfloat16 if mode == STORE_BF16 else torch.float32
+    _check(load("gemv_bf16").ni_gemv_bf16(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16),
+                                          _dev(out, "out", want), m, n, k, mode, _stream()), "gemv_bf16")
+
+
+def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
+                residual: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """y = x . w^T for bfloat16 operands with FP32 accumulation.
 
-    The product itself is a library matrix product (cuBLASLt through torch), as the
-    reference's projections are cuBLAS calls (src/op/kernels/cuda/matmul_kernel.cu:76-86).
+    Up to 16 rows (decode): the package's own bandwidth kernel; with ``residual`` (float32
+    [M, N]) the product is added into it and None is returned.  More rows: a library matrix
+    product (cuBLASLt through torch), as the reference's projections are cuBLAS calls
+    (src/op/kernels/cuda/matmul_kernel.cu:76-86); the caller adds the result to the residual.
     """
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("linear_bf16: operands must be bfloat16")
     if not x.is_cuda or not w.is_cuda:
         raise KernelError("linear_bf16: operands must be CUDA tensors")
+    m, k = x.shape
+    if m <= GEMV_MAX_ROWS and k % 8 == 0:
+        if residual is not None:
+            gemv_bf16(x, w, residual, ADD_F32)
+            return None
+        out = torch.empty(m, w.shape[0], dtype=out_dtype, device=x.device)
+        gemv_bf16(x, w, out, STORE_BF16 if out_dtype == torch.bfloat16 else STORE_F32)
+        return out
     if out_dtype == torch.bfloat16:
         return torch.matmul(x, w.t())
     return torch.mm(x, w.t(), out_dtype=torch.float32)
 
 
-def attention(q, k_pages, v_pages, out, ctx, block_table, n_q_heads, n_kv_heads, head_dim,
-              page_size, window, scale) -> None:
-    """Attention of every token of the step over its own request's cache.
+DECODE_HEAD_DIMS = (64, 128)
+PREFILL_MAX_HEAD_DIM = 128
 
-    ``ctx`` is the step context (positions, seq_of_token and per-request segments).
-    """
-    attention_generic(q, k_pages, v_pages, out, ctx.positions, ctx.seq_of_token, block_table,
-                      n_q_heads, n_kv_heads, head_dim, page_size, window, scale)
+
+def attention_decode(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token, block_table,
+                     n_q_heads, n_kv_heads, head_dim, page_size, window, scale, n_splits, scratch,
+                     tickets) -> None:
+    """Split-K attention of single query tokens (bfloat16).  ``token_list`` int32 [n_items] or
+    None for tokens 0..n_items-1.  scratch: float32, at least n_items * Hq * n_splits *
+    (head_dim + 2); tickets: int32 zeros, at least n_items * Hkv (left zero by the kernel)."""
+    if head_dim not in DECODE_HEAD_DIMS or n_q_heads // n_kv_heads > 16:
+        raise KernelError(f"attention_decode: head_dim {head_dim} / group {n_q_heads // n_kv_heads} not supported")
+    if scratch.numel() < n_items * n_q_heads * n_splits * (head_dim + 2) or tickets.numel() < n_items * n_kv_heads:
+        raise KernelError("attention_decode: scratch or tickets too small")
+    _check(load("attention_decode").ni_attention_decode(
+        _dev(q, "q", torch.bfloat16), _dev(k_pages, "k_pages", torch.bfloat16),
+        _dev(v_pages, "v_pages", torch.bfloat16), _dev(out, "out", torch.bfloat16),
+        _dev(token_list, "token_list", torch.int32) if token_list is not None else None, n_items,
+        _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
+        _dev(block_table, "block_table", torch.int32), block_table.shape[1], n_q_heads, n_kv_heads,
+        head_dim, page_size, int(window) if window else 0, float(scale), n_splits,
+        _dev(scratch, "scratch", torch.float32), _dev(tickets, "tickets", torch.int32), _stream()),
+        "attention_decode")
+
+
+def attention_prefill(q, k_pages, v_pages, out, tile_seq, tile_row0, n_tiles, cu_q, kv_len, block_table,
+                      n_q_heads, n_kv_heads, head_dim, page_size, window, scale) -> None:
+    """Flash-style causal attention of prompt portions (bfloat16): one block per (tile of 64
+    query rows, head); tile_seq / tile_row0 int32 [n_tiles] name each tile's request and
+    first row."""
+    if head_dim % 16 or head_dim > PREFILL_MAX_HEAD_DIM:
+        raise KernelError(f"attention_prefill: head_dim {head_dim} not supported (multiples of 16 up to 128)")
+    _check(load("attention_prefill").ni_attention_prefill(
+        _dev(q, "q", torch.bfloat16), _dev(k_pages, "k_pages", torch.bfloat16),
+        _dev(v_pages, "v_pages", torch.bfloat16), _dev(out, "out", torch.bfloat16),
+        _dev(tile_seq, "tile_seq", torch.int32), _dev(tile_row0, "tile_row0", torch.int32), n_tiles,
+        _dev(cu_q, "cu_q", torch.int32), _dev(kv_len, "kv_len", torch.int32),
+        _dev(block_table, "block_table", torch.int32), block_table.shape[1], n_q_heads, n_kv_heads,
+        head_dim, page_size, int(window) if window else 0, float(scale), _stream()), "attention_prefill")
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

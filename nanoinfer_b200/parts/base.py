@@ -20,6 +20,9 @@ Mixer           cache_need() -> PagedKVNeed | StateNeed | None
                     belongs to which request; must give the same result for a token
                     however the step was cut.
 FeedForward     forward(x, ctx) -> y [T, d]
+                A mixer or feed-forward with the class attribute ``adds_into_residual = True``
+                is called with ``residual=h`` as well and may add its output into h itself
+                and return None (a fused epilogue).
 Arrangement     (a block) forward(h, delta, ctx, caches) -> delta'
                     runs its norms, mixer and feed-forward; returns the addition that
                     is still pending on the residual stream.

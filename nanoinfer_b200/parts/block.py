@@ -30,8 +30,13 @@ class PreNormBlock:
 
     def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], ctx, cache) -> torch.Tensor:
         x = self.mixer_norm.forward(h, delta)
-        a = self.mixer.forward(x, ctx, cache)
+        if getattr(self.mixer, "adds_into_residual", False):
+            a = self.mixer.forward(x, ctx, cache, residual=h)     # may add in place and return None
+        else:
+            a = self.mixer.forward(x, ctx, cache)
         x = self.ffn_norm.forward(h, a)
+        if getattr(self.feed_forward, "adds_into_residual", False):
+            return self.feed_forward.forward(x, ctx, residual=h)
         return self.feed_forward.forward(x, ctx)
 
 

@@ -26,12 +26,14 @@ class SwiGLU(Part):
         self.w_gate_up = rt.weight(torch.cat([weights["gate"], weights["up"]], dim=0))
         self.w_down = rt.weight(weights["down"])
 
-    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+    adds_into_residual = True   # forward() accepts residual= and may add its output there
+
+    def forward(self, x: torch.Tensor, ctx, residual=None):
         rt = self.rt
         gate_up = rt.linear(x, self.w_gate_up)
         act = rt.empty(x.shape[0], self.inter)
         ops.swiglu(gate_up, act)
-        return rt.linear(act, self.w_down)
+        return rt.linear(act, self.w_down, residual=residual)
 
 
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)

@@ -48,7 +48,9 @@ class PagedAttention(Part):
     def cache_need(self):
         return PagedKVNeed(self.n_kv, self.head_dim, self.window)
 
-    def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
+    adds_into_residual = True   # forward() accepts residual= and may add its output there
+
+    def forward(self, x: torch.Tensor, ctx, cache, residual=None):
         rt = self.rt
         n = x.shape[0]
         qkv = rt.linear(x, self.w_qkv)
@@ -60,9 +62,44 @@ class PagedAttention(Part):
                           ctx.seq_of_token, table, pos.inv_freq, self.n_heads, self.n_kv,
                           self.head_dim, pos.rotary_dim, pos.interleaved, rt.page_size)
         att = rt.empty(n, self.n_heads * self.head_dim)
-        ops.attention(q, cache.k_pages, cache.v_pages, att, ctx, table, self.n_heads, self.n_kv,
-                      self.head_dim, rt.page_size, self.window, self.scale)
-        return rt.linear(att, self.w_o)
+        self._attend(q, cache, att, ctx, table)
+        return rt.linear(att, self.w_o, residual=residual)
+
+    def _attend(self, q, cache, att, ctx, table) -> None:
+        """Attention of every token of the step over its own request's pages.
+
+        float32: the plain kernel.  bfloat16: single query tokens (and portions of at most
+        two tokens) go to the split-K kernel, longer portions to the flash-style kernel;
+        head sizes those do not take fall back to the plain kernel, never to a wrong result."""
+        rt = self.rt
+        common = (self.n_heads, self.n_kv, self.head_dim, rt.page_size, self.window, self.scale)
+        n = q.shape[0]
+        if rt.dtype != torch.bfloat16:
+            ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
+                                  table, *common)
+            return
+        decode_ok = self.head_dim in ops.DECODE_HEAD_DIMS and self.n_heads // self.n_kv <= 16
+        prefill_ok = self.head_dim % 16 == 0 and self.head_dim <= ops.PREFILL_MAX_HEAD_DIM
+        n_dec = n if ctx.decode_only else ctx.n_dec
+        dec_list = None if ctx.decode_only else ctx.dec_tokens
+        if n_dec > 0:
+            if decode_ok:
+                splits = max(1, min((148 * 3) // max(1, n_dec * self.n_kv), max(1, ctx.max_kv_len // 256)))
+                scratch = rt.workspace("attention_decode_partials",
+                                       n_dec * self.n_heads * splits * (self.head_dim + 2), torch.float32)
+                tickets = rt.workspace("attention_decode_tickets", n_dec * self.n_kv, torch.int32, zero=True)
+                ops.attention_decode(q, cache.k_pages, cache.v_pages, att, dec_list, n_dec, ctx.positions,
+                                     ctx.seq_of_token, table, *common, splits, scratch, tickets)
+            else:
+                ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
+                                      table, *common, token_list=dec_list)
+        if not ctx.decode_only and ctx.n_tiles > 0:
+            if prefill_ok:
+                ops.attention_prefill(q, cache.k_pages, cache.v_pages, att, ctx.tile_seq, ctx.tile_row0,
+                                      ctx.n_tiles, ctx.cu_q, ctx.kv_len, table, *common)
+            else:
+                ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
+                                      table, *common, token_list=ctx.long_tokens)
 
 
 register_part("mixer", "attention", PagedAttention, replace=True)

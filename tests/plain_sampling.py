@@ -35,12 +35,22 @@ def penalise(logits: torch.Tensor, generated, penalty: float) -> torch.Tensor:
     return out
 
 
-def sample(logits, temperature, top_k=-1, top_p=1.0, repetition_penalty=1.0, generated=(), seed=0, index=0):
-    """Returns (token, margin): margin is the smallest relative distance of a decision (top-p
-    cut, draw) to the point where it would fall the other way."""
+# Two selections that differ by less than this share of the total mass cannot be told apart:
+# FP32 exp is good to about 1e-7 relative per element, and the kernel sums mass in fixed point
+# with 2^-38 per element truncated (at most 5e-7 of the total for 128k elements).
+ROUNDING = 1e-6
+
+
+def sample(logits, temperature, top_k=-1, top_p=1.0, repetition_penalty=1.0, generated=(), seed=0, index=0,
+           rounding=ROUNDING):
+    """Returns (token, acceptable, cut_margin).  ``acceptable`` is the set of ids the draw
+    reaches when its target moves by +-``rounding`` of the total mass (usually just {token});
+    ``cut_margin`` is the distance of the top-p cut to the point where one more or one fewer
+    token would be kept, as a share of the total mass (1.0 without top-p)."""
     l = penalise(logits, generated, repetition_penalty)
     if temperature <= 0:
-        return int(torch.argmax(l)), 1.0
+        t = int(torch.argmax(l))
+        return t, {t}, 1.0
     z = l * torch.tensor(1.0 / temperature, dtype=torch.float32)         # scaling (sampling_kernel.cpp:67-85)
     V = z.numel()
     kept = torch.ones(V, dtype=torch.bool)
@@ -49,7 +59,7 @@ def sample(logits, temperature, top_k=-1, top_p=1.0, repetition_penalty=1.0, gen
         kept = z >= kth                                                  # top-k (:131-140), ties kept
     e = torch.exp(z - z.max()).double()                                  # softmax numerator (:143-153)
     e[~kept] = 0.0
-    margin = 1.0
+    cut_margin = 1.0
     if 0.0 < top_p < 1.0:
         order = torch.argsort(e, descending=True, stable=True)
         cums = torch.cumsum(e[order], 0)
@@ -58,12 +68,14 @@ def sample(logits, temperature, top_k=-1, top_p=1.0, repetition_penalty=1.0, gen
         thr = e[order][idx]
         kept &= e >= thr
         below = cums[idx - 1] if idx > 0 else torch.tensor(0.0, dtype=torch.float64)
-        margin = min(margin, float(min(abs(cums[idx] - top_p * total), abs(below - top_p * total)) / total))
+        cut_margin = float(min(abs(cums[idx] - top_p * total), abs(below - top_p * total)) / total)
         e[~kept] = 0.0
     total = e.sum()
     target = uniform(seed, index) * total
     cdf = torch.cumsum(e, 0)                                             # vocabulary order
     tok = int(torch.nonzero(cdf > target)[0])
-    below = cdf[tok - 1] if tok > 0 else torch.tensor(0.0, dtype=torch.float64)
-    margin = min(margin, float(min(abs(cdf[tok] - target), abs(below - target)) / total))
-    return tok, margin
+    lo = int(torch.nonzero(cdf > max(target - rounding * total, 0.0))[0])
+    hi_hits = torch.nonzero(cdf > target + rounding * total)
+    hi = int(hi_hits[0]) if hi_hits.numel() else tok
+    acceptable = {i for i in range(lo, hi + 1) if e[i] > 0}
+    return tok, acceptable, cut_margin

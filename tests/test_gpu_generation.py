@@ -16,6 +16,11 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+# The engine's FP32 logits agree with the plain ones to rtol 1e-4 / atol 1e-5; divided by a
+# temperature of 0.7 that moves a token's probability mass by up to about 2e-4 of itself.
+LOGIT_ROUNDING = 2e-4
+
+
 def _check_greedy(raw, w, prompt, generated, dtype):
     """Every generated token is the plain arg-max given the tokens before it - unless the
     plain top-2 logits are closer than the precision of the engine's dtype can tell apart."""
@@ -61,8 +66,8 @@ def test_temperature_generation_follows_the_plain_stream(model_dirs):
     for p, o in zip(prompts, outs):
         seq = list(p)
         for i, tok in enumerate(o):
-            want, margin = ps.sample(plain.forward(raw, w, seq)[-1], 0.7, seed=1, index=i)
-            assert tok == want or margin < 1e-4, f"token {i}: engine {tok}, plain {want}"
+            want, acceptable, _ = ps.sample(plain.forward(raw, w, seq)[-1], 0.7, seed=1, index=i, rounding=LOGIT_ROUNDING)
+            assert tok in acceptable, f"token {i}: engine {tok}, plain {want}"
             seq.append(tok)
     # the same requests one at a time give the same tokens: the stream does not depend on batching
     eng2 = Engine.from_model_dir(model_dirs["b"], dtype="float32", block_size=8, num_cache_blocks=64,

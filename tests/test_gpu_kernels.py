@@ -176,3 +176,127 @@ def test_rope_kv_write(dtype, pairing, n_q, n_kv, hd, rot, page):
     # nothing else was written
     assert torch.all(kp.permute(0, 2, 1, 3)[~touched] == 7.0)
     assert torch.all(vp.permute(0, 2, 1, 3)[~touched] == 7.0)
+
+
+@pytest.mark.parametrize("mode", ["bf16", "f32", "add"])
+@pytest.mark.parametrize("m,n,k", [(1, 64, 64), (3, 100, 120), (8, 4800, 2048), (9, 333, 200), (16, 520, 8200),
+                                   (5, 2048, 8192)])
+def test_gemv_bf16(m, n, k, mode):
+    from nanoinfer_b200.kernels import ops
+    x = _randn(m, k, dtype=torch.bfloat16, seed=1)
+    w = _randn(n, k, dtype=torch.bfloat16, seed=2, scale=0.05)
+    want = x.cpu().double() @ w.cpu().double().t()
+    if mode == "bf16":
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+        ops.gemv_bf16(x, w, out, ops.STORE_BF16)
+        torch.testing.assert_close(out.cpu().double(), want, rtol=4e-3, atol=1e-3)
+    elif mode == "f32":
+        out = torch.empty(m, n, dtype=torch.float32, device=DEV)
+        ops.gemv_bf16(x, w, out, ops.STORE_F32)
+        torch.testing.assert_close(out.cpu().double(), want, rtol=1e-5, atol=1e-5 * math.sqrt(k))
+    else:
+        h = _randn(m, n, seed=3)
+        out = h.clone()
+        ops.gemv_bf16(x, w, out, ops.ADD_F32)
+        torch.testing.assert_close(out.cpu().double(), h.cpu().double() + want, rtol=1e-5, atol=1e-5 * math.sqrt(k))
+    # a row's result does not depend on the rows beside it
+    if mode == "f32" and m > 1:
+        one = torch.empty(1, n, dtype=torch.float32, device=DEV)
+        ops.gemv_bf16(x[m - 1:m].contiguous(), w, one, ops.STORE_F32)
+        assert torch.equal(one[0], out[m - 1])
+
+
+def test_gemv_refuses_what_it_cannot_take():
+    from nanoinfer_b200.kernels import ops
+    x = _randn(17, 64, dtype=torch.bfloat16)
+    w = _randn(8, 64, dtype=torch.bfloat16)
+    with pytest.raises(ops.KernelError, match="at most 16 rows"):
+        ops.gemv_bf16(x, w, torch.empty(17, 8, dtype=torch.bfloat16, device=DEV), ops.STORE_BF16)
+    with pytest.raises(ops.KernelError, match="multiple of 8"):
+        ops.gemv_bf16(_randn(2, 60, dtype=torch.bfloat16), _randn(8, 60, dtype=torch.bfloat16),
+                      torch.empty(2, 8, dtype=torch.bfloat16, device=DEV), ops.STORE_BF16)
+
+
+def _attention_case(lens, spans, n_q, n_kv, hd, page, seed, far_key=None):
+    """Paged k/v for sequences of the given lengths and queries for the spans [a, b) of each.
+    ``far_key`` = (seq, key index): that key is made to dominate the last query's scores."""
+    dtype = torch.bfloat16
+    table, k_pages, v_pages, ks, vs = _paged_setup(lens, n_kv, hd, page, dtype, seed=seed)
+    g = torch.Generator().manual_seed(seed + 1)
+    qs = [torch.randn(t, n_q, hd, generator=g).to(dtype) for t in lens]
+    if far_key is not None:
+        s_i, j = far_key
+        # make one far key stand out for the last query of that sequence: all heads of a group
+        # share one query vector and the key is three times that vector, so its score
+        # (3 sqrt(hd) after scaling) dwarfs the rest; a kernel that skips or misplaces that key
+        # cannot pass
+        rep = n_q // n_kv
+        base = torch.randn(n_kv, hd, generator=g).to(dtype)
+        qs[s_i][-1] = base.repeat_interleave(rep, dim=0)
+        ks[s_i][j] = (base.float() * 3.0).to(dtype)
+        p, slot = table[s_i, j // page], j % page
+        k_pages[p, :, slot] = ks[s_i][j]
+        vs[s_i][j] = torch.full((n_kv, hd), 5.0, dtype=dtype)
+        v_pages[p, :, slot] = vs[s_i][j]
+    q = torch.cat([qs[s][a:b] for s, (a, b) in enumerate(spans)]).reshape(-1, n_q * hd)
+    positions = torch.cat([torch.arange(a, b) for a, b in spans]).int()
+    seq_of = torch.cat([torch.full((b - a,), s) for s, (a, b) in enumerate(spans)]).int()
+    return table, k_pages, v_pages, ks, vs, qs, q, positions, seq_of
+
+
+@pytest.mark.parametrize("n_splits", [1, 3, 7])
+@pytest.mark.parametrize("n_q,n_kv,hd,page,window", [(32, 8, 64, 16, None), (8, 8, 64, 8, None), (24, 8, 128, 16, None),
+                                                      (16, 1, 64, 4, 100), (6, 2, 128, 32, 33), (16, 2, 64, 16, None)])
+def test_attention_decode(n_q, n_kv, hd, page, window, n_splits):
+    from nanoinfer_b200.kernels import ops
+    lens = [700, 1, 33, 257]
+    spans = [(t - 1, t) for t in lens]          # the last token of each sequence
+    far = (0, 5) if window is None else None    # a far key among hundreds must be found
+    table, k_pages, v_pages, ks, vs, qs, q, positions, seq_of = _attention_case(lens, spans, n_q, n_kv, hd, page, hd + n_q, far)
+    scale = 1.0 / math.sqrt(hd)
+    n = q.shape[0]
+    out = torch.zeros_like(q).to(DEV)
+    scratch = torch.empty(n * n_q * n_splits * (hd + 2), dtype=torch.float32, device=DEV)
+    tickets = torch.zeros(n * n_kv, dtype=torch.int32, device=DEV)
+    args = (positions.to(DEV), seq_of.to(DEV), table.to(DEV), n_q, n_kv, hd, page, window, scale, n_splits,
+            scratch, tickets)
+    ops.attention_decode(q.to(DEV), k_pages.to(DEV), v_pages.to(DEV), out, None, n, *args)
+    want = torch.cat([plain.attention(qs[s], ks[s], vs[s], scale, window)[a:b]
+                      for s, (a, b) in enumerate(spans)]).reshape(-1, n_q * hd)
+    # bfloat16 probabilities multiply V (2^-9 relative each) and the output is rounded once
+    torch.testing.assert_close(out.cpu().float(), want, rtol=8e-3, atol=4e-3)
+    assert torch.all(tickets == 0)              # left ready for the next launch
+    if far is not None:
+        assert out.cpu().float()[0].mean() > 4.0    # the far key's value dominates
+    # a token list picks some tokens; the others are left alone
+    out2 = torch.full_like(out, 9.0)
+    pick = torch.tensor([2, 0], dtype=torch.int32, device=DEV)
+    ops.attention_decode(q.to(DEV), k_pages.to(DEV), v_pages.to(DEV), out2, pick, 2, *args)
+    assert torch.equal(out2[0], out[0]) and torch.equal(out2[2], out[2])
+    assert torch.all(out2[1] == 9.0) and torch.all(out2[3] == 9.0)
+
+
+@pytest.mark.parametrize("n_q,n_kv,hd,page,window", [(4, 2, 16, 16, None), (3, 1, 32, 8, None), (6, 3, 48, 4, 70),
+                                                      (32, 8, 64, 16, None), (5, 5, 80, 16, None), (4, 1, 96, 16, 64),
+                                                      (2, 2, 112, 8, None), (8, 2, 128, 16, 129)])
+def test_attention_prefill(n_q, n_kv, hd, page, window):
+    from nanoinfer_b200.kernels import ops
+    lens = [300, 70, 5, 130]
+    spans = [(100, 300), (0, 70), (2, 5), (127, 130)]   # portions: late, whole, tiny, across a tile edge
+    far = (0, 3) if window is None else None
+    table, k_pages, v_pages, ks, vs, qs, q, positions, seq_of = _attention_case(lens, spans, n_q, n_kv, hd, page, hd, far)
+    scale = 1.0 / math.sqrt(hd)
+    q_lens = [b - a for a, b in spans]
+    cu_q = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    kv_len = torch.tensor([b for _, b in spans], dtype=torch.int32)
+    tiles = [(s, r0) for s, ql in enumerate(q_lens) for r0 in range(0, ql, 64)]
+    tile_seq = torch.tensor([t[0] for t in tiles], dtype=torch.int32)
+    tile_row0 = torch.tensor([t[1] for t in tiles], dtype=torch.int32)
+    out = torch.zeros_like(q).to(DEV)
+    ops.attention_prefill(q.to(DEV), k_pages.to(DEV), v_pages.to(DEV), out, tile_seq.to(DEV), tile_row0.to(DEV),
+                          len(tiles), cu_q.to(DEV), kv_len.to(DEV), table.to(DEV), n_q, n_kv, hd, page, window, scale)
+    want = torch.cat([plain.attention(qs[s], ks[s], vs[s], scale, window)[a:b]
+                      for s, (a, b) in enumerate(spans)]).reshape(-1, n_q * hd)
+    torch.testing.assert_close(out.cpu().float(), want, rtol=8e-3, atol=4e-3)
+    if far is not None:
+        assert out.cpu().float()[199].mean() > 4.0      # last row of sequence 0 found key 3

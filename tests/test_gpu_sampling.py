@@ -47,16 +47,16 @@ def test_sampler_matches_plain_selection(vocab):
         g = torch.Generator().manual_seed(r)
         gens.append(torch.randint(0, vocab, (20,), generator=g).tolist() + [int(torch.argmax(l[r]))])
     got = sampler.sample(l.clone().to(DEV), params, seeds, idxs, gens).tolist()
-    close_calls = 0
+    skipped = 0
     for r in range(rows):
         p = params[r]
-        tok, margin = ps.sample(l[r], p.temperature, p.top_k, p.top_p, p.repetition_penalty, gens[r],
-                                seeds[r], idxs[r])
-        if margin < 1e-5:          # a decision within rounding of its boundary: either side is right
-            close_calls += 1
+        tok, acceptable, cut_margin = ps.sample(l[r], p.temperature, p.top_k, p.top_p, p.repetition_penalty,
+                                                gens[r], seeds[r], idxs[r])
+        if cut_margin < ps.ROUNDING:      # the top-p cut itself is within rounding: two valid kept sets
+            skipped += 1
             continue
-        assert got[r] == tok, f"row {r} {p}: kernel {got[r]}, plain {tok} (margin {margin:.2e})"
-    assert close_calls <= 2
+        assert got[r] in acceptable, f"row {r} {p}: kernel {got[r]}, plain {tok} (acceptable {acceptable})"
+    assert skipped <= 1
 
 
 def test_draws_follow_the_distribution_and_do_not_depend_on_the_batch():

@@ -22,3 +22,5 @@ def test_filters():
     out = ps.penalise(l, [1, 4, 1], 4.0)
     assert out.tolist() == [0.0, 0.75, 1.0, 2.0, -4.0]
     assert ps.sample(l, 0.0, repetition_penalty=4.0, generated=[1])[0] == 3
+    tok, acceptable, cut = ps.sample(l, 1.0, top_p=0.7, seed=1)
+    assert acceptable == {tok} and cut > 0.01
