@@ -176,6 +176,7 @@ class ModelRunner:
                 self.caches[r] = CacheView(group=src.group, k_pages=src.k_pages, v_pages=src.v_pages,
                                            state=src.state, writable=False)
         self.use_graphs = True
+        self.h2d_bytes = 0            # bytes of step metadata copied to the device so far
         self.max_graph_batch = 256
         self._graphs: Dict[int, "_DecodeGraph"] = {}
         self._pinned: List[torch.Tensor] = []
@@ -196,6 +197,7 @@ class ModelRunner:
         self._pinned_next = (i + 1) % len(self._pinned)
         if self._pinned_used[i]:
             self._pinned_events[i].synchronize()
+        self.h2d_bytes += host.nbytes
         self._pinned[i][:n].numpy()[:] = host
         self._dev_meta[:n].copy_(self._pinned[i][:n], non_blocking=True)
         self._pinned_events[i].record()
@@ -378,6 +380,7 @@ class _DecodeGraph:
         self.logits: Optional[torch.Tensor] = None
         self.greedy_graph: Optional[torch.cuda.CUDAGraph] = None
         self.greedy_out: Optional[torch.Tensor] = None
+        self.greedy_launches = 0
 
     def _fill(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> None:
         n, o, cache = self.n, self.offsets, self.runner.cache
@@ -392,6 +395,7 @@ class _DecodeGraph:
         for g in range(len(cache.groups)):
             h[o[7 + g]:o[7 + g] + n * self.width] = cache.table_rows(g, slots).reshape(-1)
         self.dev.copy_(self.host, non_blocking=True)
+        self.runner.h2d_bytes += self.host.numel() * 4
         self.copied.record()
         self.copy_pending = True
 
@@ -421,12 +425,14 @@ class _DecodeGraph:
             torch.cuda.synchronize()
             self.greedy_out = torch.zeros(self.n, dtype=torch.int32, device=runner.rt.device)
             self.greedy_graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count()
             with torch.cuda.graph(self.greedy_graph):
                 logits = runner.model.forward(ctx, runner.caches)
                 ops.argmax(logits, self.greedy_out)
                 ctx.tokens.copy_(self.greedy_out)
                 ctx.positions.add_(1)
                 ctx.kv_len.add_(1)
+            self.greedy_launches = ops.launch_count() - before   # this package's kernels per step
         out = torch.empty(n_steps, self.n, dtype=torch.int32, device=runner.rt.device)
         for i in range(n_steps):
             self.greedy_graph.replay()

@@ -87,8 +87,18 @@ def preload(modules) -> None:
         load(m)
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernels of this package have been launched (or captured) so far."""
+    return _launches
+
+
 def _check(code: int, what: str) -> None:
+    global _launches
     if code == 0:
+        _launches += 1
         return
     if code < 0:
         raise KernelError(f"{what}: {_ERRORS.get(code, f'error {code}')}")

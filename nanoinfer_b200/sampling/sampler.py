@@ -24,6 +24,7 @@ class Sampler:
     def __init__(self, vocab_size: int, device) -> None:
         self.vocab_size = vocab_size
         self.device = device
+        self.h2d_bytes = 0     # bytes of per-row parameters copied to the device so far
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
                token_indices: Sequence[int],
@@ -54,6 +55,7 @@ class Sampler:
         k = np.asarray([p.top_k for p in params], dtype=np.int32)
         sc = np.asarray([[s, c] for s, c in zip(seeds, token_indices)], dtype=np.uint64)
         dev = logits.device
+        self.h2d_bytes += f.nbytes + k.nbytes + sc.nbytes
         ft = torch.from_numpy(f).to(dev)
         sct = torch.from_numpy(sc.view(np.int64)).to(dev)
         ops.sample(logits, out, ft[:, 0].contiguous(), torch.from_numpy(k).to(dev),
