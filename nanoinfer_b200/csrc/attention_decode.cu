@@ -288,3 +288,49 @@ NI_EXPORT int ni_attention_decode(const void* q, const void* k_pages, const void
 #undef LAUNCH
     NI_RETURN_LAUNCH_STATUS();
 }
+
+// ---- the variant that allocates nothing (see attention_decode_noalloc.h) ----------------------
+#include "attention_decode_noalloc.h"
+
+static __device__ __align__(256) float ni_noalloc_partials[NI_NOALLOC_MAX_PARTIAL_FLOATS];
+static __device__ __align__(256) int ni_noalloc_tickets[NI_NOALLOC_MAX_TICKETS];
+
+#define NI_NOALLOC_MAX_DEVICES 64
+// Device addresses of the two arrays, looked up once per device.  In host code the array names
+// above are host-side stand-ins; only cudaGetSymbolAddress yields what a kernel can use.
+static float* noalloc_partials_addr[NI_NOALLOC_MAX_DEVICES];
+static int* noalloc_tickets_addr[NI_NOALLOC_MAX_DEVICES];
+
+NI_EXPORT int ni_attention_decode_noalloc(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                          const int* token_list, int n_items, const int* positions,
+                                          const int* seq_of_token, const int* block_table, int bt_stride,
+                                          int n_q_heads, int n_kv_heads, int head_dim, int page_size,
+                                          int window, float scale, int n_splits, cudaStream_t stream) {
+    if (n_items <= 0) return NI_OK;
+    if (n_q_heads <= 0 || n_kv_heads <= 0 || n_splits <= 0 || head_dim <= 0) return NI_ERR_BAD_ARGUMENT;
+    const long long need_floats = (long long)n_items * n_q_heads * n_splits * (head_dim + 2);
+    const long long need_tickets = (long long)n_items * n_kv_heads;
+    if (need_floats > NI_NOALLOC_MAX_PARTIAL_FLOATS || need_tickets > NI_NOALLOC_MAX_TICKETS)
+        return NI_ERR_STATIC_SCRATCH_TOO_SMALL;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= NI_NOALLOC_MAX_DEVICES) return NI_ERR_BAD_ARGUMENT;
+    if (noalloc_partials_addr[dev] == nullptr || noalloc_tickets_addr[dev] == nullptr) {
+        // set-up, once per device, with that device current
+        float* p = nullptr;
+        int* t = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, ni_noalloc_partials);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaGetSymbolAddress((void**)&t, ni_noalloc_tickets);
+        if (e != cudaSuccess) return (int)e;
+        noalloc_partials_addr[dev] = p;
+        noalloc_tickets_addr[dev] = t;
+    }
+    // the tickets must start at zero; the partial results are written before they are read
+    e = cudaMemsetAsync(noalloc_tickets_addr[dev], 0, (size_t)need_tickets * sizeof(int), stream);
+    if (e != cudaSuccess) return (int)e;
+    return ni_attention_decode(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
+                               block_table, bt_stride, n_q_heads, n_kv_heads, head_dim, page_size, window,
+                               scale, n_splits, noalloc_partials_addr[dev], noalloc_tickets_addr[dev], stream);
+}
