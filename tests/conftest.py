@@ -16,12 +16,12 @@ def pytest_configure(config):
 @pytest.fixture(scope="session")
 def model_dirs(tmp_path_factory):
     """Random-weight model folders of the tiny configurations, made once per session in a
-    temporary place: {"a": dir, "b": dir, "c": dir}."""
-    from tiny_configs import TINY_A, TINY_B, TINY_C
+    temporary place: {"a": dir, "b": dir, "c": dir, "d": dir}."""
+    from tiny_configs import TINY_A, TINY_B, TINY_C, TINY_D
     from nanoinfer_b200.weights import write_random_model
     root = tmp_path_factory.mktemp("models")
     out = {}
-    for key, raw, seed in (("a", TINY_A, 0), ("b", TINY_B, 1), ("c", TINY_C, 2)):
+    for key, raw, seed in (("a", TINY_A, 0), ("b", TINY_B, 1), ("c", TINY_C, 2), ("d", TINY_D, 3)):
         d = str(root / key)
         write_random_model(d, raw, seed)
         out[key] = d

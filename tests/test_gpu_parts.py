@@ -1,0 +1,342 @@
+"""Each part alone against its plain formula, and the generality of the assembly: a toy mixer
+with state of its own, a toy routed feed-forward and another position encoding are defined
+HERE, registered, built into a model with a schedule that repeats a layer and shares a cache,
+and stepped through the engine - without a change to the package's files.
+
+The toy parts are written with torch ops (they are test code, not product kernels); the model
+they form is no published architecture.
+"""
+import math
+
+import pytest
+import torch
+
+import plain_llama as plain
+import replay_util as ru
+from helpers import random_tokens
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+# ---------------------------------------------------------------------------------------------
+# parts alone
+# ---------------------------------------------------------------------------------------------
+def _runtime(dtype, page=8):
+    from nanoinfer_b200.engine.runtime import Runtime, parse_dtype
+    return Runtime(device=torch.device(DEV), dtype=parse_dtype(dtype), page_size=page)
+
+
+def _close(got, want, dtype):
+    """float32: rounding in another order.  bfloat16: a part chains two or three products whose
+    operands are rounded to 8 bits of mantissa (2^-9 relative each): the error is bounded
+    against the size of the part's output, 2 % of its largest value."""
+    if dtype == "float32":
+        torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-5)
+    else:
+        err = (got - want).abs().max().item()
+        assert err <= 0.02 * want.abs().max().item(), f"max error {err:.4g} vs scale {want.abs().max().item():.4g}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_rmsnorm_part(dtype):
+    from nanoinfer_b200.config import NormSpec, part
+    rt = _runtime(dtype)
+    d = 120
+    g = torch.Generator().manual_seed(0)
+    gain = torch.randn(d, generator=g) * 0.1 + 1.0
+    norm = part("norm", "rmsnorm")(NormSpec("rmsnorm", 1e-6), d, {"weight": gain.to(torch.bfloat16)}, rt)
+    h = torch.randn(7, d, generator=g).to(DEV)
+    delta = torch.randn(7, d, generator=g).to(rt.dtype).to(DEV)
+    want_h = h.cpu() + delta.cpu().float()
+    x = norm.forward(h, delta)
+    assert x.dtype == rt.dtype
+    torch.testing.assert_close(h.cpu(), want_h)
+    _close(x.cpu().float(), plain.rms_norm(want_h, gain.to(torch.bfloat16), 1e-6), dtype)
+
+
+def test_rotary_part_constants():
+    from nanoinfer_b200.config import PositionSpec, RopeScaling, part
+    rt = _runtime("float32")
+    sc = dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+              original_max_position_embeddings=256)
+    enc = part("position", "rope")(PositionSpec("rope", 10000.0, 48, "interleaved", RopeScaling(**sc)), 0, {}, rt)
+    torch.testing.assert_close(enc.inv_freq.cpu(), plain.rope_inv_freq(48, 10000.0, sc), rtol=3e-7, atol=0)
+    assert enc.interleaved and enc.rotary_dim == 48
+    none = part("position", "none")(PositionSpec("none"), 0, {}, rt)
+    assert none.rotary_dim == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_swiglu_part(dtype):
+    from nanoinfer_b200.config import FeedForwardSpec, part
+    rt = _runtime(dtype)
+    d, inter = 96, 200
+    g = torch.Generator().manual_seed(1)
+    w = {k: (torch.randn(s, generator=g) * 0.05).to(torch.bfloat16)
+         for k, s in (("gate", (inter, d)), ("up", (inter, d)), ("down", (d, inter)))}
+    ffn = part("feed_forward", "swiglu")(FeedForwardSpec("swiglu", inter), d, w, rt)
+    for rows in (3, 40):          # the skinny kernel and the library product
+        x = torch.randn(rows, d, generator=g).to(rt.dtype)
+        y = ffn.forward(x.to(DEV), None)
+        want = plain.swiglu_ffn(x.float(), w["gate"], w["up"], w["down"])
+        _close(y.cpu().float(), want, dtype)
+        if dtype == "bfloat16" and rows <= 16:
+            h = torch.randn(rows, d, generator=g).to(DEV)
+            h0 = h.clone()
+            assert ffn.forward(x.to(DEV), None, residual=h) is None      # fused epilogue
+            _close((h - h0).cpu(), want, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window,pairing,hd", [(None, "half", 64), (9, "interleaved", 32), (None, "half", 16)])
+def test_attention_part_and_block(dtype, window, pairing, hd):
+    """PagedAttention alone (two steps: a portion, then the rest token by token) and inside a
+    PreNormBlock, against the plain attention block."""
+    from nanoinfer_b200.cache import CacheManager, GroupSpec
+    from nanoinfer_b200.config import FeedForwardSpec, LayerSpec, MixerSpec, NormSpec, PositionSpec, part
+    from nanoinfer_b200.engine.step import CacheView, StepContext
+    rt = _runtime(dtype, page=8)
+    d, n_q, n_kv = 80, 4, 2
+    g = torch.Generator().manual_seed(hd)
+    pos_spec = PositionSpec("rope", 10000.0, hd, pairing, None)
+    spec = MixerSpec("attention", n_q, n_kv, hd, window, 1.0 / math.sqrt(hd), pos_spec)
+    names = {"q": (n_q * hd, d), "k": (n_kv * hd, d), "v": (n_kv * hd, d), "o": (d, n_q * hd)}
+    w = {k: (torch.randn(s, generator=g) * 0.08).to(torch.bfloat16) for k, s in names.items()}
+    mixer = part("mixer", "attention")(spec, d, w, rt)
+    need = mixer.cache_need()
+    assert (need.num_kv_heads, need.head_dim, need.window) == (n_kv, hd, window)
+
+    T = 29
+    x = torch.randn(T, d, generator=g).to(rt.dtype)
+    pw = {f"p.{k}_proj.weight": v for k, v in w.items()}
+    want = plain.attention_block(x.float(), pw, "p", n_q, n_kv, hd, torch.arange(T),
+                                 plain.rope_inv_freq(hd, 10000.0, None), pairing, spec.softmax_scale, window)
+
+    cm = CacheManager([GroupSpec(n_kv, hd, window)], [8], 8, 2, 64)
+    slot = cm.admit("r")
+    shape = (8, n_kv, 8, hd)
+    cache = CacheView(group=0, k_pages=torch.zeros(shape, dtype=rt.dtype, device=DEV),
+                      v_pages=torch.zeros(shape, dtype=rt.dtype, device=DEV))
+
+    def ctx_for(start, n):
+        cm.append("r", n)
+        i32 = dict(dtype=torch.int32, device=DEV)
+        width = cm.table_width
+        return StepContext(
+            n_tokens=n, n_seqs=1, n_logit_rows=0, tokens=torch.zeros(n, **i32),
+            positions=torch.arange(start, start + n, **i32), seq_of_token=torch.zeros(n, **i32),
+            cu_q=torch.tensor([0, n], **i32), kv_len=torch.tensor([start + n], **i32),
+            slots=torch.tensor([slot], **i32), logit_rows=torch.zeros(0, **i32),
+            block_tables=[torch.from_numpy(cm.table_rows(0, [slot], width)).to(DEV)],
+            host_q_lens=[n], host_kv_lens=[start + n], host_slots=[slot], max_q_len=n, max_kv_len=start + n,
+            decode_only=(n == 1), n_dec=n if n <= 2 else 0, dec_tokens=torch.arange(n, **i32),
+            n_tiles=0 if n <= 2 else -(-n // 64), tile_seq=torch.zeros(max(1, -(-n // 64)), **i32),
+            tile_row0=torch.arange(0, max(n, 1), 64, **i32), long_tokens=torch.arange(n, **i32))
+
+    outs = [mixer.forward(x[:20].to(DEV), ctx_for(0, 20), cache)]
+    for t in range(20, T):
+        outs.append(mixer.forward(x[t:t + 1].to(DEV), ctx_for(t, 1), cache))
+    got = torch.cat(outs).cpu().float()
+    _close(got, want, dtype)
+
+    # the same mixer inside a block with norms and a feed-forward
+    inter = 120
+    fw = {k: (torch.randn(s, generator=g) * 0.05).to(torch.bfloat16)
+          for k, s in (("gate", (inter, d)), ("up", (inter, d)), ("down", (d, inter)))}
+    gains = {"weight": torch.ones(d, dtype=torch.bfloat16)}
+    layer = LayerSpec(spec, FeedForwardSpec("swiglu", inter), NormSpec("rmsnorm", 1e-5), NormSpec("rmsnorm", 1e-5))
+    weights_of = {"mixer": w, "feed_forward": fw, "mixer_norm": gains, "ffn_norm": gains}
+    block = part("arrangement", "pre_norm")(layer, d, lambda what: weights_of[what], rt)
+    cm.free("r")
+    slot = cm.admit("r")
+    h0 = torch.randn(T, d, generator=g)
+    h = h0.clone().to(DEV)
+    delta = block.forward(h, None, ctx_for(0, T), cache)
+    if delta is not None:
+        h += delta.float()
+    a = h0 + plain.attention_block(plain.rms_norm(h0, gains["weight"], 1e-5), pw, "p", n_q, n_kv, hd, torch.arange(T),
+                                   plain.rope_inv_freq(hd, 10000.0, None), pairing, spec.softmax_scale, window)
+    want_h = a + plain.swiglu_ffn(plain.rms_norm(a, gains["weight"], 1e-5), fw["gate"], fw["up"], fw["down"])
+    _close(h.cpu(), want_h, dtype)
+
+
+# ---------------------------------------------------------------------------------------------
+# toy parts, defined in the test
+# ---------------------------------------------------------------------------------------------
+DECAY = 0.9
+STATE = 24
+EXPERTS, EXPERT_WIDTH = 3, 40
+ROPE_DIVISOR = 4.0
+
+
+def _register_toys():
+    from nanoinfer_b200.config import (FeedForwardSpec, LayerRun, LayerSpec, MixerSpec, ModelConfig, NormSpec,
+                                       PositionSpec, register_architecture, register_part)
+    from nanoinfer_b200.parts.base import Part, StateNeed, WeightSlot
+    from nanoinfer_b200.parts.position import RotaryEncoding
+
+    class RunningStateMixer(Part):
+        """s_t = DECAY * s_{t-1} + W_in x_t ;  y_t = W_out s_t.  One FP32 state vector per request."""
+
+        @staticmethod
+        def weight_slots(spec, hidden_size):
+            return {"w_in": WeightSlot((STATE, hidden_size)), "w_out": WeightSlot((hidden_size, STATE))}
+
+        def __init__(self, spec, hidden_size, weights, rt):
+            super().__init__(spec, hidden_size, weights, rt)
+            self.w_in = weights["w_in"].to(rt.device, torch.float32)
+            self.w_out = weights["w_out"].to(rt.device, torch.float32)
+
+        def cache_need(self):
+            return StateNeed((STATE,), "float32")
+
+        def forward(self, x, ctx, cache):
+            u = x.float() @ self.w_in.t()
+            y = torch.empty(x.shape[0], self.hidden_size, dtype=torch.float32, device=x.device)
+            at = 0
+            for n, slot in zip(ctx.host_q_lens, ctx.host_slots):   # tokens of a request in order
+                s = cache.state[slot]
+                for t in range(at, at + n):
+                    s = DECAY * s + u[t]
+                    y[t] = self.w_out @ s
+                cache.state[slot] = s
+                at += n
+            return y.to(self.rt.dtype)
+
+    class Top1Experts(Part):
+        """Router logits in FP32, the best expert alone: y = W2[e] relu(W1[e] x)."""
+
+        @staticmethod
+        def weight_slots(spec, hidden_size):
+            return {"router": WeightSlot((EXPERTS, hidden_size)),
+                    "w1": WeightSlot((EXPERTS, EXPERT_WIDTH, hidden_size)),
+                    "w2": WeightSlot((EXPERTS, hidden_size, EXPERT_WIDTH))}
+
+        def __init__(self, spec, hidden_size, weights, rt):
+            super().__init__(spec, hidden_size, weights, rt)
+            self.w = {k: v.to(rt.device, torch.float32) for k, v in weights.items()}
+
+        def forward(self, x, ctx):
+            xf = x.float()
+            e = torch.argmax(xf @ self.w["router"].t(), dim=-1)
+            hid = torch.relu(torch.einsum("tfd,td->tf", self.w["w1"][e], xf))
+            return torch.einsum("tdf,tf->td", self.w["w2"][e], hid).to(self.rt.dtype)
+
+    class SlowRope(RotaryEncoding):
+        """Rotary encoding with every frequency divided by ROPE_DIVISOR."""
+
+        def __init__(self, spec, hidden_size, weights, rt):
+            super().__init__(spec, hidden_size, weights, rt)
+            self.inv_freq = self.inv_freq / ROPE_DIVISOR
+
+    register_part("mixer", "toy_running_state", RunningStateMixer, replace=True)
+    register_part("feed_forward", "toy_top1_experts", Top1Experts, replace=True)
+    register_part("position", "toy_slow_rope", SlowRope, replace=True)
+
+    def parse(raw):
+        d, hd = raw["width"], raw["head"]
+        norm = NormSpec("rmsnorm", raw["eps"])
+
+        def att(window, pos_kind):
+            return MixerSpec("attention", raw["heads"], raw["kv_heads"], hd, window, 1.0 / math.sqrt(hd),
+                             PositionSpec(pos_kind, 10000.0, hd if pos_kind != "none" else 0, "half", None))
+        layers = (
+            LayerSpec(att(None, "toy_slow_rope"), FeedForwardSpec("swiglu", raw["ffn"]), norm, norm),
+            LayerSpec(MixerSpec("toy_running_state"), FeedForwardSpec("toy_top1_experts"), norm, norm),
+            LayerSpec(att(raw["window"], "none"), FeedForwardSpec("swiglu", raw["ffn"]), norm, norm),
+        )
+        # layer 0 runs twice (own cache each time); the last run reads run 2's pages
+        schedule = (LayerRun(0), LayerRun(1), LayerRun(2), LayerRun(0), LayerRun(2, cache_of=2))
+        return ModelConfig("ToyHybridForTest", d, raw["vocab"], raw["max_pos"], layers, schedule, norm,
+                           tie_word_embeddings=True)
+
+    def name(scope, slot):
+        return "toy." + ".".join(str(s) for s in scope) + "." + slot
+
+    register_architecture("ToyHybridForTest", parse, name, replace=True)
+
+
+TOY_RAW = {"architectures": ["ToyHybridForTest"], "width": 64, "head": 16, "heads": 4, "kv_heads": 2, "ffn": 96,
+           "vocab": 200, "max_pos": 256, "eps": 1e-5, "window": 11}
+
+
+def _toy_plain(w, tokens):
+    """The toy model, whole sequence, from the formulas above and plain_llama's parts."""
+    raw = TOY_RAW
+    d, hd, nq, nkv = raw["width"], raw["head"], raw["heads"], raw["kv_heads"]
+    T = len(tokens)
+    pos = torch.arange(T)
+    scale = 1.0 / math.sqrt(hd)
+    slow = plain.rope_inv_freq(hd, 10000.0, None) / ROPE_DIVISOR
+    W = {k: v.float() for k, v in w.items()}
+
+    def norm(h, key):
+        return plain.rms_norm(h, W[key], raw["eps"])
+
+    def att(h, i, inv_freq, window, kv_from=None):
+        x = norm(h, f"toy.layer.{i}.mixer_norm.weight")
+        q = (x @ W[f"toy.layer.{i}.mixer.q"].t()).view(T, nq, hd)
+        k = (x @ W[f"toy.layer.{i}.mixer.k"].t()).view(T, nkv, hd)
+        v = (x @ W[f"toy.layer.{i}.mixer.v"].t()).view(T, nkv, hd)
+        if inv_freq is not None:
+            q, k = plain.rope(q, pos, inv_freq, "half"), plain.rope(k, pos, inv_freq, "half")
+        if kv_from is not None:
+            k, v = kv_from
+        o = plain.attention(q, k, v, scale, window).reshape(T, nq * hd)
+        return h + o @ W[f"toy.layer.{i}.mixer.o"].t(), (k, v)
+
+    def swiglu(h, i):
+        x = norm(h, f"toy.layer.{i}.ffn_norm.weight")
+        p = f"toy.layer.{i}.feed_forward"
+        return h + plain.swiglu_ffn(x, W[f"{p}.gate"], W[f"{p}.up"], W[f"{p}.down"])
+
+    h = plain.embedding(W["toy.embedding.weight"], torch.tensor(tokens))
+    h, _ = att(h, 0, slow, None)
+    h = swiglu(h, 0)
+    # layer 1: running state + routed experts
+    x = norm(h, "toy.layer.1.mixer_norm.weight")
+    u = x @ W["toy.layer.1.mixer.w_in"].t()
+    s = torch.zeros(STATE)
+    y = torch.empty(T, d)
+    for t in range(T):
+        s = DECAY * s + u[t]
+        y[t] = W["toy.layer.1.mixer.w_out"] @ s
+    h = h + y
+    x = norm(h, "toy.layer.1.ffn_norm.weight")
+    e = torch.argmax(x @ W["toy.layer.1.feed_forward.router"].t(), dim=-1)
+    hid = torch.relu(torch.einsum("tfd,td->tf", W["toy.layer.1.feed_forward.w1"][e], x))
+    h = h + torch.einsum("tdf,tf->td", W["toy.layer.1.feed_forward.w2"][e], hid)
+    h, kv2 = att(h, 2, None, TOY_RAW["window"])
+    h = swiglu(h, 2)
+    h, _ = att(h, 0, slow, None)
+    h = swiglu(h, 0)
+    h, _ = att(h, 2, None, TOY_RAW["window"], kv_from=kv2)
+    h = swiglu(h, 2)
+    return norm(h, "toy.final_norm.weight") @ W["toy.embedding.weight"].t()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_parts_register_build_and_step(tmp_path, dtype):
+    from nanoinfer_b200.config import load_config
+    from nanoinfer_b200.engine import ModelRunner
+    from nanoinfer_b200.weights import load_weights, write_random_model
+    _register_toys()
+    d = str(tmp_path / "toy")
+    write_random_model(d, TOY_RAW, seed=5, std=0.08)        # random-weights mode knows the toy tensors
+    cfg = load_config(d)
+    weights = load_weights(d, cfg)
+    assert "toy.layer.1.mixer.w_in" in weights and "toy.layer.1.feed_forward.router" in weights
+    reqs = {f"t{i}": random_tokens(TOY_RAW["vocab"], n, 40 + i) for i, n in enumerate([9, 70, 31, 120])}
+    want = {rid: _toy_plain(weights, toks) for rid, toks in reqs.items()}
+    for cut in (ru.whole, ru.ragged, ru.mixed):
+        steps = cut(reqs)
+        runner = ModelRunner(cfg, weights, dtype=dtype, page_size=8,
+                             num_pages=ru.max_live_tokens(steps, 64) // 8, max_requests=4)
+        # three needs, three kinds of cache: all keys, a window of keys, a state slot
+        assert [g.window for g in runner.cache.groups] == [None, TOY_RAW["window"]]
+        assert len(runner._state_runs) == 1 and runner.caches[4].writable is False
+        got = ru.run_trace(runner, steps)
+        ru.compare(got, want, dtype, label=f"toy/{cut.__name__}/{dtype}")
+        runner.cache.check_consistency()
+        assert all(p.num_free == p.num_pages for p in runner.cache.pools)

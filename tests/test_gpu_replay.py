@@ -22,6 +22,7 @@ SETUP = {
     "a": (16, [5, 17, 33, 64, 100, 128]),
     "b": (8, [1, 7, 40, 90, 130, 300, 47]),
     "c": (16, [3, 48, 250, 611, 97]),
+    "d": (16, [2, 129, 700, 65, 310]),
 }
 CUTS = {"whole": ru.whole, "tail": ru.tail_by_token, "ragged": ru.ragged, "mixed": ru.mixed}
 
@@ -57,7 +58,7 @@ def _runner(model_dir, dtype, page, steps):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("cut", ["whole", "tail", "ragged", "mixed"])
-@pytest.mark.parametrize("key", ["a", "b", "c"])
+@pytest.mark.parametrize("key", ["a", "b", "c", "d"])
 def test_replay_matches_plain(model_dirs, plain_cache, key, cut, dtype):
     raw, reqs, want = _plain(plain_cache, key, model_dirs[key])
     steps = CUTS[cut](reqs)
@@ -80,6 +81,34 @@ def test_cuts_agree_bitwise_in_float32(model_dirs, plain_cache, key):
     for cut in ("tail", "ragged", "mixed"):
         for k, row in results["whole"].items():
             assert torch.equal(row, results[cut][k]), f"{key}: {cut} differs from whole at {k}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(model_dirs, dtype):
+    """A short prompt and then hundreds of tokens one by one (captured decode steps, pages
+    taken one at a time), against the plain implementation at every position."""
+    raw, w = load_plain(model_dirs["d"])
+    reqs = {"long": random_tokens(raw["vocab_size"], 420, 11), "other": random_tokens(raw["vocab_size"], 300, 12)}
+    steps = ru.tail_by_token(reqs, tail=290)
+    runner = _runner(model_dirs["d"], dtype, 16, steps)
+    got = ru.run_trace(runner, steps)
+    ru.compare(got, ru.plain_logits(raw, w, reqs), dtype, label=f"long/{dtype}")
+    assert runner._graphs, "single-token steps are expected to run as captured graphs"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("key", ["a", "b", "d"])
+def test_first_tokens_of_a_sequence(model_dirs, key, dtype):
+    """Positions 0, 1, 2: one key, two keys; alone, token by token and as a batch of short requests."""
+    raw, w = load_plain(model_dirs[key])
+    reqs = {f"s{n}": random_tokens(raw["vocab_size"], n, 20 + n) for n in (1, 2, 3, 4)}
+    want = ru.plain_logits(raw, w, reqs)
+    page = SETUP[key][0]
+    for steps in (ru.whole(reqs), ru.tail_by_token(reqs, tail=4),
+                  [{"step": 0, "entries": [{"id": r, "tokens": t, "want": list(range(len(t)))} for r, t in reqs.items()],
+                    "end": list(reqs)}]):
+        got = ru.run_trace(_runner(model_dirs[key], dtype, page, steps), steps)
+        ru.compare(got, want, dtype, label=f"first/{key}/{dtype}")
 
 
 def test_trace_run_program(model_dirs, tmp_path):

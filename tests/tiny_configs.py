@@ -2,7 +2,9 @@
 
 A and B differ in every size and option: layers, width, head counts and grouping, head
 size, feed-forward width, vocabulary, rope theta and scaling, eps, tied or untied output.
-C has sizes that are no power of two and a head size of 48.
+C has sizes that are no power of two and a head size of 48.  D has the head size (64) and
+grouping (4 query heads per key/value head) that the split-K decode kernel takes, and a width
+that is not heads x head size.
 """
 TINY_A = {
     "architectures": ["LlamaForCausalLM"],
@@ -30,5 +32,15 @@ TINY_C = {
     "rope_theta": 10000.0,
     "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
                      "high_freq_factor": 4.0, "original_max_position_embeddings": 256},
+    "tie_word_embeddings": True, "hidden_act": "silu",
+}
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"],
+    "hidden_size": 160, "intermediate_size": 264, "num_hidden_layers": 2,
+    "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 64,
+    "vocab_size": 520, "max_position_embeddings": 1024, "rms_norm_eps": 1e-5,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 128},
     "tie_word_embeddings": True, "hidden_act": "silu",
 }
