@@ -66,15 +66,88 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
     }
 }
 
+// The same with 16-byte accesses and the row held in registers between the two passes:
+// d a multiple of 4, at most VPT * 4 * blockDim.x.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+        const uint2 r = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&r.x);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&r.y);
+        return make_float4(__bfloat162float(a.x), __bfloat162float(a.y), __bfloat162float(b.x), __bfloat162float(b.y));
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 r;
+        r.x = *reinterpret_cast<uint32_t*>(&a);
+        r.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = r;
+    }
+};
+
+template <typename TD, typename TO, int VPT>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+                                       const float* __restrict__ gain, float eps, TO* __restrict__ out,
+                                       const int* __restrict__ rows, int d) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float* hr = h + (size_t)src * d;
+    const TD* dr = delta ? delta + (size_t)src * d : nullptr;
+    TO* o = out + (size_t)r * d;
+    const int n4 = d >> 2;
+    float4 v[VPT];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < n4) {
+            v[i] = Vec4<float>::load(hr + 4 * c);
+            if (dr) {
+                const float4 dv = Vec4<TD>::load(dr + 4 * c);
+                v[i].x += dv.x; v[i].y += dv.y; v[i].z += dv.z; v[i].w += dv.w;
+                if (!rows) Vec4<float>::store(hr + 4 * c, v[i]);
+            }
+            ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+        }
+    }
+    ss = ni_block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < n4) {
+            const float4 gv = Vec4<float>::load(gain + 4 * c);
+            Vec4<TO>::store(o + 4 * c, make_float4((v[i].x * inv) * gv.x, (v[i].y * inv) * gv.y,
+                                                   (v[i].z * inv) * gv.z, (v[i].w * inv) * gv.w));
+        }
+    }
+}
+
 NI_EXPORT int ni_add_rmsnorm(float* h, const void* delta, int delta_dtype, const float* gain,
                              float eps, void* out, int out_dtype, const int* rows, int n_rows,
                              int d, cudaStream_t stream) {
     if (n_rows <= 0) return NI_OK;
     if (d <= 0) return NI_ERR_BAD_ARGUMENT;
     const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
-#define LAUNCH(TD, TO)                                                                         \
-    add_rmsnorm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(h, (const TD*)delta, gain, eps, \
-                                                                (TO*)out, rows, d)
+    const bool vec = d % 4 == 0 && d <= 4 * 4 * threads;     // the row fits 4 float4 per thread
+    const bool vec1 = vec && d <= 4 * threads;
+#define LAUNCH(TD, TO)                                                                              \
+    do {                                                                                            \
+        if (vec1)                                                                                   \
+            add_rmsnorm_vec_kernel<TD, TO, 1><<<n_rows, threads, 0, stream>>>(h, (const TD*)delta, gain, eps, \
+                                                                             (TO*)out, rows, d);   \
+        else if (vec)                                                                               \
+            add_rmsnorm_vec_kernel<TD, TO, 4><<<n_rows, threads, 0, stream>>>(h, (const TD*)delta, gain, eps, \
+                                                                             (TO*)out, rows, d);   \
+        else                                                                                        \
+            add_rmsnorm_kernel<TD, TO><<<n_rows, threads, 0, stream>>>(h, (const TD*)delta, gain, eps, \
+                                                                        (TO*)out, rows, d);         \
+    } while (0)
     if (delta_dtype == NI_DTYPE_F32 && out_dtype == NI_DTYPE_F32) LAUNCH(float, float);
     else if (delta_dtype == NI_DTYPE_BF16 && out_dtype == NI_DTYPE_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else if (delta_dtype == NI_DTYPE_F32 && out_dtype == NI_DTYPE_BF16) LAUNCH(float, __nv_bfloat16);
@@ -122,6 +195,48 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
         const float u = ni_to_float(gate_up[t * 2 * inter + inter + i]);
         out[idx] = ni_from_float<T>((g / (1.0f + expf(-g))) * u);
     }
+}
+
+// The blocked layout: columns come in blocks of 16 = 8 gate values and their 8 up values, so
+// that one thread turns two 16-byte loads into one 16-byte store (and so that a matrix-product
+// epilogue finds a gate and its up value in the same tile).  out[t, 8b + r] =
+// silu(gate_up[t, 16b + r]) * gate_up[t, 16b + 8 + r].  inter is a multiple of 8.
+template <typename T>
+__global__ void swiglu_blocked_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int n_tokens,
+                                      int inter) {
+    const int blocks_per_row = inter >> 3;
+    const size_t total = (size_t)n_tokens * blocks_per_row;
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; idx < total; idx += stride) {
+        const size_t t = idx / blocks_per_row;
+        const int b = (int)(idx - t * blocks_per_row);
+        const T* src = gate_up + t * 2 * inter + 16 * b;
+        T* dst = out + t * inter + 8 * b;
+        const float4 g0 = Vec4<T>::load(src), g1 = Vec4<T>::load(src + 4);
+        const float4 u0 = Vec4<T>::load(src + 8), u1 = Vec4<T>::load(src + 12);
+        Vec4<T>::store(dst, make_float4((g0.x / (1.0f + expf(-g0.x))) * u0.x, (g0.y / (1.0f + expf(-g0.y))) * u0.y,
+                                        (g0.z / (1.0f + expf(-g0.z))) * u0.z, (g0.w / (1.0f + expf(-g0.w))) * u0.w));
+        Vec4<T>::store(dst + 4, make_float4((g1.x / (1.0f + expf(-g1.x))) * u1.x, (g1.y / (1.0f + expf(-g1.y))) * u1.y,
+                                            (g1.z / (1.0f + expf(-g1.z))) * u1.z, (g1.w / (1.0f + expf(-g1.w))) * u1.w));
+    }
+}
+
+NI_EXPORT int ni_swiglu_blocked(const void* gate_up, void* out, int dtype, int n_tokens, int inter,
+                                cudaStream_t stream) {
+    if (n_tokens <= 0) return NI_OK;
+    if (inter <= 0 || inter % 8) return NI_ERR_BAD_ARGUMENT;
+    const int threads = 256;
+    long long blocks = ((long long)n_tokens * (inter / 8) + threads - 1) / threads;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (dtype == NI_DTYPE_F32)
+        swiglu_blocked_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, n_tokens, inter);
+    else if (dtype == NI_DTYPE_BF16)
+        swiglu_blocked_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>(
+            (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, n_tokens, inter);
+    else
+        return NI_ERR_BAD_ARGUMENT;
+    NI_RETURN_LAUNCH_STATUS();
 }
 
 NI_EXPORT int ni_swiglu(const void* gate_up, void* out, int dtype, int n_tokens, int inter,

@@ -1,18 +1,31 @@
 // Skinny matrix product for decode: y[M, N] = x[M, K] . W[N, K]^T with M <= 16 rows of
-// activations against a large bfloat16 weight matrix - a bandwidth problem.
+// activations against a large bfloat16 weight matrix - a bandwidth problem - with the
+// neighbouring element-wise work fused into its two ends.
 //
 // "Swap AB": the weight rows are the M side of the tensor-core tile (mma.sync m16n8k16, bf16
 // in, FP32 accumulate) and the batch is the 8-wide N side, so one pass over the weights serves
-// the whole batch and the FP32 FMA pipes never become the limit (they would from about four
-// rows on).  A block owns 8 or 16 weight rows; its 8 warps split K and stream their slices
-// from global memory straight into MMA fragments with 16-byte loads (the contraction index is
-// permuted identically in both operands, as in attention_decode.cu), several loads in flight
-// per thread.  Partial sums meet in shared memory and are added in warp order, so a result
-// never depends on timing.  The epilogue stores bfloat16, stores FP32 (logits) or adds into
-// the FP32 residual stream.
+// the whole batch and the FP32 FMA pipes never become the limit.  A block owns 8 or 16 weight
+// rows; its 8 warps split K and stream their slices from global memory straight into MMA
+// fragments with 16-byte loads (the contraction index is permuted identically in both
+// operands), several loads in flight per thread.  Partial sums meet in shared memory and are
+// added in warp order, so a result never depends on timing.
 //
-// Reference counterpart: cublasSgemm on FP32 weights for every projection
-// (src/op/kernels/cuda/matmul_kernel.cu:48-89) plus a separate add kernel for the residual.
+// Input side:  bfloat16 activations, or the FP32 residual stream with RMSNorm fused in: the
+//   gain is applied while the fragments are built, the sum of squares of each row is collected
+//   from the very loads that feed the MMAs, and 1/rms is applied to the finished sums (it is a
+//   per-row scalar, so it commutes with the product).  An index list can pick the rows.
+// Output side: store bfloat16 | store FP32 (logits) | add into the FP32 residual stream |
+//   SwiGLU (weight rows come in blocks of 8 gate rows + their 8 up rows) | rotary encoding and
+//   the paged K/V write of a fused QKV projection (weight rows ordered so that the two
+//   elements of a rotary pair are adjacent).
+//
+// The kernels are launched with programmatic stream serialisation: the first weight fragments
+// are requested before griddepcontrol.wait, so a kernel's weight stream starts while the
+// kernel before it drains; nothing that depends on the previous kernel is touched before the wait.
+//
+// Reference counterparts: cublasSgemm on FP32 weights for every projection
+// (src/op/kernels/cuda/matmul_kernel.cu:48-89) and separate kernels for RMSNorm, RoPE, the cache
+// write, SwiGLU and the residual add (src/model/llama.cpp:324-379).
 #include "common.cuh"
 
 #define GV_WARPS 8
@@ -21,6 +34,26 @@
 #define GV_STORE_BF16 0
 #define GV_STORE_F32 1
 #define GV_ADD_F32 2
+#define GV_SWIGLU 3
+#define GV_ROPE_KV 4
+
+struct GemvParams {
+    const void* x;            // bf16 [M, K], or FP32 [*, K] with the norm fused
+    const float* gain;        // norm: [K]
+    const int* rows;          // norm: optional source row of each of the M rows
+    float eps;
+    const __nv_bfloat16* w;   // [N, K]
+    void* out;
+    int M, N, K, mode;
+    // GV_ROPE_KV
+    const int* positions;
+    const int* seq_of_token;
+    const int* block_table;
+    const float* inv_freq;
+    __nv_bfloat16* k_pages;
+    __nv_bfloat16* v_pages;
+    int bt_stride, n_q_heads, n_kv_heads, head_dim, rotary_dim, page_size, write_cache;
+};
 
 __device__ __forceinline__ void gv_mma(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                        uint32_t b0, uint32_t b1) {
@@ -29,40 +62,42 @@ __device__ __forceinline__ void gv_mma(float c[4], uint32_t a0, uint32_t a1, uin
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-
 __device__ __forceinline__ uint4 ld_stream(const void* p) {
     uint4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
 
-// RN: weight rows per block (8 or 16).  NT: batch tiles of 8 rows (1 or 2).
-template <int RN, int NT>
-__global__ void __launch_bounds__(GV_WARPS * 32)
-gemv_bf16_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
-                 void* __restrict__ out, int M, int N, int K, int mode) {
+// RN: weight rows per block (8 or 16).  NT: batch tiles of 8 rows (1 or 2).  NORM: FP32 input + RMSNorm.
+template <int RN, int NT, bool NORM>
+__global__ void __launch_bounds__(GV_WARPS * 32) gemv_bf16_kernel(const GemvParams p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * RN;
+    const int M = p.M, N = p.N, K = p.K;
     const int n_blocks = (K + 63) / 64;            // k-blocks of 64
     const uint4 zero = make_uint4(0, 0, 0, 0);
+    pdl_launch_dependents();
 
     const bool row_a_ok = n0 + g < N;
     const bool row_b_ok = RN == 16 && n0 + g + 8 < N;
-    const __nv_bfloat16* wa = w + (size_t)(row_a_ok ? n0 + g : 0) * K;
-    const __nv_bfloat16* wb = w + (size_t)(row_b_ok ? n0 + g + 8 : 0) * K;
-    const __nv_bfloat16* xr[NT];
-    bool x_ok[NT];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-        x_ok[nt] = 8 * nt + g < M;
-        xr[nt] = x + (size_t)(x_ok[nt] ? 8 * nt + g : 0) * K;
-    }
+    const __nv_bfloat16* wa = p.w + (size_t)(row_a_ok ? n0 + g : 0) * K;
+    const __nv_bfloat16* wb = p.w + (size_t)(row_b_ok ? n0 + g + 8 : 0) * K;
 
-    float acc[NT][4];
+    float acc[NT][4], ssq[NT];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+    for (int nt = 0; nt < NT; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; ssq[nt] = 0.f; }
+
+    const void* xr[NT];
+    bool x_ok[NT];
+    bool waited = false;
 
     for (int kb = warp; kb < n_blocks; kb += GV_WARPS * GV_UNROLL) {
         uint4 fa[GV_UNROLL][2], fb[GV_UNROLL][2], fx[GV_UNROLL][NT][2];
@@ -75,9 +110,44 @@ gemv_bf16_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __res
                 const bool ok = k + 8 <= K;        // K is a multiple of 8
                 fa[u][h] = (ok && row_a_ok) ? ld_stream(wa + k) : zero;
                 fb[u][h] = (RN == 16 && ok && row_b_ok) ? ld_stream(wb + k) : zero;
+            }
+        }
+        if (!waited) {
+            // everything above reads weights only; what follows depends on the kernel before
+            pdl_wait();
+            waited = true;
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt)
-                    fx[u][nt][h] = (ok && x_ok[nt]) ? *reinterpret_cast<const uint4*>(xr[nt] + k) : zero;
+            for (int nt = 0; nt < NT; ++nt) {
+                const int m = 8 * nt + g;
+                x_ok[nt] = m < M;
+                const int src = (NORM && p.rows && x_ok[nt]) ? p.rows[m] : (x_ok[nt] ? m : 0);
+                xr[nt] = NORM ? (const void*)((const float*)p.x + (size_t)src * K)
+                              : (const void*)((const __nv_bfloat16*)p.x + (size_t)src * K);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < GV_UNROLL; ++u) {
+            const int k0 = (kb + u * GV_WARPS) * 64;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int k = k0 + 32 * h + 8 * t;
+                const bool ok = k + 8 <= K;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    if (!(ok && x_ok[nt])) { fx[u][nt][h] = zero; continue; }
+                    if (NORM) {
+                        const float4 h0 = *reinterpret_cast<const float4*>((const float*)xr[nt] + k);
+                        const float4 h1 = *reinterpret_cast<const float4*>((const float*)xr[nt] + k + 4);
+                        const float4 g0 = *reinterpret_cast<const float4*>(p.gain + k);
+                        const float4 g1 = *reinterpret_cast<const float4*>(p.gain + k + 4);
+                        ssq[nt] += h0.x * h0.x + h0.y * h0.y + h0.z * h0.z + h0.w * h0.w +
+                                   h1.x * h1.x + h1.y * h1.y + h1.z * h1.z + h1.w * h1.w;
+                        fx[u][nt][h] = make_uint4(pack2(h0.x * g0.x, h0.y * g0.y), pack2(h0.z * g0.z, h0.w * g0.w),
+                                                  pack2(h1.x * g1.x, h1.y * g1.y), pack2(h1.z * g1.z, h1.w * g1.w));
+                    } else {
+                        fx[u][nt][h] = *reinterpret_cast<const uint4*>((const __nv_bfloat16*)xr[nt] + k);
+                    }
+                }
             }
         }
 #pragma unroll
@@ -90,47 +160,161 @@ gemv_bf16_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __res
                     gv_mma(acc[nt], fa[u][h].z, fb[u][h].z, fa[u][h].w, fb[u][h].w, fx[u][nt][h].z, fx[u][nt][h].w);
                 }
     }
+    if (!waited) pdl_wait();   // a warp without work still must not run ahead of the epilogue's inputs
 
     // partial sums of the 8 warps -> shared memory -> summed in warp order
     __shared__ float red[GV_WARPS][NT][16][8];
+    __shared__ float ss_red[GV_WARPS][NT * 8];
+    __shared__ float tile[NT * 8][17];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
         red[warp][nt][g][2 * t] = acc[nt][0];
         red[warp][nt][g][2 * t + 1] = acc[nt][1];
         red[warp][nt][g + 8][2 * t] = acc[nt][2];
         red[warp][nt][g + 8][2 * t + 1] = acc[nt][3];
+        if (NORM) {
+            float s = ssq[nt];
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            if (t == 0) ss_red[warp][nt * 8 + g] = s;
+        }
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < NT * 8 * RN; idx += blockDim.x) {
-        const int row = idx % RN;                  // weight row within the block: fastest, for coalescing
+        const int row = idx % RN;                  // weight row within the block
         const int m = idx / RN;                    // batch row
-        const int n = n0 + row;
-        if (m >= M || n >= N) continue;
         float s = 0.f;
 #pragma unroll
         for (int wi = 0; wi < GV_WARPS; ++wi) s += red[wi][m >> 3][row][m & 7];
-        const size_t o = (size_t)m * N + n;
-        if (mode == GV_STORE_BF16) reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(s);
-        else if (mode == GV_STORE_F32) reinterpret_cast<float*>(out)[o] = s;
-        else reinterpret_cast<float*>(out)[o] += s;
+        if (NORM) {
+            float q = 0.f;
+#pragma unroll
+            for (int wi = 0; wi < GV_WARPS; ++wi) q += ss_red[wi][m];
+            s *= 1.0f / sqrtf(q / (float)K + p.eps);
+        }
+        tile[m][row] = s;
+    }
+    __syncthreads();
+
+    const int mode = p.mode;
+    if (mode <= GV_ADD_F32) {
+        for (int idx = threadIdx.x; idx < NT * 8 * RN; idx += blockDim.x) {
+            const int row = idx % RN, m = idx / RN, n = n0 + row;
+            if (m >= M || n >= N) continue;
+            const float s = tile[m][row];
+            const size_t o = (size_t)m * N + n;
+            if (mode == GV_STORE_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(s);
+            else if (mode == GV_STORE_F32) reinterpret_cast<float*>(p.out)[o] = s;
+            else reinterpret_cast<float*>(p.out)[o] += s;
+        }
+    } else if (mode == GV_SWIGLU) {
+        // rows 0..7 of the block: gate; rows 8..15: the matching up rows (RN == 16)
+        for (int idx = threadIdx.x; idx < NT * 8 * 8; idx += blockDim.x) {
+            const int r = idx & 7, m = idx >> 3;
+            if (m >= M || n0 + r + 8 >= N) continue;
+            const float gt = tile[m][r], up = tile[m][r + 8];
+            reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * (N / 2) + (n0 >> 1) + r] =
+                __float2bfloat16_rn((gt / (1.0f + expf(-gt))) * up);
+        }
+    } else {  // GV_ROPE_KV: rows come in adjacent rotary pairs; a block never straddles a head
+        const int hd = p.head_dim, nq = p.n_q_heads, nkv = p.n_kv_heads;
+        for (int idx = threadIdx.x; idx < NT * 8 * (RN / 2); idx += blockDim.x) {
+            const int pr = idx % (RN / 2), m = idx / (RN / 2);
+            const int n = n0 + 2 * pr;
+            if (m >= M || n + 1 >= N) continue;
+            const int head = n / hd, d = n - head * hd;
+            float a = tile[m][2 * pr], b = tile[m][2 * pr + 1];
+            const int pos = p.positions[m];
+            if (head < nq + nkv && d < p.rotary_dim) {
+                float sn, cs;
+                sincosf((float)pos * p.inv_freq[d >> 1], &sn, &cs);
+                const float ra = a * cs - b * sn, rb = a * sn + b * cs;
+                a = ra; b = rb;
+            }
+            __nv_bfloat16* dst;
+            if (head < nq) {
+                dst = reinterpret_cast<__nv_bfloat16*>(p.out) + ((size_t)m * nq + head) * hd + d;
+            } else {
+                if (!p.write_cache) continue;
+                const int page = p.block_table[(size_t)p.seq_of_token[m] * p.bt_stride + pos / p.page_size];
+                const int kvh = head < nq + nkv ? head - nq : head - nq - nkv;
+                __nv_bfloat16* base = head < nq + nkv ? p.k_pages : p.v_pages;
+                dst = base + (((size_t)page * nkv + kvh) * p.page_size + (pos % p.page_size)) * hd + d;
+            }
+            *reinterpret_cast<uint32_t*>(dst) = pack2(a, b);
+        }
     }
 }
 
-// mode: 0 store bfloat16, 1 store float32, 2 add into float32.  M <= 16, K a multiple of 8.
+template <int RN, int NT, bool NORM>
+static int launch_gemv(const GemvParams& p, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((p.N + RN - 1) / RN);
+    cfg.blockDim = dim3(GV_WARPS * 32);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_bf16_kernel<RN, NT, NORM>, p);
+    return e == cudaSuccess ? NI_OK : (int)e;
+}
+
+static int dispatch_gemv(const GemvParams& p, bool norm, cudaStream_t stream) {
+    if (p.M <= 0 || p.N <= 0) return NI_OK;
+    if (p.K <= 0 || p.mode < 0 || p.mode > GV_ROPE_KV) return NI_ERR_BAD_ARGUMENT;
+    if (p.M > 16 || p.K % 8) return NI_ERR_UNSUPPORTED_SIZE;
+    // 16 rows per block unless that leaves SMs idle; the fused epilogues need whole 16-row blocks
+    const bool rn16 = p.mode >= GV_SWIGLU || (p.N + 15) / 16 >= 2 * 148;
+    if (p.mode == GV_SWIGLU && p.N % 16) return NI_ERR_UNSUPPORTED_SIZE;
+    if (p.mode == GV_ROPE_KV && (p.head_dim % 16 || p.rotary_dim % 2 ||
+                                 p.N != (p.n_q_heads + 2 * p.n_kv_heads) * p.head_dim))
+        return NI_ERR_BAD_ARGUMENT;
+    const bool one = p.M <= 8;
+    if (norm) {
+        if (rn16) return one ? launch_gemv<16, 1, true>(p, stream) : launch_gemv<16, 2, true>(p, stream);
+        return one ? launch_gemv<8, 1, true>(p, stream) : launch_gemv<8, 2, true>(p, stream);
+    }
+    if (rn16) return one ? launch_gemv<16, 1, false>(p, stream) : launch_gemv<16, 2, false>(p, stream);
+    return one ? launch_gemv<8, 1, false>(p, stream) : launch_gemv<8, 2, false>(p, stream);
+}
+
+// x bf16 [M, K].  mode: 0 store bf16 [M, N], 1 store FP32, 2 add into FP32, 3 SwiGLU -> bf16 [M, N / 2].
 NI_EXPORT int ni_gemv_bf16(const void* x, const void* w, void* out, int M, int N, int K, int mode,
                            cudaStream_t stream) {
-    if (M <= 0 || N <= 0) return NI_OK;
-    if (K <= 0 || mode < 0 || mode > 2) return NI_ERR_BAD_ARGUMENT;
-    if (M > 16 || K % 8) return NI_ERR_UNSUPPORTED_SIZE;
-    // 16 rows per block unless that leaves SMs idle
-    const bool rn16 = (N + 15) / 16 >= 2 * 148;
-    const int rn = rn16 ? 16 : 8;
-    const int grid = (N + rn - 1) / rn;
-#define LAUNCH(RN, NT)                                                                      \
-    gemv_bf16_kernel<RN, NT><<<grid, GV_WARPS * 32, 0, stream>>>(                           \
-        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, out, M, N, K, mode)
-    if (rn16) { if (M <= 8) LAUNCH(16, 1); else LAUNCH(16, 2); }
-    else { if (M <= 8) LAUNCH(8, 1); else LAUNCH(8, 2); }
-#undef LAUNCH
-    NI_RETURN_LAUNCH_STATUS();
+    if (mode == GV_ROPE_KV) return NI_ERR_BAD_ARGUMENT;
+    GemvParams p = {};
+    p.x = x; p.w = (const __nv_bfloat16*)w; p.out = out; p.M = M; p.N = N; p.K = K; p.mode = mode;
+    return dispatch_gemv(p, false, stream);
+}
+
+// h FP32 [*, K] with RMSNorm fused: y = (norm(h[rows]) * gain) . w^T.  rows may be null (rows 0..M-1).
+NI_EXPORT int ni_gemv_norm_bf16(const float* h, const float* gain, float eps, const int* rows, const void* w,
+                                void* out, int M, int N, int K, int mode, cudaStream_t stream) {
+    if (mode == GV_ROPE_KV) return NI_ERR_BAD_ARGUMENT;
+    GemvParams p = {};
+    p.x = h; p.gain = gain; p.eps = eps; p.rows = rows; p.w = (const __nv_bfloat16*)w; p.out = out;
+    p.M = M; p.N = N; p.K = K; p.mode = mode;
+    return dispatch_gemv(p, true, stream);
+}
+
+// Fused QKV projection of single tokens with RMSNorm in front and rotary encoding + paged K/V
+// write behind: q (rotated) -> q_out bf16 [M, Hq * hd]; k (rotated), v -> their page slots.
+// The weight rows of q and k must be ordered with rotary pairs adjacent (2i, 2i + 1).
+// h may instead be bf16 activations when gain is null (no norm).
+NI_EXPORT int ni_gemv_qkv_rope(const void* x, const float* gain, float eps, const void* w, void* q_out,
+                               void* k_pages, void* v_pages, const int* positions, const int* seq_of_token,
+                               const int* block_table, int bt_stride, const float* inv_freq, int M, int K,
+                               int n_q_heads, int n_kv_heads, int head_dim, int rotary_dim, int page_size,
+                               int write_cache, cudaStream_t stream) {
+    GemvParams p = {};
+    p.x = x; p.gain = gain; p.eps = eps; p.w = (const __nv_bfloat16*)w; p.out = q_out;
+    p.M = M; p.N = (n_q_heads + 2 * n_kv_heads) * head_dim; p.K = K; p.mode = GV_ROPE_KV;
+    p.positions = positions; p.seq_of_token = seq_of_token; p.block_table = block_table; p.bt_stride = bt_stride;
+    p.inv_freq = inv_freq; p.k_pages = (__nv_bfloat16*)k_pages; p.v_pages = (__nv_bfloat16*)v_pages;
+    p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim; p.rotary_dim = rotary_dim;
+    p.page_size = page_size; p.write_cache = write_cache;
+    return dispatch_gemv(p, gain != nullptr, stream);
 }

@@ -75,6 +75,91 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, T* __restrict__ 
     }
 }
 
+// Adjacent-pair rotation with 16-byte accesses: one thread takes 8 consecutive elements (4
+// rotary pairs) of one head of one token.  head_dim a multiple of 8.
+template <typename T> struct Chunk8;
+template <> struct Chunk8<__nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float v[8]) {
+        const uint4 r = *reinterpret_cast<const uint4*>(p);
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&w[i]);
+            v[2 * i] = __bfloat162float(b.x);
+            v[2 * i + 1] = __bfloat162float(b.y);
+        }
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float v[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&b);
+        }
+        *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+template <> struct Chunk8<float> {
+    static __device__ __forceinline__ void load(const float* p, float v[8]) {
+        const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float v[8]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+};
+
+template <typename T>
+__global__ void rope_kv_write_vec_kernel(const T* __restrict__ qkv, T* __restrict__ q_out,
+                                         T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                         const int* __restrict__ positions,
+                                         const int* __restrict__ seq_of_token,
+                                         const int* __restrict__ block_table, int bt_stride,
+                                         const float* __restrict__ inv_freq, int n_tokens, int n_q_heads,
+                                         int n_kv_heads, int head_dim, int rotary_dim, int page_size,
+                                         int write_cache) {
+    const int chunks_per_head = head_dim >> 3;
+    const int heads = n_q_heads + 2 * n_kv_heads;
+    const long long total = (long long)n_tokens * heads * chunks_per_head;
+    long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; idx < total; idx += stride) {
+        const int c = (int)(idx % chunks_per_head);
+        const long long th = idx / chunks_per_head;
+        const int head = (int)(th % heads);
+        const int t = (int)(th / heads);
+        const int pos = positions[t];
+        float v[8];
+        Chunk8<T>::load(qkv + ((size_t)t * heads + head) * head_dim + 8 * c, v);
+        if (head < n_q_heads + n_kv_heads) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int d = 8 * c + 2 * i;
+                if (d < rotary_dim) {
+                    float s, cs;
+                    sincosf((float)pos * inv_freq[d >> 1], &s, &cs);
+                    const float a = v[2 * i], b = v[2 * i + 1];
+                    v[2 * i] = a * cs - b * s;
+                    v[2 * i + 1] = a * s + b * cs;
+                }
+            }
+        }
+        T* dst;
+        if (head < n_q_heads) {
+            dst = q_out + ((size_t)t * n_q_heads + head) * head_dim + 8 * c;
+        } else {
+            if (!write_cache) continue;
+            const int page = block_table[(size_t)seq_of_token[t] * bt_stride + pos / page_size];
+            const bool is_k = head < n_q_heads + n_kv_heads;
+            const int kvh = is_k ? head - n_q_heads : head - n_q_heads - n_kv_heads;
+            dst = (is_k ? k_pages : v_pages) +
+                  (((size_t)page * n_kv_heads + kvh) * page_size + (pos % page_size)) * head_dim + 8 * c;
+        }
+        Chunk8<T>::store(dst, v);
+    }
+}
+
 NI_EXPORT int ni_rope_kv_write(const void* qkv, int dtype, void* q_out, void* k_pages,
                                void* v_pages, const int* positions, const int* seq_of_token,
                                const int* block_table, int bt_stride, const float* inv_freq,
@@ -85,6 +170,20 @@ NI_EXPORT int ni_rope_kv_write(const void* qkv, int dtype, void* q_out, void* k_
     if (head_dim <= 0 || head_dim % 2 || rotary_dim < 0 || rotary_dim % 2 || rotary_dim > head_dim ||
         n_q_heads <= 0 || n_kv_heads <= 0 || page_size <= 0)
         return NI_ERR_BAD_ARGUMENT;
+    if (interleaved && head_dim % 8 == 0) {
+        const long long items = (long long)n_tokens * (n_q_heads + 2 * n_kv_heads) * (head_dim / 8);
+        long long blocks = (items + 255) / 256;
+        if (blocks > 148 * 16) blocks = 148 * 16;
+#define LAUNCHV(T)                                                                                     \
+    rope_kv_write_vec_kernel<T><<<(int)blocks, 256, 0, stream>>>(                                      \
+        (const T*)qkv, (T*)q_out, (T*)k_pages, (T*)v_pages, positions, seq_of_token, block_table,     \
+        bt_stride, inv_freq, n_tokens, n_q_heads, n_kv_heads, head_dim, rotary_dim, page_size, write_cache)
+        if (dtype == NI_DTYPE_F32) LAUNCHV(float);
+        else if (dtype == NI_DTYPE_BF16) LAUNCHV(__nv_bfloat16);
+        else return NI_ERR_BAD_ARGUMENT;
+#undef LAUNCHV
+        NI_RETURN_LAUNCH_STATUS();
+    }
     const int n_pairs = (n_q_heads + 2 * n_kv_heads) * head_dim / 2;
     const int threads = n_pairs >= 1024 ? 256 : 128;
 #define LAUNCH(T)                                                                                  \

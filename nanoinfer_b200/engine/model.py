@@ -57,5 +57,12 @@ class DecoderModel:
             delta = self.blocks[run.layer].forward(h, delta, ctx, caches[r])
         if ctx.n_logit_rows == 0:
             return rt.empty(0, cfg.vocab_size, dtype=torch.float32)
-        x = self.final_norm.forward(h, delta, rows=ctx.logit_rows)
+        norm = self.final_norm
+        if (delta is None and rt.skinny(ctx.n_logit_rows, cfg.hidden_size) and hasattr(norm, "gain")
+                and hasattr(norm, "eps")):
+            # few rows: final norm, row selection and output projection in one launch
+            logits = rt.empty(ctx.n_logit_rows, cfg.vocab_size, dtype=torch.float32)
+            ops.gemv_norm_bf16(h, norm.gain, norm.eps, ctx.logit_rows, self.lm_head, logits, ops.STORE_F32)
+            return logits
+        x = norm.forward(h, delta, rows=ctx.logit_rows)
         return rt.linear(x, self.lm_head, out_dtype=torch.float32)

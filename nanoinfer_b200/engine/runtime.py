@@ -66,6 +66,11 @@ class Runtime:
             return out
         return ops.linear_bf16(x, w, out_dtype, residual)
 
+    def skinny(self, n_rows: int, k: int) -> bool:
+        """True if a product of n_rows activations with inner size k goes to the package's own
+        bandwidth kernel (and so may carry fused prologues and epilogues)."""
+        return self.dtype == torch.bfloat16 and 0 < n_rows <= ops.GEMV_MAX_ROWS and k % 8 == 0
+
     def workspace(self, name: str, numel: int, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
         """A persistent scratch tensor of at least ``numel`` elements, shared by all layers
         (they run one after the other on one stream).  ``zero``: zero-filled when created;

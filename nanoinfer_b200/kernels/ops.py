@@ -28,6 +28,7 @@ _SIGNATURES = {
         "ni_add_rmsnorm": [_P, _P, _I, _P, _F, _P, _I, _P, _I, _I, _P],
         "ni_residual_add": [_P, _P, _I, _LL, _P],
         "ni_swiglu": [_P, _P, _I, _I, _I, _P],
+        "ni_swiglu_blocked": [_P, _P, _I, _I, _I, _P],
     },
     "rope_kv": {
         "ni_rope_kv_write": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -40,6 +41,8 @@ _SIGNATURES = {
     },
     "gemv_bf16": {
         "ni_gemv_bf16": [_P, _P, _P, _I, _I, _I, _I, _P],
+        "ni_gemv_norm_bf16": [_P, _P, _F, _P, _P, _P, _I, _I, _I, _I, _P],
+        "ni_gemv_qkv_rope": [_P, _P, _F, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     },
     "attention_decode": {
         "ni_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P],
@@ -169,13 +172,17 @@ def residual_add(h: torch.Tensor, delta: torch.Tensor) -> None:
            "residual_add")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, blocked: bool = False) -> None:
+    """out[t, i] = silu(gate[t, i]) * up[t, i].  Plain layout: gate_up = [gate | up] along the
+    columns.  Blocked layout (I a multiple of 8): columns in blocks of 8 gate values followed by
+    their 8 up values."""
     n, inter = out.shape
     if gate_up.shape != (n, 2 * inter) or gate_up.dtype != out.dtype:
         raise KernelError("swiglu: gate_up must be [T, 2I] of out's dtype")
-    _check(load("elementwise").ni_swiglu(_dev(gate_up, "gate_up"), _dev(out, "out"),
-                                         _code(out, "out"), n, inter, _stream()), "swiglu")
+    if blocked and inter % 8:
+        raise KernelError("swiglu: the blocked layout needs I to be a multiple of 8")
+    fn = load("elementwise").ni_swiglu_blocked if blocked else load("elementwise").ni_swiglu
+    _check(fn(_dev(gate_up, "gate_up"), _dev(out, "out"), _code(out, "out"), n, inter, _stream()), "swiglu")
 
 
 def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, k_pages: Optional[torch.Tensor],
@@ -238,21 +245,78 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 
 
 GEMV_MAX_ROWS = 16
-STORE_BF16, STORE_F32, ADD_F32 = 0, 1, 2
+STORE_BF16, STORE_F32, ADD_F32, SWIGLU_BF16 = 0, 1, 2, 3
+
+
+def _gemv_check(m: int, n: int, k: int, w: torch.Tensor, out: torch.Tensor, mode: int, what: str) -> None:
+    if w.shape != (n, k):
+        raise KernelError(f"{what}: shapes do not agree")
+    if m > GEMV_MAX_ROWS or k % 8:
+        raise KernelError(f"{what}: takes at most {GEMV_MAX_ROWS} rows and K a multiple of 8 "
+                          f"(got M={m}, K={k})")
+    if mode == SWIGLU_BF16:
+        if n % 16 or out.shape != (m, n // 2) or out.dtype != torch.bfloat16:
+            raise KernelError(f"{what}: the SwiGLU epilogue needs N a multiple of 16 and out bf16 [M, N/2]")
+    else:
+        want = torch.bfloat16 if mode == STORE_BF16 else torch.float32
+        if out.shape != (m, n) or out.dtype != want:
+            raise KernelError(f"{what}: out must be {want} [M, N]")
 
 
 def gemv_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int) -> None:
-    """out[M, N] (=, or += for mode ADD_F32) x[M, K] . w[N, K]^T for M <= 16, K % 8 == 0."""
+    """x[M, K] . w[N, K]^T for M <= 16, K % 8 == 0.  mode STORE_BF16 / STORE_F32: out[M, N] =;
+    ADD_F32: out[M, N] +=; SWIGLU_BF16: w's rows in blocks of 8 gate + 8 up rows,
+    out[M, N/2] = silu(gate) * up."""
     m, k = x.shape
     n = w.shape[0]
-    if w.shape[1] != k or out.shape != (m, n):
-        raise KernelError("gemv_bf16: shapes do not agree")
-    if m > GEMV_MAX_ROWS or k % 8:
-        raise KernelError(f"gemv_bf16: takes at most {GEMV_MAX_ROWS} rows and K a multiple of 8 "
-                          f"(got M={m}, K={k})")
-    want = torch.bfloat16 if mode == STORE_BF16 else torch.float32
+    _gemv_check(m, n, k, w, out, mode, "gemv_bf16")
     _check(load("gemv_bf16").ni_gemv_bf16(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16),
-                                          _dev(out, "out", want), m, n, k, mode, _stream()), "gemv_bf16")
+                                          _dev(out, "out"), m, n, k, mode, _stream()), "gemv_bf16")
+
+
+def gemv_norm_bf16(h: torch.Tensor, gain: torch.Tensor, eps: float, rows: Optional[torch.Tensor],
+                   w: torch.Tensor, out: torch.Tensor, mode: int) -> None:
+    """The same product with RMSNorm fused in front: x = norm(h[rows]) * gain, h float32
+    [*, K] (the residual stream), rows int32 [M] or None for rows 0..M-1."""
+    k = h.shape[1]
+    m = h.shape[0] if rows is None else rows.numel()
+    n = w.shape[0]
+    _gemv_check(m, n, k, w, out, mode, "gemv_norm_bf16")
+    if gain.numel() != k:
+        raise KernelError("gemv_norm_bf16: gain must have K entries")
+    _check(load("gemv_bf16").ni_gemv_norm_bf16(
+        _dev(h, "h", torch.float32), _dev(gain, "gain", torch.float32), float(eps),
+        _dev(rows, "rows", torch.int32) if rows is not None else None, _dev(w, "w", torch.bfloat16),
+        _dev(out, "out"), m, n, k, mode, _stream()), "gemv_norm_bf16")
+
+
+def gemv_qkv_rope(x: torch.Tensor, gain: Optional[torch.Tensor], eps: float, w: torch.Tensor,
+                  q_out: torch.Tensor, k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
+                  positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
+                  inv_freq: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int,
+                  page_size: int) -> None:
+    """Fused QKV projection of at most 16 single tokens: optional RMSNorm in front (x float32
+    residual stream and ``gain`` given) or bfloat16 activations (gain None); rotary encoding of
+    adjacent pairs and the paged K/V write behind.  q -> q_out bf16 [M, Hq hd]."""
+    m, k = x.shape
+    n = (n_q_heads + 2 * n_kv_heads) * head_dim
+    if w.shape != (n, k) or q_out.shape != (m, n_q_heads * head_dim):
+        raise KernelError("gemv_qkv_rope: shapes do not agree")
+    if m > GEMV_MAX_ROWS or k % 8 or head_dim % 16:
+        raise KernelError("gemv_qkv_rope: at most 16 rows, K a multiple of 8, head_dim a multiple of 16")
+    write = k_pages is not None
+    if write and tuple(k_pages.shape[1:]) != (n_kv_heads, page_size, head_dim):
+        raise KernelError("gemv_qkv_rope: pages must be [P, Hkv, page_size, head_dim]")
+    _check(load("gemv_bf16").ni_gemv_qkv_rope(
+        _dev(x, "x", torch.float32 if gain is not None else torch.bfloat16),
+        _dev(gain, "gain", torch.float32) if gain is not None else None, float(eps),
+        _dev(w, "w", torch.bfloat16), _dev(q_out, "q_out", torch.bfloat16),
+        _dev(k_pages, "k_pages", torch.bfloat16) if write else None,
+        _dev(v_pages, "v_pages", torch.bfloat16) if write else None,
+        _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
+        _dev(block_table, "block_table", torch.int32), block_table.shape[1],
+        _dev(inv_freq, "inv_freq", torch.float32), m, k, n_q_heads, n_kv_heads, head_dim, rotary_dim,
+        page_size, 1 if write else 0, _stream()), "gemv_qkv_rope")
 
 
 def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,

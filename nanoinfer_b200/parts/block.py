@@ -29,15 +29,28 @@ class PreNormBlock:
             layer_spec.feed_forward, hidden_size, weights_of("feed_forward"), rt)
 
     def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], ctx, cache) -> torch.Tensor:
-        x = self.mixer_norm.forward(h, delta)
-        if getattr(self.mixer, "adds_into_residual", False):
-            a = self.mixer.forward(x, ctx, cache, residual=h)     # may add in place and return None
+        n = h.shape[0]
+        mixer, ffn = self.mixer, self.feed_forward
+        if delta is None and _fuses(mixer, self.mixer_norm, n):
+            a = mixer.forward_fused_norm(h, self.mixer_norm, ctx, cache, residual=h)
         else:
-            a = self.mixer.forward(x, ctx, cache)
+            x = self.mixer_norm.forward(h, delta)
+            if getattr(mixer, "adds_into_residual", False):
+                a = mixer.forward(x, ctx, cache, residual=h)     # may add in place and return None
+            else:
+                a = mixer.forward(x, ctx, cache)
+        if a is None and _fuses(ffn, self.ffn_norm, n):
+            return ffn.forward_fused_norm(h, self.ffn_norm, ctx, residual=h)
         x = self.ffn_norm.forward(h, a)
-        if getattr(self.feed_forward, "adds_into_residual", False):
-            return self.feed_forward.forward(x, ctx, residual=h)
-        return self.feed_forward.forward(x, ctx)
+        if getattr(ffn, "adds_into_residual", False):
+            return ffn.forward(x, ctx, residual=h)
+        return ffn.forward(x, ctx)
+
+
+def _fuses(part_obj, norm, n_rows: int) -> bool:
+    """A mixer or feed-forward may offer forward_fused_norm(h, norm, ...): it then reads the
+    residual stream itself and runs the norm inside its first kernel."""
+    return hasattr(part_obj, "forward_fused_norm") and part_obj.can_fuse_norm(norm, n_rows)
 
 
 register_part("arrangement", "pre_norm", PreNormBlock, replace=True)

@@ -23,16 +23,40 @@ class SwiGLU(Part):
     def __init__(self, spec, hidden_size, weights, rt) -> None:
         super().__init__(spec, hidden_size, weights, rt)
         self.inter = spec.intermediate_size
-        self.w_gate_up = rt.weight(torch.cat([weights["gate"], weights["up"]], dim=0))
+        gate, up = weights["gate"], weights["up"]
+        # blocked layout: 8 gate rows, then their 8 up rows - a gate value and its up value land
+        # in the same 16-row tile of the projection, and the activation kernel works on 16 bytes
+        self.blocked = self.inter % 8 == 0
+        if self.blocked:
+            i, d = gate.shape
+            w13 = torch.stack([gate.view(i // 8, 8, d), up.view(i // 8, 8, d)], dim=1).reshape(2 * i, d)
+        else:
+            w13 = torch.cat([gate, up], dim=0)
+        self.w_gate_up = rt.weight(w13)
         self.w_down = rt.weight(weights["down"])
 
     adds_into_residual = True   # forward() accepts residual= and may add its output there
 
+    def can_fuse_norm(self, norm, n_rows: int) -> bool:
+        return (self.blocked and self.rt.skinny(n_rows, self.hidden_size) and hasattr(norm, "gain")
+                and hasattr(norm, "eps"))
+
     def forward(self, x: torch.Tensor, ctx, residual=None):
         rt = self.rt
-        gate_up = rt.linear(x, self.w_gate_up)
-        act = rt.empty(x.shape[0], self.inter)
-        ops.swiglu(gate_up, act)
+        n = x.shape[0]
+        act = rt.empty(n, self.inter)
+        if self.blocked and rt.skinny(n, self.hidden_size):
+            ops.gemv_bf16(x, self.w_gate_up, act, ops.SWIGLU_BF16)     # activation in the epilogue
+        else:
+            gate_up = rt.linear(x, self.w_gate_up)
+            ops.swiglu(gate_up, act, blocked=self.blocked)
+        return rt.linear(act, self.w_down, residual=residual)
+
+    def forward_fused_norm(self, h: torch.Tensor, norm, ctx, residual=None):
+        """As forward, with x = norm(h): norm, projection and activation in one launch."""
+        rt = self.rt
+        act = rt.empty(h.shape[0], self.inter)
+        ops.gemv_norm_bf16(h, norm.gain, norm.eps, None, self.w_gate_up, act, ops.SWIGLU_BF16)
         return rt.linear(act, self.w_down, residual=residual)
 
 

@@ -39,28 +39,54 @@ class PagedAttention(Part):
         self.n_heads, self.n_kv, self.head_dim = spec.num_heads, spec.num_kv_heads, spec.head_dim
         self.window = spec.window
         self.scale = float(spec.softmax_scale)
-        self.w_qkv = rt.weight(torch.cat([weights["q"], weights["k"], weights["v"]], dim=0))
-        self.w_o = rt.weight(weights["o"])
         self.position = part("position", spec.position.kind)(spec.position, hidden_size, {}, rt)
         if self.position.rotary_dim > spec.head_dim:
             raise ConfigError("rotary_dim must not exceed head_dim")
+        wq, wk = weights["q"], weights["k"]
+        if self.position.rotary_dim > 0 and not self.position.interleaved:
+            # Weights stored for "half" pairing (i, i + rot/2): reorder the rows of every head so
+            # that the two elements of a rotary pair are neighbours.  Scores do not change (q and
+            # k are permuted alike), every kernel then rotates adjacent pairs, and a 16-row tile
+            # of the fused projection holds whole pairs.  (The reference's exporter does the same
+            # to its weight file, tools/export_llama3.py:571-583.)
+            wq = _pairs_adjacent(wq, spec.num_heads, spec.head_dim, self.position.rotary_dim)
+            wk = _pairs_adjacent(wk, spec.num_kv_heads, spec.head_dim, self.position.rotary_dim)
+        self.w_qkv = rt.weight(torch.cat([wq, wk, weights["v"]], dim=0))
+        self.w_o = rt.weight(weights["o"])
 
     def cache_need(self):
         return PagedKVNeed(self.n_kv, self.head_dim, self.window)
 
     adds_into_residual = True   # forward() accepts residual= and may add its output there
 
+    def can_fuse_norm(self, norm, n_rows: int) -> bool:
+        """True if forward_fused_norm can take the residual stream itself (few rows, bfloat16)."""
+        return self.rt.skinny(n_rows, self.hidden_size) and hasattr(norm, "gain") and hasattr(norm, "eps")
+
     def forward(self, x: torch.Tensor, ctx, cache, residual=None):
+        return self._forward(x, None, 0.0, ctx, cache, residual)
+
+    def forward_fused_norm(self, h: torch.Tensor, norm, ctx, cache, residual=None):
+        """As forward, with x = norm(h): the norm runs inside the projection kernel."""
+        return self._forward(h, norm.gain, norm.eps, ctx, cache, residual)
+
+    def _forward(self, x, gain, eps, ctx, cache, residual):
         rt = self.rt
         n = x.shape[0]
-        qkv = rt.linear(x, self.w_qkv)
-        q = rt.empty(n, self.n_heads * self.head_dim)
         table = ctx.block_tables[cache.group]
         pos = self.position
-        ops.rope_kv_write(qkv, q, cache.k_pages if cache.writable else None,
-                          cache.v_pages if cache.writable else None, ctx.positions,
-                          ctx.seq_of_token, table, pos.inv_freq, self.n_heads, self.n_kv,
-                          self.head_dim, pos.rotary_dim, pos.interleaved, rt.page_size)
+        q = rt.empty(n, self.n_heads * self.head_dim)
+        k_pages = cache.k_pages if cache.writable else None
+        v_pages = cache.v_pages if cache.writable else None
+        if rt.skinny(n, self.hidden_size):
+            # decode: projection, rotation and cache write in one launch
+            ops.gemv_qkv_rope(x, gain, eps, self.w_qkv, q, k_pages, v_pages, ctx.positions, ctx.seq_of_token,
+                              table, pos.inv_freq, self.n_heads, self.n_kv, self.head_dim, pos.rotary_dim,
+                              rt.page_size)
+        else:
+            qkv = rt.linear(x, self.w_qkv)
+            ops.rope_kv_write(qkv, q, k_pages, v_pages, ctx.positions, ctx.seq_of_token, table, pos.inv_freq,
+                              self.n_heads, self.n_kv, self.head_dim, pos.rotary_dim, True, rt.page_size)
         att = rt.empty(n, self.n_heads * self.head_dim)
         self._attend(q, cache, att, ctx, table)
         return rt.linear(att, self.w_o, residual=residual)
@@ -100,6 +126,14 @@ class PagedAttention(Part):
             else:
                 ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
                                       table, *common, token_list=ctx.long_tokens)
+
+
+def _pairs_adjacent(w: torch.Tensor, n_heads: int, head_dim: int, rotary_dim: int) -> torch.Tensor:
+    """Rows i and i + rot/2 of every head become rows 2i and 2i + 1; rows beyond rot stay."""
+    out_dim, in_dim = w.shape
+    w = w.view(n_heads, head_dim, in_dim)
+    rot = w[:, :rotary_dim].reshape(n_heads, 2, rotary_dim // 2, in_dim).transpose(1, 2)
+    return torch.cat([rot.reshape(n_heads, rotary_dim, in_dim), w[:, rotary_dim:]], dim=1).reshape(out_dim, in_dim)
 
 
 register_part("mixer", "attention", PagedAttention, replace=True)

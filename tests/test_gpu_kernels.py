@@ -300,3 +300,97 @@ def test_attention_prefill(n_q, n_kv, hd, page, window):
     torch.testing.assert_close(out.cpu().float(), want, rtol=8e-3, atol=4e-3)
     if far is not None:
         assert out.cpu().float()[199].mean() > 4.0      # last row of sequence 0 found key 3
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 64, 64), (4, 336, 120), (8, 4800, 2048), (13, 200, 264), (16, 1000, 8200)])
+def test_gemv_with_fused_norm(m, n, k):
+    """RMSNorm (on picked rows of the FP32 residual stream) inside the skinny product."""
+    from nanoinfer_b200.kernels import ops
+    h = _randn(m + 5, k, seed=1, scale=2.0)
+    gain = _randn(k, seed=2, scale=0.2) + 1.0
+    w = _randn(n, k, dtype=torch.bfloat16, seed=3, scale=0.05)
+    rows = torch.randperm(m + 5, generator=torch.Generator().manual_seed(4))[:m].int().to(DEV)
+    eps = 1e-5
+    x = plain.rms_norm(h.cpu()[rows.cpu().long()], gain.cpu(), eps)
+    want = x.double() @ w.cpu().double().t()
+    out = torch.empty(m, n, dtype=torch.float32, device=DEV)
+    ops.gemv_norm_bf16(h, gain, eps, rows, w, out, ops.STORE_F32)
+    # the kernel rounds h * gain to bfloat16 before the product (2^-9 relative per element,
+    # averaging out over K), the statistics are exact FP32
+    scale = want.abs().max().item()
+    assert (out.cpu().double() - want).abs().max().item() <= 4e-3 * scale
+    # without a row list: rows 0..m-1
+    out2 = torch.empty(m, n, dtype=torch.float32, device=DEV)
+    ops.gemv_norm_bf16(h[:m].contiguous(), gain, eps, None, w, out2, ops.STORE_F32)
+    want2 = plain.rms_norm(h.cpu()[:m], gain.cpu(), eps).double() @ w.cpu().double().t()
+    assert (out2.cpu().double() - want2).abs().max().item() <= 4e-3 * want2.abs().max().item()
+
+
+@pytest.mark.parametrize("m,inter,k", [(1, 64, 64), (7, 200, 120), (8, 8192, 2048), (16, 264, 160)])
+def test_gemv_with_swiglu_epilogue(m, inter, k):
+    from nanoinfer_b200.kernels import ops
+    x = _randn(m, k, dtype=torch.bfloat16, seed=1)
+    gate = _randn(inter, k, dtype=torch.bfloat16, seed=2, scale=0.08)
+    up = _randn(inter, k, dtype=torch.bfloat16, seed=3, scale=0.08)
+    w13 = torch.stack([gate.view(inter // 8, 8, k), up.view(inter // 8, 8, k)], dim=1).reshape(2 * inter, k).contiguous()
+    out = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
+    ops.gemv_bf16(x, w13, out, ops.SWIGLU_BF16)
+    g = x.cpu().double() @ gate.cpu().double().t()
+    u = x.cpu().double() @ up.cpu().double().t()
+    want = (g / (1 + torch.exp(-g))) * u
+    torch.testing.assert_close(out.cpu().double(), want, rtol=4e-3, atol=1e-3)
+    # the activation kernel on the same blocked layout (the path of longer portions)
+    gu = (x.cpu().float() @ w13.cpu().float().t()).to(torch.bfloat16).to(DEV)
+    out2 = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
+    ops.swiglu(gu, out2, blocked=True)
+    gf = gu.cpu().float().view(m, inter // 8, 2, 8)
+    want2 = ((gf[:, :, 0] / (1 + torch.exp(-gf[:, :, 0]))) * gf[:, :, 1]).reshape(m, inter)
+    torch.testing.assert_close(out2.cpu().float(), want2, rtol=4e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("with_norm", [False, True])
+@pytest.mark.parametrize("n_q,n_kv,hd,rot,page,d", [(4, 2, 16, 16, 16, 64), (3, 1, 32, 32, 8, 96), (6, 3, 48, 32, 4, 120),
+                                                     (32, 8, 64, 64, 16, 2048)])
+def test_gemv_qkv_rope(n_q, n_kv, hd, rot, page, d, with_norm):
+    """Projection + (norm) + adjacent-pair rotation + paged write in one launch, against the
+    plain steps."""
+    from nanoinfer_b200.kernels import ops
+    m = 9
+    g = torch.Generator().manual_seed(hd)
+    n = (n_q + 2 * n_kv) * hd
+    w = (torch.randn(n, d, generator=g) * 0.06).to(torch.bfloat16)
+    h = torch.randn(m, d, generator=g) * 1.5
+    gain = torch.randn(d, generator=g) * 0.1 + 1.0
+    positions = torch.tensor([0, 1, 15, 16, 17, 40, 63, 64, 100][:m], dtype=torch.int32)
+    seq_of = torch.arange(m, dtype=torch.int32)
+    width = 128 // page
+    perm = torch.randperm(m * width + 3, generator=g)
+    table = perm[:m * width].view(m, width).int()
+    n_pages = m * width + 3
+    inv_freq = plain.rope_inv_freq(rot, 10000.0, None)
+    q_out = torch.empty(m, n_q * hd, dtype=torch.bfloat16, device=DEV)
+    k_pages = torch.full((n_pages, n_kv, page, hd), 7.0, dtype=torch.bfloat16, device=DEV)
+    v_pages = torch.full((n_pages, n_kv, page, hd), 7.0, dtype=torch.bfloat16, device=DEV)
+    if with_norm:
+        x_in, x_ref = h.to(DEV), plain.rms_norm(h, gain, 1e-5)
+        gain_dev = gain.to(DEV)
+    else:
+        x_in, gain_dev = h.to(torch.bfloat16).to(DEV), None
+        x_ref = h.to(torch.bfloat16).float()
+    ops.gemv_qkv_rope(x_in, gain_dev, 1e-5, w.to(DEV), q_out, k_pages, v_pages, positions.to(DEV), seq_of.to(DEV),
+                      table.to(DEV), inv_freq.to(DEV), n_q, n_kv, hd, rot, page)
+    qkv = x_ref @ w.float().t()
+    q = plain.rope(qkv[:, :n_q * hd].view(m, n_q, hd), positions, inv_freq, "interleaved")
+    k = plain.rope(qkv[:, n_q * hd:(n_q + n_kv) * hd].view(m, n_kv, hd), positions, inv_freq, "interleaved")
+    v = qkv[:, (n_q + n_kv) * hd:].view(m, n_kv, hd)
+    scale = qkv.abs().max().item()
+    tol = 6e-3 * scale
+    assert (q_out.cpu().float().view(m, n_q, hd) - q).abs().max().item() <= tol
+    kp, vp = k_pages.cpu().float(), v_pages.cpu().float()
+    touched = torch.zeros(n_pages, page, dtype=torch.bool)
+    for t in range(m):
+        p, slot = table[t, positions[t] // page], positions[t] % page
+        assert (kp[p, :, slot] - k[t]).abs().max().item() <= tol
+        assert (vp[p, :, slot] - v[t]).abs().max().item() <= tol
+        touched[p, slot] = True
+    assert torch.all(kp.permute(0, 2, 1, 3)[~touched] == 7.0) and torch.all(vp.permute(0, 2, 1, 3)[~touched] == 7.0)
