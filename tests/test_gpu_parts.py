@@ -164,6 +164,11 @@ def test_attention_part_and_block(dtype, window, pairing, hd):
 # ---------------------------------------------------------------------------------------------
 # toy parts, defined in the test
 # ---------------------------------------------------------------------------------------------
+# A routed part takes a discrete decision.  Where the plain router's best two experts are closer
+# than this share of the largest router logit, bfloat16 rounding may pick the other one, and
+# everything after that position differs for good reason: bfloat16 runs are compared up to the
+# first such position of a request (float32 runs are compared everywhere).
+CLOSE_CALL = 0.05
 DECAY = 0.9
 STATE = 24
 EXPERTS, EXPERT_WIDTH = 3, 40
@@ -262,7 +267,8 @@ TOY_RAW = {"architectures": ["ToyHybridForTest"], "width": 64, "head": 16, "head
 
 
 def _toy_plain(w, tokens):
-    """The toy model, whole sequence, from the formulas above and plain_llama's parts."""
+    """The toy model, whole sequence, from the formulas above and plain_llama's parts.
+    Returns (logits, first position whose expert choice is a close call or None)."""
     raw = TOY_RAW
     d, hd, nq, nkv = raw["width"], raw["head"], raw["heads"], raw["kv_heads"]
     T = len(tokens)
@@ -304,7 +310,11 @@ def _toy_plain(w, tokens):
         y[t] = W["toy.layer.1.mixer.w_out"] @ s
     h = h + y
     x = norm(h, "toy.layer.1.ffn_norm.weight")
-    e = torch.argmax(x @ W["toy.layer.1.feed_forward.router"].t(), dim=-1)
+    router = x @ W["toy.layer.1.feed_forward.router"].t()
+    e = torch.argmax(router, dim=-1)
+    top2 = torch.topk(router, 2, dim=-1).values
+    close = torch.nonzero((top2[:, 0] - top2[:, 1]) < CLOSE_CALL * router.abs().max())
+    first_close = int(close[0]) if close.numel() else None
     hid = torch.relu(torch.einsum("tfd,td->tf", W["toy.layer.1.feed_forward.w1"][e], x))
     h = h + torch.einsum("tdf,tf->td", W["toy.layer.1.feed_forward.w2"][e], hid)
     h, kv2 = att(h, 2, None, TOY_RAW["window"])
@@ -313,7 +323,7 @@ def _toy_plain(w, tokens):
     h = swiglu(h, 0)
     h, _ = att(h, 2, None, TOY_RAW["window"], kv_from=kv2)
     h = swiglu(h, 2)
-    return norm(h, "toy.final_norm.weight") @ W["toy.embedding.weight"].t()
+    return norm(h, "toy.final_norm.weight") @ W["toy.embedding.weight"].t(), first_close
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -327,8 +337,13 @@ def test_toy_parts_register_build_and_step(tmp_path, dtype):
     cfg = load_config(d)
     weights = load_weights(d, cfg)
     assert "toy.layer.1.mixer.w_in" in weights and "toy.layer.1.feed_forward.router" in weights
-    reqs = {f"t{i}": random_tokens(TOY_RAW["vocab"], n, 40 + i) for i, n in enumerate([9, 70, 31, 120])}
-    want = {rid: _toy_plain(weights, toks) for rid, toks in reqs.items()}
+    # token seeds chosen so that the plain router has no close call in these requests
+    reqs = {f"t{i}": random_tokens(TOY_RAW["vocab"], n, seed)
+            for i, (n, seed) in enumerate([(9, 40), (70, 75), (31, 41), (120, 100)])}
+    plain_out = {rid: _toy_plain(weights, toks) for rid, toks in reqs.items()}
+    want = {rid: o[0] for rid, o in plain_out.items()}
+    limit = {rid: (len(reqs[rid]) if o[1] is None or dtype == "float32" else o[1]) for rid, o in plain_out.items()}
+    assert sum(limit.values()) >= 0.9 * sum(len(t) for t in reqs.values()), "too little left to compare"
     for cut in (ru.whole, ru.ragged, ru.mixed):
         steps = cut(reqs)
         runner = ModelRunner(cfg, weights, dtype=dtype, page_size=8,
@@ -337,6 +352,8 @@ def test_toy_parts_register_build_and_step(tmp_path, dtype):
         assert [g.window for g in runner.cache.groups] == [None, TOY_RAW["window"]]
         assert len(runner._state_runs) == 1 and runner.caches[4].writable is False
         got = ru.run_trace(runner, steps)
+        assert len(got) == sum(len(t) for t in reqs.values())
+        got = {k: v for k, v in got.items() if k[1] < limit[k[0]]}
         ru.compare(got, want, dtype, label=f"toy/{cut.__name__}/{dtype}")
         runner.cache.check_consistency()
         assert all(p.num_free == p.num_pages for p in runner.cache.pools)
