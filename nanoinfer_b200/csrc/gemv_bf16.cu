@@ -75,181 +75,199 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
 
-// RN: weight rows per block (8 or 16).  NT: batch tiles of 8 rows (1 or 2).  NORM: FP32 input + RMSNorm.
-template <int RN, int NT, bool NORM>
-__global__ void __launch_bounds__(GV_WARPS * 32) gemv_bf16_kernel(const GemvParams p) {
+// Builds the B fragment (8 activations of one batch row at k .. k+7) and, with the norm fused,
+// adds their squares to ssq.
+template <bool NORM>
+__device__ __forceinline__ uint4 load_x8(const void* xrow, const float* gain, int k, float& ssq) {
+    if (NORM) {
+        const float4 h0 = *reinterpret_cast<const float4*>((const float*)xrow + k);
+        const float4 h1 = *reinterpret_cast<const float4*>((const float*)xrow + k + 4);
+        const float4 g0 = *reinterpret_cast<const float4*>(gain + k);
+        const float4 g1 = *reinterpret_cast<const float4*>(gain + k + 4);
+        ssq += h0.x * h0.x + h0.y * h0.y + h0.z * h0.z + h0.w * h0.w +
+               h1.x * h1.x + h1.y * h1.y + h1.z * h1.z + h1.w * h1.w;
+        return make_uint4(pack2(h0.x * g0.x, h0.y * g0.y), pack2(h0.z * g0.z, h0.w * g0.w),
+                          pack2(h1.x * g1.x, h1.y * g1.y), pack2(h1.z * g1.z, h1.w * g1.w));
+    }
+    return *reinterpret_cast<const uint4*>((const __nv_bfloat16*)xrow + k);
+}
+
+// RN: weight rows per tile (8 or 16).  NT: batch tiles of 8 rows (1 or 2).  NORM: FP32 input +
+// RMSNorm.  KEEP: the activations of a warp's K slice stay in registers (K <= 2048) and the
+// block walks `tiles_per_block` consecutive row tiles with them, so that activations are read
+// and normalised once per block, not once per 16 weight rows.
+template <int RN, int NT, bool NORM, bool KEEP>
+__global__ void __launch_bounds__(GV_WARPS * 32, NT == 1 ? 2 : 1) gemv_bf16_kernel(const GemvParams p, int tiles_per_block) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * RN;
     const int M = p.M, N = p.N, K = p.K;
     const int n_blocks = (K + 63) / 64;            // k-blocks of 64
     const uint4 zero = make_uint4(0, 0, 0, 0);
     pdl_launch_dependents();
 
-    const bool row_a_ok = n0 + g < N;
-    const bool row_b_ok = RN == 16 && n0 + g + 8 < N;
-    const __nv_bfloat16* wa = p.w + (size_t)(row_a_ok ? n0 + g : 0) * K;
-    const __nv_bfloat16* wb = p.w + (size_t)(row_b_ok ? n0 + g + 8 : 0) * K;
-
-    float acc[NT][4], ssq[NT];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; ssq[nt] = 0.f; }
-
-    const void* xr[NT];
-    bool x_ok[NT];
-    bool waited = false;
-
-    for (int kb = warp; kb < n_blocks; kb += GV_WARPS * GV_UNROLL) {
-        uint4 fa[GV_UNROLL][2], fb[GV_UNROLL][2], fx[GV_UNROLL][NT][2];
-#pragma unroll
-        for (int u = 0; u < GV_UNROLL; ++u) {
-            const int k0 = (kb + u * GV_WARPS) * 64;
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int k = k0 + 32 * h + 8 * t;
-                const bool ok = k + 8 <= K;        // K is a multiple of 8
-                fa[u][h] = (ok && row_a_ok) ? ld_stream(wa + k) : zero;
-                fb[u][h] = (RN == 16 && ok && row_b_ok) ? ld_stream(wb + k) : zero;
-            }
-        }
-        if (!waited) {
-            // everything above reads weights only; what follows depends on the kernel before
-            pdl_wait();
-            waited = true;
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                const int m = 8 * nt + g;
-                x_ok[nt] = m < M;
-                const int src = (NORM && p.rows && x_ok[nt]) ? p.rows[m] : (x_ok[nt] ? m : 0);
-                xr[nt] = NORM ? (const void*)((const float*)p.x + (size_t)src * K)
-                              : (const void*)((const __nv_bfloat16*)p.x + (size_t)src * K);
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < GV_UNROLL; ++u) {
-            const int k0 = (kb + u * GV_WARPS) * 64;
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int k = k0 + 32 * h + 8 * t;
-                const bool ok = k + 8 <= K;
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                    if (!(ok && x_ok[nt])) { fx[u][nt][h] = zero; continue; }
-                    if (NORM) {
-                        const float4 h0 = *reinterpret_cast<const float4*>((const float*)xr[nt] + k);
-                        const float4 h1 = *reinterpret_cast<const float4*>((const float*)xr[nt] + k + 4);
-                        const float4 g0 = *reinterpret_cast<const float4*>(p.gain + k);
-                        const float4 g1 = *reinterpret_cast<const float4*>(p.gain + k + 4);
-                        ssq[nt] += h0.x * h0.x + h0.y * h0.y + h0.z * h0.z + h0.w * h0.w +
-                                   h1.x * h1.x + h1.y * h1.y + h1.z * h1.z + h1.w * h1.w;
-                        fx[u][nt][h] = make_uint4(pack2(h0.x * g0.x, h0.y * g0.y), pack2(h0.z * g0.z, h0.w * g0.w),
-                                                  pack2(h1.x * g1.x, h1.y * g1.y), pack2(h1.z * g1.z, h1.w * g1.w));
-                    } else {
-                        fx[u][nt][h] = *reinterpret_cast<const uint4*>((const __nv_bfloat16*)xr[nt] + k);
-                    }
-                }
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < GV_UNROLL; ++u)
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                    gv_mma(acc[nt], fa[u][h].x, fb[u][h].x, fa[u][h].y, fb[u][h].y, fx[u][nt][h].x, fx[u][nt][h].y);
-                    gv_mma(acc[nt], fa[u][h].z, fb[u][h].z, fa[u][h].w, fb[u][h].w, fx[u][nt][h].z, fx[u][nt][h].w);
-                }
-    }
-    if (!waited) pdl_wait();   // a warp without work still must not run ahead of the epilogue's inputs
-
-    // partial sums of the 8 warps -> shared memory -> summed in warp order
     __shared__ float red[GV_WARPS][NT][16][8];
     __shared__ float ss_red[GV_WARPS][NT * 8];
     __shared__ float tile[NT * 8][17];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-        red[warp][nt][g][2 * t] = acc[nt][0];
-        red[warp][nt][g][2 * t + 1] = acc[nt][1];
-        red[warp][nt][g + 8][2 * t] = acc[nt][2];
-        red[warp][nt][g + 8][2 * t + 1] = acc[nt][3];
-        if (NORM) {
-            float s = ssq[nt];
-            s += __shfl_xor_sync(0xffffffffu, s, 1);
-            s += __shfl_xor_sync(0xffffffffu, s, 2);
-            if (t == 0) ss_red[warp][nt * 8 + g] = s;
-        }
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < NT * 8 * RN; idx += blockDim.x) {
-        const int row = idx % RN;                  // weight row within the block
-        const int m = idx / RN;                    // batch row
-        float s = 0.f;
-#pragma unroll
-        for (int wi = 0; wi < GV_WARPS; ++wi) s += red[wi][m >> 3][row][m & 7];
-        if (NORM) {
-            float q = 0.f;
-#pragma unroll
-            for (int wi = 0; wi < GV_WARPS; ++wi) q += ss_red[wi][m];
-            s *= 1.0f / sqrtf(q / (float)K + p.eps);
-        }
-        tile[m][row] = s;
-    }
-    __syncthreads();
+    __shared__ float inv_rms[NT * 8];
 
-    const int mode = p.mode;
-    if (mode <= GV_ADD_F32) {
+    uint4 fx[GV_UNROLL][NT][2];     // KEEP: this warp's activations, loaded once
+    float ssq[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) ssq[nt] = 0.f;
+    bool waited = false;
+
+    for (int ti = 0; ti < tiles_per_block; ++ti) {
+        const int n0 = (blockIdx.x * tiles_per_block + ti) * RN;
+        if (n0 >= N) break;
+        const bool row_a_ok = n0 + g < N;
+        const bool row_b_ok = RN == 16 && n0 + g + 8 < N;
+        const __nv_bfloat16* wa = p.w + (size_t)(row_a_ok ? n0 + g : 0) * K;
+        const __nv_bfloat16* wb = p.w + (size_t)(row_b_ok ? n0 + g + 8 : 0) * K;
+        float acc[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+
+        for (int kb = warp; kb < n_blocks; kb += GV_WARPS * GV_UNROLL) {
+            uint4 fa[GV_UNROLL][2], fb[GV_UNROLL][2];
+#pragma unroll
+            for (int u = 0; u < GV_UNROLL; ++u) {
+                const int k0 = (kb + u * GV_WARPS) * 64;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int k = k0 + 32 * h + 8 * t;
+                    const bool ok = k + 8 <= K;        // K is a multiple of 8
+                    fa[u][h] = (ok && row_a_ok) ? ld_stream(wa + k) : zero;
+                    fb[u][h] = (RN == 16 && ok && row_b_ok) ? ld_stream(wb + k) : zero;
+                }
+            }
+            if (!waited) {
+                // everything above reads weights only; what follows depends on the kernel before
+                pdl_wait();
+                waited = true;
+            }
+            if (!KEEP || ti == 0) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const int m = 8 * nt + g;
+                    const bool x_ok = m < M;
+                    const int src = (NORM && p.rows && x_ok) ? p.rows[m] : (x_ok ? m : 0);
+                    const void* xr = NORM ? (const void*)((const float*)p.x + (size_t)src * K)
+                                          : (const void*)((const __nv_bfloat16*)p.x + (size_t)src * K);
+#pragma unroll
+                    for (int u = 0; u < GV_UNROLL; ++u) {
+                        const int k0 = (kb + u * GV_WARPS) * 64;
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const int k = k0 + 32 * h + 8 * t;
+                            fx[u][nt][h] = (k + 8 <= K && x_ok) ? load_x8<NORM>(xr, p.gain, k, ssq[nt]) : zero;
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < GV_UNROLL; ++u)
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        gv_mma(acc[nt], fa[u][h].x, fb[u][h].x, fa[u][h].y, fb[u][h].y, fx[u][nt][h].x, fx[u][nt][h].y);
+                        gv_mma(acc[nt], fa[u][h].z, fb[u][h].z, fa[u][h].w, fb[u][h].w, fx[u][nt][h].z, fx[u][nt][h].w);
+                    }
+        }
+        if (!waited) { pdl_wait(); waited = true; }   // a warp without work must not run ahead either
+
+        // partial sums of the 8 warps -> shared memory -> summed in warp order
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            red[warp][nt][g][2 * t] = acc[nt][0];
+            red[warp][nt][g][2 * t + 1] = acc[nt][1];
+            red[warp][nt][g + 8][2 * t] = acc[nt][2];
+            red[warp][nt][g + 8][2 * t + 1] = acc[nt][3];
+            if (NORM && ti == 0) {
+                float s = ssq[nt];
+                s += __shfl_xor_sync(0xffffffffu, s, 1);
+                s += __shfl_xor_sync(0xffffffffu, s, 2);
+                if (t == 0) ss_red[warp][nt * 8 + g] = s;
+            }
+        }
+        __syncthreads();
+        if (NORM && ti == 0) {
+            if (threadIdx.x < NT * 8) {
+                float q = 0.f;
+#pragma unroll
+                for (int wi = 0; wi < GV_WARPS; ++wi) q += ss_red[wi][threadIdx.x];
+                inv_rms[threadIdx.x] = 1.0f / sqrtf(q / (float)K + p.eps);
+            }
+            __syncthreads();
+        }
         for (int idx = threadIdx.x; idx < NT * 8 * RN; idx += blockDim.x) {
-            const int row = idx % RN, m = idx / RN, n = n0 + row;
-            if (m >= M || n >= N) continue;
-            const float s = tile[m][row];
-            const size_t o = (size_t)m * N + n;
-            if (mode == GV_STORE_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(s);
-            else if (mode == GV_STORE_F32) reinterpret_cast<float*>(p.out)[o] = s;
-            else reinterpret_cast<float*>(p.out)[o] += s;
+            const int row = idx % RN;                  // weight row within the tile
+            const int m = idx / RN;                    // batch row
+            float s = 0.f;
+#pragma unroll
+            for (int wi = 0; wi < GV_WARPS; ++wi) s += red[wi][m >> 3][row][m & 7];
+            if (NORM) s *= inv_rms[m];
+            tile[m][row] = s;
         }
-    } else if (mode == GV_SWIGLU) {
-        // rows 0..7 of the block: gate; rows 8..15: the matching up rows (RN == 16)
-        for (int idx = threadIdx.x; idx < NT * 8 * 8; idx += blockDim.x) {
-            const int r = idx & 7, m = idx >> 3;
-            if (m >= M || n0 + r + 8 >= N) continue;
-            const float gt = tile[m][r], up = tile[m][r + 8];
-            reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * (N / 2) + (n0 >> 1) + r] =
-                __float2bfloat16_rn((gt / (1.0f + expf(-gt))) * up);
-        }
-    } else {  // GV_ROPE_KV: rows come in adjacent rotary pairs; a block never straddles a head
-        const int hd = p.head_dim, nq = p.n_q_heads, nkv = p.n_kv_heads;
-        for (int idx = threadIdx.x; idx < NT * 8 * (RN / 2); idx += blockDim.x) {
-            const int pr = idx % (RN / 2), m = idx / (RN / 2);
-            const int n = n0 + 2 * pr;
-            if (m >= M || n + 1 >= N) continue;
-            const int head = n / hd, d = n - head * hd;
-            float a = tile[m][2 * pr], b = tile[m][2 * pr + 1];
-            const int pos = p.positions[m];
-            if (head < nq + nkv && d < p.rotary_dim) {
-                float sn, cs;
-                sincosf((float)pos * p.inv_freq[d >> 1], &sn, &cs);
-                const float ra = a * cs - b * sn, rb = a * sn + b * cs;
-                a = ra; b = rb;
+        __syncthreads();
+
+        const int mode = p.mode;
+        if (mode <= GV_ADD_F32) {
+            for (int idx = threadIdx.x; idx < NT * 8 * RN; idx += blockDim.x) {
+                const int row = idx % RN, m = idx / RN, n = n0 + row;
+                if (m >= M || n >= N) continue;
+                const float s = tile[m][row];
+                const size_t o = (size_t)m * N + n;
+                if (mode == GV_STORE_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(s);
+                else if (mode == GV_STORE_F32) reinterpret_cast<float*>(p.out)[o] = s;
+                else reinterpret_cast<float*>(p.out)[o] += s;
             }
-            __nv_bfloat16* dst;
-            if (head < nq) {
-                dst = reinterpret_cast<__nv_bfloat16*>(p.out) + ((size_t)m * nq + head) * hd + d;
-            } else {
-                if (!p.write_cache) continue;
-                const int page = p.block_table[(size_t)p.seq_of_token[m] * p.bt_stride + pos / p.page_size];
-                const int kvh = head < nq + nkv ? head - nq : head - nq - nkv;
-                __nv_bfloat16* base = head < nq + nkv ? p.k_pages : p.v_pages;
-                dst = base + (((size_t)page * nkv + kvh) * p.page_size + (pos % p.page_size)) * hd + d;
+        } else if (mode == GV_SWIGLU) {
+            // rows 0..7 of the tile: gate; rows 8..15: the matching up rows (RN == 16)
+            for (int idx = threadIdx.x; idx < NT * 8 * 8; idx += blockDim.x) {
+                const int r = idx & 7, m = idx >> 3;
+                if (m >= M || n0 + r + 8 >= N) continue;
+                const float gt = tile[m][r], up = tile[m][r + 8];
+                reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * (N / 2) + (n0 >> 1) + r] =
+                    __float2bfloat16_rn((gt / (1.0f + expf(-gt))) * up);
             }
-            *reinterpret_cast<uint32_t*>(dst) = pack2(a, b);
+        } else {  // GV_ROPE_KV: rows come in adjacent rotary pairs; a tile never straddles a head
+            const int hd = p.head_dim, nq = p.n_q_heads, nkv = p.n_kv_heads;
+            for (int idx = threadIdx.x; idx < NT * 8 * (RN / 2); idx += blockDim.x) {
+                const int pr = idx % (RN / 2), m = idx / (RN / 2);
+                const int n = n0 + 2 * pr;
+                if (m >= M || n + 1 >= N) continue;
+                const int head = n / hd, d = n - head * hd;
+                float a = tile[m][2 * pr], b = tile[m][2 * pr + 1];
+                const int pos = p.positions[m];
+                if (head < nq + nkv && d < p.rotary_dim) {
+                    float sn, cs;
+                    sincosf((float)pos * p.inv_freq[d >> 1], &sn, &cs);
+                    const float ra = a * cs - b * sn, rb = a * sn + b * cs;
+                    a = ra; b = rb;
+                }
+                __nv_bfloat16* dst;
+                if (head < nq) {
+                    dst = reinterpret_cast<__nv_bfloat16*>(p.out) + ((size_t)m * nq + head) * hd + d;
+                } else {
+                    if (!p.write_cache) continue;
+                    const int page = p.block_table[(size_t)p.seq_of_token[m] * p.bt_stride + pos / p.page_size];
+                    const int kvh = head < nq + nkv ? head - nq : head - nq - nkv;
+                    __nv_bfloat16* base = head < nq + nkv ? p.k_pages : p.v_pages;
+                    dst = base + (((size_t)page * nkv + kvh) * p.page_size + (pos % p.page_size)) * hd + d;
+                }
+                *reinterpret_cast<uint32_t*>(dst) = pack2(a, b);
+            }
         }
     }
+    if (!waited) pdl_wait();
 }
 
-template <int RN, int NT, bool NORM>
-static int launch_gemv(const GemvParams& p, cudaStream_t stream) {
+template <int RN, int NT, bool NORM, bool KEEP>
+static int launch_gemv(const GemvParams& p, int tiles_per_block, cudaStream_t stream) {
+    const int tiles = (p.N + RN - 1) / RN;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((p.N + RN - 1) / RN);
+    cfg.gridDim = dim3((tiles + tiles_per_block - 1) / tiles_per_block);
     cfg.blockDim = dim3(GV_WARPS * 32);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = stream;
@@ -258,7 +276,7 @@ static int launch_gemv(const GemvParams& p, cudaStream_t stream) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_bf16_kernel<RN, NT, NORM>, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_bf16_kernel<RN, NT, NORM, KEEP>, p, tiles_per_block);
     return e == cudaSuccess ? NI_OK : (int)e;
 }
 
@@ -266,19 +284,34 @@ static int dispatch_gemv(const GemvParams& p, bool norm, cudaStream_t stream) {
     if (p.M <= 0 || p.N <= 0) return NI_OK;
     if (p.K <= 0 || p.mode < 0 || p.mode > GV_ROPE_KV) return NI_ERR_BAD_ARGUMENT;
     if (p.M > 16 || p.K % 8) return NI_ERR_UNSUPPORTED_SIZE;
-    // 16 rows per block unless that leaves SMs idle; the fused epilogues need whole 16-row blocks
+    // 16 rows per tile unless that leaves SMs idle; the fused epilogues need whole 16-row tiles
     const bool rn16 = p.mode >= GV_SWIGLU || (p.N + 15) / 16 >= 2 * 148;
     if (p.mode == GV_SWIGLU && p.N % 16) return NI_ERR_UNSUPPORTED_SIZE;
     if (p.mode == GV_ROPE_KV && (p.head_dim % 16 || p.rotary_dim % 2 ||
                                  p.N != (p.n_q_heads + 2 * p.n_kv_heads) * p.head_dim))
         return NI_ERR_BAD_ARGUMENT;
     const bool one = p.M <= 8;
-    if (norm) {
-        if (rn16) return one ? launch_gemv<16, 1, true>(p, stream) : launch_gemv<16, 2, true>(p, stream);
-        return one ? launch_gemv<8, 1, true>(p, stream) : launch_gemv<8, 2, true>(p, stream);
+    // Activations stay in registers when one unrolled pass covers K (<= 2048) and the batch is one
+    // tile: then a block takes several row tiles, as many as leave about two blocks per SM.
+    const bool keep = one && p.K <= 64 * GV_WARPS * GV_UNROLL;
+    int tpb = 1;
+    if (keep) {
+        const int tiles = (p.N + (rn16 ? 16 : 8) - 1) / (rn16 ? 16 : 8);
+        tpb = (tiles + 2 * 148 - 1) / (2 * 148);
+        if (tpb < 1) tpb = 1;
     }
-    if (rn16) return one ? launch_gemv<16, 1, false>(p, stream) : launch_gemv<16, 2, false>(p, stream);
-    return one ? launch_gemv<8, 1, false>(p, stream) : launch_gemv<8, 2, false>(p, stream);
+#define GO(RN, NT, NORM, KEEP) return launch_gemv<RN, NT, NORM, KEEP>(p, tpb, stream)
+    if (keep) {
+        if (norm) { if (rn16) GO(16, 1, true, true); else GO(8, 1, true, true); }
+        else { if (rn16) GO(16, 1, false, true); else GO(8, 1, false, true); }
+    }
+    if (norm) {
+        if (rn16) { if (one) GO(16, 1, true, false); else GO(16, 2, true, false); }
+        else { if (one) GO(8, 1, true, false); else GO(8, 2, true, false); }
+    }
+    if (rn16) { if (one) GO(16, 1, false, false); else GO(16, 2, false, false); }
+    if (one) GO(8, 1, false, false); else GO(8, 2, false, false);
+#undef GO
 }
 
 // x bf16 [M, K].  mode: 0 store bf16 [M, N], 1 store FP32, 2 add into FP32, 3 SwiGLU -> bf16 [M, N / 2].

@@ -97,10 +97,50 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab
     }
 }
 
-NI_EXPORT int ni_argmax(const float* logits, int* out, int n_rows, int vocab, cudaStream_t stream) {
+// Wide rows, few of them: many blocks per row.  Each block folds its slice into one 64-bit key
+// (ordered bits of the value above, 2^32 - 1 - index below, so that the larger value wins and,
+// among equals, the lower index) and merges it with atomicMax: the result does not depend on
+// the order of arrival.  A second tiny kernel unpacks the winners and leaves the keys at zero.
+#define ARGMAX_SLICE 4096
+
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const float* __restrict__ logits, unsigned long long* __restrict__ keys, int vocab) {
+    const float* row = logits + (size_t)blockIdx.y * vocab;
+    const int begin = blockIdx.x * ARGMAX_SLICE;
+    const int end = min(vocab, begin + ARGMAX_SLICE);
+    unsigned long long best = 0ull;
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        const unsigned long long key = ((unsigned long long)ordered_key(row[i]) << 32) | (0xffffffffu - (uint32_t)i);
+        best = key > best ? key : best;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
+    }
+    if ((threadIdx.x & 31) == 0 && best != 0ull) atomicMax(keys + blockIdx.y, best);
+}
+
+__global__ void argmax_finish_kernel(unsigned long long* __restrict__ keys, int* __restrict__ out, int n_rows) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= n_rows) return;
+    out[r] = (int)(0xffffffffu - (uint32_t)(keys[r] & 0xffffffffull));
+    keys[r] = 0ull;
+}
+
+// keys: n_rows 64-bit words, zero before the first call (left zero), or null for the
+// one-block-per-row kernel.
+NI_EXPORT int ni_argmax(const float* logits, int* out, int n_rows, int vocab, unsigned long long* keys,
+                        cudaStream_t stream) {
     if (n_rows <= 0) return NI_OK;
     if (vocab <= 0) return NI_ERR_BAD_ARGUMENT;
-    argmax_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, out, vocab);
+    if (keys == nullptr || vocab <= 2 * ARGMAX_SLICE || n_rows > 65535) {
+        argmax_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, out, vocab);
+        NI_RETURN_LAUNCH_STATUS();
+    }
+    dim3 grid((vocab + ARGMAX_SLICE - 1) / ARGMAX_SLICE, n_rows);
+    argmax_partial_kernel<<<grid, 256, 0, stream>>>(logits, keys, vocab);
+    argmax_finish_kernel<<<(n_rows + 127) / 128, 128, 0, stream>>>(keys, out, n_rows);
     NI_RETURN_LAUNCH_STATUS();
 }
 

@@ -421,9 +421,9 @@ class _DecodeGraph:
         runner, ctx = self.runner, self.ctx
         self._fill(entries, starts)
         if self.greedy_graph is None:
-            runner.model.forward(ctx, runner.caches)
-            torch.cuda.synchronize()
             self.greedy_out = torch.zeros(self.n, dtype=torch.int32, device=runner.rt.device)
+            ops.argmax(runner.model.forward(ctx, runner.caches), self.greedy_out)   # eager pass first
+            torch.cuda.synchronize()
             self.greedy_graph = torch.cuda.CUDAGraph()
             before = ops.launch_count()
             with torch.cuda.graph(self.greedy_graph):

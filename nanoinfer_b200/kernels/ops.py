@@ -51,7 +51,7 @@ _SIGNATURES = {
         "ni_attention_prefill": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
     },
     "sampling": {
-        "ni_argmax": [_P, _P, _I, _I, _P],
+        "ni_argmax": [_P, _P, _I, _I, _P, _P],
         "ni_repetition_penalty": [_P, _P, _P, _I, _I, _I, _P],
         "ni_sample": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P],
     },
@@ -386,11 +386,18 @@ def attention_prefill(q, k_pages, v_pages, out, tile_seq, tile_row0, n_tiles, cu
         head_dim, page_size, int(window) if window else 0, float(scale), _stream()), "attention_prefill")
 
 
+_argmax_keys: Dict[torch.device, torch.Tensor] = {}   # per device: merge keys, zero between calls
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     """out[r] = index of the largest logit of row r, ties to the lowest index."""
     n, v = logits.shape
+    keys = _argmax_keys.get(logits.device)
+    if keys is None and not torch.cuda.is_current_stream_capturing():
+        keys = _argmax_keys[logits.device] = torch.zeros(4096, dtype=torch.int64, device=logits.device)
+    use_keys = keys is not None and n <= keys.numel()
     _check(load("sampling").ni_argmax(_dev(logits, "logits", torch.float32), _dev(out, "out", torch.int32),
-                                      n, v, _stream()), "argmax")
+                                      n, v, keys.data_ptr() if use_keys else None, _stream()), "argmax")
 
 
 def repetition_penalty(logits: torch.Tensor, ids: torch.Tensor, penalties: torch.Tensor) -> None:
