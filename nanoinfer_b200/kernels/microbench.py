@@ -1,0 +1,136 @@
+"""Timing of single kernels at given sizes, for tuning and for profiler captures.
+
+    python -m nanoinfer_b200.kernels.microbench gemv --m 8 --n 16384 --k 2048 --mode swiglu --norm
+    python -m nanoinfer_b200.kernels.microbench attention_decode --batch 8 --context 3072
+    python -m nanoinfer_b200.kernels.microbench attention_prefill --tokens 2048
+
+Each case runs its kernel over several distinct copies of its inputs in turn (together
+larger than the L2 cache, so every run reads from HBM), times it with CUDA events after
+warm-up and prints microseconds per launch and the achieved GB/s or TFLOP/s.
+"""
+from __future__ import annotations
+
+import argparse
+import math
+
+import torch
+
+from . import ops
+
+DEV = "cuda:0"
+L2_BYTES = 126 << 20
+
+
+def _time(fns, iters: int) -> float:
+    """Microseconds per call, cycling through ``fns`` (one per input copy)."""
+    for f in fns:
+        f()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(iters):
+        fns[i % len(fns)]()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) * 1e3 / iters
+
+
+def gemv(args) -> None:
+    m, n, k = args.m, args.n, args.k
+    w_bytes = n * k * 2
+    copies = max(2, min(64, -(-2 * L2_BYTES // w_bytes)))
+    g = torch.Generator(device=DEV).manual_seed(0)
+    ws = [(torch.randn(n, k, device=DEV, generator=g) * 0.02).to(torch.bfloat16) for _ in range(copies)]
+    x = torch.randn(m, k, device=DEV, generator=g).to(torch.bfloat16)
+    h = torch.randn(m, k, device=DEV, generator=g)
+    gain = torch.ones(k, device=DEV)
+    mode = {"bf16": ops.STORE_BF16, "f32": ops.STORE_F32, "add": ops.ADD_F32, "swiglu": ops.SWIGLU_BF16}[args.mode]
+    if mode == ops.SWIGLU_BF16:
+        out = torch.empty(m, n // 2, dtype=torch.bfloat16, device=DEV)
+    else:
+        out = torch.zeros(m, n, dtype=torch.bfloat16 if mode == ops.STORE_BF16 else torch.float32, device=DEV)
+    if args.norm:
+        fns = [lambda w=w: ops.gemv_norm_bf16(h, gain, 1e-5, None, w, out, mode) for w in ws]
+    else:
+        fns = [lambda w=w: ops.gemv_bf16(x, w, out, mode) for w in ws]
+    us = _time(fns, args.iters)
+    print(f"gemv m={m} n={n} k={k} mode={args.mode} norm={args.norm}: {us:.2f} us, "
+          f"{w_bytes / us / 1e3:.0f} GB/s of weights ({copies} weight copies in turn)")
+
+
+def attention_decode(args) -> None:
+    b, ctx, hq, hkv, hd, page = args.batch, args.context, args.q_heads, args.kv_heads, args.head_dim, args.page
+    pages_per_seq = -(-ctx // page)
+    kv_bytes = 2 * b * ctx * hkv * hd * 2
+    copies = max(2, min(16, -(-2 * L2_BYTES // kv_bytes)))
+    g = torch.Generator(device=DEV).manual_seed(0)
+    n_pages = b * pages_per_seq
+    caches = [(torch.randn(n_pages, hkv, page, hd, device=DEV, generator=g).to(torch.bfloat16),
+               torch.randn(n_pages, hkv, page, hd, device=DEV, generator=g).to(torch.bfloat16)) for _ in range(copies)]
+    table = torch.randperm(n_pages, device=DEV, generator=g).int().view(b, pages_per_seq)
+    q = torch.randn(b, hq * hd, device=DEV, generator=g).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    positions = torch.full((b,), ctx - 1, dtype=torch.int32, device=DEV)
+    seq_of = torch.arange(b, dtype=torch.int32, device=DEV)
+    splits = args.splits or max(1, min((148 * 3) // max(1, b * hkv), max(1, ctx // 256)))
+    scratch = torch.empty(b * hq * splits * (hd + 2), dtype=torch.float32, device=DEV)
+    tickets = torch.zeros(b * hkv, dtype=torch.int32, device=DEV)
+    fns = [lambda kc=kc, vc=vc: ops.attention_decode(q, kc, vc, out, None, b, positions, seq_of, table, hq, hkv, hd,
+                                                     page, None, 1.0 / math.sqrt(hd), splits, scratch, tickets)
+           for kc, vc in caches]
+    us = _time(fns, args.iters)
+    print(f"attention_decode batch={b} context={ctx} heads={hq}/{hkv} hd={hd} page={page} splits={splits}: "
+          f"{us:.2f} us, {kv_bytes / us / 1e3:.0f} GB/s of cache")
+
+
+def attention_prefill(args) -> None:
+    t, hq, hkv, hd, page = args.tokens, args.q_heads, args.kv_heads, args.head_dim, args.page
+    g = torch.Generator(device=DEV).manual_seed(0)
+    n_pages = -(-t // page)
+    kc = torch.randn(n_pages, hkv, page, hd, device=DEV, generator=g).to(torch.bfloat16)
+    vc = torch.randn(n_pages, hkv, page, hd, device=DEV, generator=g).to(torch.bfloat16)
+    table = torch.randperm(n_pages, device=DEV, generator=g).int().view(1, n_pages)
+    q = torch.randn(t, hq * hd, device=DEV, generator=g).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    tiles = list(range(0, t, 64))[::-1]
+    tile_seq = torch.zeros(len(tiles), dtype=torch.int32, device=DEV)
+    tile_row0 = torch.tensor(tiles, dtype=torch.int32, device=DEV)
+    cu_q = torch.tensor([0, t], dtype=torch.int32, device=DEV)
+    kv_len = torch.tensor([t], dtype=torch.int32, device=DEV)
+    fn = lambda: ops.attention_prefill(q, kc, vc, out, tile_seq, tile_row0, len(tiles), cu_q, kv_len, table, hq, hkv,
+                                       hd, page, None, 1.0 / math.sqrt(hd))
+    us = _time([fn], args.iters)
+    flops = 4.0 * hq * hd * t * (t + 1) / 2
+    print(f"attention_prefill tokens={t} heads={hq}/{hkv} hd={hd}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s (causal)")
+
+
+def main() -> None:
+    ops.require_cuda()
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="case", required=True)
+    p = sub.add_parser("gemv")
+    p.add_argument("--m", type=int, default=8)
+    p.add_argument("--n", type=int, default=16384)
+    p.add_argument("--k", type=int, default=2048)
+    p.add_argument("--mode", default="bf16", choices=["bf16", "f32", "add", "swiglu"])
+    p.add_argument("--norm", action="store_true")
+    p.set_defaults(fn=gemv)
+    for name, fn in (("attention_decode", attention_decode), ("attention_prefill", attention_prefill)):
+        p = sub.add_parser(name)
+        p.add_argument("--batch", type=int, default=8)
+        p.add_argument("--context", type=int, default=3072)
+        p.add_argument("--tokens", type=int, default=2048)
+        p.add_argument("--q-heads", type=int, default=32)
+        p.add_argument("--kv-heads", type=int, default=8)
+        p.add_argument("--head-dim", type=int, default=64)
+        p.add_argument("--page", type=int, default=16)
+        p.add_argument("--splits", type=int, default=0)
+        p.set_defaults(fn=fn)
+    for sp in sub.choices.values():
+        sp.add_argument("--iters", type=int, default=200)
+    args = ap.parse_args()
+    args.fn(args)
+
+
+if __name__ == "__main__":
+    main()
