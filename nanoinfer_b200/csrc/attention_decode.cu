@@ -1,20 +1,22 @@
 // Split-K grouped-query attention for single query tokens over the paged bfloat16 cache.
 //
 // One thread block per (query token, kv head, split).  The G = Hq / Hkv query heads that
-// share a kv head are the rows of a 16-row tensor-core tile (mma.sync m16n8k16, bf16 in, FP32
-// accumulate), so every key and value is fetched once for all of them.  Each of the block's
-// warps walks its own 32-key chunks of the split's key range with its own online-softmax state
-// (FP32); K and V go from global memory straight into MMA fragments with 16-byte loads - no
-// shared-memory staging, no barrier in the loop.  That works because the contraction index of
-// an MMA may be permuted freely as long as both operands agree:
-//   S = Q K^T: thread (g, t) takes dims [32p + 8t, 32p + 8t + 8) of key 8j + g in one load and
-//              feeds them to two MMAs; Q's fragments are built with the same permutation.
-//   O = P V:   output column (tile j, lane g) is dim 8g + j (hd 64), so a thread's B fragments
-//              for all 8 column tiles of one key are one contiguous 16-byte load.
-// Warps are merged through shared memory; the split's (max, sum, unnormalised O) goes to a
-// scratch buffer; the block that arrives last for its (token, kv head) - counted with an atomic
-// ticket - merges the splits in split order and writes the bfloat16 output.  No block waits for
-// another, and the merge order is fixed, so results are reproducible.
+// share a kv head are the rows of one 16-row tensor-core tile (mma.sync m16n8k16, bf16 in, FP32
+// accumulate), so every key and value is fetched once for all of them.  A block walks its key
+// range in segments of 128 keys with two shared-memory buffers: it asks for a whole segment at
+// once with cp.async - page by page through the block table, 16 bytes at a time into
+// XOR-swizzled shared memory - and the next segment streams in while the current one is used,
+// so the memory system always sees a whole segment in flight instead of a chain of small
+// dependent loads.  Each of the 4 warps takes a quarter of a segment: scores through ldmatrix +
+// MMA, softmax in FP32 (base 2), P V through ldmatrix.trans + MMA.  Warps are merged through
+// shared memory; the split's (max, sum, unnormalised O) goes to a scratch buffer; the block
+// that arrives last for its (token, kv head) - counted with an atomic ticket - merges the
+// splits in split order and writes the bfloat16 output.  No block waits for another, and the
+// merge order is fixed, so results are reproducible.
+//
+// Launched with programmatic stream serialisation: block tables, positions and all cached
+// keys but the token's own (which the projection kernel just before writes) are requested
+// before griddepcontrol.wait, so the segment streams in while the projection drains.
 //
 // The grid does not depend on context lengths (they are read on the device), so a decode step
 // can be captured in a CUDA graph and replayed as contexts grow.
@@ -24,7 +26,6 @@
 #include "common.cuh"
 
 #define DEC_WARPS 4
-#define DEC_CHUNK 32  // keys per warp iteration
 
 __device__ __forceinline__ void mma_bf16_16816(float c[4], const uint32_t a[4], uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -32,14 +33,33 @@ __device__ __forceinline__ void mma_bf16_16816(float c[4], const uint32_t a[4], 
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void dec_ldsm_x4(uint32_t r[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void dec_ldsm_x4_trans(uint32_t r[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void dec_cp_async16(void* smem, const void* gmem) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(a), "l"(gmem));
+}
+__device__ __forceinline__ void dec_pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void dec_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
 
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
+// Element offset of (row, 16-byte chunk) in a tile of rows of HD bf16, chunks XOR-swizzled by row.
+template <int HD> __device__ __forceinline__ int dec_sw(int row, int chunk) {
+    constexpr int CH = HD / 8;
+    constexpr int MASK = ((CH & -CH) - 1) & 7;
+    return row * HD + ((chunk ^ (row & MASK)) << 3);
 }
 
-// HD: head size (multiple of 32, <= 128).  Scratch per (token, q head, split): HD + 2 floats.
-template <int HD>
+// HD: head size (64 or 128).  SEG: keys a block holds in shared memory at a time (64 per warp
+// pass).  Scratch per (token, q head, split): HD + 2 floats.
+template <int HD, int SEG>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
                         const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out,
@@ -48,10 +68,15 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         int bt_stride, int n_q_heads, int n_kv_heads, int page_size, int window,
                         float scale_log2e, int n_splits, float* __restrict__ scratch,
                         int* __restrict__ tickets) {
-    constexpr int KP = HD / 32;      // pairs of k-steps in Q K^T
-    constexpr int NT_O = HD / 8;     // output column tiles in P V
-    constexpr int VL = HD / 64 > 0 ? HD / 64 : 1;  // 16-byte V loads per key per thread (HD >= 64)
-    static_assert(HD % 32 == 0 && HD <= 128, "head size");
+    constexpr int CH = HD / 8;       // 16-byte chunks per row
+    constexpr int KS = HD / 16;      // k-steps over the head size
+    constexpr int NT_O = HD / 8;     // output column tiles
+    constexpr int WK = SEG / DEC_WARPS;   // keys per warp per segment
+    static_assert(WK % 16 == 0, "keys per warp");
+    extern __shared__ __align__(128) unsigned char dec_smem[];
+    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(dec_smem);    // [16][HD]
+    __nv_bfloat16* sKV = sQ + 16 * HD;                                  // 2 buffers of K [SEG][HD] + V [SEG][HD]
+    dec_pdl_launch_dependents();
 
     const int item = blockIdx.x;             // index into token_list
     const int kvh = blockIdx.y;
@@ -62,156 +87,165 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     const int G = n_q_heads / n_kv_heads;
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int n_keys = pos + 1 - lo;
-    // the split's key range, in whole chunks
-    const int chunks_total = (n_keys + DEC_CHUNK - 1) / DEC_CHUNK;
+    // the split's key range, in whole 64-key chunks
+    const int chunks_total = (n_keys + 63) / 64;
     const int chunks_per_split = (chunks_total + n_splits - 1) / n_splits;
-    const int k_begin = lo + split * chunks_per_split * DEC_CHUNK;
-    const int k_end = min(pos + 1, k_begin + chunks_per_split * DEC_CHUNK);
+    const int k_begin = lo + split * chunks_per_split * 64;
+    const int k_end = min(pos + 1, k_begin + chunks_per_split * 64);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-
-    // Q fragments (rows = heads of the group, zero beyond G), dims permuted as described above
-    uint32_t qa[KP][2][4];
-    {
-        const __nv_bfloat16* qbase = q + ((size_t)t_idx * n_q_heads + (size_t)kvh * G) * HD;
-#pragma unroll
-        for (int p = 0; p < KP; ++p) {
-            uint4 r0 = make_uint4(0, 0, 0, 0), r1 = make_uint4(0, 0, 0, 0);
-            if (g < G) r0 = *reinterpret_cast<const uint4*>(qbase + (size_t)g * HD + 32 * p + 8 * t);
-            if (g + 8 < G) r1 = *reinterpret_cast<const uint4*>(qbase + (size_t)(g + 8) * HD + 32 * p + 8 * t);
-            qa[p][0][0] = r0.x; qa[p][0][1] = r1.x; qa[p][0][2] = r0.y; qa[p][0][3] = r1.y;
-            qa[p][1][0] = r0.z; qa[p][1][1] = r1.z; qa[p][1][2] = r0.w; qa[p][1][3] = r1.w;
-        }
-    }
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
 
     float o[NT_O][4];
 #pragma unroll
     for (int j = 0; j < NT_O; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // rows g and g + 8
+    uint32_t qa[KS][4];
 
-    for (int c0 = k_begin + warp * DEC_CHUNK; c0 < k_end; c0 += DEC_WARPS * DEC_CHUNK) {
-        // ---- S = Q K^T for 32 keys: 4 column tiles of 8 keys ----
-        float s[4][4];
-        uint4 kf[4][KP];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            int key = c0 + 8 * j + g;
-            key = key < k_end ? key : k_end - 1;       // clamp: masked below, never out of the table
-            const int page = table[key / page_size];
-            const __nv_bfloat16* krow =
-                k_pages + (((size_t)page * n_kv_heads + kvh) * page_size + (key % page_size)) * HD;
-#pragma unroll
-            for (int p = 0; p < KP; ++p) kf[j][p] = *reinterpret_cast<const uint4*>(krow + 32 * p + 8 * t);
+    // Asks for the keys and values of segment [seg0, seg0 + SEG) into buffer `buf`; `own` selects
+    // the rows of the token's own key (true) or all other rows (false).
+    auto request = [&](int seg0, int buf, bool own_only, bool skip_own) {
+        const int seg_keys = min(SEG, k_end - seg0);
+        const int rows = ((seg_keys + 15) / 16) * 16;            // rows that MMAs may touch
+        __nv_bfloat16* sK = sKV + (size_t)buf * 2 * SEG * HD;
+        __nv_bfloat16* sV = sK + SEG * HD;
+        for (int idx = threadIdx.x; idx < rows * CH; idx += blockDim.x) {
+            const int r = idx / CH, c = idx - r * CH;
+            int key = seg0 + r;
+            key = key < k_end ? key : k_end - 1;                 // masked below; never off the table
+            if ((own_only && key != pos) || (skip_own && key == pos)) continue;
+            const int pi = page_shift >= 0 ? key >> page_shift : key / page_size;
+            const int slot = page_shift >= 0 ? key & (page_size - 1) : key - pi * page_size;
+            const size_t off = (((size_t)table[pi] * n_kv_heads + kvh) * page_size + slot) * HD + c * 8;
+            dec_cp_async16(sK + dec_sw<HD>(r, c), k_pages + off);
+            dec_cp_async16(sV + dec_sw<HD>(r, c), v_pages + off);
         }
-        // V fragments for the same 32 keys: 2 k-steps of 16 keys; this thread's 4 keys per step
-        uint4 vf[2][4][VL * (HD >= 64 ? 1 : 1)];
-#pragma unroll
-        for (int ks = 0; ks < 2; ++ks) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                int key = c0 + 16 * ks + 2 * t + (e & 1) + 8 * (e >> 1);
-                key = key < k_end ? key : k_end - 1;
-                const int page = table[key / page_size];
-                const __nv_bfloat16* vrow =
-                    v_pages + (((size_t)page * n_kv_heads + kvh) * page_size + (key % page_size)) * HD;
-                if (HD >= 64) {
-#pragma unroll
-                    for (int x = 0; x < VL; ++x)
-                        vf[ks][e][x] = *reinterpret_cast<const uint4*>(vrow + (HD / 8) * g + 8 * x);
-                } else {  // HD == 32: 4 dims per lane group
-                    const uint2 h = *reinterpret_cast<const uint2*>(vrow + 4 * g);
-                    vf[ks][e][0] = make_uint4(h.x, h.y, 0, 0);
-                }
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-#pragma unroll
-            for (int p = 0; p < KP; ++p) {
-                mma_bf16_16816(s[j], qa[p][0], kf[j][p].x, kf[j][p].y);
-                mma_bf16_16816(s[j], qa[p][1], kf[j][p].z, kf[j][p].w);
-            }
-        }
-        // ---- mask, online softmax (base 2) ----
-        float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int key = c0 + 8 * j + 2 * t;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const bool ok = key + (e & 1) < k_end;
-                s[j][e] = ok ? s[j][e] * scale_log2e : -INFINITY;
-            }
-            mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
-            mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
-        }
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);   // finite: the chunk has >= 1 key
-        const float corr0 = exp2f(m0 - mn0), corr1 = exp2f(m1 - mn1);
-        m0 = mn0; m1 = mn1;
-        float rs0 = 0.f, rs1 = 0.f;
-        uint32_t pa[2][4];   // P as A fragments for the two 16-key k-steps
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float p0 = exp2f(s[j][0] - mn0), p1 = exp2f(s[j][1] - mn0);
-            const float p2 = exp2f(s[j][2] - mn1), p3 = exp2f(s[j][3] - mn1);
-            // the sum runs over the bfloat16-rounded probabilities that multiply V
-            const __nv_bfloat162 r01 = __floats2bfloat162_rn(p0, p1), r23 = __floats2bfloat162_rn(p2, p3);
-            rs0 += __bfloat162float(r01.x) + __bfloat162float(r01.y);
-            rs1 += __bfloat162float(r23.x) + __bfloat162float(r23.y);
-            pa[j >> 1][(j & 1) * 2 + 0] = *reinterpret_cast<const uint32_t*>(&r01);
-            pa[j >> 1][(j & 1) * 2 + 1] = *reinterpret_cast<const uint32_t*>(&r23);
-        }
-        l0 = l0 * corr0 + rs0;
-        l1 = l1 * corr1 + rs1;
-#pragma unroll
-        for (int j = 0; j < NT_O; ++j) {
-            o[j][0] *= corr0; o[j][1] *= corr0; o[j][2] *= corr1; o[j][3] *= corr1;
-        }
-        // ---- O += P V ----
-#pragma unroll
-        for (int ks = 0; ks < 2; ++ks) {
-#pragma unroll
-            for (int j = 0; j < NT_O; ++j) {
-                // column tile j, lane group g <-> dim (HD / 8) * g + j; B fragment: keys e = 0..3 of this thread
-                const int x = j >> 3, w = j & 7;   // which 16-byte load, which element of it
-                uint32_t b0, b1;
-                const uint32_t* e0 = reinterpret_cast<const uint32_t*>(&vf[ks][0][x]);
-                const uint32_t* e1 = reinterpret_cast<const uint32_t*>(&vf[ks][1][x]);
-                const uint32_t* e2 = reinterpret_cast<const uint32_t*>(&vf[ks][2][x]);
-                const uint32_t* e3 = reinterpret_cast<const uint32_t*>(&vf[ks][3][x]);
-                // element w of each key's load: halves of 32-bit words
-                const uint32_t w0 = e0[w >> 1], w1 = e1[w >> 1], w2 = e2[w >> 1], w3 = e3[w >> 1];
-                if (w & 1) {
-                    b0 = (w0 >> 16) | (w1 & 0xffff0000u);
-                    b1 = (w2 >> 16) | (w3 & 0xffff0000u);
-                } else {
-                    b0 = (w0 & 0xffffu) | (w1 << 16);
-                    b1 = (w2 & 0xffffu) | (w3 << 16);
-                }
-                mma_bf16_16816(o[j], pa[ks], b0, b1);
-            }
+    };
+
+    if (k_begin < k_end) {
+        // everything but the token's own key, which the projection before us is still writing
+        request(k_begin, 0, false, true);
+    }
+    dec_pdl_wait();                                              // the projection has finished
+    if (k_begin < k_end) {
+        request(k_begin, 0, true, false);
+        for (int idx = threadIdx.x; idx < 16 * CH; idx += blockDim.x) {
+            const int r = idx / CH, c = idx - r * CH;
+            __nv_bfloat16* dst = sQ + dec_sw<HD>(r, c);
+            if (r < G)
+                dec_cp_async16(dst, q + ((size_t)t_idx * n_q_heads + (size_t)kvh * G + r) * HD + c * 8);
+            else
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
         }
     }
+    asm volatile("cp.async.commit_group;\n" ::);
+
+    int buf = 0;
+    for (int seg0 = k_begin; seg0 < k_end; seg0 += SEG, buf ^= 1) {
+        const int seg_keys = min(SEG, k_end - seg0);
+        const int rows = ((seg_keys + 15) / 16) * 16;
+        const __nv_bfloat16* sK = sKV + (size_t)buf * 2 * SEG * HD;
+        const __nv_bfloat16* sV = sK + SEG * HD;
+        // the next segment streams in while this one is used
+        if (seg0 + SEG < k_end) request(seg0 + SEG, buf ^ 1, false, false);
+        asm volatile("cp.async.commit_group;\n" ::);
+        asm volatile("cp.async.wait_group 1;\n" ::);
+        __syncthreads();
+        if (seg0 == k_begin) {
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks)
+                dec_ldsm_x4(qa[ks], sQ + dec_sw<HD>((lane & 7) + 8 * ((lane >> 3) & 1), 2 * ks + (lane >> 4)));
+        }
+        const int w0 = warp * WK;                                // this warp's rows of the segment
+        if (w0 < seg_keys) {
+            // ---- S = Q K^T for WK keys ----
+            float s[WK / 8][4];
+#pragma unroll
+            for (int j = 0; j < WK / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+            for (int jp = 0; jp < WK / 16; ++jp) {
+                if (w0 + 16 * jp < rows) {
+#pragma unroll
+                    for (int ks = 0; ks < KS; ++ks) {
+                        uint32_t b[4];
+                        const int mi = lane >> 3;
+                        dec_ldsm_x4(b, sK + dec_sw<HD>(w0 + 16 * jp + (lane & 7) + 8 * (mi >> 1), 2 * ks + (mi & 1)));
+                        mma_bf16_16816(s[2 * jp], qa[ks], b[0], b[1]);
+                        mma_bf16_16816(s[2 * jp + 1], qa[ks], b[2], b[3]);
+                    }
+                }
+            }
+            // ---- mask, online softmax (base 2) ----
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < WK / 8; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const bool ok = w0 + 8 * j + 2 * t + (e & 1) < seg_keys;
+                    s[j][e] = ok ? s[j][e] * scale_log2e : -INFINITY;
+                }
+                mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+                mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+            }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);   // finite: the warp has >= 1 key
+            const float corr0 = exp2f(m0 - mn0), corr1 = exp2f(m1 - mn1);
+            m0 = mn0; m1 = mn1;
+            float rs0 = 0.f, rs1 = 0.f;
+            uint32_t pa[WK / 16][4];
+#pragma unroll
+            for (int j = 0; j < WK / 8; ++j) {
+                // the sum runs over the bfloat16-rounded probabilities that multiply V
+                const __nv_bfloat162 r01 = __floats2bfloat162_rn(exp2f(s[j][0] - mn0), exp2f(s[j][1] - mn0));
+                const __nv_bfloat162 r23 = __floats2bfloat162_rn(exp2f(s[j][2] - mn1), exp2f(s[j][3] - mn1));
+                rs0 += __bfloat162float(r01.x) + __bfloat162float(r01.y);
+                rs1 += __bfloat162float(r23.x) + __bfloat162float(r23.y);
+                pa[j >> 1][(j & 1) * 2 + 0] = *reinterpret_cast<const uint32_t*>(&r01);
+                pa[j >> 1][(j & 1) * 2 + 1] = *reinterpret_cast<const uint32_t*>(&r23);
+            }
+            l0 = l0 * corr0 + rs0;
+            l1 = l1 * corr1 + rs1;
+#pragma unroll
+            for (int j = 0; j < NT_O; ++j) {
+                o[j][0] *= corr0; o[j][1] *= corr0; o[j][2] *= corr1; o[j][3] *= corr1;
+            }
+            // ---- O += P V ----
+#pragma unroll
+            for (int ks = 0; ks < WK / 16; ++ks) {
+                if (w0 + 16 * ks < rows) {
+#pragma unroll
+                    for (int dp = 0; dp < NT_O / 2; ++dp) {
+                        uint32_t b[4];
+                        const int mi = lane >> 3;
+                        dec_ldsm_x4_trans(b, sV + dec_sw<HD>(w0 + 16 * ks + (lane & 7) + 8 * (mi & 1), 2 * dp + (mi >> 1)));
+                        mma_bf16_16816(o[2 * dp], pa[ks], b[0], b[1]);
+                        mma_bf16_16816(o[2 * dp + 1], pa[ks], b[2], b[3]);
+                    }
+                }
+            }
+        }
+        __syncthreads();   // everyone is done with this buffer before it is refilled
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::);
     // row sums live in the 4 lanes of a row group
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
 
-    // ---- merge the block's warps (fixed order) ----
+    // ---- merge the block's warps (fixed order); the key/value tiles are no longer needed ----
     __shared__ float sm_m[DEC_WARPS][16], sm_l[DEC_WARPS][16];
-    __shared__ float sm_o[DEC_WARPS][16][HD + 1];
+    __syncthreads();
+    float (*sm_o)[16][HD + 1] = reinterpret_cast<float (*)[16][HD + 1]>(dec_smem);
+    static_assert(sizeof(float) * DEC_WARPS * 16 * (HD + 1) <= sizeof(__nv_bfloat16) * (16 + 4 * SEG) * HD, "merge buffer");
     if (t == 0) { sm_m[warp][g] = m0; sm_m[warp][g + 8] = m1; sm_l[warp][g] = l0; sm_l[warp][g + 8] = l1; }
 #pragma unroll
     for (int j = 0; j < NT_O; ++j) {
-        // C fragment columns 2t, 2t+1 of tile j are lane groups 2t, 2t+1: dims (HD/8)*(2t) + j and (HD/8)*(2t+1) + j
-        const int d0 = (HD / 8) * (2 * t) + j, d1 = (HD / 8) * (2 * t + 1) + j;
-        sm_o[warp][g][d0] = o[j][0]; sm_o[warp][g][d1] = o[j][1];
-        sm_o[warp][g + 8][d0] = o[j][2]; sm_o[warp][g + 8][d1] = o[j][3];
+        const int d = 8 * j + 2 * t;
+        sm_o[warp][g][d] = o[j][0]; sm_o[warp][g][d + 1] = o[j][1];
+        sm_o[warp][g + 8][d] = o[j][2]; sm_o[warp][g + 8][d + 1] = o[j][3];
     }
     __syncthreads();
     const size_t rec = HD + 2;
@@ -227,15 +261,20 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
             acc += sm_o[w][row][d] * f;
             ll += sm_l[w][row] * f;
         }
+        if (n_splits == 1) {   // nothing to merge with: this is the result
+            out[((size_t)t_idx * n_q_heads + (size_t)kvh * G + row) * HD + d] = __float2bfloat16_rn(acc / ll);
+            continue;
+        }
         float* dst = scratch + (((size_t)item * n_q_heads + (size_t)kvh * G + row) * n_splits + split) * rec;
         dst[2 + d] = acc;
         if (d == 0) { dst[0] = mm; dst[1] = ll; }
     }
+    if (n_splits == 1) return;
     // ---- the last block of this (token, kv head) merges the splits ----
     __shared__ int is_last;
-    __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
+        __threadfence();   // the block's partial results (ordered before by the barrier) become visible
         int* ticket = tickets + (size_t)item * n_kv_heads + kvh;
         const int prev = atomicAdd(ticket, 1);
         is_last = prev == n_splits - 1;
@@ -260,6 +299,37 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     }
 }
 
+template <int HD, int SEG>
+static int launch_decode(const void* q, const void* k_pages, const void* v_pages, void* out, const int* token_list,
+                         int n_items, const int* positions, const int* seq_of_token, const int* block_table,
+                         int bt_stride, int n_q_heads, int n_kv_heads, int page_size, int window,
+                         float scale_log2e, int n_splits, float* scratch, int* tickets, cudaStream_t stream) {
+    const size_t smem = (size_t)(16 + 4 * SEG) * HD * sizeof(__nv_bfloat16);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, SEG>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_items, n_kv_heads, n_splits);
+    cfg.blockDim = dim3(DEC_WARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_kernel<HD, SEG>, (const __nv_bfloat16*)q,
+                                       (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
+                                       (__nv_bfloat16*)out, token_list, positions, seq_of_token, block_table,
+                                       bt_stride, n_q_heads, n_kv_heads, page_size, window, scale_log2e, n_splits,
+                                       scratch, tickets);
+    return e == cudaSuccess ? NI_OK : (int)e;
+}
+
 // Scratch floats needed: n_items * n_q_heads * n_splits * (head_dim + 2); tickets: n_items * n_kv_heads
 // ints, zero before the first launch (the kernel leaves them zero).
 NI_EXPORT int ni_attention_decode(const void* q, const void* k_pages, const void* v_pages, void* out,
@@ -274,19 +344,17 @@ NI_EXPORT int ni_attention_decode(const void* q, const void* k_pages, const void
         return NI_ERR_BAD_ARGUMENT;
     if (n_q_heads / n_kv_heads > 16) return NI_ERR_UNSUPPORTED_SIZE;
     const float scale_log2e = scale * 1.4426950408889634f;
-    dim3 grid(n_items, n_kv_heads, n_splits);
-#define LAUNCH(HD)                                                                                    \
-    attention_decode_kernel<HD><<<grid, DEC_WARPS * 32, 0, stream>>>(                                 \
-        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,       \
-        (__nv_bfloat16*)out, token_list, positions, seq_of_token, block_table, bt_stride, n_q_heads, \
-        n_kv_heads, page_size, window, scale_log2e, n_splits, scratch, tickets)
     switch (head_dim) {
-        case 64: LAUNCH(64); break;
-        case 128: LAUNCH(128); break;
+        case 64:
+            return launch_decode<64, 128>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
+                                          block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
+                                          scale_log2e, n_splits, scratch, tickets, stream);
+        case 128:
+            return launch_decode<128, 64>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
+                                           block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
+                                           scale_log2e, n_splits, scratch, tickets, stream);
         default: return NI_ERR_UNSUPPORTED_SIZE;
     }
-#undef LAUNCH
-    NI_RETURN_LAUNCH_STATUS();
 }
 
 // ---- the variant that allocates nothing (see attention_decode_noalloc.h) ----------------------

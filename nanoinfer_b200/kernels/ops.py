@@ -346,6 +346,15 @@ def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
 
 
 DECODE_HEAD_DIMS = (64, 128)
+DECODE_SEGMENT_KEYS = {64: 128, 128: 64}      # keys per shared-memory buffer of a decode-attention block
+DECODE_BLOCKS_PER_SM = 3
+
+
+def decode_splits(n_items: int, n_kv_heads: int, head_dim: int, max_kv_len: int) -> int:
+    """How many blocks share one (token, kv head): as many as fill the GPU once, each with at
+    least one segment of the longest context, within a bound on the merge."""
+    fill = (148 * DECODE_BLOCKS_PER_SM) // max(1, n_items * n_kv_heads)
+    return max(1, min(64, fill, -(-max_kv_len // DECODE_SEGMENT_KEYS[head_dim])))
 PREFILL_MAX_HEAD_DIM = 128
 
 

@@ -110,7 +110,7 @@ class PagedAttention(Part):
         dec_list = None if ctx.decode_only else ctx.dec_tokens
         if n_dec > 0:
             if decode_ok:
-                splits = max(1, min((148 * 3) // max(1, n_dec * self.n_kv), max(1, ctx.max_kv_len // 256)))
+                splits = ops.decode_splits(n_dec, self.n_kv, self.head_dim, ctx.max_kv_len)
                 scratch = rt.workspace("attention_decode_partials",
                                        n_dec * self.n_heads * splits * (self.head_dim + 2), torch.float32)
                 tickets = rt.workspace("attention_decode_tickets", n_dec * self.n_kv, torch.int32, zero=True)
