@@ -64,6 +64,26 @@ def gemv(args) -> None:
           f"{w_bytes / us / 1e3:.0f} GB/s of weights ({copies} weight copies in turn)")
 
 
+def gemm(args) -> None:
+    """The tcgen05 product against the library product on the same operands."""
+    m, n, k = args.m, args.n, args.k
+    g = torch.Generator(device=DEV).manual_seed(0)
+    a = torch.randn(m, k, device=DEV, generator=g).to(torch.bfloat16)
+    b = (torch.randn(n, k, device=DEV, generator=g) * 0.02).to(torch.bfloat16)
+    mode = {"bf16": ops.STORE_BF16, "f32": ops.STORE_F32, "add": ops.ADD_F32, "swiglu": ops.SWIGLU_BF16}[args.mode]
+    if mode == ops.SWIGLU_BF16:
+        out = torch.empty(m, n // 2, dtype=torch.bfloat16, device=DEV)
+    else:
+        out = torch.zeros(m, n, dtype=torch.bfloat16 if mode == ops.STORE_BF16 else torch.float32, device=DEV)
+    us = _time([lambda: ops.gemm_tc(a, b, out, mode)], args.iters)
+    ops.check_device_errors()
+    ref = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    us_lib = _time([lambda: torch.matmul(a, b.t(), out=ref)], args.iters)
+    flops = 2.0 * m * n * k
+    print(f"gemm m={m} n={n} k={k} mode={args.mode}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s "
+          f"(library product, plain store: {us_lib:.1f} us, {flops / us_lib / 1e6:.0f} TFLOP/s)")
+
+
 def attention_decode(args) -> None:
     b, ctx, hq, hkv, hd, page = args.batch, args.context, args.q_heads, args.kv_heads, args.head_dim, args.page
     pages_per_seq = -(-ctx // page)
@@ -121,6 +141,12 @@ def main() -> None:
     p.add_argument("--mode", default="bf16", choices=["bf16", "f32", "add", "swiglu"])
     p.add_argument("--norm", action="store_true")
     p.set_defaults(fn=gemv)
+    p = sub.add_parser("gemm")
+    p.add_argument("--m", type=int, default=2048)
+    p.add_argument("--n", type=int, default=16384)
+    p.add_argument("--k", type=int, default=2048)
+    p.add_argument("--mode", default="bf16", choices=["bf16", "f32", "add", "swiglu"])
+    p.set_defaults(fn=gemm)
     for name, fn in (("attention_decode", attention_decode), ("attention_prefill", attention_prefill)):
         p = sub.add_parser(name)
         p.add_argument("--batch", type=int, default=8)

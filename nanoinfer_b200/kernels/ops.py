@@ -50,6 +50,9 @@ _SIGNATURES = {
     "attention_prefill": {
         "ni_attention_prefill": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
     },
+    "gemm_tc": {
+        "ni_gemm_tc": [_P, _P, _P, _I, _I, _I, _I, _P, _P],
+    },
     "sampling": {
         "ni_argmax": [_P, _P, _I, _I, _P, _P],
         "ni_repetition_penalty": [_P, _P, _P, _I, _I, _I, _P],
@@ -343,6 +346,49 @@ def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
     if out_dtype == torch.bfloat16:
         return torch.matmul(x, w.t())
     return torch.mm(x, w.t(), out_dtype=torch.float32)
+
+
+_error_words: Dict[torch.device, torch.Tensor] = {}
+
+
+def _error_word(device: torch.device) -> torch.Tensor:
+    w = _error_words.get(device)
+    if w is None:
+        w = _error_words[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return w
+
+
+def check_device_errors(device=None) -> None:
+    """Raise if a kernel recorded that one of its bounded waits ran out (synchronises)."""
+    for dev, w in _error_words.items():
+        if device is not None and dev != torch.device(device):
+            continue
+        code = int(w.item())
+        if code:
+            w.zero_()
+            raise KernelError(f"a kernel on {dev} gave up waiting (code {code}: 1 = loader, 2 = MMA issuer, "
+                              f"3 = epilogue of the tensor-core product)")
+
+
+def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, mode: int) -> None:
+    """out = a[M, K] . b[N, K]^T on the tcgen05 tensor cores (bfloat16 in, FP32 accumulate).
+    mode STORE_BF16 / STORE_F32 / ADD_F32 as in gemv_bf16; SWIGLU_BF16: b's rows in blocks of 8
+    gate + 8 up rows, out bf16 [M, N/2]."""
+    m, k = a.shape
+    n = b.shape[0]
+    if b.shape[1] != k:
+        raise KernelError("gemm_tc: inner sizes do not agree")
+    if k % 8:
+        raise KernelError(f"gemm_tc: K must be a multiple of 8 (got {k})")
+    if mode == SWIGLU_BF16:
+        if n % 16 or out.shape != (m, n // 2) or out.dtype != torch.bfloat16:
+            raise KernelError("gemm_tc: the SwiGLU epilogue needs N a multiple of 16 and out bf16 [M, N/2]")
+    else:
+        want = torch.bfloat16 if mode == STORE_BF16 else torch.float32
+        if out.shape != (m, n) or out.dtype != want:
+            raise KernelError(f"gemm_tc: out must be {want} [M, N]")
+    _check(load("gemm_tc").ni_gemm_tc(_dev(a, "a", torch.bfloat16), _dev(b, "b", torch.bfloat16), _dev(out, "out"),
+                                      m, n, k, mode, _error_word(a.device).data_ptr(), _stream()), "gemm_tc")
 
 
 DECODE_HEAD_DIMS = (64, 128)
