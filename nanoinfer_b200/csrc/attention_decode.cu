@@ -33,6 +33,13 @@ __device__ __forceinline__ void mma_bf16_16816(float c[4], const uint32_t a[4], 
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x with the hardware approximation (one MUFU instruction; about two units in the last place,
+// far below the bfloat16 rounding of the probabilities it feeds); 2^-inf = 0.
+__device__ __forceinline__ float dec_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void dec_ldsm_x4(uint32_t r[4], const void* p) {
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
@@ -193,15 +200,15 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
             const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);   // finite: the warp has >= 1 key
-            const float corr0 = exp2f(m0 - mn0), corr1 = exp2f(m1 - mn1);
+            const float corr0 = dec_exp2(m0 - mn0), corr1 = dec_exp2(m1 - mn1);
             m0 = mn0; m1 = mn1;
             float rs0 = 0.f, rs1 = 0.f;
             uint32_t pa[WK / 16][4];
 #pragma unroll
             for (int j = 0; j < WK / 8; ++j) {
                 // the sum runs over the bfloat16-rounded probabilities that multiply V
-                const __nv_bfloat162 r01 = __floats2bfloat162_rn(exp2f(s[j][0] - mn0), exp2f(s[j][1] - mn0));
-                const __nv_bfloat162 r23 = __floats2bfloat162_rn(exp2f(s[j][2] - mn1), exp2f(s[j][3] - mn1));
+                const __nv_bfloat162 r01 = __floats2bfloat162_rn(dec_exp2(s[j][0] - mn0), dec_exp2(s[j][1] - mn0));
+                const __nv_bfloat162 r23 = __floats2bfloat162_rn(dec_exp2(s[j][2] - mn1), dec_exp2(s[j][3] - mn1));
                 rs0 += __bfloat162float(r01.x) + __bfloat162float(r01.y);
                 rs1 += __bfloat162float(r23.x) + __bfloat162float(r23.y);
                 pa[j >> 1][(j & 1) * 2 + 0] = *reinterpret_cast<const uint32_t*>(&r01);
@@ -257,7 +264,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         float acc = 0.f, ll = 0.f;
 #pragma unroll
         for (int w = 0; w < DEC_WARPS; ++w) {
-            const float f = sm_m[w][row] == -INFINITY ? 0.f : exp2f(sm_m[w][row] - mm);
+            const float f = sm_m[w][row] == -INFINITY ? 0.f : dec_exp2(sm_m[w][row] - mm);
             acc += sm_o[w][row][d] * f;
             ll += sm_l[w][row] * f;
         }
@@ -291,7 +298,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         float acc = 0.f, ll = 0.f;
         for (int sidx = 0; sidx < n_splits; ++sidx) {
             const float ms = __ldcg(src + sidx * rec);
-            const float f = ms == -INFINITY ? 0.f : exp2f(ms - mm);
+            const float f = ms == -INFINITY ? 0.f : dec_exp2(ms - mm);
             acc += __ldcg(src + sidx * rec + 2 + d) * f;
             ll += __ldcg(src + sidx * rec + 1) * f;
         }

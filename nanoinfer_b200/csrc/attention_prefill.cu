@@ -1,6 +1,6 @@
 // Causal grouped-query attention for portions of prompts over the paged bfloat16 cache.
 //
-// Flash-style: one thread block per (64 query rows of one request, query head); keys and
+// Flash-style: one thread block per (128 query rows of one request, query head); keys and
 // values are gathered from their pages 64 keys at a time into swizzled shared memory with
 // cp.async (double buffered), scores and the P V product run on tensor cores (mma.sync
 // m16n8k16 bf16, FP32 accumulate, fragments through ldmatrix), softmax is online in FP32.
@@ -14,8 +14,8 @@
 // softmax kernel in between, with seven stream-ordered allocations per layer per chunk.
 #include "common.cuh"
 
-#define PF_WARPS 4
-#define PF_BM 64
+#define PF_WARPS 8
+#define PF_BM 128
 #define PF_BN 64
 
 __device__ __forceinline__ void pf_mma(float c[4], const uint32_t a[4], uint32_t b0, uint32_t b1) {
@@ -23,6 +23,13 @@ __device__ __forceinline__ void pf_mma(float c[4], const uint32_t a[4], uint32_t
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// 2^x with the hardware approximation (one MUFU instruction; about two units in the last place,
+// far below the bfloat16 rounding of the probabilities it feeds); 2^-inf = 0.
+__device__ __forceinline__ float pf_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 __device__ __forceinline__ void ldsm_x4(uint32_t r[4], const void* p) {
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
@@ -79,6 +86,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     const int* table = block_table + (size_t)seq * bt_stride;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
 
     // key range of the tile: up to the last row's position; from the first row's window start
     const int last_pos = pos0 + row0 + rows - 1;
@@ -106,8 +114,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
             const int r = idx / CH, c = idx - r * CH;
             int key = k0 + r;
             key = (key <= last_pos && key >= key_first) ? key : last_pos;   // masked later, never off the table
-            const int page = table[key / page_size];
-            const size_t off = (((size_t)page * n_kv_heads + kvh) * page_size + (key % page_size)) * HD + c * 8;
+            const int pi = page_shift >= 0 ? key >> page_shift : key / page_size;
+            const int slot = page_shift >= 0 ? key & (page_size - 1) : key - pi * page_size;
+            const size_t off = (((size_t)table[pi] * n_kv_heads + kvh) * page_size + slot) * HD + c * 8;
             cp_async16(dK + sw<HD>(r, c), k_pages + off);
             cp_async16(dV + sw<HD>(r, c), v_pages + off);
         }
@@ -156,18 +165,25 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                     pf_mma(s[2 * jp + 1], qa[ks], b[2], b[3]);
                 }
             }
-            // mask: causal, window, end of context
+            // Scores stay unscaled; the scale rides in the exponent's FMA: p = 2^(s * scale - m).
+            // Only tiles that touch the diagonal or a window's edge need the mask.
+            const bool need_mask = k0 + PF_BN - 1 > warp_first || (window > 0 && k0 < warp_last - window + 1);
+            if (need_mask) {
+#pragma unroll
+                for (int j = 0; j < PF_BN / 8; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = k0 + 8 * j + 2 * t + (e & 1);
+                        const int qp = (e < 2) ? qrow_a : qrow_b;
+                        bool ok = key <= qp;
+                        if (window > 0) ok = ok && key > qp - window;
+                        if (!ok) s[j][e] = -INFINITY;
+                    }
+                }
+            }
             float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
             for (int j = 0; j < PF_BN / 8; ++j) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int key = k0 + 8 * j + 2 * t + (e & 1);
-                    const int qp = (e < 2) ? qrow_a : qrow_b;
-                    bool ok = key <= qp;
-                    if (window > 0) ok = ok && key > qp - window;
-                    s[j][e] = ok ? s[j][e] * scale_log2e : -INFINITY;
-                }
                 mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
                 mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
             }
@@ -175,27 +191,32 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
             mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+            // m0, m1: running maxima of the SCALED scores (the scale is positive)
+            const float mn0 = fmaxf(m0, mx0 * scale_log2e), mn1 = fmaxf(m1, mx1 * scale_log2e);
             // a row with no visible key so far keeps max = -inf: use 0 as the reference point
             const float ref0 = mn0 == -INFINITY ? 0.f : mn0, ref1 = mn1 == -INFINITY ? 0.f : mn1;
-            const float corr0 = exp2f(m0 - ref0), corr1 = exp2f(m1 - ref1);
+            const bool rescale = mn0 != m0 || mn1 != m1;
+            const float corr0 = pf_exp2(m0 - ref0), corr1 = pf_exp2(m1 - ref1);
             m0 = mn0; m1 = mn1;
             float rs0 = 0.f, rs1 = 0.f;
             uint32_t pa[PF_BN / 16][4];
 #pragma unroll
             for (int j = 0; j < PF_BN / 8; ++j) {
-                const __nv_bfloat162 r01 = __floats2bfloat162_rn(exp2f(s[j][0] - ref0), exp2f(s[j][1] - ref0));
-                const __nv_bfloat162 r23 = __floats2bfloat162_rn(exp2f(s[j][2] - ref1), exp2f(s[j][3] - ref1));
-                rs0 += __bfloat162float(r01.x) + __bfloat162float(r01.y);
-                rs1 += __bfloat162float(r23.x) + __bfloat162float(r23.y);
+                const float p0 = pf_exp2(fmaf(s[j][0], scale_log2e, -ref0)), p1 = pf_exp2(fmaf(s[j][1], scale_log2e, -ref0));
+                const float p2 = pf_exp2(fmaf(s[j][2], scale_log2e, -ref1)), p3 = pf_exp2(fmaf(s[j][3], scale_log2e, -ref1));
+                rs0 += p0 + p1;
+                rs1 += p2 + p3;
+                const __nv_bfloat162 r01 = __floats2bfloat162_rn(p0, p1), r23 = __floats2bfloat162_rn(p2, p3);
                 pa[j >> 1][(j & 1) * 2 + 0] = *reinterpret_cast<const uint32_t*>(&r01);
                 pa[j >> 1][(j & 1) * 2 + 1] = *reinterpret_cast<const uint32_t*>(&r23);
             }
             l0 = l0 * corr0 + rs0;
             l1 = l1 * corr1 + rs1;
+            if (__any_sync(0xffffffffu, rescale)) {      // the maxima settle early: most tiles skip this
 #pragma unroll
-            for (int j = 0; j < NT_O; ++j) {
-                o[j][0] *= corr0; o[j][1] *= corr0; o[j][2] *= corr1; o[j][3] *= corr1;
+                for (int j = 0; j < NT_O; ++j) {
+                    o[j][0] *= corr0; o[j][1] *= corr0; o[j][2] *= corr1; o[j][3] *= corr1;
+                }
             }
 #pragma unroll
             for (int ks = 0; ks < PF_BN / 16; ++ks) {
@@ -252,7 +273,7 @@ template <int HD> static int launch_prefill(const void* q, const void* k_pages, 
 }
 
 // tile_seq / tile_row0: int32 [n_tiles] on the device: request index and first query row (a
-// multiple of 64 within the request's portion) of each tile.
+// multiple of 128 within the request's portion) of each tile.
 NI_EXPORT int ni_attention_prefill(const void* q, const void* k_pages, const void* v_pages, void* out,
                                    const int* tile_seq, const int* tile_row0, int n_tiles, const int* cu_q,
                                    const int* kv_len, const int* block_table, int bt_stride, int n_q_heads,

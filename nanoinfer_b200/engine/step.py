@@ -89,7 +89,7 @@ class StepContext:
 
 
 SHORT_PORTION = 2
-ATTENTION_TILE = 64
+ATTENTION_TILE = 128     # = kernels.ops.PREFILL_TILE_ROWS
 
 
 def reserve_entries(cache: CacheManager, entries: Sequence[StepEntry], admit) -> List[int]:

@@ -118,7 +118,7 @@ def attention_prefill(args) -> None:
     table = torch.randperm(n_pages, device=DEV, generator=g).int().view(1, n_pages)
     q = torch.randn(t, hq * hd, device=DEV, generator=g).to(torch.bfloat16)
     out = torch.empty_like(q)
-    tiles = list(range(0, t, 64))[::-1]
+    tiles = list(range(0, t, ops.PREFILL_TILE_ROWS))[::-1]
     tile_seq = torch.zeros(len(tiles), dtype=torch.int32, device=DEV)
     tile_row0 = torch.tensor(tiles, dtype=torch.int32, device=DEV)
     cu_q = torch.tensor([0, t], dtype=torch.int32, device=DEV)

@@ -402,6 +402,7 @@ def decode_splits(n_items: int, n_kv_heads: int, head_dim: int, max_kv_len: int)
     fill = (148 * DECODE_BLOCKS_PER_SM) // max(1, n_items * n_kv_heads)
     return max(1, min(64, fill, -(-max_kv_len // DECODE_SEGMENT_KEYS[head_dim])))
 PREFILL_MAX_HEAD_DIM = 128
+PREFILL_TILE_ROWS = 128      # query rows per block of the flash-style kernel
 
 
 def attention_decode(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token, block_table,
@@ -427,9 +428,9 @@ def attention_decode(q, k_pages, v_pages, out, token_list, n_items, positions, s
 
 def attention_prefill(q, k_pages, v_pages, out, tile_seq, tile_row0, n_tiles, cu_q, kv_len, block_table,
                       n_q_heads, n_kv_heads, head_dim, page_size, window, scale) -> None:
-    """Flash-style causal attention of prompt portions (bfloat16): one block per (tile of 64
-    query rows, head); tile_seq / tile_row0 int32 [n_tiles] name each tile's request and
-    first row."""
+    """Flash-style causal attention of prompt portions (bfloat16): one block per (tile of
+    PREFILL_TILE_ROWS query rows, head); tile_seq / tile_row0 int32 [n_tiles] name each tile's
+    request and first row."""
     if head_dim % 16 or head_dim > PREFILL_MAX_HEAD_DIM:
         raise KernelError(f"attention_prefill: head_dim {head_dim} not supported (multiples of 16 up to 128)")
     _check(load("attention_prefill").ni_attention_prefill(

@@ -282,14 +282,14 @@ def test_attention_decode(n_q, n_kv, hd, page, window, n_splits):
 def test_attention_prefill(n_q, n_kv, hd, page, window):
     from nanoinfer_b200.kernels import ops
     lens = [300, 70, 5, 130]
-    spans = [(100, 300), (0, 70), (2, 5), (127, 130)]   # portions: late, whole, tiny, across a tile edge
+    spans = [(100, 300), (0, 70), (2, 5), (127, 130)]   # portions: late and longer than a tile, whole, tiny, at a page edge
     far = (0, 3) if window is None else None
     table, k_pages, v_pages, ks, vs, qs, q, positions, seq_of = _attention_case(lens, spans, n_q, n_kv, hd, page, hd, far)
     scale = 1.0 / math.sqrt(hd)
     q_lens = [b - a for a, b in spans]
     cu_q = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
     kv_len = torch.tensor([b for _, b in spans], dtype=torch.int32)
-    tiles = [(s, r0) for s, ql in enumerate(q_lens) for r0 in range(0, ql, 64)]
+    tiles = [(s, r0) for s, ql in enumerate(q_lens) for r0 in range(0, ql, ops.PREFILL_TILE_ROWS)]
     tile_seq = torch.tensor([t[0] for t in tiles], dtype=torch.int32)
     tile_row0 = torch.tensor([t[1] for t in tiles], dtype=torch.int32)
     out = torch.zeros_like(q).to(DEV)

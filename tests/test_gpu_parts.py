@@ -131,8 +131,8 @@ def test_attention_part_and_block(dtype, window, pairing, hd):
             block_tables=[torch.from_numpy(cm.table_rows(0, [slot], width)).to(DEV)],
             host_q_lens=[n], host_kv_lens=[start + n], host_slots=[slot], max_q_len=n, max_kv_len=start + n,
             decode_only=(n == 1), n_dec=n if n <= 2 else 0, dec_tokens=torch.arange(n, **i32),
-            n_tiles=0 if n <= 2 else -(-n // 64), tile_seq=torch.zeros(max(1, -(-n // 64)), **i32),
-            tile_row0=torch.arange(0, max(n, 1), 64, **i32), long_tokens=torch.arange(n, **i32))
+            n_tiles=0 if n <= 2 else -(-n // 128), tile_seq=torch.zeros(max(1, -(-n // 128)), **i32),
+            tile_row0=torch.arange(0, max(n, 1), 128, **i32), long_tokens=torch.arange(n, **i32))
 
     outs = [mixer.forward(x[:20].to(DEV), ctx_for(0, 20), cache)]
     for t in range(20, T):
