@@ -71,6 +71,11 @@ class Runtime:
         bandwidth kernel (and so may carry fused prologues and epilogues)."""
         return self.dtype == torch.bfloat16 and 0 < n_rows <= ops.GEMV_MAX_ROWS and k % 8 == 0
 
+    def tensor_core_gemm(self, n_rows: int, k: int) -> bool:
+        """True if a product with this many rows goes to the package's tcgen05 kernel (where
+        its fused epilogue beats the library product followed by a separate kernel)."""
+        return self.dtype == torch.bfloat16 and n_rows >= 256 and k % 8 == 0
+
     def workspace(self, name: str, numel: int, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
         """A persistent scratch tensor of at least ``numel`` elements, shared by all layers
         (they run one after the other on one stream).  ``zero``: zero-filled when created;

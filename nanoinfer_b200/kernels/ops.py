@@ -392,15 +392,16 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, mode: int) -> N
 
 
 DECODE_HEAD_DIMS = (64, 128)
-DECODE_SEGMENT_KEYS = {64: 128, 128: 64}      # keys per shared-memory buffer of a decode-attention block
-DECODE_BLOCKS_PER_SM = 3
+DECODE_SEGMENT_KEYS = {64: 64, 128: 64}      # keys per shared-memory buffer of a decode-attention block
+DECODE_BLOCKS_PER_SM = 4
 
 
 def decode_splits(n_items: int, n_kv_heads: int, head_dim: int, max_kv_len: int) -> int:
-    """How many blocks share one (token, kv head): as many as fill the GPU once, each with at
-    least one segment of the longest context, within a bound on the merge."""
+    """How many blocks share one (token, kv head): as many as fill the GPU once, each with a few
+    segments of the longest context (a block's fixed costs - table look-ups, merge, ticket -
+    weigh about as much as 400 keys), within a bound on the merge."""
     fill = (148 * DECODE_BLOCKS_PER_SM) // max(1, n_items * n_kv_heads)
-    return max(1, min(64, fill, -(-max_kv_len // DECODE_SEGMENT_KEYS[head_dim])))
+    return max(1, min(64, fill, -(-max_kv_len // 384)))
 PREFILL_MAX_HEAD_DIM = 128
 PREFILL_TILE_ROWS = 128      # query rows per block of the flash-style kernel
 

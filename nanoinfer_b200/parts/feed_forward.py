@@ -47,6 +47,8 @@ class SwiGLU(Part):
         act = rt.empty(n, self.inter)
         if self.blocked and rt.skinny(n, self.hidden_size):
             ops.gemv_bf16(x, self.w_gate_up, act, ops.SWIGLU_BF16)     # activation in the epilogue
+        elif self.blocked and rt.tensor_core_gemm(n, self.hidden_size):
+            ops.gemm_tc(x, self.w_gate_up, act, ops.SWIGLU_BF16)       # tcgen05 product, activation fused
         else:
             gate_up = rt.linear(x, self.w_gate_up)
             ops.swiglu(gate_up, act, blocked=self.blocked)
