@@ -135,6 +135,11 @@ class ModelRunner:
         from .runtime import parse_dtype
         self.config = config
         self.rt = Runtime(device=torch.device(device), dtype=parse_dtype(dtype), page_size=page_size)
+        # compile (in parallel) and load what this precision needs before the first step
+        from ..kernels import ops
+        common = ["elementwise", "rope_kv", "attention_generic"]
+        ops.preload(common + (["gemm_f32"] if self.rt.dtype == torch.float32 else
+                              ["gemv_bf16", "gemm_tc", "attention_prefill", "attention_decode"]))
         self.model = DecoderModel(config, weights, self.rt)
         if max_tokens_per_request is None:
             max_tokens_per_request = min(config.max_position_embeddings, num_pages * page_size)

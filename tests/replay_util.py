@@ -140,7 +140,9 @@ def compare(got, want_by_req, dtype, label=""):
     for (rid, pos), row in got.items():
         ref = want_by_req[rid][pos]
         if dtype == "float32":
-            torch.testing.assert_close(row, ref, rtol=F32_RTOL, atol=F32_ATOL,
+            # the absolute rounding error of an FP32 dot product grows with the size of its terms:
+            # the absolute bound is taken relative to the largest logit of the row (at least 1)
+            torch.testing.assert_close(row, ref, rtol=F32_RTOL, atol=F32_ATOL * max(1.0, ref.abs().max().item()),
                                        msg=lambda m: f"{label} request {rid} position {pos}: {m}")
         else:
             err = (row - ref).abs()

@@ -139,3 +139,31 @@ def test_trace_run_program(model_dirs, tmp_path):
                 torch.testing.assert_close(logits[r], want[e["id"]][base + wpos], rtol=ru.F32_RTOL, atol=ru.F32_ATOL)
                 r += 1
             fed[e["id"]] = base + len(e["tokens"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_benchmark_layer_sizes(tmp_path_factory, dtype):
+    """The benchmark's layer sizes (width 2048, 32/8 heads of 64, feed-forward 8192, vocabulary
+    128256, llama3 rope scaling, tied output) with two layers: a prompt long enough for the
+    tensor-core projection path, then single tokens through the captured decode step."""
+    from nanoinfer_b200.weights import write_random_model
+    raw = {"architectures": ["LlamaForCausalLM"], "hidden_size": 2048, "intermediate_size": 8192,
+           "num_hidden_layers": 2, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64,
+           "vocab_size": 128256, "max_position_embeddings": 131072, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+           "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                            "original_max_position_embeddings": 8192},
+           "tie_word_embeddings": True, "hidden_act": "silu"}
+    d = str(tmp_path_factory.mktemp("bench_shape") / "m")
+    write_random_model(d, raw, seed=4)
+    raw_read, w = load_plain(d)
+    toks = random_tokens(raw["vocab_size"], 300, 5)
+    want = {"p": ru.plain_logits(raw_read, w, {"p": toks})["p"]}
+    steps = [{"step": 0, "entries": [{"id": "p", "tokens": toks[:290], "want": [0, 100, 289]}], "end": []}]
+    steps += [{"step": 1 + i, "entries": [{"id": "p", "tokens": [toks[290 + i]], "want": [0]}],
+               "end": ["p"] if i == 9 else []} for i in range(10)]
+    runner = _runner(d, dtype, 16, steps)
+    got = ru.run_trace(runner, steps)
+    assert len(got) == 13
+    ru.compare(got, want, dtype, label=f"bench-shape/{dtype}")
+    from nanoinfer_b200.kernels import ops
+    ops.check_device_errors()
