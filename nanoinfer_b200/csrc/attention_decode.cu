@@ -356,6 +356,12 @@ NI_EXPORT int ni_attention_decode(const void* q, const void* k_pages, const void
     const float scale_log2e = scale * 1.4426950408889634f;
     switch (head_dim) {
         case 64:
+            // several blocks per (token, kv head): few, fat blocks with 128-key buffers (3 per SM);
+            // one block each (large batches): 64-key buffers, so that 4 fit an SM and 512 blocks are one wave
+            if (n_splits > 1)
+                return launch_decode<64, 128>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
+                                              block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
+                                              scale_log2e, n_splits, scratch, tickets, stream);
             return launch_decode<64, 64>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
                                           block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
                                           scale_log2e, n_splits, scratch, tickets, stream);

@@ -400,7 +400,10 @@ def decode_splits(n_items: int, n_kv_heads: int, head_dim: int, max_kv_len: int)
     """How many blocks share one (token, kv head): as many as fill the GPU once, each with a few
     segments of the longest context (a block's fixed costs - table look-ups, merge, ticket -
     weigh about as much as 400 keys), within a bound on the merge."""
-    fill = (148 * DECODE_BLOCKS_PER_SM) // max(1, n_items * n_kv_heads)
+    pairs = max(1, n_items * n_kv_heads)
+    if (148 * DECODE_BLOCKS_PER_SM) // pairs <= 1:
+        return 1                                  # large batch: one lean block per pair
+    fill = (148 * 3) // pairs                     # split blocks are fatter: 3 per SM
     return max(1, min(64, fill, -(-max_kv_len // 384)))
 PREFILL_MAX_HEAD_DIM = 128
 PREFILL_TILE_ROWS = 128      # query rows per block of the flash-style kernel
