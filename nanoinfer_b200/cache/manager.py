@@ -61,11 +61,13 @@ class CacheManager:
         self.max_tokens_per_request = max_tokens_per_request
         self.table_width = -(-max_tokens_per_request // page_size)
         self.pools = [PagePool(n) for n in pages_per_group]
+        self._windowed = any(g.window is not None for g in self.groups)
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self._held: Dict[object, _Held] = {}
         # host mirror of the block tables, one row per slot; -1 = no page
         self.mirror = [np.full((max_requests, self.table_width), -1, dtype=np.int32)
                        for _ in self.groups]
+        self.table_version = 0     # bumped whenever any row of the mirror changes
 
     # ---- requests -------------------------------------------------------------------------
     def has(self, req) -> bool:
@@ -85,6 +87,7 @@ class CacheManager:
         self._held[req] = _Held(slot, len(self.groups))
         for m in self.mirror:
             m[slot, :] = -1
+        self.table_version += 1
         return slot
 
     def slot(self, req) -> int:
@@ -120,6 +123,20 @@ class CacheManager:
         need = self.pages_needed(req, n_new)
         return all(n <= p.num_free - reserve for n, p in zip(need, self.pools))
 
+    def needs_page_for_one(self, req) -> bool:
+        """True if one more token of ``req`` starts a new page (in every group alike)."""
+        return self._get(req).length % self.page_size == 0
+
+    def append_one(self, req) -> None:
+        """append(req, 1), for the decode loop."""
+        h = self._get(req)
+        if h.length % self.page_size == 0:
+            self.append(req, 1)
+        elif h.length + 1 > self.max_tokens_per_request:
+            self.append(req, 1)          # raises the limit error
+        else:
+            h.length += 1
+
     def append(self, req, n_new: int) -> None:
         """Take the pages for tokens [length, length + n_new).  All groups or none."""
         h = self._get(req)
@@ -139,10 +156,13 @@ class CacheManager:
                 start = len(h.tables[g])
                 h.tables[g].extend(pages)
                 self.mirror[g][h.slot, start:start + n] = pages
+                self.table_version += 1
         h.length += n_new
 
     def release_passed(self, req) -> int:
         """Give back the pages of windowed groups that no later query can see; returns how many."""
+        if not self._windowed:
+            return 0
         h = self._get(req)
         released = 0
         for g in range(len(self.groups)):
@@ -155,6 +175,7 @@ class CacheManager:
                 for i in range(h.first_live[g], first):
                     h.tables[g][i] = -1
                 self.mirror[g][h.slot, h.first_live[g]:first] = -1
+                self.table_version += 1
                 released += len(pages)
                 h.first_live[g] = first
         return released
@@ -165,6 +186,7 @@ class CacheManager:
         for g, table in enumerate(h.tables):
             self.pools[g].give_back([p for p in table if p >= 0])
             self.mirror[g][h.slot, :] = -1
+        self.table_version += 1
         self._free_slots.append(h.slot)
         del self._held[req]
 

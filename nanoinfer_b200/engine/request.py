@@ -41,7 +41,7 @@ class InferenceRequest:
 
     @property
     def num_remaining(self) -> int:
-        return self.num_tokens - self.num_computed_tokens
+        return len(self.prompt_tokens) + len(self.generated_tokens) - self.num_computed_tokens
 
     def next_tokens(self, n: int) -> List[int]:
         a = self.num_computed_tokens

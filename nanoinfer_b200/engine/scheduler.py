@@ -82,7 +82,11 @@ class Scheduler:
         decoding = sum(1 for r in self.running if r.num_remaining == 1)
         portion_budget = max(0, budget - decoding)
 
+        one_page, no_page = [1] * n_groups, [0] * n_groups
+
         def fits(need) -> bool:
+            if need is no_page:
+                return True
             return all(reserved[g] + need[g] <= cache.num_free_pages(g) for g in range(n_groups))
 
         i = 0
@@ -90,14 +94,18 @@ class Scheduler:
             req = self.running[i]
             if len(batch.entries) >= self.max_batch_size:
                 break
-            if req.num_remaining == 1:
+            remaining = req.num_remaining
+            if remaining == 1:
                 n = 1 if budget > 0 else 0
             else:
-                n = min(req.num_remaining, self.prefill_chunk_size, portion_budget)
+                n = min(remaining, self.prefill_chunk_size, portion_budget)
             if n <= 0:
                 i += 1
                 continue
-            need = cache.pages_needed(req.request_id, n)
+            if n == 1 and cache.has(req.request_id):
+                need = one_page if cache.needs_page_for_one(req.request_id) else no_page
+            else:
+                need = cache.pages_needed(req.request_id, n)
             while not fits(need):
                 victim = self.running[-1]
                 if victim is req:
@@ -117,9 +125,10 @@ class Scheduler:
             if req is None:
                 continue                      # running[i] is now the next request (or the end)
             batch.entries.append((req, n))
-            reserved = [a + b for a, b in zip(reserved, need)]
+            if need is not no_page:
+                reserved = [a + b for a, b in zip(reserved, need)]
             budget -= n
-            if req.num_remaining > 1:
+            if remaining > 1:
                 portion_budget -= n
             i += 1
 

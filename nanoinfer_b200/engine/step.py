@@ -100,6 +100,17 @@ def reserve_entries(cache: CacheManager, entries: Sequence[StepEntry], admit) ->
     ``admit(request)`` is called for requests the cache does not know yet.  Returns each
     entry's start position (its cached length before this step).
     """
+    if all(len(e.tokens) == 1 and cache.has(e.request) for e in entries):
+        # the decode loop: at most one new page per request, the same in every group
+        n_new_pages = sum(1 for e in entries if cache.needs_page_for_one(e.request))
+        for g in range(len(cache.groups)):
+            if n_new_pages > cache.num_free_pages(g):
+                raise OutOfPages(f"group {g}: the step needs {n_new_pages} more pages, "
+                                 f"{cache.num_free_pages(g)} are free")
+        starts = [cache.length(e.request) for e in entries]
+        for e in entries:
+            cache.append_one(e.request)
+        return starts
     need = [0] * len(cache.groups)
     new_requests = 0
     for e in entries:
@@ -221,11 +232,15 @@ class ModelRunner:
             n = len(e.tokens)
             if n == 0:
                 raise StepError(f"request {e.request!r}: an entry needs at least one token")
-            for t in e.tokens:
-                if not 0 <= int(t) < vocab:
+            if n == 1:
+                t = e.tokens[0]
+                if not 0 <= t < vocab:
                     raise StepError(f"request {e.request!r}: token id {t} is outside [0, {vocab})")
+            elif min(e.tokens) < 0 or max(e.tokens) >= vocab:
+                bad = next(t for t in e.tokens if not 0 <= t < vocab)
+                raise StepError(f"request {e.request!r}: token id {bad} is outside [0, {vocab})")
             for w in e.want:
-                if not 0 <= int(w) < n:
+                if not 0 <= w < n:
                     raise StepError(f"request {e.request!r}: wanted place {w} is outside its {n} tokens")
             held = self.cache.length(e.request) if self.cache.has(e.request) else 0
             if held + n > self.max_tokens_per_request:
@@ -342,6 +357,9 @@ class ModelRunner:
         self.cache.free(request)
 
 
+from ..kernels import ops  # noqa: E402  (after the classes above: no import cycle)
+
+
 class _DecodeGraph:
     """The forward pass of ``n`` single-token requests, captured once and replayed.
 
@@ -367,6 +385,8 @@ class _DecodeGraph:
         self.dev = torch.zeros(total, dtype=torch.int32, device=dev)
         self.copied = torch.cuda.Event()
         self.copy_pending = False
+        self.last_ids: Optional[list] = None     # requests and table version of the last full refresh
+        self.last_version = -1
         o = self.offsets
         self.host_np[o[2]:o[2] + n] = np.arange(n)            # seq_of_token
         self.host_np[o[3]:o[3] + n + 1] = np.arange(n + 1)    # cu_q
@@ -388,20 +408,30 @@ class _DecodeGraph:
         self.greedy_launches = 0
 
     def _fill(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> None:
+        """Refresh the step's metadata on the device: tokens, positions and lengths every step
+        (one small copy); slots and block tables only when a request joined or left or a page
+        was taken since the last fill (a second copy)."""
         n, o, cache = self.n, self.offsets, self.runner.cache
         if self.copy_pending:
             self.copied.synchronize()
         h = self.host_np
-        h[o[0]:o[0] + n] = [int(e.tokens[0]) for e in entries]
+        h[o[0]:o[0] + n] = [e.tokens[0] for e in entries]
         h[o[1]:o[1] + n] = starts
-        h[o[4]:o[4] + n] = np.asarray(starts, dtype=np.int32) + 1
-        slots = [cache.slot(e.request) for e in entries]
-        h[o[5]:o[5] + n] = slots
-        for g in range(len(cache.groups)):
-            h[o[7 + g]:o[7 + g] + n * self.width] = cache.table_rows(g, slots).reshape(-1)
-        self.dev.copy_(self.host, non_blocking=True)
-        self.runner.h2d_bytes += self.host.numel() * 4
-        self.copied.record()
+        h[o[4]:o[4] + n] = h[o[1]:o[1] + n] + 1
+        ids = [e.request for e in entries]
+        small = o[5]                      # tokens, positions, seq_of_token, cu_q, kv_len come first
+        if ids != self.last_ids or cache.table_version != self.last_version:
+            slots = [cache.slot(r) for r in ids]
+            h[o[5]:o[5] + n] = slots
+            for g in range(len(cache.groups)):
+                h[o[7 + g]:o[7 + g] + n * self.width] = cache.table_rows(g, slots).reshape(-1)
+            self.last_ids, self.last_version = ids, cache.table_version
+            self.dev.copy_(self.host, non_blocking=True)
+            self.runner.h2d_bytes += self.host.numel() * 4
+        else:
+            self.dev[:small].copy_(self.host[:small], non_blocking=True)
+            self.runner.h2d_bytes += small * 4
+        self.copied.record(ops.current_stream_object())
         self.copy_pending = True
 
     def _capture(self) -> None:
@@ -422,7 +452,6 @@ class _DecodeGraph:
         return self.logits
 
     def run_greedy(self, entries: Sequence[StepEntry], starts: Sequence[int], n_steps: int) -> torch.Tensor:
-        from ..kernels import ops
         runner, ctx = self.runner, self.ctx
         self._fill(entries, starts)
         if self.greedy_graph is None:

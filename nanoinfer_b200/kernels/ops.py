@@ -112,7 +112,21 @@ def _check(code: int, what: str) -> None:
 
 
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """The raw handle of torch's current stream on the current device (the C accessors: the Python
+    wrapper costs more than a short kernel's launch)."""
+    return torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice())
+
+
+_stream_objects: Dict[int, "torch.cuda.Stream"] = {}
+
+
+def current_stream_object() -> "torch.cuda.Stream":
+    """torch's current stream as an object (for Event.record), cached by raw handle."""
+    raw = _stream()
+    obj = _stream_objects.get(raw)
+    if obj is None:
+        obj = _stream_objects[raw] = torch.cuda.current_stream()
+    return obj
 
 
 def _dev(t: torch.Tensor, name: str, dtype=None) -> int:
