@@ -16,7 +16,7 @@
 
 #define PF_WARPS 8
 #define PF_BM 128
-#define PF_BN 64
+#define PF_BN 128
 
 __device__ __forceinline__ void pf_mma(float c[4], const uint32_t a[4], uint32_t b0, uint32_t b1) {
     asm volatile(
