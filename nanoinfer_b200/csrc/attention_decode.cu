@@ -31,6 +31,11 @@
 #include "common.cuh"
 
 #define DEC_WARPS 4
+// A token may attend to keys that the kernel before this one writes in the same step: its own,
+// and those of the tokens before it in the same short portion of a prompt.  Only keys older
+// than the last DEC_FRESH_KEYS are fetched before that kernel is known to have finished; callers
+// send no token here whose portion has more tokens than this.
+#define DEC_FRESH_KEYS 2
 
 __device__ __forceinline__ void mma_bf16_16816(float c[4], const uint32_t a[4], uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -113,9 +118,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // rows g and g + 8
     uint32_t qa[KS][4];
 
-    // Asks for the keys and values of segment [seg0, seg0 + SEG) into buffer `buf`; `own` selects
-    // the rows of the token's own key (true) or all other rows (false).
-    auto request = [&](int seg0, int buf, bool own_only, bool skip_own) {
+    // Asks for the keys and values of segment [seg0, seg0 + SEG) into buffer `buf`.  The last
+    // `fresh` keys up to the token's own may be written in this very step by the kernel before
+    // this one (the token's own key, and the keys of the tokens before it in a short portion of
+    // a prompt); `fresh_only` selects those rows, `skip_fresh` all other rows.
+    const int first_fresh = pos - DEC_FRESH_KEYS + 1;
+    auto request = [&](int seg0, int buf, bool fresh_only, bool skip_fresh) {
         const int seg_keys = min(SEG, k_end - seg0);
         const int rows = ((seg_keys + 15) / 16) * 16;            // rows that MMAs may touch
         __nv_bfloat16* sK = sKV + (size_t)buf * 2 * SEG * HD;
@@ -124,7 +132,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
             const int r = idx / CH, c = idx - r * CH;
             int key = seg0 + r;
             key = key < k_end ? key : k_end - 1;                 // masked below; never off the table
-            if ((own_only && key != pos) || (skip_own && key == pos)) continue;
+            if ((fresh_only && key < first_fresh) || (skip_fresh && key >= first_fresh)) continue;
             const int pi = page_shift >= 0 ? key >> page_shift : key / page_size;
             const int slot = page_shift >= 0 ? key & (page_size - 1) : key - pi * page_size;
             const size_t off = (((size_t)table[pi] * n_kv_heads + kvh) * page_size + slot) * HD + c * 8;
@@ -134,7 +142,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     };
 
     if (k_begin < k_end) {
-        // everything but the token's own key, which the projection before us is still writing
+        // everything but the fresh keys, which the projection before us may still be writing
         request(k_begin, 0, false, true);
     }
     dec_pdl_wait();                                              // the projection has finished
@@ -342,6 +350,8 @@ static int launch_decode(const void* q, const void* k_pages, const void* v_pages
 
 // Scratch floats needed: n_items * n_q_heads * n_splits * (head_dim + 2); tickets: n_items * n_kv_heads
 // ints, zero before the first launch (the kernel leaves them zero).
+NI_EXPORT int ni_attention_decode_fresh_keys() { return DEC_FRESH_KEYS; }
+
 NI_EXPORT int ni_attention_decode(const void* q, const void* k_pages, const void* v_pages, void* out,
                                   const int* token_list, int n_items, const int* positions,
                                   const int* seq_of_token, const int* block_table, int bt_stride,

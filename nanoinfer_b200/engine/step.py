@@ -88,7 +88,7 @@ class StepContext:
     long_tokens: Optional[torch.Tensor] = None
 
 
-SHORT_PORTION = 2
+SHORT_PORTION = 2        # at most kernels.ops.DECODE_FRESH_KEYS (checked below)
 ATTENTION_TILE = 128     # = kernels.ops.PREFILL_TILE_ROWS
 
 
@@ -358,6 +358,9 @@ class ModelRunner:
 
 
 from ..kernels import ops  # noqa: E402  (after the classes above: no import cycle)
+
+if SHORT_PORTION > ops.DECODE_FRESH_KEYS:
+    raise ImportError("SHORT_PORTION exceeds the keys that the decode-attention kernel fetches late")
 
 
 class _DecodeGraph:

@@ -46,6 +46,7 @@ _SIGNATURES = {
     },
     "attention_decode": {
         "ni_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P],
+        "ni_attention_decode_fresh_keys": [],
     },
     "attention_prefill": {
         "ni_attention_prefill": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
@@ -82,6 +83,8 @@ def load(module: str) -> ctypes.CDLL:
             f = getattr(lib, fn)
             f.argtypes = argtypes
             f.restype = _I
+        if module == "attention_decode" and lib.ni_attention_decode_fresh_keys() != DECODE_FRESH_KEYS:
+            raise KernelError("attention_decode: DEC_FRESH_KEYS of the built kernel differs from ops.DECODE_FRESH_KEYS")
         _libs[module] = lib
     return lib
 
@@ -408,6 +411,10 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, mode: int) -> N
 DECODE_HEAD_DIMS = (64, 128)
 DECODE_SEGMENT_KEYS = {64: 64, 128: 64}      # keys per shared-memory buffer of a decode-attention block
 DECODE_BLOCKS_PER_SM = 4
+# The decode kernel reads all but a token's last DECODE_FRESH_KEYS keys while the kernel that
+# writes this step's keys may still run, so a portion sent to it has at most this many tokens
+# (the same constant as in attention_decode.cu; ni_attention_decode_fresh_keys() returns it).
+DECODE_FRESH_KEYS = 2
 
 
 def decode_splits(n_items: int, n_kv_heads: int, head_dim: int, max_kv_len: int) -> int:
