@@ -40,6 +40,7 @@ LLAMA_3_2_1B = {
 FULL_LAYERS = 16
 START_CONTEXT = 2048
 PREFILL_TOKENS = 2048
+BATCHED_TOKENS = 4 * PREFILL_TOKENS     # token budget of one step of the end-to-end run
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -141,15 +142,16 @@ def run_ours(args):
     pk = peaks()
     vocab = raw["vocab_size"]
     K, W = args.steps, args.warmup
-    # 16 spare tokens: in the end-to-end run the first requests start decoding while the last
-    # prompts are still being prefilled
-    end_context = START_CONTEXT + W + K + 16
+    # spare tokens: in the end-to-end run the first requests start decoding while the last
+    # prompts are still being prefilled (one prefill step takes BATCHED_TOKENS of prompt)
+    spare = max(16, -(-args.batch * START_CONTEXT // BATCHED_TOKENS) + 8)
+    end_context = START_CONTEXT + W + K + spare
     max_batch = max(args.batch, 64 if args.points else args.batch)
     page = 16
     pages_per_request = -(-end_context // page)
     ecfg = EngineConfig(max_batch_size=max_batch, max_sequences=max_batch, prefill_chunk_size=PREFILL_TOKENS,
                         block_size=page, num_cache_blocks=max_batch * pages_per_request + 8,
-                        max_num_batched_tokens=PREFILL_TOKENS * 4, max_model_len=pages_per_request * page,
+                        max_num_batched_tokens=BATCHED_TOKENS, max_model_len=pages_per_request * page,
                         dtype="bfloat16", device=device)
     engine = Engine.from_weights(config, device_weights(config, 0, device), ecfg)
     runner = engine.runner
@@ -220,7 +222,7 @@ def run_ours(args):
 
     # ---- end to end through Engine.step: host ids in, host ids out ----
     prompts = [prompt(START_CONTEXT) for _ in range(args.batch)]
-    ids = [engine.add_request(p, W + K + 16, SamplingParams.greedy()) for p in prompts]
+    ids = [engine.add_request(p, W + K + spare, SamplingParams.greedy()) for p in prompts]
     engine.stop_token_ids = ()
     for rid in ids:
         engine.get_request(rid).stop_token_ids = frozenset()

@@ -31,6 +31,7 @@ class EngineConfig:
     max_model_len: Optional[int] = None  # most tokens a request may hold (default: model limit)
     dtype: str = "bfloat16"
     device: str = "cuda:0"
+    overlap_steps: bool = True          # launch a decode step before the previous step's tokens are read
 
 
 @dataclass
@@ -38,6 +39,16 @@ class StepOutput:
     request_id: int
     token: int
     finished: bool
+
+
+@dataclass
+class _InFlight:
+    """A launched step whose sampled tokens have not been read yet."""
+    batch: ScheduledBatch
+    emitting: List[InferenceRequest]
+    ids: Optional[torch.Tensor]              # the sampled ids where the sampler left them
+    host: Optional[torch.Tensor] = None      # their copy on the host (pinned when ids are on a GPU)
+    ready: Optional["torch.cuda.Event"] = None
 
 
 class Engine:
@@ -55,6 +66,9 @@ class Engine:
         self._next_id = 0
         self._running = False
         self.num_steps = 0
+        self._inflight: Optional[_InFlight] = None
+        self._pinned: List[torch.Tensor] = []       # two buffers for sampled ids, used in turn
+        self._pinned_next = 0
 
     @classmethod
     def from_model_dir(cls, model_dir: str, config: Optional[EngineConfig] = None, **overrides) -> "Engine":
@@ -118,35 +132,97 @@ class Engine:
         return list(self.scheduler.requests[request_id].generated_tokens)
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._inflight is not None
 
     def get_scheduler_stats(self) -> SchedulerStats:
         return self.scheduler.stats()
 
     # ---- stepping -------------------------------------------------------------------------
     def step(self) -> List[StepOutput]:
-        """One scheduling decision, one forward pass over its batch, one token for every
-        request whose last pending token was in it."""
+        """One scheduling decision and one forward pass over its batch; returns one token for
+        every request whose last pending token was in a step that has been read.
+
+        With ``overlap_steps`` a step's sampled ids stay on the device: when the next decision
+        is already known (the same requests go on decoding), the next step is launched with
+        those ids fed on the device, and only then are they read and reported - the host's
+        work hides behind the running step, and a request's tokens are reported one call
+        later.  A request that turns out to have hit a stop token has then run one token too
+        many; that token is dropped.  In every other situation the tokens are read first."""
+        outputs: List[StepOutput] = []
+        previous = self._inflight
+        chain = previous is not None and self._can_chain(previous)
+        if previous is not None and not chain:
+            outputs += self._collect(previous)
+            previous = self._inflight = None
+        launched = self._launch(previous)
+        if previous is not None:
+            outputs += self._collect(previous)
+        self._inflight = launched
+        if launched is not None and not self._may_stay_in_flight(launched):
+            outputs += self._collect(launched)
+            self._inflight = None
+        return outputs
+
+    def _may_stay_in_flight(self, step: _InFlight) -> bool:
+        return (self.config.overlap_steps and bool(step.emitting)
+                and getattr(self.runner, "can_feed_device_tokens", lambda n: False)(len(step.emitting)))
+
+    def _can_chain(self, previous: _InFlight) -> bool:
+        return (len(previous.emitting) == len(previous.batch.entries)
+                and not any(r.sampling_params.use_repetition_penalty() for r in previous.emitting)
+                and self.runner.can_feed_device_tokens(len(previous.emitting))
+                and self.scheduler.can_continue_decoding(previous.batch))
+
+    def _launch(self, feed: Optional[_InFlight]) -> Optional[_InFlight]:
+        """Schedule, run and sample one step without reading its tokens.  ``feed``: the step
+        still in flight whose ids are this step's tokens, in the same order."""
         batch = self.scheduler.schedule()
         if not batch.entries:
-            return []
+            return None
         entries, emitting = [], []
         for req, n in batch.entries:
             want = [n - 1] if n == req.num_remaining else []
             entries.append(StepEntry(req.request_id, req.next_tokens(n), want))
             if want:
                 emitting.append(req)
-        logits = self.runner.step(entries)
-        sampled: Dict[int, int] = {}
+        if feed is not None:
+            assert [r for r, _ in batch.entries] == feed.emitting, "the chained batch must repeat the one in flight"
+            logits = self.runner.step(entries, device_tokens=feed.ids)
+        else:
+            logits = self.runner.step(entries)
+        step = _InFlight(batch, emitting, None)
         if emitting:
-            ids = self.sampler.sample(
+            step.ids = self.sampler.sample(
                 logits, [r.sampling_params for r in emitting], [r.seed for r in emitting],
-                [len(r.generated_tokens) for r in emitting], [r.generated_tokens for r in emitting])
-            for req, tok in zip(emitting, ids.tolist()):
-                sampled[req.request_id] = int(tok)
-        finished = self.scheduler.update_after_step(batch, sampled)
+                [len(r.generated_tokens) + r.num_pending for r in emitting], [r.generated_tokens for r in emitting])
+            if step.ids.is_cuda:
+                if not self._pinned:
+                    cap = max(self.config.max_batch_size, len(emitting))
+                    self._pinned = [torch.empty(cap, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+                if len(emitting) > self._pinned[0].numel():
+                    self._pinned = [torch.empty(2 * len(emitting), dtype=torch.int32, pin_memory=True) for _ in range(2)]
+                step.host = self._pinned[self._pinned_next][:len(emitting)]
+                self._pinned_next ^= 1
+                step.host.copy_(step.ids, non_blocking=True)
+                step.ready = torch.cuda.Event()
+                step.ready.record()
+            else:
+                step.host = step.ids
+        self.scheduler.advance(batch, emitting)
         self.num_steps += 1
-        done = {r.request_id for r in finished}
+        return step
+
+    def _collect(self, step: _InFlight) -> List[StepOutput]:
+        """Read a launched step's tokens and book them."""
+        if not step.emitting:
+            return []
+        if step.ready is not None:
+            step.ready.synchronize()
+        sampled: Dict[int, int] = {}
+        for req, tok in zip(step.emitting, step.host.tolist()):
+            if not req.is_finished() and req.num_pending > 0:      # else: it ended meanwhile
+                sampled[req.request_id] = int(tok)
+        done = {r.request_id for r in self.scheduler.commit(sampled)}
         return [StepOutput(rid, tok, rid in done) for rid, tok in sampled.items()]
 
     def run(self) -> None:

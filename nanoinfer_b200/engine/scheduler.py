@@ -174,20 +174,52 @@ class Scheduler:
         self.waiting.appendleft(req)
 
     # ---- after the forward pass -----------------------------------------------------------
-    def update_after_step(self, batch: ScheduledBatch, sampled: Dict[int, int]) -> List[InferenceRequest]:
-        """Advance every scheduled request by its tokens; ``sampled[request_id]`` is the
-        token drawn for requests whose last token was in this step.  Returns the requests
-        that finished; their pages and slots are given back."""
-        finished = []
+    def advance(self, batch: ScheduledBatch, emitting) -> None:
+        """The batch has been launched: its tokens count as computed, and every request in
+        ``emitting`` has one sampled token on the way (known to the host at ``commit``)."""
         for req, n in batch.entries:
             req.num_computed_tokens += n
-            if req.request_id in sampled:
-                if not req.add_token(sampled[req.request_id]):
-                    finished.append(req)
+        for req in emitting:
+            req.num_pending += 1
+
+    def commit(self, sampled: Dict[int, int]) -> List[InferenceRequest]:
+        """``sampled[request_id]`` is the token drawn for a request whose token was on the way.
+        A request that finished or was dropped meanwhile ignores it.  Returns the requests that
+        finished; their pages and slots are given back."""
+        finished = []
+        for rid, tok in sampled.items():
+            req = self.requests[rid]
+            if req.is_finished() or req.num_pending == 0:
+                continue
+            if not req.add_token(tok):
+                finished.append(req)
         for req in finished:
-            self._drop(req)
+            if req in self.running:
+                self._drop(req)
+            else:
+                self.waiting.remove(req)      # finished while preempted
             self.num_finished += 1
         return finished
+
+    def update_after_step(self, batch: ScheduledBatch, sampled: Dict[int, int]) -> List[InferenceRequest]:
+        """advance + commit in one call, for a step whose tokens are read at once."""
+        self.advance(batch, [req for req, _ in batch.entries if req.request_id in sampled])
+        return self.commit(sampled)
+
+    def can_continue_decoding(self, previous: ScheduledBatch) -> bool:
+        """True if the next decision is known without the tokens of ``previous``, the batch
+        still in flight: it held every running request, all of them get their token from it
+        and go on decoding, nobody waits for admission, and every page they need is free - so
+        the next batch is the same requests in the same order, one token each."""
+        if self.waiting or len(previous.entries) != len(self.running):
+            return False
+        need = 0
+        for (req, _), running in zip(previous.entries, self.running):
+            if req is not running or req.num_pending != 1 or req.num_remaining != 1 or req.pending_reaches_limit():
+                return False
+            need += self.cache.needs_page_for_one(req.request_id)
+        return (len(self.running) <= min(self.max_batch_size, self.max_num_batched_tokens)
+                and all(need <= self.cache.num_free_pages(g) for g in range(len(self.cache.groups))))
 
     def stats(self) -> SchedulerStats:
         return SchedulerStats(len(self.running), len(self.waiting), self.num_finished,

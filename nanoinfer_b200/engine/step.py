@@ -23,6 +23,7 @@ from ..cache import CacheManager, GroupSpec, OutOfPages
 from ..config.model_config import ModelConfig
 from ..parts.base import PagedKVNeed, StateNeed
 from .model import DecoderModel
+from .request import PENDING_TOKEN
 from .runtime import Runtime
 
 
@@ -220,7 +221,7 @@ class ModelRunner:
         self._pinned_used[i] = True
         return self._dev_meta
 
-    def _validate(self, entries: Sequence[StepEntry]) -> None:
+    def _validate(self, entries: Sequence[StepEntry], pending_ok: bool = False) -> None:
         if not entries:
             raise StepError("a step needs at least one entry")
         seen = set()
@@ -234,7 +235,7 @@ class ModelRunner:
                 raise StepError(f"request {e.request!r}: an entry needs at least one token")
             if n == 1:
                 t = e.tokens[0]
-                if not 0 <= t < vocab:
+                if not 0 <= t < vocab and not (pending_ok and t == PENDING_TOKEN):
                     raise StepError(f"request {e.request!r}: token id {t} is outside [0, {vocab})")
             elif min(e.tokens) < 0 or max(e.tokens) >= vocab:
                 bad = next(t for t in e.tokens if not 0 <= t < vocab)
@@ -307,13 +308,17 @@ class ModelRunner:
             tile_row0=view(10))
 
     # ---- the step -------------------------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run one batch; returns FP32 logits [number of wanted places, vocab] on the device,
-        ordered by entry and then by ``want``.  The tensor is valid until the next step."""
-        self._validate(entries)
+        ordered by entry and then by ``want``.  The tensor is valid until the next step.
+        ``device_tokens`` (int32 on the device, one per entry): the tokens of a step of single
+        tokens that the host has not read yet (entries then carry PENDING_TOKEN)."""
+        self._validate(entries, pending_ok=device_tokens is not None)
+        if device_tokens is not None and not (self._graphable(entries) and device_tokens.numel() == len(entries)):
+            raise StepError("tokens can be fed from the device only to a replayed step of single tokens")
         if self._graphable(entries):
             starts = reserve_entries(self.cache, entries, self.admit)
-            logits = self._decode_graph(len(entries)).run(entries, starts)
+            logits = self._decode_graph(len(entries)).run(entries, starts, device_tokens)
         else:
             ctx = self.build_context(entries)
             logits = self.model.forward(ctx, self.caches)
@@ -328,6 +333,10 @@ class ModelRunner:
         state update is not), can be captured once per batch size and replayed."""
         return (self.use_graphs and not self._state_runs and len(entries) <= self.max_graph_batch
                 and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries))
+
+    def can_feed_device_tokens(self, n: int) -> bool:
+        """True if a step of ``n`` single tokens can take its tokens from a device tensor."""
+        return self.use_graphs and not self._state_runs and 0 < n <= self.max_graph_batch
 
     def _decode_graph(self, n: int) -> "_DecodeGraph":
         g = self._graphs.get(n)
@@ -447,8 +456,11 @@ class _DecodeGraph:
         with torch.cuda.graph(self.graph):
             self.logits = runner.model.forward(self.ctx, runner.caches)
 
-    def run(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> torch.Tensor:
+    def run(self, entries: Sequence[StepEntry], starts: Sequence[int],
+            device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         self._fill(entries, starts)
+        if device_tokens is not None:
+            self.ctx.tokens.copy_(device_tokens)      # after the host's copy, before the replay
         if self.graph is None:
             self._capture()
         self.graph.replay()

@@ -45,6 +45,29 @@ class FakeRunner:
         self.cache.free(request)
 
 
+class FakeFeedingRunner(FakeRunner):
+    """A fake runner that, like the real one, can take the tokens of a step of single tokens from
+    the previous step's sampled ids, so that the engine overlaps its steps."""
+
+    def __init__(self, *args, **kw):
+        super().__init__(*args, **kw)
+        self.fed_steps = 0
+
+    def can_feed_device_tokens(self, n):
+        return n > 0
+
+    def step(self, entries, device_tokens=None):
+        if device_tokens is not None:
+            from nanoinfer_b200.engine.request import PENDING_TOKEN
+            from nanoinfer_b200.engine import StepEntry
+            assert all(list(e.tokens) == [PENDING_TOKEN] for e in entries) and len(device_tokens) == len(entries)
+            entries = [StepEntry(e.request, [int(t)], e.want) for e, t in zip(entries, device_tokens.tolist())]
+            self.fed_steps += 1
+        else:
+            assert all(t >= 0 for e in entries for t in e.tokens), "a pending token reached the runner unfed"
+        return super().step(entries)
+
+
 class ArgmaxSampler:
     def sample(self, logits, params, seeds, token_indices, generated=None):
         return torch.argmax(logits, dim=-1).int()

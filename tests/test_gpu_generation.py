@@ -103,6 +103,40 @@ def test_stop_token_from_config_ends_generation(model_dirs):
     assert eng.get_request(0).finish_reason == "stop"
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_overlapped_steps_change_no_token(model_dirs, dtype):
+    """Launching a decode step from the ids still on the device gives the tokens of the engine that
+    reads every step's ids first: greedy and sampled, with a stop token that is seen one step late."""
+    from nanoinfer_b200 import Engine, SamplingParams
+    raw, _ = load_plain(model_dirs["a"])
+    prompts = [random_tokens(raw["vocab_size"], n, 20 + i) for i, n in enumerate([9, 3, 21])]
+    params = [SamplingParams.greedy(), SamplingParams(temperature=0.8, top_k=20, seed=5), SamplingParams.greedy()]
+    outs, feeds = [], []
+    for overlap in (False, True):
+        eng = Engine.from_model_dir(model_dirs["a"], dtype=dtype, block_size=16, num_cache_blocks=32,
+                                    max_sequences=4, overlap_steps=overlap)
+        eng.stop_token_ids = ()
+        free_run = eng.generate(prompts, max_new_tokens=20, sampling_params=params)
+        fed = [0]
+        inner = eng.runner.step
+
+        def counting(entries, device_tokens=None, inner=inner, fed=fed):
+            fed[0] += device_tokens is not None
+            return inner(entries, device_tokens=device_tokens) if device_tokens is not None else inner(entries)
+        eng.runner.step = counting
+        eng.stop_token_ids = (free_run[0][6],)            # request 0 stops in mid-flight
+        stopped = eng.generate(prompts, max_new_tokens=20, sampling_params=params)
+        outs.append((free_run, stopped))
+        feeds.append(fed[0])
+        eng.runner.cache.check_consistency()
+        assert eng.runner.cache.num_free_pages() == 32
+    assert outs[0] == outs[1]
+    assert feeds[0] == 0 and feeds[1] >= 5
+    free_run, stopped = outs[1]
+    stop = free_run[0][6]
+    assert stopped[0] == free_run[0][:free_run[0].index(stop) + 1]
+
+
 def test_command_line(model_dirs, tmp_path):
     raw, w = load_plain(model_dirs["a"])
     prompt = random_tokens(raw["vocab_size"], 11, 4)

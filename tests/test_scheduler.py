@@ -1,7 +1,7 @@
 """The scheduler's decisions and the engine loop, on the host with a fake runner."""
 import pytest
 
-from fakes import ArgmaxSampler, FakeRunner, expected_continuation
+from fakes import ArgmaxSampler, FakeFeedingRunner, FakeRunner, expected_continuation
 from nanoinfer_b200.engine import Engine, EngineConfig, RequestState
 from nanoinfer_b200.sampling import SamplingParams
 
@@ -138,3 +138,70 @@ def test_generate_keeps_prompt_order_and_default_params():
     assert SamplingParams().temperature == 1.0 and SamplingParams().top_k == -1
     assert SamplingParams().top_p == 1.0 and SamplingParams().seed == -1
     assert SamplingParams.greedy().use_greedy() and not SamplingParams().use_greedy()
+
+
+# ---- overlapped steps: a decode step is launched before the previous step's tokens are read ----
+
+def test_overlapped_steps_give_the_same_tokens_one_call_later():
+    prompts = [[3, 1, 4], [1, 5, 9, 2, 6], [5, 3]]
+    runner = FakeFeedingRunner(num_pages=64, max_tokens=128)
+    eng, _ = make(runner)
+    ids = [eng.add_request(p, 9) for p in prompts]
+    first = eng.step()                       # prompts: nothing in flight before, tokens stay in flight
+    assert first == [] and eng.has_work()
+    second = eng.step()                      # launched from the ids in flight, then those are reported
+    assert sorted(o.request_id for o in second) == ids and runner.fed_steps == 1
+    eng.run()
+    for rid, p in zip(ids, prompts):
+        assert eng.get_request_result(rid) == expected_continuation(p, 9, 50)
+        assert eng.get_request(rid).finish_reason == "length"
+    assert runner.fed_steps >= 6 and not eng.has_work()
+    runner.cache.check_consistency()
+    assert runner.cache.num_free_pages() == 64 and runner.cache.num_free_slots == 4
+
+
+def test_overlapped_steps_drop_the_token_run_past_a_stop_token():
+    prompt = [2, 7, 1]
+    free_run = expected_continuation(prompt, 12, 50)
+    stop = free_run[5]
+    want = free_run[:free_run.index(stop) + 1]
+    runner = FakeFeedingRunner(num_pages=64, max_tokens=128)
+    eng, _ = make(runner)
+    eng.stop_token_ids = (stop,)
+    a = eng.add_request(prompt, 12)
+    other = eng.add_request([9, 9, 8], 12)
+    eng.run()
+    assert eng.get_request_result(a) == want and eng.get_request(a).finish_reason == "stop"
+    assert eng.get_request_result(other) == expected_continuation([9, 9, 8], 12, 50, stop=(stop,))
+    assert runner.fed_steps > 0
+    runner.cache.check_consistency()
+    assert runner.cache.num_free_pages() == 64
+
+
+def test_overlapped_steps_read_first_when_the_batch_changes():
+    """A request that arrives, a request that ends by length and a page shortage all make the
+    engine read the tokens in flight before it decides."""
+    runner = FakeFeedingRunner(num_pages=6, page_size=4, max_tokens=24)
+    eng, _ = make(runner, prefill_chunk_size=8)
+    a = eng.add_request([1, 2, 3], 14)
+    eng.step(); eng.step(); eng.step()
+    fed = runner.fed_steps
+    assert fed == 2
+    b = eng.add_request([4, 5, 6, 7, 8], 14)         # waiting: the next step is not a repeat
+    eng.step()
+    assert runner.fed_steps == fed and [r for r, _, _ in runner.steps[-1]] == [a, b]
+    eng.run()                                         # 6 pages of 4 cannot hold 17 + 19 tokens: preemption
+    assert eng.get_scheduler_stats().num_preemptions >= 1
+    assert eng.get_request_result(a) == expected_continuation([1, 2, 3], 14, 50)
+    assert eng.get_request_result(b) == expected_continuation([4, 5, 6, 7, 8], 14, 50)
+    runner.cache.check_consistency()
+    assert runner.cache.num_free_pages() == 6
+
+
+def test_overlap_can_be_switched_off():
+    runner = FakeFeedingRunner(num_pages=64, max_tokens=128)
+    eng, _ = make(runner, overlap_steps=False)
+    a = eng.add_request([1, 2, 3], 5)
+    assert [o.request_id for o in eng.step()] == [a]
+    eng.run()
+    assert runner.fed_steps == 0 and eng.get_request_result(a) == expected_continuation([1, 2, 3], 5, 50)
