@@ -2,7 +2,7 @@
 
     python -m nanoinfer_b200.kernels.microbench gemv --m 8 --n 16384 --k 2048 --mode swiglu --norm
     python -m nanoinfer_b200.kernels.microbench attention_decode --batch 8 --context 3072
-    python -m nanoinfer_b200.kernels.microbench attention_prefill --tokens 2048
+    python -m nanoinfer_b200.kernels.microbench attention_prefill --tokens 2048 --kernel tc
 
 Each case runs its kernel over several distinct copies of its inputs in turn (together
 larger than the L2 cache, so every run reads from HBM), times it with CUDA events after
@@ -124,10 +124,12 @@ def attention_prefill(args) -> None:
     cu_q = torch.tensor([0, t], dtype=torch.int32, device=DEV)
     kv_len = torch.tensor([t], dtype=torch.int32, device=DEV)
     fn = lambda: ops.attention_prefill(q, kc, vc, out, tile_seq, tile_row0, len(tiles), cu_q, kv_len, table, hq, hkv,
-                                       hd, page, None, 1.0 / math.sqrt(hd))
+                                       hd, page, None, 1.0 / math.sqrt(hd), kernel=args.kernel)
     us = _time([fn], args.iters)
+    ops.check_device_errors()
     flops = 4.0 * hq * hd * t * (t + 1) / 2
-    print(f"attention_prefill tokens={t} heads={hq}/{hkv} hd={hd}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s (causal)")
+    print(f"attention_prefill tokens={t} heads={hq}/{hkv} hd={hd} kernel={args.kernel or 'default'}: {us:.1f} us, "
+          f"{flops / us / 1e6:.0f} TFLOP/s (causal)")
 
 
 def main() -> None:
@@ -157,6 +159,7 @@ def main() -> None:
         p.add_argument("--head-dim", type=int, default=64)
         p.add_argument("--page", type=int, default=16)
         p.add_argument("--splits", type=int, default=0)
+        p.add_argument("--kernel", default=None, choices=["tc", "mma"], help="prefill: insist on one kernel")
         p.set_defaults(fn=fn)
     for sp in sub.choices.values():
         sp.add_argument("--iters", type=int, default=200)

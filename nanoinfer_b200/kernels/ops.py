@@ -51,6 +51,10 @@ _SIGNATURES = {
     "attention_prefill": {
         "ni_attention_prefill": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
     },
+    "attention_prefill_tc": {
+        "ni_attention_prefill_tc": [_P, _P, _P, _P, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P],
+        "ni_attention_prefill_tc_supports": [_I, _I, _I, _I],
+    },
     "gemm_tc": {
         "ni_gemm_tc": [_P, _P, _P, _I, _I, _I, _I, _P, _P],
     },
@@ -384,7 +388,8 @@ def check_device_errors(device=None) -> None:
         if code:
             w.zero_()
             raise KernelError(f"a kernel on {dev} gave up waiting (code {code}: 1 = loader, 2 = MMA issuer, "
-                              f"3 = epilogue of the tensor-core product)")
+                              f"3 = epilogue of the tensor-core product; 11 = loader, 12 = MMA issuer, "
+                              f"13 = softmax of the tensor-core prefill attention)")
 
 
 def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, mode: int) -> None:
@@ -451,13 +456,34 @@ def attention_decode(q, k_pages, v_pages, out, token_list, n_items, positions, s
         "attention_decode")
 
 
+def attention_prefill_tc_supports(n_q_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    """True if the tcgen05 prefill attention takes the case: head size 64 or 128, an even number of
+    query heads per kv head, a page size from 8 to 128 that divides 128."""
+    return (n_kv_heads > 0 and n_q_heads % n_kv_heads == 0 and (n_q_heads // n_kv_heads) % 2 == 0
+            and head_dim in (64, 128) and 8 <= page_size <= 128 and 128 % page_size == 0)
+
+
 def attention_prefill(q, k_pages, v_pages, out, tile_seq, tile_row0, n_tiles, cu_q, kv_len, block_table,
-                      n_q_heads, n_kv_heads, head_dim, page_size, window, scale) -> None:
-    """Flash-style causal attention of prompt portions (bfloat16): one block per (tile of
-    PREFILL_TILE_ROWS query rows, head); tile_seq / tile_row0 int32 [n_tiles] name each tile's
-    request and first row."""
+                      n_q_heads, n_kv_heads, head_dim, page_size, window, scale, kernel: Optional[str] = None) -> None:
+    """Flash-style causal attention of prompt portions (bfloat16): one block per tile of
+    PREFILL_TILE_ROWS query rows and query head (mma.sync kernel) or pair of query heads
+    (tcgen05 kernel, where it takes the case); tile_seq / tile_row0 int32 [n_tiles] name each
+    tile's request and first row.  ``kernel``: "tc" or "mma" to insist on one of the two."""
     if head_dim % 16 or head_dim > PREFILL_MAX_HEAD_DIM:
         raise KernelError(f"attention_prefill: head_dim {head_dim} not supported (multiples of 16 up to 128)")
+    tc_ok = attention_prefill_tc_supports(n_q_heads, n_kv_heads, head_dim, page_size)
+    if kernel == "tc" and not tc_ok:
+        raise KernelError("attention_prefill: the tcgen05 kernel does not take this case")
+    if tc_ok and kernel != "mma":
+        _check(load("attention_prefill_tc").ni_attention_prefill_tc(
+            _dev(q, "q", torch.bfloat16), _dev(k_pages, "k_pages", torch.bfloat16),
+            _dev(v_pages, "v_pages", torch.bfloat16), _dev(out, "out", torch.bfloat16), q.shape[0], k_pages.shape[0],
+            _dev(tile_seq, "tile_seq", torch.int32), _dev(tile_row0, "tile_row0", torch.int32), n_tiles,
+            _dev(cu_q, "cu_q", torch.int32), _dev(kv_len, "kv_len", torch.int32),
+            _dev(block_table, "block_table", torch.int32), block_table.shape[1], n_q_heads, n_kv_heads,
+            head_dim, page_size, int(window) if window else 0, float(scale), _error_word(q.device).data_ptr(),
+            _stream()), "attention_prefill_tc")
+        return
     _check(load("attention_prefill").ni_attention_prefill(
         _dev(q, "q", torch.bfloat16), _dev(k_pages, "k_pages", torch.bfloat16),
         _dev(v_pages, "v_pages", torch.bfloat16), _dev(out, "out", torch.bfloat16),

@@ -302,6 +302,52 @@ def test_attention_prefill(n_q, n_kv, hd, page, window):
         assert out.cpu().float()[199].mean() > 4.0      # last row of sequence 0 found key 3
 
 
+@pytest.mark.parametrize("far_at", [3, 640])
+@pytest.mark.parametrize("n_q,n_kv,hd,page,window", [(32, 8, 64, 16, None), (4, 2, 64, 8, None), (8, 2, 128, 16, 129),
+                                                      (2, 1, 128, 32, None), (16, 2, 64, 64, 300), (4, 1, 64, 128, None),
+                                                      (6, 1, 128, 8, None)])
+def test_attention_prefill_tensor_core(n_q, n_kv, hd, page, window, far_at):
+    """The tcgen05 kernel: several key tiles per query tile, a portion that starts late, tiny and
+    page-edge portions, and a dominant key either in the first tile or in a late one (there the
+    running maximum jumps and the accumulator in tensor memory is rescaled)."""
+    from nanoinfer_b200.kernels import ops
+    assert ops.attention_prefill_tc_supports(n_q, n_kv, hd, page)
+    lens = [700, 70, 5, 130, 513]
+    spans = [(100, 700), (0, 70), (2, 5), (127, 130), (0, 513)]
+    far = (0, far_at) if window is None else None
+    table, k_pages, v_pages, ks, vs, qs, q, positions, seq_of = _attention_case(lens, spans, n_q, n_kv, hd, page, hd + page, far)
+    scale = 1.0 / math.sqrt(hd)
+    q_lens = [b - a for a, b in spans]
+    cu_q = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    kv_len = torch.tensor([b for _, b in spans], dtype=torch.int32)
+    tiles = [(s, r0) for s, ql in enumerate(q_lens) for r0 in range(0, ql, ops.PREFILL_TILE_ROWS)]
+    tile_seq = torch.tensor([t[0] for t in tiles], dtype=torch.int32)
+    tile_row0 = torch.tensor([t[1] for t in tiles], dtype=torch.int32)
+    out = torch.full_like(q, 7.0).to(DEV)
+    ops.attention_prefill(q.to(DEV), k_pages.to(DEV), v_pages.to(DEV), out, tile_seq.to(DEV), tile_row0.to(DEV),
+                          len(tiles), cu_q.to(DEV), kv_len.to(DEV), table.to(DEV), n_q, n_kv, hd, page, window, scale,
+                          kernel="tc")
+    ops.check_device_errors()
+    want = torch.cat([plain.attention(qs[s], ks[s], vs[s], scale, window)[a:b]
+                      for s, (a, b) in enumerate(spans)]).reshape(-1, n_q * hd)
+    torch.testing.assert_close(out.cpu().float(), want, rtol=8e-3, atol=4e-3)
+    if far is not None:
+        assert out.cpu().float()[599].mean() > 4.0      # last row of sequence 0 found the far key
+
+
+def test_attention_prefill_tensor_core_declines_what_it_cannot_take():
+    from nanoinfer_b200.kernels import ops
+    assert not ops.attention_prefill_tc_supports(5, 5, 64, 16)      # one query head per kv head
+    assert not ops.attention_prefill_tc_supports(8, 2, 96, 16)      # head size
+    assert not ops.attention_prefill_tc_supports(8, 2, 64, 4)       # page size
+    assert not ops.attention_prefill_tc_supports(8, 2, 64, 48)
+    q = torch.zeros(4, 5 * 64, dtype=torch.bfloat16, device=DEV)
+    kp = torch.zeros(2, 5, 16, 64, dtype=torch.bfloat16, device=DEV)
+    z = torch.zeros(2, dtype=torch.int32, device=DEV)
+    with pytest.raises(ops.KernelError):
+        ops.attention_prefill(q, kp, kp, q.clone(), z, z, 1, z, z, z.view(1, 2), 5, 5, 64, 16, None, 0.125, kernel="tc")
+
+
 @pytest.mark.parametrize("m,n,k", [(1, 64, 64), (4, 336, 120), (8, 4800, 2048), (13, 200, 264), (16, 1000, 8200)])
 def test_gemv_with_fused_norm(m, n, k):
     """RMSNorm (on picked rows of the FP32 residual stream) inside the skinny product."""
