@@ -13,13 +13,22 @@
 //   warps 4-7   softmax of stream 0 (each warp one quarter of the 128 TMEM lanes = rows)
 //   warps 8-11  softmax of stream 1
 //
-// Tensor memory (512 columns): scores of stream s in columns [128 s, 128 s + 128), overwritten
-// in place by the bfloat16 probabilities (the A operand of P V is read from tensor memory);
-// outputs in columns [256 + HD s, 256 + HD s + HD).
+// Tensor memory (512 columns).  The A operand of P V is read from tensor memory, where the softmax
+// threads leave the probabilities as bfloat16 pairs.  64-wide heads: scores of stream s in columns
+// [128 s, +128), probabilities in [256 + 64 s, +64), outputs in [384 + 64 s, +64); since scores and
+// probabilities do not share columns, the scores of the next tile are computed while the
+// exponentials of this one run, and no product is on a stream's critical path.  128-wide heads:
+// the probabilities overwrite the scores, outputs in [256 + 128 s, +128).
+//
+// The unit that computes exponentials bounds a tile's time (128 x 128 of them per stream against
+// about 600 tensor-core cycles), so the two streams take turns at it instead of sharing it.
 //
 // The running maximum of a row is only raised when it grows by more than 8 (a factor 256 in
 // the probabilities, harmless in FP32 sums and bfloat16 products); only then is the output
 // accumulator rescaled, which is rare after the first tiles.
+//
+// The MMA warp runs its loop with all lanes and lets one elected lane issue, so that descriptors
+// and addresses stay warp-uniform values; descriptors are built once and advanced by additions.
 //
 // Every wait on an mbarrier is bounded (about a second) and watches a block-wide abort flag;
 // a wait that runs out records a code in the error word, and the block frees its tensor memory
@@ -40,6 +49,7 @@
 #define AT_BN 128
 #define AT_THREADS 384
 #define AT_RESCALE_STEP 8.0f
+
 
 #define AT_ERR_PRODUCER 11
 #define AT_ERR_MMA 12
@@ -195,17 +205,6 @@ __device__ __forceinline__ uint32_t at_pack(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-#ifdef AT_TRACE
-// Timing probe for tuning (never built into the library): clock64 stamps of block (0, 0).
-__device__ long long* at_trace_buf = nullptr;
-#define AT_STAMP(who, tile, point)                                                                   \
-    do {                                                                                             \
-        if (trace_ptr && (tile) < 64) trace_ptr[((who) * 64 + (tile)) * 8 + (point)] = clock64();    \
-    } while (0)
-#else
-#define AT_STAMP(who, tile, point) do {} while (0)
-#endif
-
 struct AtParams {
     __nv_bfloat16* out;            // [n_tokens, Hq * HD]
     const int* tile_seq;
@@ -225,7 +224,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     constexpr int HALVES = HD / 64;
     constexpr int HALF_BYTES = AT_BN * 128;              // a [128][64] bf16 tile: 16 KB
     constexpr int TILE_BYTES = HALVES * HALF_BYTES;      // Q of one stream, or K, or V
-    constexpr uint32_t O_COL = 256;
+    // Tensor-memory columns.  With 64-wide heads there is room to keep the probabilities beside the
+    // scores, so the next tile's scores are computed while this tile's exponentials run; with
+    // 128-wide heads the probabilities overwrite the scores (ALIAS).
+    constexpr bool ALIAS = HD > 64;
+    constexpr uint32_t P_COL = ALIAS ? 0 : 256;          // + 128 s (alias) or + 64 s
+    constexpr uint32_t P_STRIDE = ALIAS ? AT_BN : 64;
+    constexpr uint32_t O_COL = ALIAS ? 256 : 384;
     extern __shared__ uint8_t at_smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>(((uintptr_t)at_smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* sQ = base;                                   // [2 streams][HALVES][128][64]
@@ -241,13 +246,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     uint64_t* p_full = s_full + 2;                        // [2] its probabilities are (128 arrivals)
     uint64_t* o_done = p_full + 2;                        // [2] its P V product has finished
     uint64_t* turn = o_done + 2;                          // [2] stream s may use the exponential unit (128 arrivals)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(turn + 2);
+    uint64_t* s_free = turn + 2;                          // [2] its scores are in registers (128 arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef AT_TRACE
-    long long* const trace_ptr = (blockIdx.x == 0 && blockIdx.y == 0) ? at_trace_buf : nullptr;
-#endif
 
     // ---- the tile's place ----
     const int seq = p.tile_seq[blockIdx.x];
@@ -273,7 +276,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
         for (int s = 0; s < 2; ++s) {
             at_mbar_init(&s_full[s], 1); at_mbar_init(&p_full[s], 128); at_mbar_init(&o_done[s], 1);
-            at_mbar_init(&turn[s], 128);
+            at_mbar_init(&turn[s], 128); at_mbar_init(&s_free[s], 128);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -378,30 +381,69 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 scores(1, 0);
                 if (leader) at_commit(&k_empty[0]);
             }
-            for (int i = 0; i < n_tiles && ok; ++i) {
-                const int stage = i % STAGES;
-                const uint32_t par = (uint32_t)i & 1u;
-                for (int s = 0; s < 2 && ok; ++s) {
-                    if (!wait_all(&p_full[s], par)) { ok = false; break; }
-                    if (lane == 0) AT_STAMP(2 + s, i, 0);
-                    if (s == 0 && !wait_all(&v_full[stage], (uint32_t)(i / STAGES) & 1u)) { ok = false; break; }
-                    at_fence_after();
-                    const uint64_t dv = dv0 + (uint64_t)((stage * TILE_BYTES) >> 4);
-                    if (leader) {
+            auto outputs = [&](int s, int i) {     // O_s += P_s V_i, 16 keys at a time
+                const uint64_t dv = dv0 + (uint64_t)(((i % STAGES) * TILE_BYTES) >> 4);
+                if (leader) {
 #pragma unroll
-                        for (int kk = 0; kk < AT_BN / 16; ++kk)      // O_s += P_s V_i, 16 keys at a time
-                            at_mma_ts(tmem_base + O_COL + s * HD, tmem_base + s * AT_BN + kk * 8,
-                                      dv + (uint64_t)((kk * 2048) >> 4), idesc_o, (i | kk) != 0 ? 1u : 0u);
-                        at_commit(&o_done[s]);
-                        if (s == 1) at_commit(&v_empty[stage]);
-                    }
-                    if (i + 1 < n_tiles) {
-                        if (s == 0 && !wait_all(&k_full[(i + 1) % STAGES], (uint32_t)((i + 1) / STAGES) & 1u)) { ok = false; break; }
+                    for (int kk = 0; kk < AT_BN / 16; ++kk)
+                        at_mma_ts(tmem_base + O_COL + s * HD, tmem_base + P_COL + s * P_STRIDE + kk * 8,
+                                  dv + (uint64_t)((kk * 2048) >> 4), idesc_o, (i | kk) != 0 ? 1u : 0u);
+                    at_commit(&o_done[s]);
+                }
+            };
+            if (ALIAS) {
+                // per stream: P V of tile i, then the scores of tile i + 1 over the same columns
+                for (int i = 0; i < n_tiles && ok; ++i) {
+                    const int stage = i % STAGES;
+                    const uint32_t par = (uint32_t)i & 1u;
+                    for (int s = 0; s < 2 && ok; ++s) {
+                        if (!wait_all(&p_full[s], par)) { ok = false; break; }
+                        if (s == 0 && !wait_all(&v_full[stage], (uint32_t)(i / STAGES) & 1u)) { ok = false; break; }
                         at_fence_after();
-                        scores(s, i + 1);
-                        if (s == 1 && leader) at_commit(&k_empty[(i + 1) % STAGES]);
+                        outputs(s, i);
+                        if (s == 1 && leader) at_commit(&v_empty[stage]);
+                        if (i + 1 < n_tiles) {
+                            if (s == 0 && !wait_all(&k_full[(i + 1) % STAGES], (uint32_t)((i + 1) / STAGES) & 1u)) { ok = false; break; }
+                            at_fence_after();
+                            scores(s, i + 1);
+                            if (s == 1 && leader) at_commit(&k_empty[(i + 1) % STAGES]);
+                        }
                     }
-                    if (lane == 0) AT_STAMP(2 + s, i, 1);
+                }
+            } else {
+                // The softmax warps free a stream's score columns early in a tile (once the scores
+                // are in registers) and fill its probability columns at the tile's end, and the two
+                // streams run half a tile apart; the events therefore come in this order:
+                // scores of 0 free, probabilities of 1 (tile before), scores of 1 free, probabilities of 0.
+                for (int i = 0; i < n_tiles && ok; ++i) {
+                    const uint32_t par = (uint32_t)i & 1u;
+                    const bool more = i + 1 < n_tiles;
+                    const int next = (i + 1) % STAGES;
+                    if (more) {
+                        if (!wait_all(&s_free[0], par) || !wait_all(&k_full[next], (uint32_t)((i + 1) / STAGES) & 1u)) { ok = false; break; }
+                        at_fence_after();
+                        scores(0, i + 1);
+                    }
+                    if (i > 0) {
+                        if (!wait_all(&p_full[1], par ^ 1u)) { ok = false; break; }
+                        at_fence_after();
+                        outputs(1, i - 1);
+                        if (leader) at_commit(&v_empty[(i - 1) % STAGES]);
+                    }
+                    if (more) {
+                        if (!wait_all(&s_free[1], par)) { ok = false; break; }
+                        at_fence_after();
+                        scores(1, i + 1);
+                        if (leader) at_commit(&k_empty[next]);
+                    }
+                    if (!wait_all(&p_full[0], par) || !wait_all(&v_full[i % STAGES], (uint32_t)(i / STAGES) & 1u)) { ok = false; break; }
+                    at_fence_after();
+                    outputs(0, i);
+                }
+                if (ok && wait_all(&p_full[1], (uint32_t)(n_tiles - 1) & 1u)) {
+                    at_fence_after();
+                    outputs(1, n_tiles - 1);
+                    if (leader) at_commit(&v_empty[(n_tiles - 1) % STAGES]);
                 }
             }
             __syncwarp();
@@ -414,6 +456,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int pos = first_pos + r;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const uint32_t t_s = lane_base + s * AT_BN;
+        const uint32_t t_p = lane_base + P_COL + s * P_STRIDE;
         const uint32_t t_o = lane_base + O_COL + s * HD;
         const float sc = p.scale_log2e;
         float m_used = -INFINITY, l = 0.f;
@@ -423,7 +466,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // (the collective tensor-memory loads below need the whole warp: decide as one)
             if (!__all_sync(0xffffffffu, at_wait(&s_full[s], par, abort_flag, p.error, AT_ERR_SOFTMAX))) { ok = false; break; }
             at_fence_after();
-            if (r == 0) AT_STAMP(s, i, 0);
             const int kbase = (j_begin + i) * AT_BN;
             // visible columns of this row: [c_lo, c_hi)
             const int c_hi = min(AT_BN, pos - kbase + 1);
@@ -434,7 +476,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
             for (int c = 0; c < 4; ++c) at_ld32_async(t_s + 32 * c, v + 32 * c);
             at_wait_ld();
-            if (r == 0) AT_STAMP(s, i, 1);
+            if (!ALIAS) {                                // the score columns may be written again
+                at_fence_before();
+                at_mbar_arrive(&s_free[s]);
+            }
+            bool o_waited = false;                       // P V of the tile before is known to have finished
             float mx = -INFINITY;
             if (masked) {
 #pragma unroll
@@ -450,7 +496,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
                 mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
             }
-            if (r == 0) AT_STAMP(s, i, 5);
             mx *= sc;                                    // sc > 0
             const bool raise = mx > m_used + AT_RESCALE_STEP || (i == 0 && mx > -INFINITY);
             float alpha = 1.0f;
@@ -464,6 +509,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 // before this one must have finished
                 if (!__all_sync(0xffffffffu, at_wait(&o_done[s], par ^ 1u, abort_flag, p.error, AT_ERR_SOFTMAX))) { ok = false; break; }
                 at_fence_after();
+                o_waited = true;
 #pragma unroll 1
                 for (int c = 0; c < HD / 32; ++c) {
                     uint32_t o[32];
@@ -473,7 +519,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     at_st32(t_o + 32 * c, o);
                 }
             }
-            if (r == 0) AT_STAMP(s, i, 6);
             // The exponentials of the two streams take turns (0, 1, 0, 1, ...): the unit that
             // computes them is what a tile's time is made of, so sharing it gains nothing, and
             // this way one stream's products always run beside the other stream's softmax.
@@ -481,7 +526,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 const uint32_t turn_par = s == 1 ? par : par ^ 1u;     // stream 1 follows 0's tile i; 0 follows 1's tile i - 1
                 if (!__all_sync(0xffffffffu, at_wait(&turn[s], turn_par, abort_flag, p.error, AT_ERR_SOFTMAX))) { ok = false; break; }
             }
-            if (r == 0) AT_STAMP(s, i, 2);
             // probabilities, written over the scores as bfloat16 pairs (pair e lands in v[e / 2],
             // whose score has been used by then)
             const float m_ref = m_used == -INFINITY ? 0.f : m_used;     // a row that sees nothing yet
@@ -508,14 +552,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
             }
             l += sum0 + sum1;
-            if (r == 0) AT_STAMP(s, i, 3);
             at_mbar_arrive(&turn[s ^ 1]);
-            at_st32(t_s, v);
-            at_st32(t_s + 32, v + 32);
+            if (!ALIAS && i > 0 && !o_waited) {
+                // the probability columns are still being read by P V of the tile before (long
+                // finished in practice: it was issued a whole tile ago)
+                if (!__all_sync(0xffffffffu, at_wait(&o_done[s], par ^ 1u, abort_flag, p.error, AT_ERR_SOFTMAX))) { ok = false; break; }
+                at_fence_after();
+            }
+            at_st32(t_p, v);
+            at_st32(t_p + 32, v + 32);
             at_wait_st();
             at_fence_before();
             at_mbar_arrive(&p_full[s]);
-            if (r == 0) AT_STAMP(s, i, 4);
         }
         // ---- the finished rows: O / l -> bfloat16 ----
         if (ok && n_tiles > 0 &&
@@ -597,12 +645,6 @@ static int launch_at(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
     attention_prefill_tc_kernel<HD, STAGES><<<grid, AT_THREADS, smem, stream>>>(mq, mk, mv, p);
     NI_RETURN_LAUNCH_STATUS();
 }
-
-#ifdef AT_TRACE
-NI_EXPORT int ni_attention_prefill_tc_set_trace(long long* buf) {
-    return (int)cudaMemcpyToSymbol(at_trace_buf, &buf, sizeof(buf));
-}
-#endif
 
 // 1 if this kernel takes the case, else 0 (the caller then uses the mma.sync kernel).
 NI_EXPORT int ni_attention_prefill_tc_supports(int n_q_heads, int n_kv_heads, int head_dim, int page_size) {
