@@ -14,16 +14,20 @@ and gives them back only at its end (src/engine/kv_cache_manager.cpp:120-220,
 src/engine/engine.cpp:142-173); its block tables are rebuilt and copied every step
 (src/engine/block_table.cpp:156-221).  It has no per-request state.
 
-This class is host-side bookkeeping only; the device tensors belong to the engine.
+This is host-side bookkeeping only; the device tensors belong to the engine.  The books are
+kept by compiled code (csrc/host_cache.cpp, as the reference keeps them in C++); this class maps
+request keys to integers, turns error codes into exceptions and exposes the mirror as arrays.
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
 
 import numpy as np
 
-from .page_pool import OutOfPages, PagePool
+from . import native
+from .page_pool import OutOfPages, PagePoolError
 
 
 @dataclass(frozen=True)
@@ -38,14 +42,23 @@ class CacheError(RuntimeError):
     pass
 
 
-class _Held:
-    __slots__ = ("slot", "length", "tables", "first_live")
+class _PoolView:
+    """The page pool of one group, as the manager's ``pools[g]``."""
 
-    def __init__(self, slot: int, n_groups: int) -> None:
-        self.slot = slot
-        self.length = 0                       # tokens whose keys/values are (being) cached
-        self.tables: List[List[int]] = [[] for _ in range(n_groups)]
-        self.first_live = [0] * n_groups      # index of the first page not yet released
+    def __init__(self, lib, handle, group: int) -> None:
+        self._lib, self._h, self._g = lib, handle, group
+        self.num_pages = lib.ni_cache_pool_num_pages(handle, group)
+
+    @property
+    def num_free(self) -> int:
+        return self._lib.ni_cache_pool_num_free(self._h, self._g)
+
+    @property
+    def num_taken(self) -> int:
+        return self.num_pages - self.num_free
+
+    def is_taken(self, page: int) -> bool:
+        return bool(self._lib.ni_cache_pool_is_taken(self._h, self._g, int(page)))
 
 
 class CacheManager:
@@ -55,66 +68,88 @@ class CacheManager:
             raise ValueError("page_size, max_requests and max_tokens_per_request must be positive")
         if len(groups) != len(pages_per_group):
             raise ValueError("one page count per group is needed")
+        if any(n <= 0 for n in pages_per_group):
+            raise ValueError("a page pool needs at least one page")
         self.groups = list(groups)
         self.page_size = page_size
         self.max_requests = max_requests
         self.max_tokens_per_request = max_tokens_per_request
-        self.table_width = -(-max_tokens_per_request // page_size)
-        self.pools = [PagePool(n) for n in pages_per_group]
+        self._lib = lib = native.lib()
+        n = len(self.groups)
+        pages = (ctypes.c_int32 * n)(*[int(p) for p in pages_per_group])
+        windows = (ctypes.c_int32 * n)(*[-1 if g.window is None else int(g.window) for g in self.groups])
+        self._h = lib.ni_cache_create(n, pages, windows, page_size, max_requests, max_tokens_per_request)
+        if not self._h:
+            raise ValueError("the cache manager could not be created from these sizes")
+        self.table_width = lib.ni_cache_table_width(self._h)
+        self.pools = [_PoolView(lib, self._h, g) for g in range(n)]
         self._windowed = any(g.window is not None for g in self.groups)
-        self._free_slots = list(range(max_requests - 1, -1, -1))
-        self._held: Dict[object, _Held] = {}
-        # host mirror of the block tables, one row per slot; -1 = no page
-        self.mirror = [np.full((max_requests, self.table_width), -1, dtype=np.int32)
-                       for _ in self.groups]
-        self.table_version = 0     # bumped whenever any row of the mirror changes
+        # the compiled manager's mirror of the block tables, one row per slot; -1 = no page
+        self.mirror = [np.ctypeslib.as_array(lib.ni_cache_mirror(self._h, g), shape=(max_requests, self.table_width))
+                       for g in range(n)]
+        self._keys: Dict[object, int] = {}      # request key -> the integer the compiled side knows
+        self._next_key = 0
+        self._needed = (ctypes.c_int32 * n)()
 
-    # ---- requests -------------------------------------------------------------------------
-    def has(self, req) -> bool:
-        return req in self._held
+    def __del__(self) -> None:
+        if getattr(self, "_h", None):
+            self.mirror = []
+            self._lib.ni_cache_destroy(self._h)
+            self._h = None
 
-    @property
-    def num_free_slots(self) -> int:
-        return len(self._free_slots)
+    # ---- errors ---------------------------------------------------------------------------
+    def _raise(self, rc: int, req=None):
+        msg = self._lib.ni_cache_last_error(self._h).decode()
+        if req is not None:
+            msg = f"request {req!r}: {msg}"
+        if rc == native.ERR_OUT_OF_PAGES:
+            raise OutOfPages(msg)
+        if rc == native.ERR_PAGE:
+            raise PagePoolError(msg)
+        raise CacheError(msg)
 
-    def admit(self, req) -> int:
-        """Give ``req`` a slot and empty block tables; returns the slot."""
-        if req in self._held:
-            raise CacheError(f"request {req!r} is already admitted")
-        if not self._free_slots:
-            raise CacheError("no free request slot")
-        slot = self._free_slots.pop()
-        self._held[req] = _Held(slot, len(self.groups))
-        for m in self.mirror:
-            m[slot, :] = -1
-        self.table_version += 1
-        return slot
-
-    def slot(self, req) -> int:
-        return self._get(req).slot
-
-    def length(self, req) -> int:
-        return self._get(req).length
-
-    def _get(self, req) -> _Held:
+    def _key(self, req) -> int:
         try:
-            return self._held[req]
+            return self._keys[req]
         except KeyError:
             raise CacheError(f"request {req!r} is not admitted") from None
 
-    # ---- pages ----------------------------------------------------------------------------
-    def _first_needed_page(self, g: int, length: int) -> int:
-        """Index of the first page that a query at position >= ``length`` can still see."""
-        w = self.groups[g].window
-        if w is None:
-            return 0
-        return max(0, length - w + 1) // self.page_size
+    @property
+    def table_version(self) -> int:
+        """Bumped whenever any row of the mirror changes."""
+        return self._lib.ni_cache_table_version(self._h)
 
+    # ---- requests -------------------------------------------------------------------------
+    def has(self, req) -> bool:
+        return req in self._keys
+
+    @property
+    def num_free_slots(self) -> int:
+        return self._lib.ni_cache_num_free_slots(self._h)
+
+    def admit(self, req) -> int:
+        """Give ``req`` a slot and empty block tables; returns the slot."""
+        if req in self._keys:
+            raise CacheError(f"request {req!r} is already admitted")
+        key = self._next_key
+        slot = self._lib.ni_cache_admit(self._h, key)
+        if slot < 0:
+            self._raise(slot)
+        self._next_key += 1
+        self._keys[req] = key
+        return slot
+
+    def slot(self, req) -> int:
+        return self._lib.ni_cache_slot(self._h, self._key(req))
+
+    def length(self, req) -> int:
+        return self._lib.ni_cache_length(self._h, self._key(req))
+
+    # ---- pages ----------------------------------------------------------------------------
     def pages_needed(self, req, n_new: int) -> List[int]:
         """Pages each group must still take so that ``n_new`` more tokens fit."""
-        h = self._get(req)
-        total = -(-(h.length + n_new) // self.page_size)
-        return [total - len(t) for t in h.tables]
+        self._lib.ni_cache_pages_needed(self._h, self._key(req), n_new, self._needed)
+        return list(self._needed)
 
     def pages_for_new_request(self, n_new: int) -> List[int]:
         return [-(-n_new // self.page_size) for _ in self.groups]
@@ -125,73 +160,44 @@ class CacheManager:
 
     def needs_page_for_one(self, req) -> bool:
         """True if one more token of ``req`` starts a new page (in every group alike)."""
-        return self._get(req).length % self.page_size == 0
+        return self._lib.ni_cache_needs_page_for_one(self._h, self._key(req)) == 1
 
     def append_one(self, req) -> None:
         """append(req, 1), for the decode loop."""
-        h = self._get(req)
-        if h.length % self.page_size == 0:
-            self.append(req, 1)
-        elif h.length + 1 > self.max_tokens_per_request:
-            self.append(req, 1)          # raises the limit error
-        else:
-            h.length += 1
+        rc = self._lib.ni_cache_append_one(self._h, self._key(req))
+        if rc != 0:
+            self._raise(rc, req)
 
     def append(self, req, n_new: int) -> None:
         """Take the pages for tokens [length, length + n_new).  All groups or none."""
-        h = self._get(req)
         if n_new < 0:
             raise ValueError("n_new must not be negative")
-        if h.length + n_new > self.max_tokens_per_request:
-            raise CacheError(f"request {req!r} would hold {h.length + n_new} tokens, more than "
-                             f"max_tokens_per_request {self.max_tokens_per_request}")
-        need = self.pages_needed(req, n_new)
-        for g, n in enumerate(need):
-            if n > self.pools[g].num_free:
-                raise OutOfPages(f"group {g}: request {req!r} needs {n} more pages, "
-                                 f"{self.pools[g].num_free} are free")
-        for g, n in enumerate(need):
-            if n > 0:
-                pages = self.pools[g].take(n)
-                start = len(h.tables[g])
-                h.tables[g].extend(pages)
-                self.mirror[g][h.slot, start:start + n] = pages
-                self.table_version += 1
-        h.length += n_new
+        rc = self._lib.ni_cache_append(self._h, self._key(req), n_new)
+        if rc != 0:
+            self._raise(rc, req)
 
     def release_passed(self, req) -> int:
         """Give back the pages of windowed groups that no later query can see; returns how many."""
         if not self._windowed:
             return 0
-        h = self._get(req)
-        released = 0
-        for g in range(len(self.groups)):
-            if self.groups[g].window is None:
-                continue
-            first = min(self._first_needed_page(g, h.length), len(h.tables[g]))
-            if first > h.first_live[g]:
-                pages = h.tables[g][h.first_live[g]:first]
-                self.pools[g].give_back(pages)
-                for i in range(h.first_live[g], first):
-                    h.tables[g][i] = -1
-                self.mirror[g][h.slot, h.first_live[g]:first] = -1
-                self.table_version += 1
-                released += len(pages)
-                h.first_live[g] = first
-        return released
+        rc = self._lib.ni_cache_release_passed(self._h, self._key(req))
+        if rc < 0:
+            self._raise(rc, req)
+        return rc
 
     def free(self, req) -> None:
         """Give back everything ``req`` holds: pages of all groups and its slot."""
-        h = self._get(req)
-        for g, table in enumerate(h.tables):
-            self.pools[g].give_back([p for p in table if p >= 0])
-            self.mirror[g][h.slot, :] = -1
-        self.table_version += 1
-        self._free_slots.append(h.slot)
-        del self._held[req]
+        rc = self._lib.ni_cache_free(self._h, self._key(req))
+        if rc != 0:
+            self._raise(rc, req)
+        del self._keys[req]
 
     def block_table(self, req, group: int = 0) -> List[int]:
-        return list(self._get(req).tables[group])
+        out = (ctypes.c_int32 * self.table_width)()
+        n = self._lib.ni_cache_block_table(self._h, self._key(req), group, out, self.table_width)
+        if n < 0:
+            self._raise(n, req)
+        return list(out[:n])
 
     def table_rows(self, group: int, slots: Sequence[int], width: Optional[int] = None) -> np.ndarray:
         """Rows of the host mirror for the given slots: int32 [len(slots), width]."""
@@ -207,12 +213,5 @@ class CacheManager:
 
     def check_consistency(self) -> None:
         """Every taken page is held by exactly one request, and nothing else is taken."""
-        for g, pool in enumerate(self.pools):
-            held = [p for h in self._held.values() for p in h.tables[g] if p >= 0]
-            if len(held) != len(set(held)):
-                raise CacheError(f"group {g}: a page is held twice")
-            if len(held) != pool.num_taken or any(not pool.is_taken(p) for p in held):
-                raise CacheError(f"group {g}: {pool.num_taken} pages taken, {len(held)} held")
-        slots = [h.slot for h in self._held.values()]
-        if len(slots) != len(set(slots)) or len(slots) + len(self._free_slots) != self.max_requests:
-            raise CacheError("request slots are inconsistent")
+        if self._lib.ni_cache_check(self._h) != 0:
+            raise CacheError(self._lib.ni_cache_last_error(self._h).decode())

@@ -1,4 +1,4 @@
-"""Free-list of cache pages.
+"""Free-list of cache pages (the compiled PagePool of csrc/host_cache.cpp behind a thin class).
 
 Same contract as the reference's BlockManager without its prefix-cache bookkeeping
 (src/engine/block_manager.cpp:17-182): pages are handed out from a LIFO stack whose first
@@ -8,7 +8,10 @@ is an error and changes nothing.
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Iterable, List
+
+from . import native
 
 
 class OutOfPages(RuntimeError):
@@ -23,40 +26,42 @@ class PagePool:
     def __init__(self, num_pages: int) -> None:
         if num_pages <= 0:
             raise ValueError("a page pool needs at least one page")
+        self._lib = native.lib()
         self.num_pages = num_pages
-        self._free: List[int] = list(range(num_pages - 1, -1, -1))
-        self._taken = bytearray(num_pages)
+        self._h = self._lib.ni_pool_create(num_pages)
+
+    def __del__(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.ni_pool_destroy(self._h)
+            self._h = None
 
     @property
     def num_free(self) -> int:
-        return len(self._free)
+        return self._lib.ni_pool_num_free(self._h)
 
     @property
     def num_taken(self) -> int:
-        return self.num_pages - len(self._free)
+        return self.num_pages - self.num_free
 
     def is_taken(self, page: int) -> bool:
-        return 0 <= page < self.num_pages and bool(self._taken[page])
+        return bool(self._lib.ni_pool_is_taken(self._h, int(page)))
+
+    def _message(self) -> str:
+        return self._lib.ni_pool_last_error(self._h).decode()
 
     def take(self, n: int) -> List[int]:
         if n < 0:
             raise ValueError("cannot take a negative number of pages")
-        if n > len(self._free):
-            raise OutOfPages(f"asked for {n} pages, {len(self._free)} of {self.num_pages} are free")
-        pages = [self._free.pop() for _ in range(n)]
-        for p in pages:
-            self._taken[p] = 1
-        return pages
+        out = (ctypes.c_int32 * max(n, 1))()
+        rc = self._lib.ni_pool_take(self._h, n, out)
+        if rc == native.ERR_OUT_OF_PAGES:
+            raise OutOfPages(self._message())
+        if rc != 0:
+            raise PagePoolError(self._message())
+        return list(out[:n])
 
     def give_back(self, pages: Iterable[int]) -> None:
-        pages = list(pages)
-        seen = set()
-        for p in pages:
-            if not 0 <= p < self.num_pages:
-                raise PagePoolError(f"page {p} is outside the pool of {self.num_pages}")
-            if not self._taken[p] or p in seen:
-                raise PagePoolError(f"page {p} is not held (freed twice?)")
-            seen.add(p)
-        for p in pages:
-            self._taken[p] = 0
-            self._free.append(p)
+        pages = [int(p) for p in pages]
+        arr = (ctypes.c_int32 * max(len(pages), 1))(*pages)
+        if self._lib.ni_pool_give_back(self._h, arr, len(pages)) != 0:
+            raise PagePoolError(self._message())

@@ -232,33 +232,46 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         }
     } else if (warp == 1) {
-        // ---- MMA issuer ----
-        if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc(BN);
-            int stage = 0, acc = 0;
-            uint32_t phase = 0, acc_phase = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1)) { atomicExch(p.error, TC_ERR_TIMEOUT_MMA); break; }
-                tc_fence_after();
-                const uint32_t tmem_d = tmem_base + acc * BN;
-                for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!mbar_wait(&full[stage], phase)) { atomicExch(p.error, TC_ERR_TIMEOUT_MMA); ok = false; break; }
-                    tc_fence_after();
-#pragma unroll
-                    for (int k = 0; k < TC_BK / 16; ++k) {
-                        const uint64_t da = umma_desc(sA + stage * A_BYTES + k * 32);
-                        const uint64_t db = umma_desc(sB + stage * B_BYTES + k * 32);
-                        umma_mma(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
-                    }
-                    umma_commit(&empty[stage]);           // the stage is free once these MMAs have read it
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
-                }
-                if (!ok) break;
-                umma_commit(&acc_full[acc]);              // the accumulator is complete
-                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        // ---- MMA issuer: the whole warp runs the loop, so that descriptors and addresses are
+        // warp-uniform values (built once, advanced by additions); one elected lane issues ----
+        constexpr uint32_t idesc = umma_idesc(BN);
+        uint32_t elected;
+        asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.b32 %0, 1, 0, p;\n}\n" : "=r"(elected));
+        const bool leader = elected != 0;
+        const uint64_t da0 = umma_desc(sA), db0 = umma_desc(sB);
+        int stage = 0, acc = 0;
+        uint32_t phase = 0, acc_phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            if (!__all_sync(0xffffffffu, mbar_wait(&acc_empty[acc], acc_phase ^ 1))) {
+                if (leader) atomicExch(p.error, TC_ERR_TIMEOUT_MMA);
+                break;
             }
+            tc_fence_after();
+            const uint32_t tmem_d = tmem_base + acc * BN;
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                if (!__all_sync(0xffffffffu, mbar_wait(&full[stage], phase))) {
+                    if (leader) atomicExch(p.error, TC_ERR_TIMEOUT_MMA);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint64_t da = da0 + (uint64_t)((stage * A_BYTES) >> 4);
+                const uint64_t db = db0 + (uint64_t)((stage * B_BYTES) >> 4);
+                if (leader) {
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k)
+                        umma_mma(tmem_d, da + (uint64_t)((k * 32) >> 4), db + (uint64_t)((k * 32) >> 4), idesc,
+                                 (kb | k) != 0 ? 1u : 0u);
+                    umma_commit(&empty[stage]);           // the stage is free once these MMAs have read it
+                }
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (!ok) break;
+            if (leader) umma_commit(&acc_full[acc]);      // the accumulator is complete
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
+        __syncwarp();
     } else {
         // ---- epilogue: warps 2..5, each its own quarter of the 128 accumulator lanes ----
         const int quarter = warp & 3;

@@ -13,6 +13,7 @@ trace replay both drive this one class.
 """
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
@@ -372,6 +373,22 @@ if SHORT_PORTION > ops.DECODE_FRESH_KEYS:
     raise ImportError("SHORT_PORTION exceeds the keys that the decode-attention kernel fetches late")
 
 
+class _quiet_collector:
+    """Stream capture must not be disturbed by the garbage collector: if it frees an older CUDA
+    graph (or anything else whose release is a CUDA call) while a stream is capturing, the capture
+    is invalidated.  Collect first, then keep the collector off until the capture has ended."""
+
+    def __enter__(self):
+        gc.collect()
+        self.was_enabled = gc.isenabled()
+        gc.disable()
+
+    def __exit__(self, *exc):
+        if self.was_enabled:
+            gc.enable()
+        return False
+
+
 class _DecodeGraph:
     """The forward pass of ``n`` single-token requests, captured once and replayed.
 
@@ -453,7 +470,7 @@ class _DecodeGraph:
         runner.model.forward(self.ctx, runner.caches)
         torch.cuda.synchronize()
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
+        with _quiet_collector(), torch.cuda.graph(self.graph):
             self.logits = runner.model.forward(self.ctx, runner.caches)
 
     def run(self, entries: Sequence[StepEntry], starts: Sequence[int],
@@ -475,7 +492,7 @@ class _DecodeGraph:
             torch.cuda.synchronize()
             self.greedy_graph = torch.cuda.CUDAGraph()
             before = ops.launch_count()
-            with torch.cuda.graph(self.greedy_graph):
+            with _quiet_collector(), torch.cuda.graph(self.greedy_graph):
                 logits = runner.model.forward(ctx, runner.caches)
                 ops.argmax(logits, self.greedy_out)
                 ctx.tokens.copy_(self.greedy_out)

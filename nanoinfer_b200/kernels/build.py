@@ -1,6 +1,7 @@
-"""Building the CUDA kernels: one shared library per .cu file of ``csrc``.
+"""Building the native code: one shared library per .cu file (CUDA kernels, nvcc) and per .cpp
+file (host-side runtime, the C++ compiler) of ``csrc``.
 
-Each library is compiled for sm_100a with nvcc at its first use (or ahead of time by
+Each CUDA library is compiled for sm_100a with nvcc at its first use (or ahead of time by
 ``build_all``) into ``csrc/_build`` inside the package, or, when that folder cannot be
 written, into ``$NANOINFER_B200_BUILD_DIR`` or a per-user folder under the system's
 temporary directory.  A library is rebuilt when its source, a shared header or the
@@ -24,6 +25,7 @@ CSRC_DIR = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__
 
 NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC", "-shared"]
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall"]
 
 _lock = threading.Lock()
 
@@ -33,7 +35,15 @@ class KernelBuildError(RuntimeError):
 
 
 def module_names() -> List[str]:
-    return sorted(f[:-3] for f in os.listdir(CSRC_DIR) if f.endswith(".cu"))
+    return sorted(os.path.splitext(f)[0] for f in os.listdir(CSRC_DIR) if f.endswith((".cu", ".cpp")))
+
+
+def _source_file(module: str) -> str:
+    """``module``.cu (a CUDA library) or ``module``.cpp (host code)."""
+    for ext in (".cu", ".cpp"):
+        if os.path.isfile(os.path.join(CSRC_DIR, module + ext)):
+            return module + ext
+    raise KernelBuildError(f"no source '{module}.cu' or '{module}.cpp' in {CSRC_DIR}")
 
 
 def _writable_dir(path: str) -> bool:
@@ -67,6 +77,13 @@ def build_dir() -> str:
     raise KernelBuildError("no writable folder for the compiled kernels; tried " + ", ".join(candidates))
 
 
+def _find_cxx() -> Optional[str]:
+    for c in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++")):
+        if c and os.path.isfile(c) and os.access(c, os.X_OK):
+            return c
+    return None
+
+
 def _find_nvcc() -> Optional[str]:
     for c in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
         if c and os.path.isfile(c) and os.access(c, os.X_OK):
@@ -76,8 +93,9 @@ def _find_nvcc() -> Optional[str]:
 
 def _source_hash(module: str) -> str:
     h = hashlib.sha256()
-    h.update(" ".join(NVCC_FLAGS).encode())
-    names = [module + ".cu"] + sorted(f for f in os.listdir(CSRC_DIR) if f.endswith((".cuh", ".h")))
+    src = _source_file(module)
+    h.update(" ".join(NVCC_FLAGS if src.endswith(".cu") else CXX_FLAGS).encode())
+    names = [src] + sorted(f for f in os.listdir(CSRC_DIR) if f.endswith((".cuh", ".h")))
     for n in names:
         with open(os.path.join(CSRC_DIR, n), "rb") as f:
             h.update(n.encode())
@@ -99,13 +117,21 @@ def _is_current(module: str) -> bool:
 
 
 def _compile(module: str, log) -> None:
-    nvcc = _find_nvcc()
-    if nvcc is None:
-        raise KernelBuildError(f"the CUDA library for '{module}' is not built and nvcc was not found "
-                               f"(set NVCC or put nvcc on PATH); there is no fallback path")
+    src = _source_file(module)
     lib = library_path(module)
     tmp = f"{lib}.tmp{os.getpid()}_{threading.get_ident()}"
-    cmd = [nvcc] + NVCC_FLAGS + ["-I", CSRC_DIR, "-o", tmp, os.path.join(CSRC_DIR, module + ".cu")]
+    if src.endswith(".cu"):
+        nvcc = _find_nvcc()
+        if nvcc is None:
+            raise KernelBuildError(f"the CUDA library for '{module}' is not built and nvcc was not found "
+                                   f"(set NVCC or put nvcc on PATH); there is no fallback path")
+        cmd = [nvcc] + NVCC_FLAGS + ["-I", CSRC_DIR, "-o", tmp, os.path.join(CSRC_DIR, src)]
+    else:
+        cxx = _find_cxx()
+        if cxx is None:
+            raise KernelBuildError(f"the host library for '{module}' is not built and no C++ compiler was found "
+                                   f"(set CXX or put g++ on PATH); there is no fallback path")
+        cmd = [cxx] + CXX_FLAGS + ["-I", CSRC_DIR, "-o", tmp, os.path.join(CSRC_DIR, src)]
     t0 = time.time()
     proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, cwd=build_dir())
     last = t0
@@ -116,15 +142,15 @@ def _compile(module: str, log) -> None:
         except subprocess.TimeoutExpired:
             if time.time() - last >= 5.0:
                 last = time.time()
-                log(f"[nanoinfer_b200] compiling {module}.cu for sm_100a ... {last - t0:.0f} s")
+                log(f"[nanoinfer_b200] compiling {src} ... {last - t0:.0f} s")
     if proc.returncode != 0:
         if os.path.exists(tmp):
             os.remove(tmp)
-        raise KernelBuildError(f"nvcc failed on {module}.cu:\n{out.decode(errors='replace')}")
+        raise KernelBuildError(f"{cmd[0]} failed on {src}:\n{out.decode(errors='replace')}")
     os.replace(tmp, lib)
     with open(lib + ".hash", "w") as f:
         f.write(_source_hash(module))
-    log(f"[nanoinfer_b200] compiled {module}.cu in {time.time() - t0:.1f} s")
+    log(f"[nanoinfer_b200] compiled {src} in {time.time() - t0:.1f} s")
 
 
 def _log(msg: str) -> None:
@@ -137,11 +163,11 @@ def ensure_built(modules: Iterable[str], log=_log) -> Dict[str, str]:
     known = set(module_names())
     for m in modules:
         if m not in known:
-            raise KernelBuildError(f"no kernel source '{m}.cu' in {CSRC_DIR}")
+            raise KernelBuildError(f"no source '{m}.cu' or '{m}.cpp' in {CSRC_DIR}")
     with _lock:
         todo = [m for m in modules if not _is_current(m)]
         if todo:
-            log(f"[nanoinfer_b200] compiling {len(todo)} CUDA file(s) for sm_100a: {', '.join(todo)}")
+            log(f"[nanoinfer_b200] compiling {len(todo)} file(s) (CUDA for sm_100a, host C++): {', '.join(todo)}")
             errors: List[BaseException] = []
 
             def work(m):
