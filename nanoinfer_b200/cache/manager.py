@@ -15,7 +15,7 @@ src/engine/engine.cpp:142-173); its block tables are rebuilt and copied every st
 (src/engine/block_table.cpp:156-221).  It has no per-request state.
 
 This is host-side bookkeeping only; the device tensors belong to the engine.  The books are
-kept by compiled code (csrc/host_cache.cpp, as the reference keeps them in C++); this class maps
+kept by compiled code (csrc/host_runtime.cpp, as the reference keeps them in C++); this class maps
 request keys to integers, turns error codes into exceptions and exposes the mirror as arrays.
 """
 from __future__ import annotations
@@ -87,8 +87,11 @@ class CacheManager:
         # the compiled manager's mirror of the block tables, one row per slot; -1 = no page
         self.mirror = [np.ctypeslib.as_array(lib.ni_cache_mirror(self._h, g), shape=(max_requests, self.table_width))
                        for g in range(n)]
-        self._keys: Dict[object, int] = {}      # request key -> the integer the compiled side knows
-        self._next_key = 0
+        # The compiled side knows requests by integers: a non-negative int key is used as it is
+        # (so the compiled scheduler and this class mean the same request by an engine's request
+        # id), any other key gets a number of its own from a range far above.
+        self._keys: Dict[object, int] = {}
+        self._next_key = 1 << 62
         self._needed = (ctypes.c_int32 * n)()
 
     def __del__(self) -> None:
@@ -108,7 +111,15 @@ class CacheManager:
             raise PagePoolError(msg)
         raise CacheError(msg)
 
+    @staticmethod
+    def _is_plain(req) -> bool:
+        return type(req) is int and 0 <= req < (1 << 62)
+
     def _key(self, req) -> int:
+        if self._is_plain(req):
+            if not self._lib.ni_cache_has(self._h, req):
+                raise CacheError(f"request {req!r} is not admitted")
+            return req
         try:
             return self._keys[req]
         except KeyError:
@@ -121,6 +132,8 @@ class CacheManager:
 
     # ---- requests -------------------------------------------------------------------------
     def has(self, req) -> bool:
+        if self._is_plain(req):
+            return bool(self._lib.ni_cache_has(self._h, req))
         return req in self._keys
 
     @property
@@ -129,14 +142,16 @@ class CacheManager:
 
     def admit(self, req) -> int:
         """Give ``req`` a slot and empty block tables; returns the slot."""
-        if req in self._keys:
+        if self.has(req):
             raise CacheError(f"request {req!r} is already admitted")
-        key = self._next_key
+        plain = self._is_plain(req)
+        key = req if plain else self._next_key
         slot = self._lib.ni_cache_admit(self._h, key)
         if slot < 0:
             self._raise(slot)
-        self._next_key += 1
-        self._keys[req] = key
+        if not plain:
+            self._next_key += 1
+            self._keys[req] = key
         return slot
 
     def slot(self, req) -> int:
@@ -190,7 +205,7 @@ class CacheManager:
         rc = self._lib.ni_cache_free(self._h, self._key(req))
         if rc != 0:
             self._raise(rc, req)
-        del self._keys[req]
+        self._keys.pop(req, None)
 
     def block_table(self, req, group: int = 0) -> List[int]:
         out = (ctypes.c_int32 * self.table_width)()

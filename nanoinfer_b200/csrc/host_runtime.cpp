@@ -1,6 +1,7 @@
-// Host-side bookkeeping of the paged cache: page pools, per-request block tables, the mirror of
-// the tables that the step function uploads, and request slots.  Plain C++17, no CUDA; exported
-// as C functions over opaque handles (the Python classes of nanoinfer_b200.cache are thin
+// The host-side runtime: the paged cache's books (page pools, per-request block tables, the
+// mirror of the tables that the step function uploads, request slots) and the scheduler that
+// decides each step's batch.  Plain C++17, no CUDA; exported as C functions over opaque handles
+// (the Python classes of nanoinfer_b200.cache and nanoinfer_b200.engine.scheduler are thin
 // wrappers).  Every function returns 0 / a count, or a negative code with a message kept in the
 // object (ni_cache_last_error); a refused call changes nothing.
 //
@@ -14,8 +15,10 @@
 // (src/engine/block_table.cpp:22-221: rebuilt and flattened every step) and KVCacheManager
 // (src/engine/kv_cache_manager.cpp:120-220: one group, whole prompt reserved at admission,
 // everything given back at the end).
+#include <algorithm>
 #include <cstdint>
 #include <cstdio>
+#include <deque>
 #include <string>
 #include <unordered_map>
 #include <vector>
@@ -323,4 +326,285 @@ NI_HOST_EXPORT int ni_cache_block_table(void* c, long long req, int g, int32_t* 
     const auto& t = h->tables[(size_t)g];
     for (int i = 0; i < (int)t.size() && i < cap; ++i) out[i] = t[(size_t)i];
     return (int)t.size();
+}
+
+// ---- scheduler -----------------------------------------------------------------------------------
+// First come, first served, continuous batching, chunked prefill.  Every step is ONE batch: each
+// running request contributes its next tokens - one token if it is decoding, otherwise a portion of
+// at most prefill_chunk_size - and waiting requests are admitted in arrival order while the token
+// budget, the batch size, the request slots and the pages allow.  Pages are taken portion by
+// portion (by the step function; the scheduler only counts them).
+//
+// When pages run out: the most recently admitted running request is preempted - its pages and slot
+// are given back, it returns to the FRONT of the waiting queue and is recomputed later from its
+// prompt plus the tokens it had generated.  If the request that needs the page is the only one
+// running, the pool is too small for it: it fails and the engine goes on.
+//
+// The reference admits by batch size and sequence count only, reserves a whole prompt's pages when
+// the request is added, runs every prefill portion as a forward pass of its own
+// (src/engine/scheduler.cpp:51-91, src/engine/engine.cpp:142-173,215-250) and stops the engine
+// when a decode step finds no free page (src/engine/engine.cpp:403-404,194-198).
+//
+// The scheduler knows requests by id and by counts only; token ids, sampling and stop conditions
+// stay with the caller, who reports each sampled token with ni_sched_commit.
+namespace {
+
+enum ReqState { kWaiting = 0, kRunning = 1, kFinished = 2, kFailed = 3 };
+
+struct SchedRequest {
+    int prompt_len = 0, max_new = 0;
+    int n_generated = 0;      // sampled tokens known to the host
+    int n_pending = 0;        // sampled tokens still on the device
+    int n_computed = 0;       // tokens whose keys/values are in the cache
+    int state = kWaiting;
+    int n_preempt = 0;
+    int remaining() const { return prompt_len + n_generated + n_pending - n_computed; }
+};
+
+struct Scheduler {
+    CacheManager* cache;
+    int max_batch, max_seqs, chunk, token_budget;
+    std::deque<long long> waiting;
+    std::vector<long long> running;            // in order of admission
+    std::unordered_map<long long, SchedRequest> reqs;
+    long long n_finished = 0, n_preemptions = 0;
+    // the last decision
+    std::vector<long long> e_ids, preempted, failed;
+    std::vector<int> e_n;
+    std::string error;
+
+    void drop(long long id) {
+        running.erase(std::remove(running.begin(), running.end(), id), running.end());
+        if (cache->held.count(id)) cache->free_request(id);
+    }
+    void preempt(long long id) {
+        drop(id);
+        SchedRequest& r = reqs[id];
+        r.n_computed = 0;
+        r.state = kWaiting;
+        ++r.n_preempt;
+        ++n_preemptions;
+        waiting.push_front(id);
+    }
+    void fail(long long id) {
+        reqs[id].state = kFailed;
+        ++n_finished;
+        failed.push_back(id);
+    }
+
+    void schedule() {
+        e_ids.clear(); e_n.clear(); preempted.clear(); failed.clear();
+        const int G = cache->n_groups();
+        std::vector<int> reserved((size_t)G, 0), need((size_t)G, 0);
+        int budget = token_budget;
+        int decoding = 0;
+        for (long long id : running) decoding += reqs[id].remaining() == 1;
+        int portion_budget = std::max(0, budget - decoding);   // decode tokens are set aside first
+        auto fits = [&]() {
+            for (int g = 0; g < G; ++g)
+                if (reserved[(size_t)g] + need[(size_t)g] > cache->pools[(size_t)g].num_free()) return false;
+            return true;
+        };
+        size_t i = 0;
+        while (i < running.size()) {
+            const long long id = running[i];
+            if ((int)e_ids.size() >= max_batch) break;
+            const int remaining = reqs[id].remaining();
+            const int n = remaining == 1 ? (budget > 0 ? 1 : 0) : std::min(std::min(remaining, chunk), portion_budget);
+            if (n <= 0) { ++i; continue; }
+            auto it = cache->held.find(id);
+            if (it != cache->held.end()) cache->pages_needed(it->second, n, need.data());
+            else std::fill(need.begin(), need.end(), (n + cache->page_size - 1) / cache->page_size);
+            bool gone = false;
+            while (!fits()) {
+                const long long victim = running.back();
+                if (victim == id) {
+                    if (running.size() == 1) {      // alone and still no room: the pool cannot hold this request
+                        drop(id);
+                        fail(id);
+                    } else {
+                        preempt(id);
+                        preempted.push_back(id);
+                    }
+                    gone = true;
+                    break;
+                }
+                preempt(victim);
+                preempted.push_back(victim);
+            }
+            if (gone) continue;                      // running[i] is now the next request (or the end)
+            e_ids.push_back(id);
+            e_n.push_back(n);
+            for (int g = 0; g < G; ++g) reserved[(size_t)g] += need[(size_t)g];
+            budget -= n;
+            if (remaining > 1) portion_budget -= n;
+            ++i;
+        }
+        // admit waiting requests in arrival order; stop at the first that does not fit
+        int slots_left = (int)cache->free_slots.size();
+        while (!waiting.empty() && preempted.empty() && (int)running.size() < max_seqs &&
+               (int)e_ids.size() < max_batch && slots_left > 0) {
+            const long long id = waiting.front();
+            SchedRequest& r = reqs[id];
+            const int n = std::min(std::min(r.remaining(), chunk), portion_budget);
+            if (n <= 0) break;
+            std::fill(need.begin(), need.end(), (n + cache->page_size - 1) / cache->page_size);
+            if (!fits()) {
+                if (running.empty() && e_ids.empty()) {   // nothing runs and the first portion still does not fit
+                    waiting.pop_front();
+                    fail(id);
+                    continue;
+                }
+                break;
+            }
+            waiting.pop_front();
+            r.state = kRunning;
+            running.push_back(id);
+            e_ids.push_back(id);
+            e_n.push_back(n);
+            for (int g = 0; g < G; ++g) reserved[(size_t)g] += need[(size_t)g];
+            budget -= n;
+            portion_budget -= n;
+            --slots_left;
+        }
+    }
+
+    // True if the next decision is known without the tokens of the batch in flight (prev): it held
+    // every running request, all of them get their token from it and go on decoding, nobody waits
+    // for admission, and every page they need is free.
+    bool can_continue(const long long* prev, int n_prev) {
+        if (!waiting.empty() || n_prev != (int)running.size()) return false;
+        int need = 0;
+        for (int i = 0; i < n_prev; ++i) {
+            if (prev[i] != running[(size_t)i]) return false;
+            const SchedRequest& r = reqs[prev[i]];
+            if (r.n_pending != 1 || r.remaining() != 1 || r.n_generated + r.n_pending >= r.max_new) return false;
+            auto it = cache->held.find(prev[i]);
+            if (it == cache->held.end()) return false;
+            need += it->second.length % cache->page_size == 0;
+        }
+        if ((int)running.size() > std::min(max_batch, token_budget)) return false;
+        for (auto& pool : cache->pools)
+            if (need > pool.num_free()) return false;
+        return true;
+    }
+};
+
+}  // namespace
+
+NI_HOST_EXPORT void* ni_sched_create(void* cache, int max_batch_size, int max_sequences, int prefill_chunk_size,
+                                     int max_num_batched_tokens) {
+    if (!cache || max_batch_size <= 0 || max_sequences <= 0 || prefill_chunk_size <= 0 || max_num_batched_tokens <= 0)
+        return nullptr;
+    auto* s = new Scheduler();
+    s->cache = static_cast<CacheManager*>(cache);
+    s->max_batch = max_batch_size;
+    s->max_seqs = std::min(max_sequences, s->cache->max_requests);
+    s->chunk = prefill_chunk_size;
+    s->token_budget = max_num_batched_tokens;
+    return s;
+}
+NI_HOST_EXPORT void ni_sched_destroy(void* s) { delete static_cast<Scheduler*>(s); }
+NI_HOST_EXPORT int ni_sched_add(void* s, long long id, int prompt_len, int max_new_tokens) {
+    auto* sc = static_cast<Scheduler*>(s);
+    if (sc->reqs.count(id) || prompt_len <= 0 || max_new_tokens <= 0) return kErrArgument;
+    SchedRequest r;
+    r.prompt_len = prompt_len;
+    r.max_new = max_new_tokens;
+    sc->reqs.emplace(id, r);
+    sc->waiting.push_back(id);
+    return kOk;
+}
+NI_HOST_EXPORT int ni_sched_has_work(void* s) {
+    auto* sc = static_cast<Scheduler*>(s);
+    return (!sc->waiting.empty() || !sc->running.empty()) ? 1 : 0;
+}
+// Decides the next batch.  Returns the number of entries; the decision is read with ni_sched_result.
+NI_HOST_EXPORT int ni_sched_schedule(void* s) {
+    auto* sc = static_cast<Scheduler*>(s);
+    sc->schedule();
+    return (int)sc->e_ids.size();
+}
+// what: 0 = entry ids, 1 = entry token counts, 2 = preempted ids, 3 = failed ids.  Returns the count.
+NI_HOST_EXPORT int ni_sched_result(void* s, int what, long long* out, int cap) {
+    auto* sc = static_cast<Scheduler*>(s);
+    int n = 0;
+    auto copy = [&](const std::vector<long long>& v) {
+        n = (int)v.size();
+        for (int i = 0; i < n && i < cap; ++i) out[i] = v[(size_t)i];
+    };
+    if (what == 0) copy(sc->e_ids);
+    else if (what == 2) copy(sc->preempted);
+    else if (what == 3) copy(sc->failed);
+    else if (what == 1) {
+        n = (int)sc->e_n.size();
+        for (int i = 0; i < n && i < cap; ++i) out[i] = sc->e_n[(size_t)i];
+    } else return kErrArgument;
+    return n;
+}
+// The batch has been launched: its tokens count as computed, and every emitting request has one
+// more sampled token on the way.
+NI_HOST_EXPORT int ni_sched_advance(void* s, int n, const long long* ids, const int* counts, int n_emitting,
+                                    const long long* emitting) {
+    auto* sc = static_cast<Scheduler*>(s);
+    for (int i = 0; i < n; ++i) {
+        auto it = sc->reqs.find(ids[i]);
+        if (it == sc->reqs.end()) return kErrArgument;
+        it->second.n_computed += counts[i];
+    }
+    for (int i = 0; i < n_emitting; ++i) {
+        auto it = sc->reqs.find(emitting[i]);
+        if (it == sc->reqs.end()) return kErrArgument;
+        it->second.n_pending += 1;
+    }
+    return kOk;
+}
+// A token on the way has been read.  finished != 0: it ends the request (stop token or length):
+// the request leaves the running list (or the waiting queue) and its pages and slot are given back.
+NI_HOST_EXPORT int ni_sched_commit(void* s, long long id, int finished) {
+    auto* sc = static_cast<Scheduler*>(s);
+    auto it = sc->reqs.find(id);
+    if (it == sc->reqs.end()) return kErrArgument;
+    SchedRequest& r = it->second;
+    if (r.state == kFinished || r.state == kFailed || r.n_pending == 0) return kErrArgument;
+    r.n_pending -= 1;
+    r.n_generated += 1;
+    if (finished) {
+        if (r.state == kRunning) sc->drop(id);
+        else sc->waiting.erase(std::remove(sc->waiting.begin(), sc->waiting.end(), id), sc->waiting.end());
+        r.state = kFinished;
+        ++sc->n_finished;
+    }
+    return kOk;
+}
+NI_HOST_EXPORT int ni_sched_can_continue(void* s, const long long* prev, int n_prev) {
+    return static_cast<Scheduler*>(s)->can_continue(prev, n_prev) ? 1 : 0;
+}
+// field: 0 state, 1 computed tokens, 2 pending tokens, 3 generated tokens, 4 preemptions, 5 remaining.
+NI_HOST_EXPORT int ni_sched_get(void* s, long long id, int field) {
+    auto* sc = static_cast<Scheduler*>(s);
+    auto it = sc->reqs.find(id);
+    if (it == sc->reqs.end()) return kErrArgument;
+    const SchedRequest& r = it->second;
+    switch (field) {
+        case 0: return r.state;
+        case 1: return r.n_computed;
+        case 2: return r.n_pending;
+        case 3: return r.n_generated;
+        case 4: return r.n_preempt;
+        case 5: return r.remaining();
+        default: return kErrArgument;
+    }
+}
+// what: 0 running, 1 waiting, 2 finished, 3 total requests, 4 preemptions.
+NI_HOST_EXPORT long long ni_sched_stat(void* s, int what) {
+    auto* sc = static_cast<Scheduler*>(s);
+    switch (what) {
+        case 0: return (long long)sc->running.size();
+        case 1: return (long long)sc->waiting.size();
+        case 2: return sc->n_finished;
+        case 3: return (long long)sc->reqs.size();
+        case 4: return sc->n_preemptions;
+        default: return kErrArgument;
+    }
 }

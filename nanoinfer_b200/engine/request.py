@@ -1,5 +1,10 @@
 """One generation request and its life cycle
-(the reference's InferenceRequest, src/engine/inference_request.cpp:14-169)."""
+(the reference's InferenceRequest, src/engine/inference_request.cpp:14-169).
+
+The request holds what only the caller's side needs: its tokens, sampling parameters, stop
+tokens, the reason it ended and its times.  Once it has been added to a scheduler, the
+counts that scheduling runs on (tokens computed, sampled tokens still on the device, waiting or
+running, preemptions) are kept by the compiled scheduler and read from there."""
 from __future__ import annotations
 
 import enum
@@ -29,14 +34,36 @@ class InferenceRequest:
         self.seed = seed
         self.stop_token_ids = frozenset(stop_token_ids)
         self.generated_tokens: List[int] = []
-        self.num_computed_tokens = 0      # tokens whose keys/values are in the cache
-        self.num_pending = 0              # sampled tokens of this request that are still on the device
-        self.state = RequestState.WAITING
+        self._scheduler = None            # set by Scheduler.add_request
+        self._ended: Optional[RequestState] = None
         self.finish_reason: Optional[str] = None
-        self.num_preemptions = 0
         self.arrival_time = time.perf_counter()
         self.first_token_time: Optional[float] = None
         self.finish_time: Optional[float] = None
+
+    # ---- counts kept by the scheduler -----------------------------------------------------
+    def _count(self, field: int) -> int:
+        return self._scheduler.request_field(self.request_id, field) if self._scheduler is not None else 0
+
+    @property
+    def num_computed_tokens(self) -> int:
+        """Tokens whose keys/values are in the cache."""
+        return self._count(1)
+
+    @property
+    def num_pending(self) -> int:
+        """Sampled tokens of this request that are still on the device."""
+        return self._count(2)
+
+    @property
+    def num_preemptions(self) -> int:
+        return self._count(4)
+
+    @property
+    def state(self) -> RequestState:
+        if self._ended is not None:
+            return self._ended
+        return RequestState.RUNNING if self._count(0) == 1 else RequestState.WAITING
 
     # tokens that have to be run: the prompt and everything generated so far
     @property
@@ -45,7 +72,9 @@ class InferenceRequest:
 
     @property
     def num_remaining(self) -> int:
-        return len(self.prompt_tokens) + len(self.generated_tokens) + self.num_pending - self.num_computed_tokens
+        if self._scheduler is not None:
+            return self._count(5)
+        return len(self.prompt_tokens) + len(self.generated_tokens)
 
     def next_tokens(self, n: int) -> List[int]:
         """The next ``n`` tokens to run; PENDING_TOKEN where the token is not on the host yet."""
@@ -55,10 +84,6 @@ class InferenceRequest:
             return self.prompt_tokens[a:a + n]
         known = (self.prompt_tokens[a:] if a < p else []) + self.generated_tokens[max(a - p, 0):a + n - p]
         return known + [PENDING_TOKEN] * (n - len(known))
-
-    def pending_reaches_limit(self) -> bool:
-        """True if the tokens still on the device take the request to max_new_tokens."""
-        return len(self.generated_tokens) + self.num_pending >= self.max_new_tokens
 
     def is_prefill(self) -> bool:
         return self.num_remaining > 1
@@ -71,7 +96,6 @@ class InferenceRequest:
         (a stop token or max_new_tokens, src/engine/inference_request.cpp:61-73)."""
         if self.first_token_time is None:
             self.first_token_time = time.perf_counter()
-        self.num_pending = max(0, self.num_pending - 1)
         self.generated_tokens.append(int(token))
         if int(token) in self.stop_token_ids:
             self.finish("stop")
@@ -82,12 +106,12 @@ class InferenceRequest:
         return True
 
     def finish(self, reason: str) -> None:
-        self.state = RequestState.FINISHED
+        self._ended = RequestState.FINISHED
         self.finish_reason = reason
         self.finish_time = time.perf_counter()
 
     def fail(self, reason: str) -> None:
-        self.state = RequestState.FAILED
+        self._ended = RequestState.FAILED
         self.finish_reason = reason
         self.finish_time = time.perf_counter()
 

@@ -15,15 +15,19 @@ and slot are given back, it returns to the FRONT of the waiting queue and is rec
 later from its prompt plus the tokens it had generated.  If the request that needs the page
 is the only one running, the pool is simply too small for it: it fails with reason
 "out_of_pages" and the engine goes on.
+
+The decisions are made by compiled code (csrc/host_runtime.cpp, as the reference's scheduler is
+C++); it knows requests by id and by counts.  This class keeps the request objects, translates
+a decision into (request, number of tokens) pairs and reports sampled tokens back.
 """
 from __future__ import annotations
 
-from collections import deque
+import ctypes
 from dataclasses import dataclass, field
-from typing import Deque, Dict, List, Optional, Tuple
+from typing import Dict, List, Tuple
 
-from ..cache import CacheManager
-from .request import InferenceRequest, RequestState
+from ..cache import CacheManager, native
+from .request import InferenceRequest
 
 
 @dataclass
@@ -47,6 +51,10 @@ class SchedulerStats:
     num_preemptions: int
 
 
+def _ids(values) -> "ctypes.Array":
+    return (ctypes.c_longlong * max(len(values), 1))(*values)
+
+
 class Scheduler:
     def __init__(self, cache: CacheManager, max_batch_size: int = 32, max_sequences: int = 128,
                  prefill_chunk_size: int = 512, max_num_batched_tokens: int = 2048) -> None:
@@ -57,130 +65,64 @@ class Scheduler:
         self.max_sequences = min(max_sequences, cache.max_requests)
         self.prefill_chunk_size = prefill_chunk_size
         self.max_num_batched_tokens = max_num_batched_tokens
-        self.waiting: Deque[InferenceRequest] = deque()
-        self.running: List[InferenceRequest] = []   # in order of admission
         self.requests: Dict[int, InferenceRequest] = {}
-        self.num_finished = 0
-        self.num_preemptions = 0
+        self._lib = native.lib()
+        self._h = self._lib.ni_sched_create(cache._h, max_batch_size, max_sequences, prefill_chunk_size,
+                                            max_num_batched_tokens)
+        if not self._h:
+            raise ValueError("the scheduler could not be created from these limits")
+        self._buf = (ctypes.c_longlong * max(max_batch_size, cache.max_requests, 1))()
+
+    def __del__(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.ni_sched_destroy(self._h)
+            self._h = None
+
+    def request_field(self, request_id: int, field_index: int) -> int:
+        """A count of a request as the compiled scheduler keeps it (0 state, 1 computed tokens,
+        2 tokens on the way, 3 generated tokens, 4 preemptions, 5 remaining tokens)."""
+        return self._lib.ni_sched_get(self._h, request_id, field_index)
 
     def add_request(self, req: InferenceRequest) -> None:
+        if type(req.request_id) is not int or req.request_id < 0:
+            raise ValueError("request ids are non-negative integers")
+        if self._lib.ni_sched_add(self._h, req.request_id, len(req.prompt_tokens), req.max_new_tokens) != 0:
+            raise ValueError(f"request {req.request_id} cannot be added (id in use, empty prompt or no tokens to generate)")
         self.requests[req.request_id] = req
-        req.state = RequestState.WAITING
-        self.waiting.append(req)
+        req._scheduler = self
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self._lib.ni_sched_has_work(self._h))
+
+    def _result(self, what: int) -> List[int]:
+        n = self._lib.ni_sched_result(self._h, what, self._buf, len(self._buf))
+        return list(self._buf[:n])
 
     # ---- one scheduling decision ----------------------------------------------------------
     def schedule(self) -> ScheduledBatch:
-        cache = self.cache
         batch = ScheduledBatch()
-        n_groups = len(cache.groups)
-        reserved = [0] * n_groups            # pages this step's entries will take
-        budget = self.max_num_batched_tokens
-        # decoding requests need one token each: set that aside before portions are cut
-        decoding = sum(1 for r in self.running if r.num_remaining == 1)
-        portion_budget = max(0, budget - decoding)
-
-        one_page, no_page = [1] * n_groups, [0] * n_groups
-
-        def fits(need) -> bool:
-            if need is no_page:
-                return True
-            return all(reserved[g] + need[g] <= cache.num_free_pages(g) for g in range(n_groups))
-
-        i = 0
-        while i < len(self.running):
-            req = self.running[i]
-            if len(batch.entries) >= self.max_batch_size:
-                break
-            remaining = req.num_remaining
-            if remaining == 1:
-                n = 1 if budget > 0 else 0
-            else:
-                n = min(remaining, self.prefill_chunk_size, portion_budget)
-            if n <= 0:
-                i += 1
-                continue
-            if n == 1 and cache.has(req.request_id):
-                need = one_page if cache.needs_page_for_one(req.request_id) else no_page
-            else:
-                need = cache.pages_needed(req.request_id, n)
-            while not fits(need):
-                victim = self.running[-1]
-                if victim is req:
-                    if len(self.running) == 1:
-                        # alone and still no room: the pool cannot hold this request
-                        self._drop(req)
-                        req.fail("out_of_pages")
-                        self.num_finished += 1
-                        batch.failed.append(req)
-                    else:
-                        self._preempt(req)
-                        batch.preempted.append(req)
-                    req = None
-                    break
-                self._preempt(victim)
-                batch.preempted.append(victim)
-            if req is None:
-                continue                      # running[i] is now the next request (or the end)
-            batch.entries.append((req, n))
-            if need is not no_page:
-                reserved = [a + b for a, b in zip(reserved, need)]
-            budget -= n
-            if remaining > 1:
-                portion_budget -= n
-            i += 1
-
-        # admit waiting requests in arrival order; stop at the first that does not fit
-        slots_left = cache.num_free_slots
-        while (self.waiting and not batch.preempted and len(self.running) < self.max_sequences
-               and len(batch.entries) < self.max_batch_size and slots_left > 0):
-            req = self.waiting[0]
-            n = min(req.num_remaining, self.prefill_chunk_size, portion_budget)
-            if n <= 0:
-                break
-            need = cache.pages_for_new_request(n)
-            if not fits(need):
-                if not self.running and not batch.entries:
-                    # nothing is running and the first portion still does not fit
-                    self.waiting.popleft()
-                    req.fail("out_of_pages")
-                    self.num_finished += 1
-                    batch.failed.append(req)
-                    continue
-                break
-            self.waiting.popleft()
-            req.state = RequestState.RUNNING
-            self.running.append(req)
-            batch.entries.append((req, n))
-            reserved = [a + b for a, b in zip(reserved, need)]
-            budget -= n
-            portion_budget -= n
-            slots_left -= 1
+        n = self._lib.ni_sched_schedule(self._h)
+        if n:
+            ids, counts = self._result(0), self._result(1)
+            batch.entries = [(self.requests[i], c) for i, c in zip(ids, counts)]
+        batch.preempted = [self.requests[i] for i in self._result(2)]
+        for i in self._result(3):
+            req = self.requests[i]
+            req.fail("out_of_pages")
+            batch.failed.append(req)
         return batch
-
-    def _drop(self, req: InferenceRequest) -> None:
-        self.running.remove(req)
-        if self.cache.has(req.request_id):
-            self.cache.free(req.request_id)
-
-    def _preempt(self, req: InferenceRequest) -> None:
-        self._drop(req)
-        req.num_computed_tokens = 0
-        req.state = RequestState.WAITING
-        req.num_preemptions += 1
-        self.num_preemptions += 1
-        self.waiting.appendleft(req)
 
     # ---- after the forward pass -----------------------------------------------------------
     def advance(self, batch: ScheduledBatch, emitting) -> None:
         """The batch has been launched: its tokens count as computed, and every request in
         ``emitting`` has one sampled token on the way (known to the host at ``commit``)."""
-        for req, n in batch.entries:
-            req.num_computed_tokens += n
-        for req in emitting:
-            req.num_pending += 1
+        n = len(batch.entries)
+        counts = (ctypes.c_int32 * max(n, 1))(*[c for _, c in batch.entries])
+        emit = [r.request_id for r in emitting]
+        rc = self._lib.ni_sched_advance(self._h, n, _ids([r.request_id for r, _ in batch.entries]), counts,
+                                        len(emit), _ids(emit))
+        if rc != 0:
+            raise RuntimeError("the scheduler does not know a request of this batch")
 
     def commit(self, sampled: Dict[int, int]) -> List[InferenceRequest]:
         """``sampled[request_id]`` is the token drawn for a request whose token was on the way.
@@ -191,14 +133,10 @@ class Scheduler:
             req = self.requests[rid]
             if req.is_finished() or req.num_pending == 0:
                 continue
-            if not req.add_token(tok):
+            alive = req.add_token(tok)
+            self._lib.ni_sched_commit(self._h, rid, 0 if alive else 1)
+            if not alive:
                 finished.append(req)
-        for req in finished:
-            if req in self.running:
-                self._drop(req)
-            else:
-                self.waiting.remove(req)      # finished while preempted
-            self.num_finished += 1
         return finished
 
     def update_after_step(self, batch: ScheduledBatch, sampled: Dict[int, int]) -> List[InferenceRequest]:
@@ -211,16 +149,17 @@ class Scheduler:
         still in flight: it held every running request, all of them get their token from it
         and go on decoding, nobody waits for admission, and every page they need is free - so
         the next batch is the same requests in the same order, one token each."""
-        if self.waiting or len(previous.entries) != len(self.running):
-            return False
-        need = 0
-        for (req, _), running in zip(previous.entries, self.running):
-            if req is not running or req.num_pending != 1 or req.num_remaining != 1 or req.pending_reaches_limit():
-                return False
-            need += self.cache.needs_page_for_one(req.request_id)
-        return (len(self.running) <= min(self.max_batch_size, self.max_num_batched_tokens)
-                and all(need <= self.cache.num_free_pages(g) for g in range(len(self.cache.groups))))
+        ids = [r.request_id for r, _ in previous.entries]
+        return bool(self._lib.ni_sched_can_continue(self._h, _ids(ids), len(ids)))
+
+    @property
+    def num_preemptions(self) -> int:
+        return self._lib.ni_sched_stat(self._h, 4)
+
+    @property
+    def num_finished(self) -> int:
+        return self._lib.ni_sched_stat(self._h, 2)
 
     def stats(self) -> SchedulerStats:
-        return SchedulerStats(len(self.running), len(self.waiting), self.num_finished,
-                              len(self.requests), self.num_preemptions)
+        st = self._lib.ni_sched_stat
+        return SchedulerStats(st(self._h, 0), st(self._h, 1), st(self._h, 2), st(self._h, 3), st(self._h, 4))
