@@ -78,12 +78,12 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 // Builds the B fragment (8 activations of one batch row at k .. k+7) and, with the norm fused,
 // adds their squares to ssq.
 template <bool NORM>
-__device__ __forceinline__ uint4 load_x8(const void* xrow, const float* gain, int k, float& ssq) {
-    if (NORM) {
+__device__ __forceinline__ uint4 load_x8(const void* xrow, const float* gain8, int k, float& ssq) {
+    if (NORM) {   // gain8: the gains of elements k .. k+7
         const float4 h0 = *reinterpret_cast<const float4*>((const float*)xrow + k);
         const float4 h1 = *reinterpret_cast<const float4*>((const float*)xrow + k + 4);
-        const float4 g0 = *reinterpret_cast<const float4*>(gain + k);
-        const float4 g1 = *reinterpret_cast<const float4*>(gain + k + 4);
+        const float4 g0 = *reinterpret_cast<const float4*>(gain8);
+        const float4 g1 = *reinterpret_cast<const float4*>(gain8 + 4);
         ssq += h0.x * h0.x + h0.y * h0.y + h0.z * h0.z + h0.w * h0.w +
                h1.x * h1.x + h1.y * h1.y + h1.z * h1.z + h1.w * h1.w;
         return make_uint4(pack2(h0.x * g0.x, h0.y * g0.y), pack2(h0.z * g0.z, h0.w * g0.w),
@@ -109,6 +109,18 @@ __global__ void __launch_bounds__(GV_WARPS * 32, NT == 1 ? 2 : 1) gemv_bf16_kern
     __shared__ float ss_red[GV_WARPS][NT * 8];
     __shared__ float tile[NT * 8][17];
     __shared__ float inv_rms[NT * 8];
+
+    // KEEP with the norm fused: the gain does not depend on the kernel before this one, so each
+    // warp stages the gains of its own K slice in shared memory before the wait; afterwards only
+    // the residual rows come from memory.
+    __shared__ __align__(16) float s_gain[(NORM && KEEP) ? GV_WARPS : 1][(NORM && KEEP) ? GV_UNROLL * 64 : 4];
+    if (NORM && KEEP) {
+        for (int i = lane; i < GV_UNROLL * 16; i += 32) {
+            const int u = i >> 4, k = (warp + u * GV_WARPS) * 64 + 4 * (i & 15);
+            if (k + 4 <= K) *reinterpret_cast<float4*>(&s_gain[warp][4 * i]) = *reinterpret_cast<const float4*>(p.gain + k);
+        }
+        __syncwarp();
+    }
 
     uint4 fx[GV_UNROLL][NT][2];     // KEEP: this warp's activations, loaded once
     float ssq[NT];
@@ -141,7 +153,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32, NT == 1 ? 2 : 1) gemv_bf16_kern
                 }
             }
             if (!waited) {
-                // everything above reads weights only; what follows depends on the kernel before
+                // everything above reads weights (and the gain) only; what follows depends on the kernel before
                 pdl_wait();
                 waited = true;
             }
@@ -159,7 +171,8 @@ __global__ void __launch_bounds__(GV_WARPS * 32, NT == 1 ? 2 : 1) gemv_bf16_kern
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
                             const int k = k0 + 32 * h + 8 * t;
-                            fx[u][nt][h] = (k + 8 <= K && x_ok) ? load_x8<NORM>(xr, p.gain, k, ssq[nt]) : zero;
+                            const float* gain8 = (NORM && KEEP) ? &s_gain[warp][u * 64 + 32 * h + 8 * t] : p.gain + k;
+                            fx[u][nt][h] = (k + 8 <= K && x_ok) ? load_x8<NORM>(xr, gain8, k, ssq[nt]) : zero;
                         }
                     }
                 }
