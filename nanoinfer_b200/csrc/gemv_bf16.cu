@@ -114,6 +114,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32, NT == 1 ? 2 : 1) gemv_bf16_kern
     // warp stages the gains of its own K slice in shared memory before the wait; afterwards only
     // the residual rows come from memory.
     __shared__ __align__(16) float s_gain[(NORM && KEEP) ? GV_WARPS : 1][(NORM && KEEP) ? GV_UNROLL * 64 : 4];
+    static_assert(!KEEP || NT * GV_UNROLL <= 8, "activation registers");
     if (NORM && KEEP) {
         for (int i = lane; i < GV_UNROLL * 16; i += 32) {
             const int u = i >> 4, k = (warp + u * GV_WARPS) * 64 + 4 * (i & 15);
@@ -304,19 +305,25 @@ static int dispatch_gemv(const GemvParams& p, bool norm, cudaStream_t stream) {
                                  p.N != (p.n_q_heads + 2 * p.n_kv_heads) * p.head_dim))
         return NI_ERR_BAD_ARGUMENT;
     const bool one = p.M <= 8;
-    // Activations stay in registers when one unrolled pass covers K (<= 2048) and the batch is one
-    // tile: then a block takes several row tiles, as many as leave about two blocks per SM.
-    const bool keep = one && p.K <= 64 * GV_WARPS * GV_UNROLL;
+    // Activations stay in registers when one unrolled pass covers K (<= 2048): then a block takes
+    // several row tiles, as many as leave about two blocks per SM (one block per SM with two batch
+    // tiles, whose registers allow no more), and reads and normalises the activations once.
+    const bool keep = p.K <= 64 * GV_WARPS * GV_UNROLL;
     int tpb = 1;
     if (keep) {
         const int tiles = (p.N + (rn16 ? 16 : 8) - 1) / (rn16 ? 16 : 8);
-        tpb = (tiles + 2 * 148 - 1) / (2 * 148);
+        const int blocks = (one ? 2 : 1) * 148;
+        tpb = (tiles + blocks - 1) / blocks;
         if (tpb < 1) tpb = 1;
     }
 #define GO(RN, NT, NORM, KEEP) return launch_gemv<RN, NT, NORM, KEEP>(p, tpb, stream)
-    if (keep) {
+    if (keep && one) {
         if (norm) { if (rn16) GO(16, 1, true, true); else GO(8, 1, true, true); }
         else { if (rn16) GO(16, 1, false, true); else GO(8, 1, false, true); }
+    }
+    if (keep) {
+        if (norm) { if (rn16) GO(16, 2, true, true); else GO(8, 2, true, true); }
+        else { if (rn16) GO(16, 2, false, true); else GO(8, 2, false, true); }
     }
     if (norm) {
         if (rn16) { if (one) GO(16, 1, true, false); else GO(16, 2, true, false); }

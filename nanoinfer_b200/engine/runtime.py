@@ -69,7 +69,7 @@ class Runtime:
     def skinny(self, n_rows: int, k: int) -> bool:
         """True if a product of n_rows activations with inner size k goes to the package's own
         bandwidth kernel (and so may carry fused prologues and epilogues)."""
-        return self.dtype == torch.bfloat16 and 0 < n_rows <= ops.GEMV_MAX_ROWS and k % 8 == 0
+        return self.dtype == torch.bfloat16 and 0 < n_rows <= ops.SKINNY_ROWS and k % 8 == 0
 
     def tensor_core_gemm(self, n_rows: int, k: int) -> bool:
         """True if a product with this many rows goes to the package's tcgen05 kernel (where
