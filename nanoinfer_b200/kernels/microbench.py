@@ -1,6 +1,7 @@
 """Timing of single kernels at given sizes, for tuning and for profiler captures.
 
     python -m nanoinfer_b200.kernels.microbench gemv --m 8 --n 16384 --k 2048 --mode swiglu --norm
+    python -m nanoinfer_b200.kernels.microbench gemm_swap --m 64 --n 16384 --k 2048 --mode swiglu
     python -m nanoinfer_b200.kernels.microbench attention_decode --batch 8 --context 3072
     python -m nanoinfer_b200.kernels.microbench attention_prefill --tokens 2048 --kernel tc
 
@@ -84,6 +85,31 @@ def gemm(args) -> None:
           f"(library product, plain store: {us_lib:.1f} us, {flops / us_lib / 1e6:.0f} TFLOP/s)")
 
 
+def gemm_swap(args) -> None:
+    """The swapped-operand tensor-core product (9..128 rows) against the library product; weights
+    cycle through copies larger than L2."""
+    m, n, k = args.m, args.n, args.k
+    w_bytes = n * k * 2
+    copies = max(2, min(64, -(-2 * L2_BYTES // w_bytes)))
+    g = torch.Generator(device=DEV).manual_seed(0)
+    ws = [(torch.randn(n, k, device=DEV, generator=g) * 0.02).to(torch.bfloat16) for _ in range(copies)]
+    x = torch.randn(m, k, device=DEV, generator=g).to(torch.bfloat16)
+    mode = {"bf16": ops.STORE_BF16, "f32": ops.STORE_F32, "add": ops.ADD_F32, "swiglu": ops.SWIGLU_BF16}[args.mode]
+    if mode == ops.SWIGLU_BF16:
+        out = torch.empty(m, n // 2, dtype=torch.bfloat16, device=DEV)
+    else:
+        out = torch.zeros(m, n, dtype=torch.bfloat16 if mode == ops.STORE_BF16 else torch.float32, device=DEV)
+    need = ops.gemm_swap_scratch(m, n, k)
+    scratch = torch.empty(max(need, 1), dtype=torch.float32, device=DEV)
+    tickets = torch.zeros(-(-n // 128), dtype=torch.int32, device=DEV)
+    us = _time([lambda w=w: ops.gemm_swap_tc(x, w, out, mode, scratch, tickets) for w in ws], args.iters)
+    ops.check_device_errors()
+    ref = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    us_lib = _time([lambda w=w: torch.matmul(x, w.t(), out=ref) for w in ws], args.iters)
+    print(f"gemm_swap m={m} n={n} k={k} mode={args.mode}: {us:.2f} us, {w_bytes / us / 1e3:.0f} GB/s of weights "
+          f"(library product, plain store: {us_lib:.2f} us, {w_bytes / us_lib / 1e3:.0f} GB/s; {copies} weight copies in turn)")
+
+
 def attention_decode(args) -> None:
     b, ctx, hq, hkv, hd, page = args.batch, args.context, args.q_heads, args.kv_heads, args.head_dim, args.page
     pages_per_seq = -(-ctx // page)
@@ -149,6 +175,12 @@ def main() -> None:
     p.add_argument("--k", type=int, default=2048)
     p.add_argument("--mode", default="bf16", choices=["bf16", "f32", "add", "swiglu"])
     p.set_defaults(fn=gemm)
+    p = sub.add_parser("gemm_swap")
+    p.add_argument("--m", type=int, default=64)
+    p.add_argument("--n", type=int, default=16384)
+    p.add_argument("--k", type=int, default=2048)
+    p.add_argument("--mode", default="bf16", choices=["bf16", "f32", "add", "swiglu"])
+    p.set_defaults(fn=gemm_swap)
     for name, fn in (("attention_decode", attention_decode), ("attention_prefill", attention_prefill)):
         p = sub.add_parser(name)
         p.add_argument("--batch", type=int, default=8)

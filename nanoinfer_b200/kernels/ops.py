@@ -55,6 +55,11 @@ _SIGNATURES = {
         "ni_attention_prefill_tc": [_P, _P, _P, _P, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P],
         "ni_attention_prefill_tc_supports": [_I, _I, _I, _I],
     },
+    "gemm_swap_tc": {
+        "ni_gemm_swap_tc": [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+        "ni_gemm_swap_tc_splits": [_I, _I, _I],
+        "ni_gemm_swap_tc_scratch": [_I, _I, _I],
+    },
     "gemm_tc": {
         "ni_gemm_tc": [_P, _P, _P, _I, _I, _I, _I, _P, _P],
     },
@@ -392,7 +397,7 @@ def check_device_errors(device=None) -> None:
         if code:
             w.zero_()
             raise KernelError(f"a kernel on {dev} gave up waiting (code {code}: 1 = loader, 2 = MMA issuer, "
-                              f"3 = epilogue of the tensor-core product; 11 = loader, 12 = MMA issuer, "
+                              f"3 = epilogue of the tensor-core product; 21-23 the same of the swapped-operand product; 11 = loader, 12 = MMA issuer, "
                               f"13 = softmax of the tensor-core prefill attention)")
 
 
@@ -415,6 +420,55 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, mode: int) -> N
             raise KernelError(f"gemm_tc: out must be {want} [M, N]")
     _check(load("gemm_tc").ni_gemm_tc(_dev(a, "a", torch.bfloat16), _dev(b, "b", torch.bfloat16), _dev(out, "out"),
                                       m, n, k, mode, _error_word(a.device).data_ptr(), _stream()), "gemm_tc")
+
+
+ROPE_KV = 4                 # gemm_swap_tc: rotary encoding + paged K/V write of a fused QKV projection
+SWAP_MAX_ROWS = 128         # most activation rows of the swapped-operand tensor-core product
+
+
+def gemm_swap_scratch(m: int, n: int, k: int) -> int:
+    """FP32 words of scratch that gemm_swap_tc needs for this product (0: K is not split)."""
+    f = load("gemm_swap_tc").ni_gemm_swap_tc_scratch
+    f.restype = ctypes.c_longlong
+    return int(f(m, n, k))
+
+
+def gemm_swap_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, scratch=None, tickets=None,
+                 rope=None) -> None:
+    """out = x[M, K] . w[N, K]^T for up to SWAP_MAX_ROWS rows on the tcgen05 tensor cores with the
+    weights on the tile's 128 lanes (bfloat16 in, FP32 accumulate).  mode: STORE_BF16 / STORE_F32 /
+    ADD_F32 / SWIGLU_BF16 as in gemv_bf16, or ROPE_KV with ``rope`` = (positions, seq_of_token,
+    block_table, inv_freq, k_pages, v_pages, n_q_heads, n_kv_heads, head_dim, rotary_dim, page_size)
+    and out = q [M, Hq * hd].  ``scratch`` (FP32, gemm_swap_scratch words) and ``tickets`` (int32
+    zeros, one per 128 weight rows; left zero) are needed when K is split."""
+    m, k = x.shape
+    n = w.shape[0]
+    if m > SWAP_MAX_ROWS or k % 8:
+        raise KernelError(f"gemm_swap_tc: takes at most {SWAP_MAX_ROWS} rows and K a multiple of 8 (M={m}, K={k})")
+    if w.shape[1] != k:
+        raise KernelError("gemm_swap_tc: inner sizes differ")
+    need = gemm_swap_scratch(m, n, k)
+    if need and (scratch is None or tickets is None or scratch.numel() < need or tickets.numel() < -(-n // 128)):
+        raise KernelError("gemm_swap_tc: scratch or tickets missing or too small")
+    if mode == ROPE_KV:
+        pos, seq, table, inv_freq, kp, vp, nq, nkv, hd, rot, page = rope
+        extra = (_dev(pos, "positions", torch.int32), _dev(seq, "seq_of_token", torch.int32),
+                 _dev(table, "block_table", torch.int32), table.shape[1], _dev(inv_freq, "inv_freq", torch.float32),
+                 _dev(kp, "k_pages", torch.bfloat16) if kp is not None else None,
+                 _dev(vp, "v_pages", torch.bfloat16) if vp is not None else None, nq, nkv, hd, rot, page)
+        if out.shape != (m, nq * hd) or out.dtype != torch.bfloat16:
+            raise KernelError("gemm_swap_tc: with ROPE_KV out is q, bfloat16 [M, Hq * hd]")
+    else:
+        extra = (None, None, None, 0, None, None, None, 0, 0, 0, 0, 0)
+        want = (m, n // 2) if mode == SWIGLU_BF16 else (m, n)
+        dt = torch.float32 if mode in (STORE_F32, ADD_F32) else torch.bfloat16
+        if tuple(out.shape) != want or out.dtype != dt:
+            raise KernelError(f"gemm_swap_tc: out must be {dt} {list(want)}")
+    _check(load("gemm_swap_tc").ni_gemm_swap_tc(
+        _dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16), _dev(out, "out"), m, n, k, mode,
+        _dev(scratch, "scratch", torch.float32) if need else None,
+        _dev(tickets, "tickets", torch.int32) if need else None, *extra,
+        _error_word(x.device).data_ptr(), _stream()), "gemm_swap_tc")
 
 
 DECODE_HEAD_DIMS = (64, 128)

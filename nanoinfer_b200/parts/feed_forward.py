@@ -49,6 +49,8 @@ class SwiGLU(Part):
             ops.gemv_bf16(x, self.w_gate_up, act, ops.SWIGLU_BF16)     # activation in the epilogue
         elif self.blocked and rt.tensor_core_gemm(n, self.hidden_size):
             ops.gemm_tc(x, self.w_gate_up, act, ops.SWIGLU_BF16)       # tcgen05 product, activation fused
+        elif self.blocked and rt.swapped_gemm(n, 2 * self.inter, self.hidden_size, fused=True):
+            ops.gemm_swap_tc(x, self.w_gate_up, act, ops.SWIGLU_BF16)  # weights on the tile's lanes, activation fused
         else:
             gate_up = rt.linear(x, self.w_gate_up)
             ops.swiglu(gate_up, act, blocked=self.blocked)

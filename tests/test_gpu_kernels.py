@@ -475,3 +475,87 @@ def test_gemm_tc(m, n, k, mode):
         ref = ((w4[:, :, 0] / (1 + torch.exp(-w4[:, :, 0]))) * w4[:, :, 1]).reshape(m, n // 2)
         torch.testing.assert_close(out.cpu().double(), ref, rtol=4e-3, atol=1e-3)
     ops.check_device_errors()
+
+
+def _swap_scratch(ops, m, n, k):
+    need = ops.gemm_swap_scratch(m, n, k)
+    scratch = torch.full((max(need, 1),), float("nan"), dtype=torch.float32, device=DEV)
+    tickets = torch.zeros(-(-n // 128), dtype=torch.int32, device=DEV)
+    return scratch, tickets
+
+
+@pytest.mark.parametrize("mode", ["bf16", "f32", "add", "swiglu"])
+@pytest.mark.parametrize("m,n,k", [(9, 256, 64), (64, 16384, 2048), (33, 2048, 2048), (100, 1008, 200), (128, 2048, 8192),
+                                   (17, 4800, 2056), (1, 48, 64), (32, 128, 640)])
+def test_gemm_swap_tc(m, n, k, mode):
+    """The swapped-operand tcgen05 product (weights on the tile's lanes, the batch on its columns)
+    against a float64 product: every batch-tile width, ragged N and K, K cut into slices that a
+    ticket combines, every epilogue; the second launch finds the tickets at zero again."""
+    from nanoinfer_b200.kernels import ops
+    x = _randn(m, k, dtype=torch.bfloat16, seed=1)
+    w = _randn(n, k, dtype=torch.bfloat16, seed=2, scale=0.05)
+    want = x.cpu().double() @ w.cpu().double().t()
+    tol = 1e-5 * math.sqrt(k)
+    scratch, tickets = _swap_scratch(ops, m, n, k)
+    for _ in range(2):
+        if mode == "bf16":
+            out = torch.full((m, n), 7.0, dtype=torch.bfloat16, device=DEV)
+            ops.gemm_swap_tc(x, w, out, ops.STORE_BF16, scratch, tickets)
+            torch.testing.assert_close(out.cpu().double(), want, rtol=4e-3, atol=1e-3)
+        elif mode == "f32":
+            out = torch.full((m, n), 7.0, dtype=torch.float32, device=DEV)
+            ops.gemm_swap_tc(x, w, out, ops.STORE_F32, scratch, tickets)
+            torch.testing.assert_close(out.cpu().double(), want, rtol=1e-5, atol=tol)
+        elif mode == "add":
+            h = _randn(m, n, seed=3)
+            out = h.clone()
+            ops.gemm_swap_tc(x, w, out, ops.ADD_F32, scratch, tickets)
+            torch.testing.assert_close(out.cpu().double(), h.cpu().double() + want, rtol=1e-5, atol=tol)
+        else:
+            out = torch.full((m, n // 2), 7.0, dtype=torch.bfloat16, device=DEV)
+            ops.gemm_swap_tc(x, w, out, ops.SWIGLU_BF16, scratch, tickets)
+            w4 = want.view(m, n // 16, 2, 8)
+            ref = ((w4[:, :, 0] / (1 + torch.exp(-w4[:, :, 0]))) * w4[:, :, 1]).reshape(m, n // 2)
+            torch.testing.assert_close(out.cpu().double(), ref, rtol=4e-3, atol=1e-3)
+        ops.check_device_errors()
+        assert torch.all(tickets == 0)
+
+
+@pytest.mark.parametrize("n_q,n_kv,hd,rot,page,d,m", [(4, 2, 32, 32, 16, 128, 9), (32, 8, 64, 64, 16, 2048, 64),
+                                                      (6, 3, 48, 32, 8, 200, 33), (8, 1, 128, 128, 32, 512, 128)])
+def test_gemm_swap_tc_qkv_rope(n_q, n_kv, hd, rot, page, d, m):
+    """Fused QKV projection + adjacent-pair rotation + paged K/V write for 9..128 rows."""
+    from nanoinfer_b200.kernels import ops
+    g = torch.Generator().manual_seed(hd + m)
+    n = (n_q + 2 * n_kv) * hd
+    w = (torch.randn(n, d, generator=g) * 0.06).to(torch.bfloat16)
+    x = torch.randn(m, d, generator=g).to(torch.bfloat16)
+    positions = torch.randint(0, 128, (m,), generator=g).int()
+    seq_of = torch.arange(m, dtype=torch.int32)
+    width = 128 // page
+    n_pages = m * width + 3
+    table = torch.randperm(n_pages, generator=g)[:m * width].view(m, width).int()
+    inv_freq = plain.rope_inv_freq(rot, 10000.0, None)
+    q_out = torch.empty(m, n_q * hd, dtype=torch.bfloat16, device=DEV)
+    k_pages = torch.full((n_pages, n_kv, page, hd), 7.0, dtype=torch.bfloat16, device=DEV)
+    v_pages = torch.full((n_pages, n_kv, page, hd), 7.0, dtype=torch.bfloat16, device=DEV)
+    scratch, tickets = _swap_scratch(ops, m, n, d)
+    ops.gemm_swap_tc(x.to(DEV), w.to(DEV), q_out, ops.ROPE_KV, scratch, tickets,
+                     rope=(positions.to(DEV), seq_of.to(DEV), table.to(DEV), inv_freq.to(DEV), k_pages, v_pages,
+                           n_q, n_kv, hd, rot, page))
+    ops.check_device_errors()
+    qkv = x.float() @ w.float().t()
+    q = plain.rope(qkv[:, :n_q * hd].view(m, n_q, hd), positions, inv_freq, "interleaved")
+    k = plain.rope(qkv[:, n_q * hd:(n_q + n_kv) * hd].view(m, n_kv, hd), positions, inv_freq, "interleaved")
+    v = qkv[:, (n_q + n_kv) * hd:].view(m, n_kv, hd)
+    tol = 6e-3 * qkv.abs().max().item()
+    assert (q_out.cpu().float().view(m, n_q, hd) - q).abs().max().item() <= tol
+    kp, vp = k_pages.cpu().float(), v_pages.cpu().float()
+    touched = torch.zeros(n_pages, page, dtype=torch.bool)
+    for t in range(m):
+        p, slot = table[t, positions[t] // page], positions[t] % page
+        assert (kp[p, :, slot] - k[t]).abs().max().item() <= tol
+        assert (vp[p, :, slot] - v[t]).abs().max().item() <= tol
+        touched[p, slot] = True
+    assert torch.all(kp.permute(0, 2, 1, 3)[~touched] == 7.0) and torch.all(vp.permute(0, 2, 1, 3)[~touched] == 7.0)
+    assert torch.all(tickets == 0)
