@@ -76,12 +76,12 @@ def gemm(args) -> None:
         out = torch.empty(m, n // 2, dtype=torch.bfloat16, device=DEV)
     else:
         out = torch.zeros(m, n, dtype=torch.bfloat16 if mode == ops.STORE_BF16 else torch.float32, device=DEV)
-    us = _time([lambda: ops.gemm_tc(a, b, out, mode)], args.iters)
+    us = _time([lambda: ops.gemm_tc(a, b, out, mode, kernel=args.kernel, accumulators=args.accumulators)], args.iters)
     ops.check_device_errors()
     ref = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
     us_lib = _time([lambda: torch.matmul(a, b.t(), out=ref)], args.iters)
     flops = 2.0 * m * n * k
-    print(f"gemm m={m} n={n} k={k} mode={args.mode}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s "
+    print(f"gemm m={m} n={n} k={k} mode={args.mode} kernel={args.kernel or 'default'}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s "
           f"(library product, plain store: {us_lib:.1f} us, {flops / us_lib / 1e6:.0f} TFLOP/s)")
 
 
@@ -174,6 +174,8 @@ def main() -> None:
     p.add_argument("--n", type=int, default=16384)
     p.add_argument("--k", type=int, default=2048)
     p.add_argument("--mode", default="bf16", choices=["bf16", "f32", "add", "swiglu"])
+    p.add_argument("--kernel", default=None, choices=["single", "pair"])
+    p.add_argument("--accumulators", type=int, default=2)
     p.set_defaults(fn=gemm)
     p = sub.add_parser("gemm_swap")
     p.add_argument("--m", type=int, default=64)

@@ -442,12 +442,13 @@ def test_gemv_qkv_rope(n_q, n_kv, hd, rot, page, d, with_norm):
     assert torch.all(kp.permute(0, 2, 1, 3)[~touched] == 7.0) and torch.all(vp.permute(0, 2, 1, 3)[~touched] == 7.0)
 
 
+@pytest.mark.parametrize("kernel", ["single", "pair"])
 @pytest.mark.parametrize("mode", ["bf16", "f32", "add", "swiglu"])
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (2048, 512, 2048), (200, 336, 200), (17, 4800, 2048), (300, 128, 8200),
-                                   (1, 48, 64), (130, 1000, 120)])
-def test_gemm_tc(m, n, k, mode):
+                                   (1, 48, 64), (130, 1000, 120), (2048, 8192, 512)])
+def test_gemm_tc(m, n, k, mode, kernel):
     """The tcgen05/TMEM product against a float64 product: full tiles, ragged edges in M, N and
-    K, every epilogue."""
+    K, every epilogue; one SM per tile and two SMs per tile (cta_group::2)."""
     from nanoinfer_b200.kernels import ops
     if mode == "swiglu" and n % 16:
         n = n - n % 16
@@ -457,20 +458,20 @@ def test_gemm_tc(m, n, k, mode):
     tol = 1e-5 * math.sqrt(k)
     if mode == "bf16":
         out = torch.full((m, n), 7.0, dtype=torch.bfloat16, device=DEV)
-        ops.gemm_tc(a, b, out, ops.STORE_BF16)
+        ops.gemm_tc(a, b, out, ops.STORE_BF16, kernel=kernel)
         torch.testing.assert_close(out.cpu().double(), want, rtol=4e-3, atol=1e-3)
     elif mode == "f32":
         out = torch.full((m, n), 7.0, dtype=torch.float32, device=DEV)
-        ops.gemm_tc(a, b, out, ops.STORE_F32)
+        ops.gemm_tc(a, b, out, ops.STORE_F32, kernel=kernel)
         torch.testing.assert_close(out.cpu().double(), want, rtol=1e-5, atol=tol)
     elif mode == "add":
         h = _randn(m, n, seed=3)
         out = h.clone()
-        ops.gemm_tc(a, b, out, ops.ADD_F32)
+        ops.gemm_tc(a, b, out, ops.ADD_F32, kernel=kernel)
         torch.testing.assert_close(out.cpu().double(), h.cpu().double() + want, rtol=1e-5, atol=tol)
     else:
         out = torch.full((m, n // 2), 7.0, dtype=torch.bfloat16, device=DEV)
-        ops.gemm_tc(a, b, out, ops.SWIGLU_BF16)
+        ops.gemm_tc(a, b, out, ops.SWIGLU_BF16, kernel=kernel)
         w4 = want.view(m, n // 16, 2, 8)
         ref = ((w4[:, :, 0] / (1 + torch.exp(-w4[:, :, 0]))) * w4[:, :, 1]).reshape(m, n // 2)
         torch.testing.assert_close(out.cpu().double(), ref, rtol=4e-3, atol=1e-3)
