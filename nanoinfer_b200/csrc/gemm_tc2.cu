@@ -204,17 +204,19 @@ __device__ __forceinline__ void tc_epilogue_row(const TcParams& p, int row, int 
     }
 }
 
-#define TC2_BN 256            // columns of the pair's tile; each block holds TC2_BN / 2 rows of B
 #define TC2_STAGES 6
 
-template <int ACCS>          // accumulators per block: 2 = the epilogue of a tile overlaps the next tile's products
+// BN: columns of the pair's tile (128, 192 or 256; each block holds BN / 2 rows of B): narrower
+// tiles give small products more tiles than there are pairs of SMs.  ACCS: accumulators per block
+// (2: the epilogue of a tile overlaps the next tile's products).
+template <int BN, int ACCS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcParams p) {
-    constexpr int BN = TC2_BN, STAGES = TC2_STAGES;
+    constexpr int STAGES = TC2_STAGES;
     constexpr int A_BYTES = TC_BM * TC_BK * 2;            // this block's rows of A: 16 KB
     constexpr int B_BYTES = (BN / 2) * TC_BK * 2;         // this block's half of B: 16 KB
-    constexpr int ACC_COLS = ACCS * BN;
-    static_assert(ACC_COLS <= 512 && (ACC_COLS & (ACC_COLS - 1)) == 0, "tensor memory columns");
+    constexpr int ACC_COLS = ACCS * BN <= 128 ? 128 : (ACCS * BN <= 256 ? 256 : 512);
+    static_assert(ACCS * BN <= 512 && BN % 32 == 0, "tensor memory columns");
     extern __shared__ uint8_t tc_smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* sA = base;
@@ -375,20 +377,20 @@ static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_
     return r == CUDA_SUCCESS ? NI_OK : NI_ERR_BAD_ARGUMENT;
 }
 
-template <int ACCS>
+template <int BN, int ACCS>
 static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, cudaStream_t stream) {
-    constexpr size_t smem = 1024 + (size_t)TC2_STAGES * (TC_BM * TC_BK * 2 + (TC2_BN / 2) * TC_BK * 2) + 256;
+    constexpr size_t smem = 1024 + (size_t)TC2_STAGES * (TC_BM * TC_BK * 2 + (BN / 2) * TC_BK * 2) + 256;
     static bool configured = false;
     static int n_sms = 0;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel<ACCS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel<BN, ACCS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         int dev = 0;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
         configured = true;
     }
-    const int tiles = ((p.M + 2 * TC_BM - 1) / (2 * TC_BM)) * ((p.N + TC2_BN - 1) / TC2_BN);
+    const int tiles = ((p.M + 2 * TC_BM - 1) / (2 * TC_BM)) * ((p.N + BN - 1) / BN);
     const int pairs = tiles < n_sms / 2 ? tiles : n_sms / 2;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * pairs);
@@ -402,26 +404,37 @@ static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mb, const TcPara
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<ACCS>, ma, mb, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<BN, ACCS>, ma, mb, p);
     return e == cudaSuccess ? NI_OK : (int)e;
 }
 
 // a: bf16 [M, K]; b: bf16 [N, K]; K a multiple of 8; both 16-byte aligned.  mode 0 store bf16 [M, N],
 // 1 store FP32, 2 add into FP32 [M, N], 3 SwiGLU over blocked columns -> bf16 [M, N / 2].
 // error: a device int, zero on entry; non-zero afterwards if a wait inside the kernel ran out.
-// accumulators: 1 or 2 per block.
+// accumulators: 1 or 2 per block.  tile_n: 128, 192 or 256 columns per tile, or 0: as many as give every
+// pair of SMs about two tiles.
 NI_EXPORT int ni_gemm_tc2(const void* a, const void* b, void* out, int M, int N, int K, int mode, int accumulators,
-                          int* error, cudaStream_t stream) {
+                          int tile_n, int* error, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return NI_OK;
     if (K <= 0 || mode < 0 || mode > TC_SWIGLU || error == nullptr) return NI_ERR_BAD_ARGUMENT;
     if (K % 8 || ((uintptr_t)a & 15) || ((uintptr_t)b & 15)) return NI_ERR_UNSUPPORTED_SIZE;
     if (mode == TC_SWIGLU && N % 16) return NI_ERR_UNSUPPORTED_SIZE;
+    if (tile_n == 0) {
+        const long long tiles_m = (M + 2 * TC_BM - 1) / (2 * TC_BM);
+        tile_n = 256;
+        if (tiles_m * ((N + 255) / 256) < 2 * 74) tile_n = 192;
+        if (tiles_m * ((N + 191) / 192) < 2 * 74) tile_n = 128;
+    }
+    if (tile_n != 128 && tile_n != 192 && tile_n != 256) return NI_ERR_BAD_ARGUMENT;
     CUtensorMap ma, mb;
     int rc = make_map(&ma, a, M, K, TC_BM);
     if (rc != NI_OK) return rc;
-    rc = make_map(&mb, b, N, K, TC2_BN / 2);
+    rc = make_map(&mb, b, N, K, tile_n / 2);
     if (rc != NI_OK) return rc;
     TcParams p;
     p.out = out; p.M = M; p.N = N; p.K = K; p.mode = mode; p.error = error;
-    return accumulators == 1 ? launch_tc2<1>(ma, mb, p, stream) : launch_tc2<2>(ma, mb, p, stream);
+    const bool one = accumulators == 1;
+    if (tile_n == 128) return one ? launch_tc2<128, 1>(ma, mb, p, stream) : launch_tc2<128, 2>(ma, mb, p, stream);
+    if (tile_n == 192) return one ? launch_tc2<192, 1>(ma, mb, p, stream) : launch_tc2<192, 2>(ma, mb, p, stream);
+    return one ? launch_tc2<256, 1>(ma, mb, p, stream) : launch_tc2<256, 2>(ma, mb, p, stream);
 }

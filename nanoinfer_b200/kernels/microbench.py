@@ -76,7 +76,7 @@ def gemm(args) -> None:
         out = torch.empty(m, n // 2, dtype=torch.bfloat16, device=DEV)
     else:
         out = torch.zeros(m, n, dtype=torch.bfloat16 if mode == ops.STORE_BF16 else torch.float32, device=DEV)
-    us = _time([lambda: ops.gemm_tc(a, b, out, mode, kernel=args.kernel, accumulators=args.accumulators)], args.iters)
+    us = _time([lambda: ops.gemm_tc(a, b, out, mode, kernel=args.kernel, accumulators=args.accumulators, tile_n=args.tile_n)], args.iters)
     ops.check_device_errors()
     ref = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
     us_lib = _time([lambda: torch.matmul(a, b.t(), out=ref)], args.iters)
@@ -176,6 +176,7 @@ def main() -> None:
     p.add_argument("--mode", default="bf16", choices=["bf16", "f32", "add", "swiglu"])
     p.add_argument("--kernel", default=None, choices=["single", "pair"])
     p.add_argument("--accumulators", type=int, default=2)
+    p.add_argument("--tile-n", type=int, default=0, help="pair kernel: 128, 192 or 256 columns per tile (0: by size)")
     p.set_defaults(fn=gemm)
     p = sub.add_parser("gemm_swap")
     p.add_argument("--m", type=int, default=64)

@@ -61,7 +61,7 @@ _SIGNATURES = {
         "ni_gemm_swap_tc_scratch": [_I, _I, _I],
     },
     "gemm_tc2": {
-        "ni_gemm_tc2": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+        "ni_gemm_tc2": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     },
     "gemm_tc": {
         "ni_gemm_tc": [_P, _P, _P, _I, _I, _I, _I, _P, _P],
@@ -405,12 +405,12 @@ def check_device_errors(device=None) -> None:
 
 
 def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, mode: int, kernel: Optional[str] = None,
-            accumulators: int = 2) -> None:
+            accumulators: int = 2, tile_n: int = 0) -> None:
     """out = a[M, K] . b[N, K]^T on the tcgen05 tensor cores (bfloat16 in, FP32 accumulate).
     mode STORE_BF16 / STORE_F32 / ADD_F32 as in gemv_bf16; SWIGLU_BF16: b's rows in blocks of 8
     gate + 8 up rows, out bf16 [M, N/2].  ``kernel``: "pair" = two SMs per 256 x 256 tile
-    (gemm_tc2.cu), "single" = one SM per 128 x 256 tile (gemm_tc.cu); default: the pair kernel
-    from 256 rows and 256 columns on."""
+    (gemm_tc2.cu; ``tile_n`` 128 / 192 / 256 columns per tile, 0 = chosen by size), "single" = one SM per
+    128 x 256 tile (gemm_tc.cu); default: the pair kernel from 256 rows and 256 columns on."""
     m, k = a.shape
     n = b.shape[0]
     if b.shape[1] != k:
@@ -428,7 +428,7 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, mode: int, kern
         kernel = "pair" if (GEMM_PAIR_DEFAULT and m >= 256 and n >= 256) else "single"
     if kernel == "pair":
         _check(load("gemm_tc2").ni_gemm_tc2(_dev(a, "a", torch.bfloat16), _dev(b, "b", torch.bfloat16), _dev(out, "out"),
-                                            m, n, k, mode, accumulators, _error_word(a.device).data_ptr(), _stream()),
+                                            m, n, k, mode, accumulators, tile_n, _error_word(a.device).data_ptr(), _stream()),
                "gemm_tc2")
         return
     _check(load("gemm_tc").ni_gemm_tc(_dev(a, "a", torch.bfloat16), _dev(b, "b", torch.bfloat16), _dev(out, "out"),

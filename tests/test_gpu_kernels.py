@@ -445,7 +445,7 @@ def test_gemv_qkv_rope(n_q, n_kv, hd, rot, page, d, with_norm):
 @pytest.mark.parametrize("kernel", ["single", "pair"])
 @pytest.mark.parametrize("mode", ["bf16", "f32", "add", "swiglu"])
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (2048, 512, 2048), (200, 336, 200), (17, 4800, 2048), (300, 128, 8200),
-                                   (1, 48, 64), (130, 1000, 120), (2048, 8192, 512)])
+                                   (1, 48, 64), (130, 1000, 120), (2048, 8192, 512), (2048, 4608, 128)])
 def test_gemm_tc(m, n, k, mode, kernel):
     """The tcgen05/TMEM product against a float64 product: full tiles, ragged edges in M, N and
     K, every epilogue; one SM per tile and two SMs per tile (cta_group::2)."""
