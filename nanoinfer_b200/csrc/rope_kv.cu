@@ -110,6 +110,9 @@ template <> struct Chunk8<float> {
     }
 };
 
+// Adjacent-pair rotation with 16-byte accesses.  A block takes one token at a time: the token's
+// rotary_dim / 2 (cos, sin) pairs are computed once into shared memory (they are the same for all
+// of its heads) and its page is looked up once; then every thread rotates 8-element chunks.
 template <typename T>
 __global__ void rope_kv_write_vec_kernel(const T* __restrict__ qkv, T* __restrict__ q_out,
                                          T* __restrict__ k_pages, T* __restrict__ v_pages,
@@ -119,44 +122,63 @@ __global__ void rope_kv_write_vec_kernel(const T* __restrict__ qkv, T* __restric
                                          const float* __restrict__ inv_freq, int n_tokens, int n_q_heads,
                                          int n_kv_heads, int head_dim, int rotary_dim, int page_size,
                                          int write_cache) {
+    extern __shared__ float rope_cs[];                 // [rotary_dim / 2][cos, sin]
     const int chunks_per_head = head_dim >> 3;
     const int heads = n_q_heads + 2 * n_kv_heads;
-    const long long total = (long long)n_tokens * heads * chunks_per_head;
-    long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long stride = (long long)gridDim.x * blockDim.x;
-    for (; idx < total; idx += stride) {
-        const int c = (int)(idx % chunks_per_head);
-        const long long th = idx / chunks_per_head;
-        const int head = (int)(th % heads);
-        const int t = (int)(th / heads);
+    const int items = heads * chunks_per_head;
+    for (int t = blockIdx.x; t < n_tokens; t += gridDim.x) {
         const int pos = positions[t];
-        float v[8];
-        Chunk8<T>::load(qkv + ((size_t)t * heads + head) * head_dim + 8 * c, v);
-        if (head < n_q_heads + n_kv_heads) {
+        __syncthreads();                               // the table of the token before is no longer read
+        for (int i = threadIdx.x; i < (rotary_dim >> 1); i += blockDim.x) {
+            float s, cs;
+            sincosf((float)pos * inv_freq[i], &s, &cs);
+            rope_cs[2 * i] = cs;
+            rope_cs[2 * i + 1] = s;
+        }
+        __syncthreads();
+        const int page = write_cache ? block_table[(size_t)seq_of_token[t] * bt_stride + pos / page_size] : 0;
+        const int slot = pos % page_size;
+        // four chunks per thread and pass: all loads are issued before the first store, since what
+        // bounds this kernel is the number of bytes in flight
+        for (int item0 = threadIdx.x; item0 < items; item0 += 4 * blockDim.x) {
+            float v[4][8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int d = 8 * c + 2 * i;
-                if (d < rotary_dim) {
-                    float s, cs;
-                    sincosf((float)pos * inv_freq[d >> 1], &s, &cs);
-                    const float a = v[2 * i], b = v[2 * i + 1];
-                    v[2 * i] = a * cs - b * s;
-                    v[2 * i + 1] = a * s + b * cs;
+            for (int u = 0; u < 4; ++u) {
+                const int item = item0 + u * blockDim.x;
+                if (item < items) {
+                    const int head = item / chunks_per_head, c = item - head * chunks_per_head;
+                    Chunk8<T>::load(qkv + ((size_t)t * heads + head) * head_dim + 8 * c, v[u]);
                 }
             }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int item = item0 + u * blockDim.x;
+                if (item >= items) continue;
+                const int head = item / chunks_per_head, c = item - head * chunks_per_head;
+                if (head < n_q_heads + n_kv_heads) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int d = 8 * c + 2 * i;
+                        if (d < rotary_dim) {
+                            const float cs = rope_cs[d], sn = rope_cs[d + 1];
+                            const float a = v[u][2 * i], b = v[u][2 * i + 1];
+                            v[u][2 * i] = a * cs - b * sn;
+                            v[u][2 * i + 1] = a * sn + b * cs;
+                        }
+                    }
+                }
+                T* dst;
+                if (head < n_q_heads) {
+                    dst = q_out + ((size_t)t * n_q_heads + head) * head_dim + 8 * c;
+                } else {
+                    if (!write_cache) continue;
+                    const bool is_k = head < n_q_heads + n_kv_heads;
+                    const int kvh = is_k ? head - n_q_heads : head - n_q_heads - n_kv_heads;
+                    dst = (is_k ? k_pages : v_pages) + (((size_t)page * n_kv_heads + kvh) * page_size + slot) * head_dim + 8 * c;
+                }
+                Chunk8<T>::store(dst, v[u]);
+            }
         }
-        T* dst;
-        if (head < n_q_heads) {
-            dst = q_out + ((size_t)t * n_q_heads + head) * head_dim + 8 * c;
-        } else {
-            if (!write_cache) continue;
-            const int page = block_table[(size_t)seq_of_token[t] * bt_stride + pos / page_size];
-            const bool is_k = head < n_q_heads + n_kv_heads;
-            const int kvh = is_k ? head - n_q_heads : head - n_q_heads - n_kv_heads;
-            dst = (is_k ? k_pages : v_pages) +
-                  (((size_t)page * n_kv_heads + kvh) * page_size + (pos % page_size)) * head_dim + 8 * c;
-        }
-        Chunk8<T>::store(dst, v);
     }
 }
 
@@ -171,11 +193,11 @@ NI_EXPORT int ni_rope_kv_write(const void* qkv, int dtype, void* q_out, void* k_
         n_q_heads <= 0 || n_kv_heads <= 0 || page_size <= 0)
         return NI_ERR_BAD_ARGUMENT;
     if (interleaved && head_dim % 8 == 0) {
-        const long long items = (long long)n_tokens * (n_q_heads + 2 * n_kv_heads) * (head_dim / 8);
-        long long blocks = (items + 255) / 256;
-        if (blocks > 148 * 16) blocks = 148 * 16;
+        const int items = (n_q_heads + 2 * n_kv_heads) * (head_dim / 8);
+        const int threads = items >= 512 ? 256 : (items >= 256 ? 128 : 64);      // about four chunks per thread
+        const int blocks = n_tokens < 148 * 16 ? n_tokens : 148 * 16;
 #define LAUNCHV(T)                                                                                     \
-    rope_kv_write_vec_kernel<T><<<(int)blocks, 256, 0, stream>>>(                                      \
+    rope_kv_write_vec_kernel<T><<<blocks, threads, rotary_dim * sizeof(float), stream>>>(               \
         (const T*)qkv, (T*)q_out, (T*)k_pages, (T*)v_pages, positions, seq_of_token, block_table,     \
         bt_stride, inv_freq, n_tokens, n_q_heads, n_kv_heads, head_dim, rotary_dim, page_size, write_cache)
         if (dtype == NI_DTYPE_F32) LAUNCHV(float);
