@@ -560,3 +560,39 @@ def test_gemm_swap_tc_qkv_rope(n_q, n_kv, hd, rot, page, d, m):
         touched[p, slot] = True
     assert torch.all(kp.permute(0, 2, 1, 3)[~touched] == 7.0) and torch.all(vp.permute(0, 2, 1, 3)[~touched] == 7.0)
     assert torch.all(tickets == 0)
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+def test_attention_kernels_at_a_long_context(hd):
+    """A late portion of a 4,500-token sequence: the prefill kernels walk 36 key tiles per query tile
+    (their stage rings and barrier phases wrap many times), the decode kernel splits 4,500 keys; one
+    key among the first hundred is made to dominate the last query."""
+    from nanoinfer_b200.kernels import ops
+    n_q, n_kv, page = 4, 2, 16
+    lens, spans = [4500], [(4000, 4500)]
+    table, k_pages, v_pages, ks, vs, qs, q, positions, seq_of = _attention_case(lens, spans, n_q, n_kv, hd, page, 3 * hd, (0, 70))
+    scale = 1.0 / math.sqrt(hd)
+    want = plain.attention(qs[0], ks[0], vs[0], scale, None)[4000:4500].reshape(-1, n_q * hd)
+    dev = [t.to(DEV) for t in (q, k_pages, v_pages, table)]
+    cu_q = torch.tensor([0, 500], dtype=torch.int32, device=DEV)
+    kv_len = torch.tensor([4500], dtype=torch.int32, device=DEV)
+    rows = list(range(0, 500, ops.PREFILL_TILE_ROWS))
+    tile_seq = torch.zeros(len(rows), dtype=torch.int32, device=DEV)
+    tile_row0 = torch.tensor(rows, dtype=torch.int32, device=DEV)
+    for kernel in ("tc", "mma"):
+        out = torch.full_like(dev[0], 7.0)
+        ops.attention_prefill(dev[0], dev[1], dev[2], out, tile_seq, tile_row0, len(rows), cu_q, kv_len, dev[3],
+                              n_q, n_kv, hd, page, None, scale, kernel=kernel)
+        ops.check_device_errors()
+        torch.testing.assert_close(out.cpu().float(), want, rtol=8e-3, atol=4e-3)
+        assert out.cpu().float()[499].mean() > 4.0
+    # the last token alone, through the decode kernel
+    n_splits = 12
+    q1 = dev[0][499:500].contiguous()
+    out1 = torch.zeros_like(q1)
+    scratch = torch.empty(n_q * n_splits * (hd + 2), dtype=torch.float32, device=DEV)
+    tickets = torch.zeros(n_kv, dtype=torch.int32, device=DEV)
+    ops.attention_decode(q1, dev[1], dev[2], out1, None, 1, torch.tensor([4499], dtype=torch.int32, device=DEV),
+                         torch.zeros(1, dtype=torch.int32, device=DEV), dev[3], n_q, n_kv, hd, page, None, scale, n_splits,
+                         scratch, tickets)
+    torch.testing.assert_close(out1.cpu().float(), want[499:500], rtol=8e-3, atol=4e-3)
