@@ -38,7 +38,7 @@ LLAMA_3_2_1B = {
     "tie_word_embeddings": True, "hidden_act": "silu",
 }
 FULL_LAYERS = 16
-START_CONTEXT = 2048
+START_CONTEXT = 2048          # tokens each request holds when decoding starts (--context overrides)
 PREFILL_TOKENS = 2048
 BATCHED_TOKENS = 4 * PREFILL_TOKENS     # token budget of one step of the end-to-end run
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
@@ -142,6 +142,7 @@ def run_ours(args):
     pk = peaks()
     vocab = raw["vocab_size"]
     K, W = args.steps, args.warmup
+    START_CONTEXT = args.context
     # spare tokens: in the end-to-end run the first requests start decoding while the last
     # prompts are still being prefilled (one prefill step takes BATCHED_TOKENS of prompt)
     spare = max(16, -(-args.batch * START_CONTEXT // BATCHED_TOKENS) + 8)
@@ -269,6 +270,7 @@ def main():
     ap.add_argument("--steps", type=int, default=2024)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=START_CONTEXT, help="tokens per request when decoding starts")
     ap.add_argument("--layers", type=int, default=FULL_LAYERS)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", dest="points", action="store_false", help="skip the batch 1 and 64 points")
