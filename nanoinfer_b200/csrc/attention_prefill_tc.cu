@@ -2,7 +2,7 @@
 // fifth-generation tensor cores: S = Q K^T and O += P V are tcgen05.mma instructions with their
 // accumulators in tensor memory; Q, K and V tiles come into 128-byte-swizzled shared memory by TMA
 // (one box per cache page and kv head: a page's keys of one head are contiguous); the softmax
-// runs in FP32 on CUDA cores, one thread per query row, between the two products.
+// runs in FP32 on CUDA cores, two threads per query row, between the two products.
 //
 // One block works on 128 query rows of one request for TWO query heads that share a kv head
 // (streams 0 and 1).  Both streams use the same K/V tiles, and while the softmax warps of one
@@ -10,8 +10,9 @@
 //
 //   warp 0      TMA: Q once, then K and V tiles through rings of shared-memory stages
 //   warp 1      issues every MMA and commits it to mbarriers; owns the tensor memory
-//   warps 4-7   softmax of stream 0 (each warp one quarter of the 128 TMEM lanes = rows)
-//   warps 8-11  softmax of stream 1
+//   warps 2-9   softmax of stream 0: two warps per quarter of the 128 TMEM lanes (= rows), each with
+//               half of a tile's columns
+//   warps 10-17 softmax of stream 1
 //
 // Tensor memory (512 columns).  The A operand of P V is read from tensor memory, where the softmax
 // threads leave the probabilities as bfloat16 pairs.  64-wide heads: scores of stream s in columns
@@ -47,7 +48,7 @@
 
 #define AT_BM 128
 #define AT_BN 128
-#define AT_THREADS 384
+#define AT_THREADS 576
 #define AT_RESCALE_STEP 8.0f
 
 
@@ -243,12 +244,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     uint64_t* v_full = k_empty + STAGES;
     uint64_t* v_empty = v_full + STAGES;
     uint64_t* s_full = v_empty + STAGES;                  // [2] scores of a stream are in tensor memory
-    uint64_t* p_full = s_full + 2;                        // [2] its probabilities are (128 arrivals)
+    uint64_t* p_full = s_full + 2;                        // [2] its probabilities are (256 arrivals)
     uint64_t* o_done = p_full + 2;                        // [2] its P V product has finished
-    uint64_t* turn = o_done + 2;                          // [2] stream s may use the exponential unit (128 arrivals)
-    uint64_t* s_free = turn + 2;                          // [2] its scores are in registers (128 arrivals)
+    uint64_t* turn = o_done + 2;                          // [2] stream s may use the exponential unit (256 arrivals)
+    uint64_t* s_free = turn + 2;                          // [2] its scores are in registers (256 arrivals)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    // row maxima (per tile) and row sums (at the end) that the two halves of a row exchange
+    float (*row_max)[2][2][AT_BM] = reinterpret_cast<float (*)[2][2][AT_BM]>(tmem_slot + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -275,8 +278,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             at_mbar_init(&v_full[s], 1); at_mbar_init(&v_empty[s], 1);
         }
         for (int s = 0; s < 2; ++s) {
-            at_mbar_init(&s_full[s], 1); at_mbar_init(&p_full[s], 128); at_mbar_init(&o_done[s], 1);
-            at_mbar_init(&turn[s], 128); at_mbar_init(&s_free[s], 128);
+            at_mbar_init(&s_full[s], 1); at_mbar_init(&p_full[s], 256); at_mbar_init(&o_done[s], 1);
+            at_mbar_init(&turn[s], 256); at_mbar_init(&s_free[s], 256);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -448,16 +451,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             __syncwarp();
         }
-    } else if (warp >= 4) {
-        // ---- softmax of one stream: a thread per query row ----
-        const int s = (warp - 4) >> 2;
-        const int quarter = warp & 3;
+    } else {
+        // ---- softmax of one stream: TWO threads per query row, each with half of a tile's columns
+        // (one warp alone cannot issue a row's 128 exponentials fast enough; the halves exchange
+        // their row maxima through shared memory and meet at a named barrier of their 64 threads) ----
+        const int sw = warp - 2;                            // warps 2..17; any four in a row cover the four lane quarters
+        const int s = sw >> 3;                              // stream
+        const int half = (sw >> 2) & 1;                     // which 64 of a tile's 128 columns
+        const int quarter = warp & 3;                       // which 32 of the 128 rows (= this warp's TMEM lanes)
         const int r = quarter * 32 + lane;
         const int pos = first_pos + r;
+        const int pair_bar = 2 + s * 4 + quarter;           // named barrier of the two warps that share these rows
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        const uint32_t t_s = lane_base + s * AT_BN;
-        const uint32_t t_p = lane_base + P_COL + s * P_STRIDE;
-        const uint32_t t_o = lane_base + O_COL + s * HD;
+        const uint32_t t_s = lane_base + s * AT_BN + 64 * half;
+        const uint32_t t_p = lane_base + P_COL + s * P_STRIDE + 32 * half;
+        const uint32_t t_o = lane_base + O_COL + s * HD + (HD / 2) * half;
         const float sc = p.scale_log2e;
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
@@ -466,15 +474,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // (the collective tensor-memory loads below need the whole warp: decide as one)
             if (!__all_sync(0xffffffffu, at_wait(&s_full[s], par, abort_flag, p.error, AT_ERR_SOFTMAX))) { ok = false; break; }
             at_fence_after();
-            const int kbase = (j_begin + i) * AT_BN;
-            // visible columns of this row: [c_lo, c_hi)
-            const int c_hi = min(AT_BN, pos - kbase + 1);
+            const int kbase = (j_begin + i) * AT_BN + 64 * half;        // key of this thread's column 0
+            // visible columns of this row among its 64: [c_lo, c_hi)
+            const int c_hi = min(64, pos - kbase + 1);
             const int c_lo = p.window > 0 ? max(0, pos - p.window + 1 - kbase) : 0;
-            const bool masked = (kbase + AT_BN - 1 > first_pos) || (p.window > 0 && kbase < last_pos - p.window + 1);
-            // the row's 128 scores, read once
-            uint32_t v[AT_BN];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) at_ld32_async(t_s + 32 * c, v + 32 * c);
+            const int tile_k0 = (j_begin + i) * AT_BN;
+            const bool masked = (tile_k0 + AT_BN - 1 > first_pos) || (p.window > 0 && tile_k0 < last_pos - p.window + 1);
+            // the row's 64 scores of this half, read once
+            uint32_t v[64];
+            at_ld32_async(t_s, v);
+            at_ld32_async(t_s + 32, v + 32);
             at_wait_ld();
             if (!ALIAS) {                                // the score columns may be written again
                 at_fence_before();
@@ -484,34 +493,39 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             float mx = -INFINITY;
             if (masked) {
 #pragma unroll
-                for (int e = 0; e < AT_BN; ++e)
+                for (int e = 0; e < 64; ++e)
                     mx = fmaxf(mx, (e >= c_lo && e < c_hi) ? __uint_as_float(v[e]) : -INFINITY);
             } else {
                 float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                for (int e = 0; e < AT_BN; e += 8) {
+                for (int e = 0; e < 64; e += 8) {
 #pragma unroll
                     for (int u = 0; u < 4; ++u)
                         m4[u] = at_max3(m4[u], __uint_as_float(v[e + 2 * u]), __uint_as_float(v[e + 2 * u + 1]));
                 }
                 mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
             }
+            // the other half's maximum of the same row (buffers alternate by tile, so a value is
+            // never overwritten before its reader has passed the next barrier)
+            row_max[par][s][half][r] = mx;
+            asm volatile("bar.sync %0, 64;\n" ::"r"(pair_bar) : "memory");
+            mx = fmaxf(mx, row_max[par][s][half ^ 1][r]);
             mx *= sc;                                    // sc > 0
-            const bool raise = mx > m_used + AT_RESCALE_STEP || (i == 0 && mx > -INFINITY);
+            const bool raise = mx > m_used + AT_RESCALE_STEP || (m_used == -INFINITY && mx > -INFINITY);
             float alpha = 1.0f;
             if (raise) {
-                alpha = at_exp2(m_used - mx);            // 0 on the first tile
+                alpha = at_exp2(m_used - mx);            // 0 while nothing has been seen
                 m_used = mx;
                 l *= alpha;
             }
             if (i > 0 && __any_sync(0xffffffffu, raise)) {
-                // the accumulator of the rows whose maximum rose is scaled down; P V of the tile
-                // before this one must have finished
+                // the accumulator of the rows whose maximum rose is scaled down (each half its own
+                // columns); P V of the tile before this one must have finished
                 if (!__all_sync(0xffffffffu, at_wait(&o_done[s], par ^ 1u, abort_flag, p.error, AT_ERR_SOFTMAX))) { ok = false; break; }
                 at_fence_after();
                 o_waited = true;
 #pragma unroll 1
-                for (int c = 0; c < HD / 32; ++c) {
+                for (int c = 0; c < HD / 64; ++c) {
                     uint32_t o[32];
                     at_ld32(t_o + 32 * c, o);
 #pragma unroll
@@ -519,20 +533,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     at_st32(t_o + 32 * c, o);
                 }
             }
-            // The exponentials of the two streams take turns (0, 1, 0, 1, ...): the unit that
-            // computes them is what a tile's time is made of, so sharing it gains nothing, and
-            // this way one stream's products always run beside the other stream's softmax.
+            // The exponentials of the two streams take turns (0, 1, 0, 1, ...), so that one
+            // stream's products always run beside the other stream's softmax.
             if (s == 1 || i > 0) {
                 const uint32_t turn_par = s == 1 ? par : par ^ 1u;     // stream 1 follows 0's tile i; 0 follows 1's tile i - 1
                 if (!__all_sync(0xffffffffu, at_wait(&turn[s], turn_par, abort_flag, p.error, AT_ERR_SOFTMAX))) { ok = false; break; }
             }
-            // probabilities, written over the scores as bfloat16 pairs (pair e lands in v[e / 2],
-            // whose score has been used by then)
+            // probabilities, written as bfloat16 pairs (pair e lands in v[e / 2], whose score has
+            // been used by then)
             const float m_ref = m_used == -INFINITY ? 0.f : m_used;     // a row that sees nothing yet
             float sum0 = 0.f, sum1 = 0.f;
             if (masked) {       // (two copies of the loop: the common one carries no mask arithmetic)
 #pragma unroll
-                for (int e = 0; e < AT_BN; e += 2) {
+                for (int e = 0; e < 64; e += 2) {
                     float p0 = at_exp2(fmaf(__uint_as_float(v[e]), sc, -m_ref));
                     float p1 = at_exp2(fmaf(__uint_as_float(v[e + 1]), sc, -m_ref));
                     p0 = (e >= c_lo && e < c_hi) ? p0 : 0.f;
@@ -543,7 +556,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
             } else {
 #pragma unroll
-                for (int e = 0; e < AT_BN; e += 2) {
+                for (int e = 0; e < 64; e += 2) {
                     const float p0 = at_exp2(fmaf(__uint_as_float(v[e]), sc, -m_ref));
                     const float p1 = at_exp2(fmaf(__uint_as_float(v[e + 1]), sc, -m_ref));
                     sum0 += p0;
@@ -560,29 +573,33 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 at_fence_after();
             }
             at_st32(t_p, v);
-            at_st32(t_p + 32, v + 32);
             at_wait_st();
             at_fence_before();
             at_mbar_arrive(&p_full[s]);
         }
-        // ---- the finished rows: O / l -> bfloat16 ----
+        // ---- the finished rows: O / l -> bfloat16; the row's sum is the two halves' together ----
+        row_max[0][s][half][r] = l;                        // (the buffer of an even tile; see below)
         if (ok && n_tiles > 0 &&
             __all_sync(0xffffffffu, at_wait(&o_done[s], (uint32_t)(n_tiles - 1) & 1u, abort_flag, p.error, AT_ERR_SOFTMAX))) {
             at_fence_after();
-            const float inv = 1.0f / l;
-            __nv_bfloat16* orow = p.out + (size_t)(q_begin + row0 + r) * ((size_t)p.n_q_heads * HD) + (size_t)(head0 + s) * HD;
+            // Both warps of the pair pass this barrier after their last tile's exchange, whichever
+            // buffer that used; the sums go through buffer 0, written above after the last read of it.
+            asm volatile("bar.sync %0, 64;\n" ::"r"(pair_bar) : "memory");
+            const float inv = 1.0f / (l + row_max[0][s][half ^ 1][r]);
+            __nv_bfloat16* orow = p.out + (size_t)(q_begin + row0 + r) * ((size_t)p.n_q_heads * HD) +
+                                  (size_t)(head0 + s) * HD + (HD / 2) * half;
 #pragma unroll 1
-            for (int c = 0; c < HD / 32; ++c) {
-                uint32_t v[32];
-                at_ld32(t_o + 32 * c, v);
+            for (int c = 0; c < HD / 64; ++c) {
+                uint32_t o[32];
+                at_ld32(t_o + 32 * c, o);
                 if (r < rows) {
 #pragma unroll
                     for (int e = 0; e < 32; e += 8) {
                         uint4 w;
-                        w.x = at_pack(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv);
-                        w.y = at_pack(__uint_as_float(v[e + 2]) * inv, __uint_as_float(v[e + 3]) * inv);
-                        w.z = at_pack(__uint_as_float(v[e + 4]) * inv, __uint_as_float(v[e + 5]) * inv);
-                        w.w = at_pack(__uint_as_float(v[e + 6]) * inv, __uint_as_float(v[e + 7]) * inv);
+                        w.x = at_pack(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv);
+                        w.y = at_pack(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv);
+                        w.z = at_pack(__uint_as_float(o[e + 4]) * inv, __uint_as_float(o[e + 5]) * inv);
+                        w.w = at_pack(__uint_as_float(o[e + 6]) * inv, __uint_as_float(o[e + 7]) * inv);
                         *reinterpret_cast<uint4*>(orow + 32 * c + e) = w;
                     }
                 }
@@ -633,7 +650,7 @@ template <int HD, int STAGES>
 static int launch_at(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AtParams& p,
                      int n_tiles, cudaStream_t stream) {
     constexpr size_t tile = (size_t)(HD / 64) * AT_BN * 128;
-    constexpr size_t smem = 1024 + (2 + 2 * STAGES) * tile + 512;
+    constexpr size_t smem = 1024 + (2 + 2 * STAGES) * tile + 512 + 2 * 2 * 2 * AT_BM * sizeof(float);
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, STAGES>,
