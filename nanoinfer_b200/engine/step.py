@@ -197,6 +197,9 @@ class ModelRunner:
         self.h2d_bytes = 0            # bytes of step metadata copied to the device so far
         self.max_graph_batch = 256
         self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self._portion_graphs: Dict[tuple, "_PortionGraph"] = {}       # by step shape, least recently used first
+        self._portion_seen: Dict[tuple, int] = {}
+        self.max_portion_graphs = 8
         self._pinned: List[torch.Tensor] = []
         self._pinned_events: List[torch.cuda.Event] = []
         self._pinned_next = 0
@@ -255,21 +258,24 @@ class ModelRunner:
             self.caches[r].state[slot].zero_()
         return slot
 
-    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
-        """Take pages for the entries' tokens and upload the step's metadata."""
+    def _layout(self, entries: Sequence[StepEntry], starts: Sequence[int], full_width: bool):
+        """The step's metadata as host arrays, in the order they lie in one buffer: tokens,
+        positions, request of each token, row offsets, kv lengths, slots, logit rows, tokens of
+        short portions, tokens of long portions, attention tiles (request, first row), block
+        tables per group.  ``full_width``: tables at the cache's full width (what a captured
+        graph needs) instead of the width this step uses."""
         cache = self.cache
-        starts = reserve_entries(cache, entries, self.admit)
         q_lens = [len(e.tokens) for e in entries]
         kv_lens = [s + q for s, q in zip(starts, q_lens)]
         slots = [cache.slot(e.request) for e in entries]
-        n_tokens, n_seqs = sum(q_lens), len(entries)
+        n_seqs = len(entries)
         tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
         positions = np.concatenate([np.arange(s, s + q, dtype=np.int32) for s, q in zip(starts, q_lens)])
         seq_of_token = np.repeat(np.arange(n_seqs, dtype=np.int32), q_lens)
         cu_q = np.zeros(n_seqs + 1, dtype=np.int32)
         np.cumsum(q_lens, out=cu_q[1:])
         rows = [int(cu_q[i]) + int(w) for i, e in enumerate(entries) for w in e.want]
-        width = max(1, -(-max(kv_lens) // cache.page_size))
+        width = cache.table_width if full_width else max(1, -(-max(kv_lens) // cache.page_size))
         tables = [cache.table_rows(g, slots, width).reshape(-1) for g in range(len(cache.groups))]
         dec, long_tok, tiles = [], [], []
         for i, ql in enumerate(q_lens):
@@ -279,34 +285,43 @@ class ModelRunner:
                 long_tok.extend(range(int(cu_q[i]), int(cu_q[i]) + ql))
                 tiles.extend((starts[i] + r0, i, r0) for r0 in range(0, ql, ATTENTION_TILE))
         tiles.sort(key=lambda x: -x[0])      # most keys first
-        n_fixed = 7
         parts = [tokens, positions, seq_of_token, cu_q, np.asarray(kv_lens, dtype=np.int32),
                  np.asarray(slots, dtype=np.int32), np.asarray(rows, dtype=np.int32),
                  np.asarray(dec, dtype=np.int32), np.asarray(long_tok, dtype=np.int32),
                  np.asarray([x[1] for x in tiles], dtype=np.int32),
                  np.asarray([x[2] for x in tiles], dtype=np.int32)] + tables
-        n_fixed = 11
         offsets, total = [], 0
         for p in parts:
             offsets.append(total)
             total += _round_up(max(p.size, 1), 4)
-        host = np.zeros(total, dtype=np.int32)
-        for o, p in zip(offsets, parts):
-            host[o:o + p.size] = p
-        dev = self._upload(host)
+        return parts, offsets, total, q_lens, kv_lens, slots, width
+
+    def _context(self, dev: torch.Tensor, parts, offsets, q_lens, kv_lens, slots, width, max_kv_len) -> StepContext:
+        """Views of the uploaded buffer ``dev`` as a StepContext."""
+        n_fixed, n_seqs = 11, len(q_lens)
 
         def view(i):
             return dev[offsets[i]:offsets[i] + parts[i].size]
 
         return StepContext(
-            n_tokens=n_tokens, n_seqs=n_seqs, n_logit_rows=len(rows), tokens=view(0),
+            n_tokens=sum(q_lens), n_seqs=n_seqs, n_logit_rows=parts[6].size, tokens=view(0),
             positions=view(1), seq_of_token=view(2), cu_q=view(3), kv_len=view(4), slots=view(5),
             logit_rows=view(6),
-            block_tables=[view(n_fixed + g).view(n_seqs, width) for g in range(len(cache.groups))],
+            block_tables=[view(n_fixed + g).view(n_seqs, width) for g in range(len(self.cache.groups))],
             host_q_lens=q_lens, host_kv_lens=kv_lens, host_slots=slots, max_q_len=max(q_lens),
-            max_kv_len=max(kv_lens), decode_only=all(q == 1 for q in q_lens), n_dec=len(dec),
-            dec_tokens=view(7), long_tokens=view(8), n_tiles=len(tiles), tile_seq=view(9),
+            max_kv_len=max_kv_len, decode_only=all(q == 1 for q in q_lens), n_dec=parts[7].size,
+            dec_tokens=view(7), long_tokens=view(8), n_tiles=parts[9].size, tile_seq=view(9),
             tile_row0=view(10))
+
+    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+        """Take pages for the entries' tokens and upload the step's metadata."""
+        starts = reserve_entries(self.cache, entries, self.admit)
+        parts, offsets, total, q_lens, kv_lens, slots, width = self._layout(entries, starts, full_width=False)
+        host = np.zeros(total, dtype=np.int32)
+        for o, p in zip(offsets, parts):
+            host[o:o + p.size] = p
+        dev = self._upload(host)
+        return self._context(dev, parts, offsets, q_lens, kv_lens, slots, width, max(kv_lens))
 
     # ---- the step -------------------------------------------------------------------------
     def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -320,6 +335,9 @@ class ModelRunner:
         if self._graphable(entries):
             starts = reserve_entries(self.cache, entries, self.admit)
             logits = self._decode_graph(len(entries)).run(entries, starts, device_tokens)
+        elif self._portion_graphable(entries):
+            starts = reserve_entries(self.cache, entries, self.admit)
+            logits = self._portion_graph(entries).run(entries, starts)
         else:
             ctx = self.build_context(entries)
             logits = self.model.forward(ctx, self.caches)
@@ -334,6 +352,33 @@ class ModelRunner:
         state update is not), can be captured once per batch size and replayed."""
         return (self.use_graphs and not self._state_runs and len(entries) <= self.max_graph_batch
                 and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries))
+
+    # ---- steps with prompt portions as CUDA graphs -------------------------------------------
+    def _portion_graphable(self, entries: Sequence[StepEntry]) -> bool:
+        """A step's launches depend only on how many tokens each entry brings and how many logit
+        rows it wants (everything else is metadata in device memory), so a shape that comes back -
+        the same portion size step after step while a prompt is cut into portions - is captured at
+        its second appearance and replayed from then on."""
+        if not self.use_graphs or self._state_runs or self.rt.dtype != torch.bfloat16:
+            return False
+        sig = tuple((len(e.tokens), len(e.want)) for e in entries)
+        if sig in self._portion_graphs:
+            return True
+        seen = self._portion_seen.get(sig, 0) + 1
+        self._portion_seen[sig] = seen
+        if len(self._portion_seen) > 4096:
+            self._portion_seen.clear()
+        return seen >= 2
+
+    def _portion_graph(self, entries: Sequence[StepEntry]) -> "_PortionGraph":
+        sig = tuple((len(e.tokens), len(e.want)) for e in entries)
+        g = self._portion_graphs.pop(sig, None)
+        if g is None:
+            if len(self._portion_graphs) >= self.max_portion_graphs:       # drop the least recently used
+                self._portion_graphs.pop(next(iter(self._portion_graphs)))
+            g = _PortionGraph(self)
+        self._portion_graphs[sig] = g                                      # most recently used last
+        return g
 
     def can_feed_device_tokens(self, n: int) -> bool:
         """True if a step of ``n`` single tokens can take its tokens from a device tensor."""
@@ -387,6 +432,45 @@ class _quiet_collector:
         if self.was_enabled:
             gc.enable()
         return False
+
+
+class _PortionGraph:
+    """The forward pass of one step shape (tokens and wanted rows per entry), captured once and
+    replayed: metadata in a static device buffer refreshed by one copy from pinned memory, block
+    tables at their full width, split counts chosen for the longest request the cache allows."""
+
+    def __init__(self, runner: ModelRunner) -> None:
+        self.runner = runner
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.host = self.host_np = self.dev = None
+        self.copied = torch.cuda.Event()
+        self.copy_pending = False
+
+    def run(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> torch.Tensor:
+        runner = self.runner
+        parts, offsets, total, q_lens, kv_lens, slots, width = runner._layout(entries, starts, full_width=True)
+        if self.host is None:
+            self.host = torch.zeros(total, dtype=torch.int32, pin_memory=True)
+            self.host_np = self.host.numpy()
+            self.dev = torch.zeros(total, dtype=torch.int32, device=runner.rt.device)
+        if self.copy_pending:
+            self.copied.synchronize()
+        for o, p in zip(offsets, parts):
+            self.host_np[o:o + p.size] = p
+        self.dev.copy_(self.host, non_blocking=True)
+        self.copied.record(ops.current_stream_object())
+        self.copy_pending = True
+        runner.h2d_bytes += total * 4
+        if self.graph is None:
+            ctx = runner._context(self.dev, parts, offsets, q_lens, kv_lens, slots, width, runner.max_tokens_per_request)
+            runner.model.forward(ctx, runner.caches)        # eager first: loads what is missing, sizes the workspaces
+            torch.cuda.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with _quiet_collector(), torch.cuda.graph(self.graph):
+                self.logits = runner.model.forward(ctx, runner.caches)
+        self.graph.replay()
+        return self.logits
 
 
 class _DecodeGraph:

@@ -70,6 +70,47 @@ def test_replay_matches_plain(model_dirs, plain_cache, key, cut, dtype):
     assert runner.cache.num_free_pages(0) == runner.cache.pools[0].num_pages
 
 
+def test_repeated_portion_shapes_are_replayed_from_a_graph(model_dirs, plain_cache):
+    """Portions of one size, step after step (the way a scheduler cuts prompts): from the second
+    appearance the step is a replayed graph; the logits must not notice, also when the same graph
+    serves another request, another position in the cache and a portion beside a decoded token."""
+    key = "d"
+    raw, reqs, want = _plain(plain_cache, key, model_dirs[key])
+    page = SETUP[key][0]
+    steps, s = [], 0
+    items = list(reqs.items())
+    for rid, toks in items[:3]:                       # one request at a time, portions of 24
+        for at in range(0, len(toks), 24):
+            n = min(24, len(toks) - at)
+            steps.append({"step": s, "entries": [{"id": rid, "tokens": toks[at:at + n], "want": list(range(n))}],
+                          "end": [rid] if at + n == len(toks) else []})
+            s += 1
+    (ra, ta), (rb, tb) = items[3], items[4]           # a portion of one beside single tokens of another
+    steps.append({"step": s, "entries": [{"id": rb, "tokens": tb[:40], "want": list(range(40))}], "end": []})
+    s += 1
+    at_a, at_b = 0, 40
+    while at_a < len(ta):
+        n = min(16, len(ta) - at_a)
+        entries = [{"id": ra, "tokens": ta[at_a:at_a + n], "want": list(range(n))}]
+        if at_b < len(tb):
+            entries.append({"id": rb, "tokens": [tb[at_b]], "want": [0]})
+            at_b += 1
+        at_a += n
+        steps.append({"step": s, "entries": entries, "end": [ra] if at_a == len(ta) else []})
+        s += 1
+    while at_b < len(tb):
+        steps.append({"step": s, "entries": [{"id": rb, "tokens": [tb[at_b]], "want": [0]}], "end": []})
+        at_b += 1
+        s += 1
+    steps[-1]["end"] = [rb]
+    runner = _runner(model_dirs[key], "bfloat16", page, steps)
+    got = ru.run_trace(runner, steps)
+    assert len(got) == sum(len(t) for t in reqs.values())
+    ru.compare(got, want, "bfloat16", label="portion graphs")
+    assert any(sig == ((24, 24),) for sig in runner._portion_graphs) and any(len(sig) == 2 for sig in runner._portion_graphs)
+    assert runner.cache.num_free_pages(0) == runner.cache.pools[0].num_pages
+
+
 @pytest.mark.parametrize("key", ["a", "b"])
 def test_cuts_agree_bitwise_in_float32(model_dirs, plain_cache, key):
     """The 32-bit path fixes the order of every sum, so the cut cannot change a single bit."""
