@@ -76,17 +76,23 @@ def test_temperature_generation_follows_the_plain_stream(model_dirs):
     assert eng2.generate(prompts, max_new_tokens=24, sampling_params=sp) == outs
 
 
-def test_few_pages_force_preemption_and_tokens_stay_the_same(model_dirs):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_few_pages_force_preemption_and_tokens_stay_the_same(model_dirs, dtype):
     from nanoinfer_b200 import Engine, SamplingParams
     raw, w = load_plain(model_dirs["a"])
     prompts = [random_tokens(raw["vocab_size"], n, 90 + i) for i, n in enumerate([30, 28, 25])]
-    eng = Engine.from_model_dir(model_dirs["a"], dtype="float32", block_size=16, num_cache_blocks=7,
+    eng = Engine.from_model_dir(model_dirs["a"], dtype=dtype, block_size=16, num_cache_blocks=7,
                                 max_sequences=4, prefill_chunk_size=16)
     eng.stop_token_ids = ()
     outs = eng.generate(prompts, max_new_tokens=40, sampling_params=SamplingParams.greedy())
     assert eng.get_scheduler_stats().num_preemptions >= 1
     for p, o in zip(prompts, outs):
-        assert o == plain.greedy_generate(raw, w, p, 40)
+        assert len(o) == 40
+        if dtype == "float32":
+            assert o == plain.greedy_generate(raw, w, p, 40)
+        else:
+            _check_greedy(raw, w, p, o, dtype)
+    eng.runner.cache.check_consistency()
     assert eng.runner.cache.num_free_pages() == 7
 
 
