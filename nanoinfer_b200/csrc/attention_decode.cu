@@ -304,14 +304,33 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
         const int row = idx / HD, d = idx - row * HD;
         const float* src = scratch + ((size_t)item * n_q_heads + (size_t)kvh * G + row) * n_splits * rec;
-        float mm = -INFINITY;
-        for (int sidx = 0; sidx < n_splits; ++sidx) mm = fmaxf(mm, __ldcg(src + sidx * rec));
-        float acc = 0.f, ll = 0.f;
-        for (int sidx = 0; sidx < n_splits; ++sidx) {
-            const float ms = __ldcg(src + sidx * rec);
-            const float f = ms == -INFINITY ? 0.f : dec_exp2(ms - mm);
-            acc += __ldcg(src + sidx * rec + 2 + d) * f;
-            ll += __ldcg(src + sidx * rec + 1) * f;
+        // Eight splits at a time: their 24 loads are issued together (one after the other, each
+        // followed by its use, they cost a memory round trip per split), then merged in split order.
+        float mm = -INFINITY, acc = 0.f, ll = 0.f;
+        for (int s0 = 0; s0 < n_splits; s0 += 8) {
+            float ms[8], ls[8], as[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const bool ok = s0 + j < n_splits;
+                const float* r = src + (size_t)(ok ? s0 + j : s0) * rec;
+                ms[j] = __ldcg(r);
+                ls[j] = __ldcg(r + 1);
+                as[j] = __ldcg(r + 2 + d);
+                if (!ok) ms[j] = -INFINITY;
+            }
+            float cm = mm;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) cm = fmaxf(cm, ms[j]);
+            const float f0 = mm == -INFINITY ? 0.f : dec_exp2(mm - cm);
+            acc *= f0;
+            ll *= f0;
+            mm = cm;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float f = ms[j] == -INFINITY ? 0.f : dec_exp2(ms[j] - cm);
+                acc += as[j] * f;
+                ll += ls[j] * f;
+            }
         }
         out[((size_t)t_idx * n_q_heads + (size_t)kvh * G + row) * HD + d] = __float2bfloat16_rn(acc / ll);
     }
