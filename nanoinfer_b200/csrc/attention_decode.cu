@@ -128,14 +128,30 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         const int rows = ((seg_keys + 15) / 16) * 16;            // rows that MMAs may touch
         __nv_bfloat16* sK = sKV + (size_t)buf * 2 * SEG * HD;
         __nv_bfloat16* sV = sK + SEG * HD;
-        for (int idx = threadIdx.x; idx < rows * CH; idx += blockDim.x) {
-            const int r = idx / CH, c = idx - r * CH;
+        // Two passes over this thread's chunks: first all page look-ups, then all copies.  In one
+        // pass every copy would wait for its own look-up before the next look-up is even issued.
+        constexpr int ITERS = SEG * CH / (DEC_WARPS * 32);
+        int page[ITERS];
+#pragma unroll
+        for (int it = 0; it < ITERS; ++it) {
+            const int idx = threadIdx.x + it * DEC_WARPS * 32;
+            const int r = idx / CH;
             int key = seg0 + r;
             key = key < k_end ? key : k_end - 1;                 // masked below; never off the table
-            if ((fresh_only && key < first_fresh) || (skip_fresh && key >= first_fresh)) continue;
+            const bool need = idx < rows * CH && !((fresh_only && key < first_fresh) || (skip_fresh && key >= first_fresh));
+            const int pi = page_shift >= 0 ? key >> page_shift : key / page_size;
+            page[it] = need ? table[pi] : -1;
+        }
+#pragma unroll
+        for (int it = 0; it < ITERS; ++it) {
+            if (page[it] < 0) continue;
+            const int idx = threadIdx.x + it * DEC_WARPS * 32;
+            const int r = idx / CH, c = idx - r * CH;
+            int key = seg0 + r;
+            key = key < k_end ? key : k_end - 1;
             const int pi = page_shift >= 0 ? key >> page_shift : key / page_size;
             const int slot = page_shift >= 0 ? key & (page_size - 1) : key - pi * page_size;
-            const size_t off = (((size_t)table[pi] * n_kv_heads + kvh) * page_size + slot) * HD + c * 8;
+            const size_t off = (((size_t)page[it] * n_kv_heads + kvh) * page_size + slot) * HD + c * 8;
             dec_cp_async16(sK + dec_sw<HD>(r, c), k_pages + off);
             dec_cp_async16(sV + dec_sw<HD>(r, c), v_pages + off);
         }

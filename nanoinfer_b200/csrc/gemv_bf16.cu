@@ -123,6 +123,21 @@ __global__ void __launch_bounds__(GV_WARPS * 32, NT == 1 ? 2 : 1) gemv_bf16_kern
         __syncwarp();
     }
 
+    // Fused QKV projection: the position and the cache page of every batch row are step metadata
+    // (not written by the kernel before this one), so they are fetched now; in the epilogue the
+    // chain position -> block-table entry -> address would cost two memory round trips.
+    __shared__ int s_pos[NT * 8], s_page[NT * 8];
+    if (p.mode == GV_ROPE_KV && threadIdx.x < NT * 8) {
+        const int m = threadIdx.x;
+        int pos = 0, page = 0;
+        if (m < M) {
+            pos = p.positions[m];
+            if (p.write_cache) page = p.block_table[(size_t)p.seq_of_token[m] * p.bt_stride + pos / p.page_size];
+        }
+        s_pos[m] = pos;
+        s_page[m] = page;
+    }
+
     uint4 fx[GV_UNROLL][NT][2];     // KEEP: this warp's activations, loaded once
     float ssq[NT];
 #pragma unroll
@@ -253,7 +268,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32, NT == 1 ? 2 : 1) gemv_bf16_kern
                 if (m >= M || n + 1 >= N) continue;
                 const int head = n / hd, d = n - head * hd;
                 float a = tile[m][2 * pr], b = tile[m][2 * pr + 1];
-                const int pos = p.positions[m];
+                const int pos = s_pos[m];
                 if (head < nq + nkv && d < p.rotary_dim) {
                     float sn, cs;
                     sincosf((float)pos * p.inv_freq[d >> 1], &sn, &cs);
@@ -265,7 +280,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32, NT == 1 ? 2 : 1) gemv_bf16_kern
                     dst = reinterpret_cast<__nv_bfloat16*>(p.out) + ((size_t)m * nq + head) * hd + d;
                 } else {
                     if (!p.write_cache) continue;
-                    const int page = p.block_table[(size_t)p.seq_of_token[m] * p.bt_stride + pos / p.page_size];
+                    const int page = s_page[m];
                     const int kvh = head < nq + nkv ? head - nq : head - nq - nkv;
                     __nv_bfloat16* base = head < nq + nkv ? p.k_pages : p.v_pages;
                     dst = base + (((size_t)page * nkv + kvh) * p.page_size + (pos % p.page_size)) * hd + d;
