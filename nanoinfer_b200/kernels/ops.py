@@ -499,14 +499,19 @@ DECODE_FRESH_KEYS = 2
 
 
 def decode_splits(n_items: int, n_kv_heads: int, head_dim: int, max_kv_len: int) -> int:
-    """How many blocks share one (token, kv head): as many as fill the GPU once, each with a few
-    segments of the longest context (a block's fixed costs - table look-ups, merge, ticket -
-    weigh about as much as 400 keys), within a bound on the merge."""
+    """How many blocks share one (token, kv head): as many as fill the GPU once (three blocks of
+    the split kernel are resident per SM; a second wave costs more than longer blocks), each with
+    at least 384 keys of the longest context - 256 when there are few pairs, whose blocks are
+    bound by latency, not by bandwidth - and cut so that no block is left with a short remainder."""
     pairs = max(1, n_items * n_kv_heads)
     if (148 * DECODE_BLOCKS_PER_SM) // pairs <= 1:
         return 1                                  # large batch: one lean block per pair
-    fill = (148 * 3) // pairs                     # split blocks are fatter: 3 per SM
-    return max(1, min(64, fill, -(-max_kv_len // 384)))
+    fill = (148 * 3) // pairs
+    keys_per_split = 256 if pairs <= 16 else 384
+    target = max(1, min(64, fill, -(-max_kv_len // keys_per_split)))
+    chunks = -(-max_kv_len // 64)                 # the kernel cuts a context into 64-key chunks
+    per_split = -(-chunks // target)
+    return max(1, -(-chunks // per_split))
 PREFILL_MAX_HEAD_DIM = 128
 PREFILL_TILE_ROWS = 128      # query rows per block of the flash-style kernel
 
