@@ -144,30 +144,40 @@ __global__ void __launch_bounds__(GV_WARPS * 32, NT == 1 ? 2 : 1) gemv_bf16_kern
     for (int nt = 0; nt < NT; ++nt) ssq[nt] = 0.f;
     bool waited = false;
 
-    for (int ti = 0; ti < tiles_per_block; ++ti) {
-        const int n0 = (blockIdx.x * tiles_per_block + ti) * RN;
-        if (n0 >= N) break;
+    // This warp's weight fragments of one pass over K (GV_UNROLL k-blocks of 64).
+    uint4 fa[GV_UNROLL][2], fb[GV_UNROLL][2];
+    auto load_weights = [&](int n0, int kb) {
         const bool row_a_ok = n0 + g < N;
         const bool row_b_ok = RN == 16 && n0 + g + 8 < N;
         const __nv_bfloat16* wa = p.w + (size_t)(row_a_ok ? n0 + g : 0) * K;
         const __nv_bfloat16* wb = p.w + (size_t)(row_b_ok ? n0 + g + 8 : 0) * K;
+#pragma unroll
+        for (int u = 0; u < GV_UNROLL; ++u) {
+            const int k0 = (kb + u * GV_WARPS) * 64;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int k = k0 + 32 * h + 8 * t;
+                const bool ok = k + 8 <= K;        // K is a multiple of 8
+                fa[u][h] = (ok && row_a_ok) ? ld_stream(wa + k) : zero;
+                fb[u][h] = (RN == 16 && ok && row_b_ok) ? ld_stream(wb + k) : zero;
+            }
+        }
+    };
+    // KEEP: one pass covers K, so a tile is one batch of loads per warp; the batch of the NEXT tile
+    // is issued right after this tile's MMAs (into the same registers), so that it is in flight
+    // while this tile's partial sums go through shared memory and the epilogue.
+    bool prefetched = false;
+
+    for (int ti = 0; ti < tiles_per_block; ++ti) {
+        const int n0 = (blockIdx.x * tiles_per_block + ti) * RN;
+        if (n0 >= N) break;
         float acc[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
 
         for (int kb = warp; kb < n_blocks; kb += GV_WARPS * GV_UNROLL) {
-            uint4 fa[GV_UNROLL][2], fb[GV_UNROLL][2];
-#pragma unroll
-            for (int u = 0; u < GV_UNROLL; ++u) {
-                const int k0 = (kb + u * GV_WARPS) * 64;
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int k = k0 + 32 * h + 8 * t;
-                    const bool ok = k + 8 <= K;        // K is a multiple of 8
-                    fa[u][h] = (ok && row_a_ok) ? ld_stream(wa + k) : zero;
-                    fb[u][h] = (RN == 16 && ok && row_b_ok) ? ld_stream(wb + k) : zero;
-                }
-            }
+            if (!prefetched) load_weights(n0, kb);
+            prefetched = false;
             if (!waited) {
                 // everything above reads weights (and the gain) only; what follows depends on the kernel before
                 pdl_wait();
@@ -202,6 +212,10 @@ __global__ void __launch_bounds__(GV_WARPS * 32, NT == 1 ? 2 : 1) gemv_bf16_kern
                         gv_mma(acc[nt], fa[u][h].x, fb[u][h].x, fa[u][h].y, fb[u][h].y, fx[u][nt][h].x, fx[u][nt][h].y);
                         gv_mma(acc[nt], fa[u][h].z, fb[u][h].z, fa[u][h].w, fb[u][h].w, fx[u][nt][h].z, fx[u][nt][h].w);
                     }
+            if (KEEP && ti + 1 < tiles_per_block && n0 + RN < N) {
+                load_weights(n0 + RN, kb);      // (KEEP: this is the warp's only pass over K)
+                prefetched = true;
+            }
         }
         if (!waited) { pdl_wait(); waited = true; }   // a warp without work must not run ahead either
 
