@@ -383,6 +383,16 @@ static int launch_decode(const void* q, const void* k_pages, const void* v_pages
     return e == cudaSuccess ? NI_OK : (int)e;
 }
 
+static int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
 // Scratch floats needed: n_items * n_q_heads * n_splits * (head_dim + 2); tickets: n_items * n_kv_heads
 // ints, zero before the first launch (the kernel leaves them zero).
 NI_EXPORT int ni_attention_decode_fresh_keys() { return DEC_FRESH_KEYS; }
@@ -401,9 +411,10 @@ NI_EXPORT int ni_attention_decode(const void* q, const void* k_pages, const void
     const float scale_log2e = scale * 1.4426950408889634f;
     switch (head_dim) {
         case 64:
-            // several blocks per (token, kv head): few, fat blocks with 128-key buffers (3 per SM);
-            // one block each (large batches): 64-key buffers, so that 4 fit an SM and 512 blocks are one wave
-            if (n_splits > 1)
+            // while all blocks fit the GPU at 3 per SM: fat blocks with 128-key buffers; beyond that
+            // (large batches, one block per token and kv head): 64-key buffers, so that 4 fit an SM and
+            // 512 blocks are still one wave
+            if (n_splits > 1 || (long long)n_items * n_kv_heads <= 3LL * sm_count())
                 return launch_decode<64, 128>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
                                               block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
                                               scale_log2e, n_splits, scratch, tickets, stream);
