@@ -37,7 +37,19 @@ LLAMA_3_2_1B = {
                      "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
     "tie_word_embeddings": True, "hidden_act": "silu",
 }
-FULL_LAYERS = 16
+_LLAMA3_ROPE = {"rope_type": "llama3", "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                "original_max_position_embeddings": 8192}
+# The sizes of the two larger models of the family, for runs at other kernel sizes (--shape);
+# the default run and the published line are the 1B shape.
+SHAPES = {
+    "llama-3.2-1b": LLAMA_3_2_1B,
+    "llama-3.2-3b": dict(LLAMA_3_2_1B, hidden_size=3072, intermediate_size=8192, num_hidden_layers=28,
+                         num_attention_heads=24, num_key_value_heads=8, head_dim=128,
+                         rope_scaling=dict(_LLAMA3_ROPE, factor=32.0), tie_word_embeddings=True),
+    "llama-3.1-8b": dict(LLAMA_3_2_1B, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32,
+                         num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                         rope_scaling=dict(_LLAMA3_ROPE, factor=8.0), tie_word_embeddings=False),
+}
 START_CONTEXT = 2048          # tokens each request holds when decoding starts (--context overrides)
 PREFILL_TOKENS = 2048
 BATCHED_TOKENS = 4 * PREFILL_TOKENS     # token budget of one step of the end-to-end run
@@ -136,23 +148,28 @@ def run_ours(args):
 
     device = "cuda:0"
     torch.cuda.set_device(0)
-    raw = dict(LLAMA_3_2_1B, num_hidden_layers=args.layers)
+    full_layers = SHAPES[args.shape]["num_hidden_layers"]
+    if args.layers is None:
+        args.layers = full_layers
+    raw = dict(SHAPES[args.shape], num_hidden_layers=args.layers)
     config = config_from_dict(raw)
     nums = model_numbers(raw, args.layers)
     pk = peaks()
     vocab = raw["vocab_size"]
     K, W = args.steps, args.warmup
     START_CONTEXT = args.context
+    PREFILL = args.prefill_tokens
+    BATCHED = max(BATCHED_TOKENS, PREFILL)
     # spare tokens: in the end-to-end run the first requests start decoding while the last
     # prompts are still being prefilled (one prefill step takes BATCHED_TOKENS of prompt)
-    spare = max(16, -(-args.batch * START_CONTEXT // BATCHED_TOKENS) + 8)
-    end_context = START_CONTEXT + W + K + spare
+    spare = max(16, -(-args.batch * START_CONTEXT // BATCHED) + 8)
+    end_context = max(START_CONTEXT + W + K + spare, PREFILL)
     max_batch = max(args.batch, 64 if args.points else args.batch)
     page = 16
     pages_per_request = -(-end_context // page)
-    ecfg = EngineConfig(max_batch_size=max_batch, max_sequences=max_batch, prefill_chunk_size=PREFILL_TOKENS,
+    ecfg = EngineConfig(max_batch_size=max_batch, max_sequences=max_batch, prefill_chunk_size=PREFILL,
                         block_size=page, num_cache_blocks=max_batch * pages_per_request + 8,
-                        max_num_batched_tokens=BATCHED_TOKENS, max_model_len=pages_per_request * page,
+                        max_num_batched_tokens=BATCHED, max_model_len=pages_per_request * page,
                         dtype="bfloat16", device=device)
     engine = Engine.from_weights(config, device_weights(config, 0, device), ecfg)
     runner = engine.runner
@@ -170,16 +187,16 @@ def run_ours(args):
         torch.cuda.synchronize()
         return a.elapsed_time(b)
 
-    # ---- prefill: one prompt of 2,048 tokens in one step, logits of the last place ----
+    # ---- prefill: one prompt (2,048 tokens unless asked otherwise) in one step, logits of the last place ----
     prefill_ms = []
     for i in range(3 + 3):
-        p = prompt(PREFILL_TOKENS)
-        ms = timed(lambda: runner.step([StepEntry(("prefill", i), p, [PREFILL_TOKENS - 1])]))
+        p = prompt(PREFILL)
+        ms = timed(lambda: runner.step([StepEntry(("prefill", i), p, [PREFILL - 1])]))
         runner.end(("prefill", i))
         if i >= 3:
             prefill_ms.append(ms)
     prefill_ms = sorted(prefill_ms)[len(prefill_ms) // 2]
-    T = PREFILL_TOKENS
+    T = PREFILL
     prefill_flops = 2.0 * T * nums["linear_params"] + nums["attn_flops_per_key_query"] * T * (T + 1) / 2 \
         + 2.0 * nums["lm_head_params"]
     prefill = {"value": round(T / (prefill_ms / 1e3), 1), "tokens": T, "ms": round(prefill_ms, 3),
@@ -208,8 +225,8 @@ def run_ours(args):
     ms_per_step = ms_total / K
     value = args.batch * K / (ms_total / 1e3)
     mean_ctx = START_CONTEXT + W + (K + 1) / 2.0
-    step_bytes = 2.0 * (nums["linear_params"] + nums["lm_head_params"]) + 4.0 * nums["norm_params"] \
-        + args.batch * mean_ctx * nums["kv_bytes_per_token"]
+    weight_bytes = 2.0 * (nums["linear_params"] + nums["lm_head_params"]) + 4.0 * nums["norm_params"]
+    step_bytes = weight_bytes + args.batch * mean_ctx * nums["kv_bytes_per_token"]
     achieved = step_bytes / (ms_per_step / 1e3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                 "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk["source"],
@@ -249,13 +266,13 @@ def run_ours(args):
         "metric": "decode_tokens_per_second", "value": round(value, 1), "unit": "tok/s", "n_gpus": 1,
         "steps": K, "warmup": W, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
-        "config": {"model": "llama-3.2-1b-shape", "global_batch": args.batch, "seq_len": end_context,
-                   "parallelism": "single-gpu", "layers": args.layers, "layers_full_model": FULL_LAYERS,
+        "config": {"model": args.shape + "-shape", "global_batch": args.batch, "seq_len": end_context,
+                   "parallelism": "single-gpu", "layers": args.layers, "layers_full_model": full_layers,
                    "hidden_size": raw["hidden_size"], "intermediate_size": raw["intermediate_size"],
                    "q_heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"],
                    "head_dim": raw["head_dim"], "vocab_size": vocab, "start_context": START_CONTEXT,
-                   "kv_page_size": page, "weights": "random N(0,0.02) bf16, tied",
-                   "l2_policy": "inputs larger than L2 (weights 2.5 GB per step)",
+                   "kv_page_size": page, "weights": "random N(0,0.02) bf16" + (", tied" if raw["tie_word_embeddings"] else ""),
+                   "l2_policy": "inputs larger than L2 (weights %.1f GB per step)" % (weight_bytes / 1e9),
                    "decode_loop": "cuda graph replay, device-side argmax and feedback"},
         "clocks": clk, "e2e": e2e, "gpu_launches": launches_per_step * K, "prefill": prefill,
         "roofline": roofline, "points": points,
@@ -271,7 +288,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=START_CONTEXT, help="tokens per request when decoding starts")
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS)
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="length of the timed prompt")
+    ap.add_argument("--shape", default="llama-3.2-1b", choices=sorted(SHAPES), help="layer sizes of the model")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (both are reported)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", dest="points", action="store_false", help="skip the batch 1 and 64 points")
     args = ap.parse_args()

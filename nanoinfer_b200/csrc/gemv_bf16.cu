@@ -29,7 +29,6 @@
 #include "common.cuh"
 
 #define GV_WARPS 8
-#define GV_UNROLL 4
 
 #define GV_STORE_BF16 0
 #define GV_STORE_F32 1
@@ -93,11 +92,13 @@ __device__ __forceinline__ uint4 load_x8(const void* xrow, const float* gain8, i
 }
 
 // RN: weight rows per tile (8 or 16).  NT: batch tiles of 8 rows (1 or 2).  NORM: FP32 input +
-// RMSNorm.  KEEP: the activations of a warp's K slice stay in registers (K <= 2048) and the
-// block walks `tiles_per_block` consecutive row tiles with them, so that activations are read
-// and normalised once per block, not once per 16 weight rows.
-template <int RN, int NT, bool NORM, bool KEEP>
-__global__ void __launch_bounds__(GV_WARPS * 32, NT == 1 ? 2 : 1) gemv_bf16_kernel(const GemvParams p, int tiles_per_block) {
+// RMSNorm.  U: k-blocks of 64 a warp has in flight per pass (a pass of the block covers
+// 64 * GV_WARPS * U of K).  KEEP: one pass covers K, the activations of a warp's K slice stay in
+// registers and the block walks `tiles_per_block` consecutive row tiles with them, so that
+// activations are read and normalised once per block, not once per 16 weight rows (U = 4 for K
+// <= 2048 with two blocks per SM; U = 6 and 8 for K up to 3072 and 4096 with one).
+template <int RN, int NT, bool NORM, bool KEEP, int U>
+__global__ void __launch_bounds__(GV_WARPS * 32, (NT == 1 && U <= 4) ? 2 : 1) gemv_bf16_kernel(const GemvParams p, int tiles_per_block) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int M = p.M, N = p.N, K = p.K;
@@ -113,10 +114,10 @@ __global__ void __launch_bounds__(GV_WARPS * 32, NT == 1 ? 2 : 1) gemv_bf16_kern
     // KEEP with the norm fused: the gain does not depend on the kernel before this one, so each
     // warp stages the gains of its own K slice in shared memory before the wait; afterwards only
     // the residual rows come from memory.
-    __shared__ __align__(16) float s_gain[(NORM && KEEP) ? GV_WARPS : 1][(NORM && KEEP) ? GV_UNROLL * 64 : 4];
-    static_assert(!KEEP || NT * GV_UNROLL <= 8, "activation registers");
+    __shared__ __align__(16) float s_gain[(NORM && KEEP) ? GV_WARPS : 1][(NORM && KEEP) ? U * 64 : 4];
+    static_assert(!KEEP || NT * U <= 8, "activation registers");
     if (NORM && KEEP) {
-        for (int i = lane; i < GV_UNROLL * 16; i += 32) {
+        for (int i = lane; i < U * 16; i += 32) {
             const int u = i >> 4, k = (warp + u * GV_WARPS) * 64 + 4 * (i & 15);
             if (k + 4 <= K) *reinterpret_cast<float4*>(&s_gain[warp][4 * i]) = *reinterpret_cast<const float4*>(p.gain + k);
         }
@@ -138,21 +139,21 @@ __global__ void __launch_bounds__(GV_WARPS * 32, NT == 1 ? 2 : 1) gemv_bf16_kern
         s_page[m] = page;
     }
 
-    uint4 fx[GV_UNROLL][NT][2];     // KEEP: this warp's activations, loaded once
+    uint4 fx[U][NT][2];     // KEEP: this warp's activations, loaded once
     float ssq[NT];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) ssq[nt] = 0.f;
     bool waited = false;
 
-    // This warp's weight fragments of one pass over K (GV_UNROLL k-blocks of 64).
-    uint4 fa[GV_UNROLL][2], fb[GV_UNROLL][2];
+    // This warp's weight fragments of one pass over K (U k-blocks of 64).
+    uint4 fa[U][2], fb[U][2];
     auto load_weights = [&](int n0, int kb) {
         const bool row_a_ok = n0 + g < N;
         const bool row_b_ok = RN == 16 && n0 + g + 8 < N;
         const __nv_bfloat16* wa = p.w + (size_t)(row_a_ok ? n0 + g : 0) * K;
         const __nv_bfloat16* wb = p.w + (size_t)(row_b_ok ? n0 + g + 8 : 0) * K;
 #pragma unroll
-        for (int u = 0; u < GV_UNROLL; ++u) {
+        for (int u = 0; u < U; ++u) {
             const int k0 = (kb + u * GV_WARPS) * 64;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -175,7 +176,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32, NT == 1 ? 2 : 1) gemv_bf16_kern
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
 
-        for (int kb = warp; kb < n_blocks; kb += GV_WARPS * GV_UNROLL) {
+        for (int kb = warp; kb < n_blocks; kb += GV_WARPS * U) {
             if (!prefetched) load_weights(n0, kb);
             prefetched = false;
             if (!waited) {
@@ -192,7 +193,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32, NT == 1 ? 2 : 1) gemv_bf16_kern
                     const void* xr = NORM ? (const void*)((const float*)p.x + (size_t)src * K)
                                           : (const void*)((const __nv_bfloat16*)p.x + (size_t)src * K);
 #pragma unroll
-                    for (int u = 0; u < GV_UNROLL; ++u) {
+                    for (int u = 0; u < U; ++u) {
                         const int k0 = (kb + u * GV_WARPS) * 64;
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
@@ -204,7 +205,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32, NT == 1 ? 2 : 1) gemv_bf16_kern
                 }
             }
 #pragma unroll
-            for (int u = 0; u < GV_UNROLL; ++u)
+            for (int u = 0; u < U; ++u)
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -306,7 +307,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32, NT == 1 ? 2 : 1) gemv_bf16_kern
     if (!waited) pdl_wait();
 }
 
-template <int RN, int NT, bool NORM, bool KEEP>
+template <int RN, int NT, bool NORM, bool KEEP, int U>
 static int launch_gemv(const GemvParams& p, int tiles_per_block, cudaStream_t stream) {
     const int tiles = (p.N + RN - 1) / RN;
     cudaLaunchConfig_t cfg = {};
@@ -319,7 +320,7 @@ static int launch_gemv(const GemvParams& p, int tiles_per_block, cudaStream_t st
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_bf16_kernel<RN, NT, NORM, KEEP>, p, tiles_per_block);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_bf16_kernel<RN, NT, NORM, KEEP, U>, p, tiles_per_block);
     return e == cudaSuccess ? NI_OK : (int)e;
 }
 
@@ -334,32 +335,42 @@ static int dispatch_gemv(const GemvParams& p, bool norm, cudaStream_t stream) {
                                  p.N != (p.n_q_heads + 2 * p.n_kv_heads) * p.head_dim))
         return NI_ERR_BAD_ARGUMENT;
     const bool one = p.M <= 8;
-    // Activations stay in registers when one unrolled pass covers K (<= 2048): then a block takes
-    // several row tiles, as many as leave about two blocks per SM (one block per SM with two batch
-    // tiles, whose registers allow no more), and reads and normalises the activations once.
-    const bool keep = p.K <= 64 * GV_WARPS * GV_UNROLL;
+    // Activations stay in registers when one unrolled pass covers K: up to 2048 with four k-blocks
+    // per warp in flight (two blocks per SM; one with two batch tiles, whose registers allow no
+    // more), up to 3072 and 4096 with six and eight (one batch tile, one block per SM).  Then a
+    // block takes several row tiles, as many as leave that many blocks per SM, and reads and
+    // normalises the activations once.
+    const int unroll = p.K <= 64 * GV_WARPS * 4 ? 4 : p.K <= 64 * GV_WARPS * 6 ? 6 : 8;
+    const bool keep = p.K <= 64 * GV_WARPS * 4 || (one && p.K <= 64 * GV_WARPS * 8);
     int tpb = 1;
     if (keep) {
         const int tiles = (p.N + (rn16 ? 16 : 8) - 1) / (rn16 ? 16 : 8);
-        const int blocks = (one ? 2 : 1) * 148;
+        const int blocks = ((one && unroll == 4) ? 2 : 1) * 148;
         tpb = (tiles + blocks - 1) / blocks;
         if (tpb < 1) tpb = 1;
     }
-#define GO(RN, NT, NORM, KEEP) return launch_gemv<RN, NT, NORM, KEEP>(p, tpb, stream)
+#define GO(RN, NT, NORM, KEEP, U) return launch_gemv<RN, NT, NORM, KEEP, U>(p, tpb, stream)
+#define GO_KEEP1(U)                                                                              \
+    do {                                                                                         \
+        if (norm) { if (rn16) GO(16, 1, true, true, U); else GO(8, 1, true, true, U); }          \
+        else { if (rn16) GO(16, 1, false, true, U); else GO(8, 1, false, true, U); }             \
+    } while (0)
     if (keep && one) {
-        if (norm) { if (rn16) GO(16, 1, true, true); else GO(8, 1, true, true); }
-        else { if (rn16) GO(16, 1, false, true); else GO(8, 1, false, true); }
+        if (unroll == 4) GO_KEEP1(4);
+        if (unroll == 6) GO_KEEP1(6);
+        GO_KEEP1(8);
     }
     if (keep) {
-        if (norm) { if (rn16) GO(16, 2, true, true); else GO(8, 2, true, true); }
-        else { if (rn16) GO(16, 2, false, true); else GO(8, 2, false, true); }
+        if (norm) { if (rn16) GO(16, 2, true, true, 4); else GO(8, 2, true, true, 4); }
+        else { if (rn16) GO(16, 2, false, true, 4); else GO(8, 2, false, true, 4); }
     }
     if (norm) {
-        if (rn16) { if (one) GO(16, 1, true, false); else GO(16, 2, true, false); }
-        else { if (one) GO(8, 1, true, false); else GO(8, 2, true, false); }
+        if (rn16) { if (one) GO(16, 1, true, false, 4); else GO(16, 2, true, false, 4); }
+        else { if (one) GO(8, 1, true, false, 4); else GO(8, 2, true, false, 4); }
     }
-    if (rn16) { if (one) GO(16, 1, false, false); else GO(16, 2, false, false); }
-    if (one) GO(8, 1, false, false); else GO(8, 2, false, false);
+    if (rn16) { if (one) GO(16, 1, false, false, 4); else GO(16, 2, false, false, 4); }
+    if (one) GO(8, 1, false, false, 4); else GO(8, 2, false, false, 4);
+#undef GO_KEEP1
 #undef GO
 }
 

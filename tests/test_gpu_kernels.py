@@ -180,7 +180,8 @@ def test_rope_kv_write(dtype, pairing, n_q, n_kv, hd, rot, page):
 
 @pytest.mark.parametrize("mode", ["bf16", "f32", "add"])
 @pytest.mark.parametrize("m,n,k", [(1, 64, 64), (3, 100, 120), (8, 4800, 2048), (9, 333, 200), (16, 520, 8200),
-                                   (5, 2048, 8192)])
+                                   (5, 2048, 8192), (7, 1000, 3072), (8, 600, 4096), (2, 328, 2056),
+                                   (3, 200, 3080), (9, 200, 3072)])
 def test_gemv_bf16(m, n, k, mode):
     from nanoinfer_b200.kernels import ops
     x = _randn(m, k, dtype=torch.bfloat16, seed=1)
@@ -348,7 +349,8 @@ def test_attention_prefill_tensor_core_declines_what_it_cannot_take():
         ops.attention_prefill(q, kp, kp, q.clone(), z, z, 1, z, z, z.view(1, 2), 5, 5, 64, 16, None, 0.125, kernel="tc")
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 64, 64), (4, 336, 120), (8, 4800, 2048), (13, 200, 264), (16, 1000, 8200)])
+@pytest.mark.parametrize("m,n,k", [(1, 64, 64), (4, 336, 120), (8, 4800, 2048), (13, 200, 264), (16, 1000, 8200),
+                                   (8, 5120, 3072), (5, 1000, 4096), (3, 264, 2600), (6, 200, 4104)])
 def test_gemv_with_fused_norm(m, n, k):
     """RMSNorm (on picked rows of the FP32 residual stream) inside the skinny product."""
     from nanoinfer_b200.kernels import ops
@@ -372,7 +374,8 @@ def test_gemv_with_fused_norm(m, n, k):
     assert (out2.cpu().double() - want2).abs().max().item() <= 4e-3 * want2.abs().max().item()
 
 
-@pytest.mark.parametrize("m,inter,k", [(1, 64, 64), (7, 200, 120), (8, 8192, 2048), (16, 264, 160)])
+@pytest.mark.parametrize("m,inter,k", [(1, 64, 64), (7, 200, 120), (8, 8192, 2048), (16, 264, 160), (8, 4096, 3072),
+                                       (4, 2048, 4096)])
 def test_gemv_with_swiglu_epilogue(m, inter, k):
     from nanoinfer_b200.kernels import ops
     x = _randn(m, k, dtype=torch.bfloat16, seed=1)
@@ -396,7 +399,7 @@ def test_gemv_with_swiglu_epilogue(m, inter, k):
 
 @pytest.mark.parametrize("with_norm", [False, True])
 @pytest.mark.parametrize("n_q,n_kv,hd,rot,page,d", [(4, 2, 16, 16, 16, 64), (3, 1, 32, 32, 8, 96), (6, 3, 48, 32, 4, 120),
-                                                     (32, 8, 64, 64, 16, 2048)])
+                                                     (32, 8, 64, 64, 16, 2048), (24, 8, 128, 128, 16, 3072), (8, 2, 128, 128, 16, 4096)])
 def test_gemv_qkv_rope(n_q, n_kv, hd, rot, page, d, with_norm):
     """Projection + (norm) + adjacent-pair rotation + paged write in one launch, against the
     plain steps."""

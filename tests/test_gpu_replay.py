@@ -182,18 +182,29 @@ def test_trace_run_program(model_dirs, tmp_path):
             fed[e["id"]] = base + len(e["tokens"])
 
 
+_LAYER_SIZES = {
+    # width, q heads, kv heads, head size, feed-forward, vocabulary, rope factor, tied output
+    "1b": (2048, 32, 8, 64, 8192, 128256, 32.0, True),
+    "3b": (3072, 24, 8, 128, 8192, 32064, 32.0, True),      # odd group of 3, a width that is no power of two
+    "8b": (4096, 32, 8, 128, 14336, 32064, 8.0, False),
+}
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_benchmark_layer_sizes(tmp_path_factory, dtype):
-    """The benchmark's layer sizes (width 2048, 32/8 heads of 64, feed-forward 8192, vocabulary
-    128256, llama3 rope scaling, tied output) with two layers: a prompt long enough for the
+@pytest.mark.parametrize("shape", sorted(_LAYER_SIZES))
+def test_benchmark_layer_sizes(tmp_path_factory, dtype, shape):
+    """The layer sizes of the family's models (1B: width 2048, 32/8 heads of 64, feed-forward 8192,
+    vocabulary 128256, tied output; 3B and 8B: heads of 128, with a smaller vocabulary to keep the
+    plain implementation quick), llama3 rope scaling, two layers: a prompt long enough for the
     tensor-core projection path, then single tokens through the captured decode step."""
     from nanoinfer_b200.weights import write_random_model
-    raw = {"architectures": ["LlamaForCausalLM"], "hidden_size": 2048, "intermediate_size": 8192,
-           "num_hidden_layers": 2, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64,
-           "vocab_size": 128256, "max_position_embeddings": 131072, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
-           "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+    width, hq, hkv, hd, inter, vocab, factor, tied = _LAYER_SIZES[shape]
+    raw = {"architectures": ["LlamaForCausalLM"], "hidden_size": width, "intermediate_size": inter,
+           "num_hidden_layers": 2, "num_attention_heads": hq, "num_key_value_heads": hkv, "head_dim": hd,
+           "vocab_size": vocab, "max_position_embeddings": 131072, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+           "rope_scaling": {"rope_type": "llama3", "factor": factor, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
                             "original_max_position_embeddings": 8192},
-           "tie_word_embeddings": True, "hidden_act": "silu"}
+           "tie_word_embeddings": tied, "hidden_act": "silu"}
     d = str(tmp_path_factory.mktemp("bench_shape") / "m")
     write_random_model(d, raw, seed=4)
     raw_read, w = load_plain(d)
@@ -205,6 +216,6 @@ def test_benchmark_layer_sizes(tmp_path_factory, dtype):
     runner = _runner(d, dtype, 16, steps)
     got = ru.run_trace(runner, steps)
     assert len(got) == 13
-    ru.compare(got, want, dtype, label=f"bench-shape/{dtype}")
+    ru.compare(got, want, dtype, label=f"layer-sizes-{shape}/{dtype}")
     from nanoinfer_b200.kernels import ops
     ops.check_device_errors()
