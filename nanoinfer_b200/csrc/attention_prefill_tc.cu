@@ -35,7 +35,7 @@
 // a wait that runs out records a code in the error word, and the block frees its tensor memory
 // and returns.
 //
-// Takes head sizes 64 and 128, an even number of query heads per kv head, and page sizes 8 to
+// Takes head sizes 64 and 128, two or more query heads per kv head, and page sizes 8 to
 // 128 that divide 128; everything else is the business of attention_prefill.cu.
 //
 // Reference counterpart: src/op/kernels/cuda/prefill_attention_kernel.cu:321-475 (gathered FP32
@@ -268,8 +268,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int j_begin = p.window > 0 ? max(0, first_pos - p.window + 1) / AT_BN : 0;
     const int n_tiles = j_end - j_begin;
     const int G = p.n_q_heads / p.n_kv_heads;
-    const int head0 = 2 * blockIdx.y;                     // streams: heads head0 and head0 + 1
-    const int kvh = head0 / G;
+    // A kv head's group of query heads is cut into blocks of two (the two streams).  The last
+    // block of an odd group has one head left: its second stream runs that head again, so that
+    // the streams' hand-offs stay as they are, and stores nothing.
+    const int blocks_per_kv = (G + 1) / 2;
+    const int kvh = blockIdx.y / blocks_per_kv;
+    const int first = 2 * (blockIdx.y - kvh * blocks_per_kv);
+    const int head0 = kvh * G + first;
+    const int head1 = first + 1 < G ? head0 + 1 : head0;
 
     if (threadIdx.x == 0) {
         at_mbar_init(q_full, 1);
@@ -303,7 +309,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             at_mbar_expect_tx(q_full, 2 * TILE_BYTES);
             for (int s = 0; s < 2; ++s)
                 for (int h = 0; h < HALVES; ++h)
-                    at_tma_2d(sQ + s * TILE_BYTES + h * HALF_BYTES, &map_q, (head0 + s) * HD + h * 64, q_begin + row0, q_full);
+                    at_tma_2d(sQ + s * TILE_BYTES + h * HALF_BYTES, &map_q, (s ? head1 : head0) * HD + h * 64, q_begin + row0, q_full);
         }
         const int* table = p.block_table + (size_t)seq * p.bt_stride;
         const int pages_held = (kvl + p.page_size - 1) / p.page_size;
@@ -587,12 +593,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             asm volatile("bar.sync %0, 64;\n" ::"r"(pair_bar) : "memory");
             const float inv = 1.0f / (l + row_max[0][s][half ^ 1][r]);
             __nv_bfloat16* orow = p.out + (size_t)(q_begin + row0 + r) * ((size_t)p.n_q_heads * HD) +
-                                  (size_t)(head0 + s) * HD + (HD / 2) * half;
+                                  (size_t)(s ? head1 : head0) * HD + (HD / 2) * half;
+            const bool stores = r < rows && (s == 0 || head1 != head0);
 #pragma unroll 1
             for (int c = 0; c < HD / 64; ++c) {
                 uint32_t o[32];
                 at_ld32(t_o + 32 * c, o);
-                if (r < rows) {
+                if (stores) {
 #pragma unroll
                     for (int e = 0; e < 32; e += 8) {
                         uint4 w;
@@ -658,7 +665,7 @@ static int launch_at(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(n_tiles, p.n_q_heads / 2);
+    dim3 grid(n_tiles, p.n_kv_heads * ((p.n_q_heads / p.n_kv_heads + 1) / 2));
     attention_prefill_tc_kernel<HD, STAGES><<<grid, AT_THREADS, smem, stream>>>(mq, mk, mv, p);
     NI_RETURN_LAUNCH_STATUS();
 }
@@ -666,7 +673,9 @@ static int launch_at(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
 // 1 if this kernel takes the case, else 0 (the caller then uses the mma.sync kernel).
 NI_EXPORT int ni_attention_prefill_tc_supports(int n_q_heads, int n_kv_heads, int head_dim, int page_size) {
     if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads) return 0;
-    if ((n_q_heads / n_kv_heads) % 2) return 0;
+    const int group = n_q_heads / n_kv_heads;
+    if (group == 1) return 0;                 // two streams on one head would do every product twice
+    if ((long long)n_kv_heads * ((group + 1) / 2) > 65535) return 0;
     if (head_dim != 64 && head_dim != 128) return 0;
     if (page_size < 8 || page_size > 128 || 128 % page_size) return 0;
     return 1;
@@ -681,7 +690,7 @@ NI_EXPORT int ni_attention_prefill_tc(const void* q, const void* k_pages, const 
                                       int n_q_heads, int n_kv_heads, int head_dim, int page_size, int window,
                                       float scale, int* error, cudaStream_t stream) {
     if (n_tiles <= 0) return NI_OK;
-    if (n_tokens <= 0 || n_pages <= 0 || error == nullptr || n_q_heads > 2 * 65535) return NI_ERR_BAD_ARGUMENT;
+    if (n_tokens <= 0 || n_pages <= 0 || error == nullptr) return NI_ERR_BAD_ARGUMENT;
     if (!ni_attention_prefill_tc_supports(n_q_heads, n_kv_heads, head_dim, page_size)) return NI_ERR_UNSUPPORTED_SIZE;
     if (((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) || ((uintptr_t)out & 15))
         return NI_ERR_UNSUPPORTED_SIZE;

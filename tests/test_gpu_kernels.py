@@ -306,7 +306,8 @@ def test_attention_prefill(n_q, n_kv, hd, page, window):
 @pytest.mark.parametrize("far_at", [3, 640])
 @pytest.mark.parametrize("n_q,n_kv,hd,page,window", [(32, 8, 64, 16, None), (4, 2, 64, 8, None), (8, 2, 128, 16, 129),
                                                       (2, 1, 128, 32, None), (16, 2, 64, 64, 300), (4, 1, 64, 128, None),
-                                                      (6, 1, 128, 8, None)])
+                                                      (6, 1, 128, 8, None), (6, 2, 128, 16, None), (5, 1, 64, 16, 200),
+                                                      (9, 3, 64, 32, None)])
 def test_attention_prefill_tensor_core(n_q, n_kv, hd, page, window, far_at):
     """The tcgen05 kernel: several key tiles per query tile, a portion that starts late, tiny and
     page-edge portions, and a dominant key either in the first tile or in a late one (there the
