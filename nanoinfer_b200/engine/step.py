@@ -200,6 +200,10 @@ class ModelRunner:
         self._portion_graphs: Dict[tuple, "_PortionGraph"] = {}       # by step shape, least recently used first
         self._portion_seen: Dict[tuple, int] = {}
         self.max_portion_graphs = 8
+        # A capture costs about three runs of the step (an eager run that sizes the workspaces, the
+        # capture, the first replay) and a replay saves only the launch overhead, so a shape must
+        # have come back a few times before it is worth one.
+        self.portion_graph_after = 4
         self._pinned: List[torch.Tensor] = []
         self._pinned_events: List[torch.cuda.Event] = []
         self._pinned_next = 0
@@ -358,7 +362,7 @@ class ModelRunner:
         """A step's launches depend only on how many tokens each entry brings and how many logit
         rows it wants (everything else is metadata in device memory), so a shape that comes back -
         the same portion size step after step while a prompt is cut into portions - is captured at
-        its second appearance and replayed from then on."""
+        its ``portion_graph_after``-th appearance and replayed from then on."""
         if not self.use_graphs or self._state_runs or self.rt.dtype != torch.bfloat16:
             return False
         sig = tuple((len(e.tokens), len(e.want)) for e in entries)
@@ -368,7 +372,7 @@ class ModelRunner:
         self._portion_seen[sig] = seen
         if len(self._portion_seen) > 4096:
             self._portion_seen.clear()
-        return seen >= 2
+        return seen >= self.portion_graph_after
 
     def _portion_graph(self, entries: Sequence[StepEntry]) -> "_PortionGraph":
         sig = tuple((len(e.tokens), len(e.want)) for e in entries)

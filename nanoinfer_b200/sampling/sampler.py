@@ -25,6 +25,8 @@ class Sampler:
         self.vocab_size = vocab_size
         self.device = device
         self.h2d_bytes = 0     # bytes of per-row parameters copied to the device so far
+        self._dev = None       # the parameters' place on the device, and the pinned buffers they come from
+        self._host, self._events, self._used, self._next = [], [], [], 0
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
                token_indices: Sequence[int],
@@ -51,13 +53,40 @@ class Sampler:
                 pen = np.asarray([p.repetition_penalty for p in params], dtype=np.float32)
                 ops.repetition_penalty(logits, torch.from_numpy(ids).to(logits.device),
                                        torch.from_numpy(pen).to(logits.device))
-        f = np.asarray([[p.temperature, p.top_p] for p in params], dtype=np.float32)
-        k = np.asarray([p.top_k for p in params], dtype=np.int32)
-        sc = np.asarray([[s, c] for s, c in zip(seeds, token_indices)], dtype=np.uint64)
-        dev = logits.device
-        self.h2d_bytes += f.nbytes + k.nbytes + sc.nbytes
-        ft = torch.from_numpy(f).to(dev)
-        sct = torch.from_numpy(sc.view(np.int64)).to(dev)
-        ops.sample(logits, out, ft[:, 0].contiguous(), torch.from_numpy(k).to(dev),
-                   ft[:, 1].contiguous(), sct[:, 0].contiguous(), sct[:, 1].contiguous())
+        seed_t, count_t, temp_t, top_p_t, top_k_t = self._upload(logits.device, params, seeds, token_indices)
+        ops.sample(logits, out, temp_t, top_k_t, top_p_t, seed_t, count_t)
         return out
+
+    # Per-row parameters travel in ONE copy from pinned memory (a copy from pageable memory would
+    # hold the host until the stream has run everything before it - the whole step).  Words of 4
+    # bytes: seeds int64 [n], token counters int64 [n], temperature, top_p float32 [n], top_k int32 [n].
+    _RING = 4
+
+    def _upload(self, device, params, seeds, token_indices):
+        n = len(params)
+        words = 7 * n
+        if self._dev is None or self._dev.numel() < words:
+            cap = max(7 * 64, 2 * words)
+            self._dev = torch.empty(cap, dtype=torch.int32, device=device)
+            pin = device.type == "cuda"
+            self._host = [torch.empty(cap, dtype=torch.int32, pin_memory=pin) for _ in range(self._RING)]
+            self._events = [torch.cuda.Event() if pin else None for _ in range(self._RING)]
+            self._used = [False] * self._RING
+        i = self._next
+        self._next = (i + 1) % self._RING
+        if self._used[i] and self._events[i] is not None:
+            self._events[i].synchronize()          # the copy that read this buffer last has run
+        h = self._host[i][:words].numpy()
+        h[0:2 * n].view(np.int64)[:] = np.asarray(seeds, dtype=np.uint64).view(np.int64)
+        h[2 * n:4 * n].view(np.int64)[:] = np.asarray(token_indices, dtype=np.int64)
+        h[4 * n:5 * n].view(np.float32)[:] = [p.temperature for p in params]
+        h[5 * n:6 * n].view(np.float32)[:] = [p.top_p for p in params]
+        h[6 * n:7 * n] = [p.top_k for p in params]
+        d = self._dev[:words]
+        d.copy_(self._host[i][:words], non_blocking=True)
+        if self._events[i] is not None:
+            self._events[i].record()
+            self._used[i] = True
+        self.h2d_bytes += 4 * words
+        return (d[0:2 * n].view(torch.int64), d[2 * n:4 * n].view(torch.int64), d[4 * n:5 * n].view(torch.float32),
+                d[5 * n:6 * n].view(torch.float32), d[6 * n:7 * n])

@@ -72,7 +72,7 @@ def test_replay_matches_plain(model_dirs, plain_cache, key, cut, dtype):
 
 def test_repeated_portion_shapes_are_replayed_from_a_graph(model_dirs, plain_cache):
     """Portions of one size, step after step (the way a scheduler cuts prompts): from the second
-    appearance the step is a replayed graph; the logits must not notice, also when the same graph
+    appearance (as set here) the step is a replayed graph; the logits must not notice, also when the same graph
     serves another request, another position in the cache and a portion beside a decoded token."""
     key = "d"
     raw, reqs, want = _plain(plain_cache, key, model_dirs[key])
@@ -104,6 +104,7 @@ def test_repeated_portion_shapes_are_replayed_from_a_graph(model_dirs, plain_cac
         s += 1
     steps[-1]["end"] = [rb]
     runner = _runner(model_dirs[key], "bfloat16", page, steps)
+    runner.portion_graph_after = 2
     got = ru.run_trace(runner, steps)
     assert len(got) == sum(len(t) for t in reqs.values())
     ru.compare(got, want, "bfloat16", label="portion graphs")
