@@ -502,14 +502,28 @@ def decode_splits(n_items: int, n_kv_heads: int, head_dim: int, max_kv_len: int)
     """How many blocks share one (token, kv head): as many as fill the GPU once (three blocks of
     the split kernel are resident per SM; a second wave costs more than longer blocks), each with
     at least 384 keys of the longest context - 256 when there are few pairs, whose blocks are
-    bound by latency, not by bandwidth - and cut so that no block is left with a short remainder."""
+    bound by latency, not by bandwidth - and cut so that no block is left with a short remainder.
+    More pairs than the GPU holds at once: one lean block per pair with heads of 64 (four of
+    those fit an SM); with heads of 128 (three per SM) the count, up to 4, that fills the last
+    wave best (512 pairs: 58 % of two waves unsplit, 87 % of four waves in three parts)."""
     pairs = max(1, n_items * n_kv_heads)
+    chunks = -(-max_kv_len // 64)                 # the kernel cuts a context into 64-key chunks
+    slots = 148 * 3
+    if head_dim > 64 and pairs > slots:
+        best, best_fill = 1, 0.0
+        for s in range(1, 5):
+            if s > 1 and chunks < 6 * s:
+                break
+            fill = pairs * s / (-(-pairs * s // slots) * slots)
+            if fill > best_fill + 0.03:
+                best, best_fill = s, fill
+        per_split = -(-chunks // best)
+        return max(1, -(-chunks // per_split))
     if (148 * DECODE_BLOCKS_PER_SM) // pairs <= 1:
         return 1                                  # large batch: one lean block per pair
-    fill = (148 * 3) // pairs
+    fill = slots // pairs
     keys_per_split = 256 if pairs <= 16 else 384
     target = max(1, min(64, fill, -(-max_kv_len // keys_per_split)))
-    chunks = -(-max_kv_len // 64)                 # the kernel cuts a context into 64-key chunks
     per_split = -(-chunks // target)
     return max(1, -(-chunks // per_split))
 PREFILL_MAX_HEAD_DIM = 128
