@@ -412,9 +412,9 @@ NI_EXPORT int ni_attention_decode(const void* q, const void* k_pages, const void
     switch (head_dim) {
         case 64:
             // while all blocks fit the GPU at 3 per SM: fat blocks with 128-key buffers; beyond that
-            // (large batches, one block per token and kv head): 64-key buffers, so that 4 fit an SM and
-            // 512 blocks are still one wave
-            if (n_splits > 1 || (long long)n_items * n_kv_heads <= 3LL * sm_count())
+            // (large batches with one block per token and kv head, middle batches in two or three
+            // splits): 64-key buffers, so that 4 fit an SM and 512 to 592 blocks are still one wave
+            if ((long long)n_items * n_kv_heads * n_splits <= 3LL * sm_count())
                 return launch_decode<64, 128>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
                                               block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
                                               scale_log2e, n_splits, scratch, tickets, stream);
