@@ -204,6 +204,11 @@ class ModelRunner:
         # capture, the first replay) and a replay saves only the launch overhead, so a shape must
         # have come back a few times before it is worth one.
         self.portion_graph_after = 4
+        # The same holds for a batch size of single tokens, though a replay saves more there (the
+        # step is short): a size is captured when it comes for the third time.  Sizes that pass
+        # once or twice (a batch that shrinks as its requests end) run without a graph.
+        self.decode_graph_after = 3
+        self._decode_seen: Dict[int, int] = {}
         self._pinned: List[torch.Tensor] = []
         self._pinned_events: List[torch.cuda.Event] = []
         self._pinned_next = 0
@@ -336,7 +341,7 @@ class ModelRunner:
         self._validate(entries, pending_ok=device_tokens is not None)
         if device_tokens is not None and not (self._graphable(entries) and device_tokens.numel() == len(entries)):
             raise StepError("tokens can be fed from the device only to a replayed step of single tokens")
-        if self._graphable(entries):
+        if self._graphable(entries) and (device_tokens is not None or self._decode_graph_due(len(entries), count=True)):
             starts = reserve_entries(self.cache, entries, self.admit)
             logits = self._decode_graph(len(entries)).run(entries, starts, device_tokens)
         elif self._portion_graphable(entries):
@@ -384,9 +389,21 @@ class ModelRunner:
         self._portion_graphs[sig] = g                                      # most recently used last
         return g
 
+    def _decode_graph_due(self, n: int, count: bool) -> bool:
+        """True if a step of ``n`` single tokens runs as a graph: the size has a graph already, or
+        comes for the ``decode_graph_after``-th time.  ``count``: this call is such a step."""
+        if n in self._graphs:
+            return True
+        seen = self._decode_seen.get(n, 0) + 1
+        if count:
+            self._decode_seen[n] = seen
+        return seen >= self.decode_graph_after
+
     def can_feed_device_tokens(self, n: int) -> bool:
-        """True if a step of ``n`` single tokens can take its tokens from a device tensor."""
-        return self.use_graphs and not self._state_runs and 0 < n <= self.max_graph_batch
+        """True if the next step of ``n`` single tokens can take its tokens from a device tensor
+        (it then runs as a replayed graph, whose token buffer they are copied into)."""
+        return (self.use_graphs and not self._state_runs and 0 < n <= self.max_graph_batch
+                and self._decode_graph_due(n, count=False))
 
     def _decode_graph(self, n: int) -> "_DecodeGraph":
         g = self._graphs.get(n)
