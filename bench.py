@@ -27,29 +27,16 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-LLAMA_3_2_1B = {
-    "architectures": ["LlamaForCausalLM"],
-    "hidden_size": 2048, "intermediate_size": 8192, "num_hidden_layers": 16,
-    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64,
-    "vocab_size": 128256, "max_position_embeddings": 131072, "rms_norm_eps": 1e-5,
-    "rope_theta": 500000.0,
-    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
-                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
-    "tie_word_embeddings": True, "hidden_act": "silu",
-}
-_LLAMA3_ROPE = {"rope_type": "llama3", "low_freq_factor": 1.0, "high_freq_factor": 4.0,
-                "original_max_position_embeddings": 8192}
-# The sizes of the two larger models of the family, for runs at other kernel sizes (--shape);
-# the default run and the published line are the 1B shape.
-SHAPES = {
-    "llama-3.2-1b": LLAMA_3_2_1B,
-    "llama-3.2-3b": dict(LLAMA_3_2_1B, hidden_size=3072, intermediate_size=8192, num_hidden_layers=28,
-                         num_attention_heads=24, num_key_value_heads=8, head_dim=128,
-                         rope_scaling=dict(_LLAMA3_ROPE, factor=32.0), tie_word_embeddings=True),
-    "llama-3.1-8b": dict(LLAMA_3_2_1B, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32,
-                         num_attention_heads=32, num_key_value_heads=8, head_dim=128,
-                         rope_scaling=dict(_LLAMA3_ROPE, factor=8.0), tie_word_embeddings=False),
-}
+# The layer sizes come from the package's config.json files of the family's published sizes; the
+# default run and the published line are the 1B shape, --shape names the others.
+SHAPE_NAMES = ["llama-3.1-8b", "llama-3.2-1b", "llama-3.2-3b"]
+
+
+def shape_config(name):
+    from nanoinfer_b200.config import preset
+    return preset(name)
+
+
 START_CONTEXT = 2048          # tokens each request holds when decoding starts (--context overrides)
 PREFILL_TOKENS = 2048
 BATCHED_TOKENS = 4 * PREFILL_TOKENS     # token budget of one step of the end-to-end run
@@ -148,10 +135,11 @@ def run_ours(args):
 
     device = "cuda:0"
     torch.cuda.set_device(0)
-    full_layers = SHAPES[args.shape]["num_hidden_layers"]
+    full = shape_config(args.shape)
+    full_layers = full["num_hidden_layers"]
     if args.layers is None:
         args.layers = full_layers
-    raw = dict(SHAPES[args.shape], num_hidden_layers=args.layers)
+    raw = dict(full, num_hidden_layers=args.layers)
     config = config_from_dict(raw)
     nums = model_numbers(raw, args.layers)
     pk = peaks()
@@ -301,9 +289,10 @@ def run_serving(args):
 
     w = WORKLOADS[args.workload]
     shape = args.shape or w["shape"]
-    full_layers = SHAPES[shape]["num_hidden_layers"]
+    full = shape_config(shape)
+    full_layers = full["num_hidden_layers"]
     layers = args.layers or full_layers
-    raw = dict(SHAPES[shape], num_hidden_layers=layers)
+    raw = dict(full, num_hidden_layers=layers)
     config = config_from_dict(raw)
     device = "cuda:0"
     torch.cuda.set_device(0)
@@ -372,7 +361,7 @@ def main():
     ap.add_argument("--batch", type=int, default=None, help="requests (default 8; a serving workload's own count)")
     ap.add_argument("--context", type=int, default=START_CONTEXT, help="tokens per request when decoding starts")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="length of the timed prompt")
-    ap.add_argument("--shape", default=None, choices=sorted(SHAPES), help="layer sizes of the model (default: the 1B shape)")
+    ap.add_argument("--shape", default=None, choices=SHAPE_NAMES, help="layer sizes of the model (default: the 1B shape)")
     ap.add_argument("--workload", default="decode", choices=["decode"] + sorted(WORKLOADS),
                     help="decode: the timed decode step (the published line); the others serve a set of requests")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (both are reported)")

@@ -6,6 +6,7 @@ time to first token, prefill and decode tokens per second).  Prompts are token i
 
     bin/nanoinfer generate --model DIR --prompt-ids 1,15,7 --max-new-tokens 32
     bin/nanoinfer random-model --config config.json --seed 0 --out DIR
+    bin/nanoinfer random-model --preset llama-3.2-1b --layers 4 --out DIR
 """
 from __future__ import annotations
 
@@ -71,8 +72,17 @@ def _random_model(args) -> int:
     import torch
 
     from .weights import write_random_model
-    with open(args.config) as f:
-        raw = json.load(f)
+    if (args.config is None) == (args.preset is None):
+        print("random-model: give either --config FILE or --preset NAME", file=sys.stderr)
+        return 2
+    if args.preset is not None:
+        from .config import preset
+        raw = preset(args.preset)
+    else:
+        with open(args.config) as f:
+            raw = json.load(f)
+    if args.layers is not None:
+        raw = dict(raw, num_hidden_layers=args.layers)
     dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[args.dtype]
     write_random_model(args.out, raw, args.seed, args.std, dtype)
     print(f"wrote {args.out}/config.json and model.safetensors (seed {args.seed})", file=sys.stderr)
@@ -103,7 +113,9 @@ def main(argv=None) -> int:
     g.add_argument("--max-num-batched-tokens", type=int, default=2048)
     g.set_defaults(func=_generate)
     r = sub.add_parser("random-model", help="write a model folder with random weights")
-    r.add_argument("--config", required=True, help="a config.json to build the model from")
+    r.add_argument("--config", help="a config.json to build the model from")
+    r.add_argument("--preset", help="or one of the package's config.json files: llama-3.2-1b, llama-3.2-3b, llama-3.1-8b")
+    r.add_argument("--layers", type=int, help="another number of layers than the configuration names")
     r.add_argument("--out", required=True)
     r.add_argument("--seed", type=int, default=0)
     r.add_argument("--std", type=float, default=0.02)

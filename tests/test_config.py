@@ -84,3 +84,26 @@ def test_schedule_validation():
         with_schedule([LayerRun(0, cache_of=0)]).validate()
     with pytest.raises(ConfigError, match="no cache of its own"):
         with_schedule([LayerRun(0), LayerRun(1, cache_of=0), LayerRun(1, cache_of=1)]).validate()
+
+
+def test_presets_are_configurations_of_the_family():
+    """The package's config.json files of the published sizes parse like any other; the command
+    line's random-model takes one of them or a file, not both and not neither."""
+    from nanoinfer_b200.config import preset, preset_names
+    assert preset_names() == ["llama-3.1-8b", "llama-3.2-1b", "llama-3.2-3b"]
+    sizes = {}
+    for name in preset_names():
+        cfg = config_from_dict(preset(name))
+        m = cfg.layers[0].mixer
+        sizes[name] = (cfg.num_layers, cfg.hidden_size, m.num_heads, m.num_kv_heads, m.head_dim,
+                       cfg.layers[0].feed_forward.intermediate_size, cfg.tie_word_embeddings)
+        assert cfg.vocab_size == 128256 and m.position.theta == 500000.0 and cfg.final_norm.eps == 1e-5
+    assert sizes["llama-3.2-1b"] == (16, 2048, 32, 8, 64, 8192, True)
+    assert sizes["llama-3.2-3b"] == (28, 3072, 24, 8, 128, 8192, True)
+    assert sizes["llama-3.1-8b"] == (32, 4096, 32, 8, 128, 14336, False)
+    assert config_from_dict(preset("llama-3.1-8b")).layers[0].mixer.position.scaling.factor == 8.0
+    with pytest.raises(KeyError, match="llama-3.2-1b"):
+        preset("llama-9")
+    from nanoinfer_b200.cli import main
+    assert main(["random-model", "--out", "unused"]) == 2
+    assert main(["random-model", "--out", "unused", "--preset", "llama-3.2-1b", "--config", "x.json"]) == 2
