@@ -24,3 +24,23 @@ def test_filters():
     assert ps.sample(l, 0.0, repetition_penalty=4.0, generated=[1])[0] == 3
     tok, acceptable, cut = ps.sample(l, 1.0, top_p=0.7, seed=1)
     assert acceptable == {tok} and cut > 0.01
+
+
+def test_sampler_packs_the_rows_parameters_into_one_buffer():
+    """The sampler's per-row parameters travel as one buffer of 4-byte words (seeds and token
+    counters as 64-bit values first, so that they stay aligned); the views handed to the kernel
+    must read back what went in, also when the ring of host buffers comes round."""
+    from nanoinfer_b200.sampling import Sampler, SamplingParams
+    s = Sampler(vocab_size=100, device=torch.device("cpu"))
+    for n in (1, 3, 5, 70):                          # 70 rows outgrow the first buffer
+        params = [SamplingParams(temperature=0.5 + r, top_k=r - 1, top_p=1.0 / (r + 1)) for r in range(n)]
+        seeds = [(1 << 55) - 1 - r for r in range(n)]
+        counts = list(range(10, 10 + n))
+        for _ in range(6):                           # more calls than host buffers
+            seed_t, count_t, temp_t, top_p_t, top_k_t = s._upload(torch.device("cpu"), params, seeds, counts)
+            assert seed_t.dtype == torch.int64 and seed_t.tolist() == seeds
+            assert count_t.dtype == torch.int64 and count_t.tolist() == counts
+            assert temp_t.dtype == torch.float32 and temp_t.tolist() == [0.5 + r for r in range(n)]
+            assert torch.allclose(top_p_t, torch.tensor([1.0 / (r + 1) for r in range(n)]))
+            assert top_k_t.dtype == torch.int32 and top_k_t.tolist() == [r - 1 for r in range(n)]
+    assert s.h2d_bytes == 6 * 28 * (1 + 3 + 5 + 70)
