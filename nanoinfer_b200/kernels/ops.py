@@ -530,6 +530,8 @@ def decode_splits(n_items: int, n_kv_heads: int, head_dim: int, max_kv_len: int)
     target = max(1, min(64, fill, -(-max_kv_len // keys_per_split)))
     per_split = -(-chunks // target)
     return max(1, -(-chunks // per_split))
+
+
 PREFILL_MAX_HEAD_DIM = 128
 PREFILL_TILE_ROWS = 128      # query rows per block of the flash-style kernel
 
