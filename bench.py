@@ -56,9 +56,11 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+    """Samples SM clocks, load and throttle reasons with nvidia-smi from before the warm-up until
+    the last timed region has ended (every 20 ms, so that even a run of a few steps is covered);
+    the clock reported is the median over the samples taken under load."""
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,utilization.gpu")
     NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self):
@@ -67,7 +69,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -84,22 +86,29 @@ class ClockSampler:
                 self.proc.wait(timeout=5)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
-        sm, mx, reasons = [], 0, set()
+        sm, loaded, mx, reasons = [], [], 0, set()
         for line in self.lines:
             f = [x.strip() for x in line.split(",")]
-            if len(f) < 6:
+            if len(f) < 7:
                 continue
             try:
-                sm.append(int(f[0]))
+                clock = int(f[0])
                 mx = max(mx, int(f[1]))
             except ValueError:
                 continue
-            for name, v in zip(self.NAMES, f[2:6]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+            sm.append(clock)
+            try:
+                busy = int(f[6]) >= 50
+            except ValueError:
+                busy = False
+            if busy:
+                loaded.append(clock)
+                for name, v in zip(self.NAMES, f[2:6]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+        use = sorted(loaded or sm)
+        return {"sm_mhz": use[len(use) // 2] if use else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm), "samples_under_load": len(loaded)}
 
 
 def device_weights(config, seed, device):
@@ -175,6 +184,9 @@ def run_ours(args):
         torch.cuda.synchronize()
         return a.elapsed_time(b)
 
+    clocks = ClockSampler()
+    clocks.start()              # from before the first warm-up to after the last timed region
+
     # ---- prefill: one prompt (2,048 tokens unless asked otherwise) in one step, logits of the last place ----
     prefill_ms = []
     for i in range(5 + 3):                     # a step shape that keeps coming back is replayed from a graph
@@ -184,6 +196,7 @@ def run_ours(args):
         if i >= 5:
             prefill_ms.append(ms)
     prefill_ms = sorted(prefill_ms)[len(prefill_ms) // 2]
+    ops.check_device_errors(device)
     T = PREFILL
     prefill_flops = 2.0 * T * nums["linear_params"] + nums["attn_flops_per_key_query"] * T * (T + 1) / 2 \
         + 2.0 * nums["lm_head_params"]
@@ -191,7 +204,7 @@ def run_ours(args):
                "frac": round(prefill_flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
 
     # ---- decode on the device: K replays of the captured step ----
-    def decode_device(batch, tag, clocks=None):
+    def decode_device(batch, tag):
         reqs = [(tag, i) for i in range(batch)]
         last = []
         for r in reqs:
@@ -200,16 +213,13 @@ def run_ours(args):
         toks = runner.greedy_decode_on_device(reqs, last, W)          # warm-up (captures the graph)
         per_step = runner._decode_graph(batch).greedy_launches        # this package's kernels per replay
         last = toks[-1].tolist()
-        if clocks:
-            clocks.start()
         ms = timed(lambda: runner.greedy_decode_on_device(reqs, last, K))
-        clk = clocks.stop() if clocks else None
+        ops.check_device_errors(device)      # a kernel that gave up a wait would make the time meaningless
         for r in reqs:
             runner.end(r)
-        return ms, per_step, clk
+        return ms, per_step
 
-    clocks = ClockSampler()
-    ms_total, launches_per_step, clk = decode_device(args.batch, "main", clocks)
+    ms_total, launches_per_step = decode_device(args.batch, "main")
     ms_per_step = ms_total / K
     value = args.batch * K / (ms_total / 1e3)
     mean_ctx = START_CONTEXT + W + (K + 1) / 2.0
@@ -223,7 +233,7 @@ def run_ours(args):
     points = {}
     if args.points:
         for b in (1, 64):
-            ms_b, _, _ = decode_device(b, f"b{b}")
+            ms_b, _ = decode_device(b, f"b{b}")
             points[f"decode_b{b}"] = round(b * K / (ms_b / 1e3), 1)
 
     # ---- end to end through Engine.step: host ids in, host ids out ----
@@ -245,6 +255,8 @@ def run_ours(args):
         produced += len(engine.step())
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
+    clk = clocks.stop()
+    ops.check_device_errors(device)
     assert produced == args.batch * K, f"end-to-end run produced {produced} tokens, expected {args.batch * K}"
     e2e = {"value": round(produced / e2e_s, 1), "unit": "tok/s", "ms_per_step": round(e2e_s / K * 1e3, 4),
            "h2d_bytes_per_step": int((runner.h2d_bytes + getattr(engine.sampler, "h2d_bytes", 0)) / K),

@@ -46,6 +46,7 @@ _SIGNATURES = {
     "ni_sched_result": ([_P, _I, _LP, _I], _I),
     "ni_sched_advance": ([_P, _I, _LP, _IP, _I, _LP], _I),
     "ni_sched_commit": ([_P, _LL, _I], _I),
+    "ni_sched_abort": ([_P, _LL], _I),
     "ni_sched_can_continue": ([_P, _LP, _I], _I),
     "ni_sched_get": ([_P, _LL, _I], _I),
     "ni_sched_stat": ([_P, _I], _LL),

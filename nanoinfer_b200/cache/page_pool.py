@@ -1,4 +1,4 @@
-"""Free-list of cache pages (the compiled PagePool of csrc/host_cache.cpp behind a thin class).
+"""Free-list of cache pages (the compiled PagePool of csrc/host_runtime.cpp behind a thin class).
 
 Same contract as the reference's BlockManager without its prefix-cache bookkeeping
 (src/engine/block_manager.cpp:17-182): pages are handed out from a LIFO stack whose first

@@ -383,16 +383,6 @@ static int launch_decode(const void* q, const void* k_pages, const void* v_pages
     return e == cudaSuccess ? NI_OK : (int)e;
 }
 
-static int sm_count() {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    }
-    return n;
-}
-
 // Scratch floats needed: n_items * n_q_heads * n_splits * (head_dim + 2); tickets: n_items * n_kv_heads
 // ints, zero before the first launch (the kernel leaves them zero).
 NI_EXPORT int ni_attention_decode_fresh_keys() { return DEC_FRESH_KEYS; }
@@ -414,7 +404,7 @@ NI_EXPORT int ni_attention_decode(const void* q, const void* k_pages, const void
             // while all blocks fit the GPU at 3 per SM: fat blocks with 128-key buffers; beyond that
             // (large batches with one block per token and kv head, middle batches in two or three
             // splits): 64-key buffers, so that 4 fit an SM and 512 to 592 blocks are still one wave
-            if ((long long)n_items * n_kv_heads * n_splits <= 3LL * sm_count())
+            if ((long long)n_items * n_kv_heads * n_splits <= 3LL * ni_sm_count())
                 return launch_decode<64, 128>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
                                               block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
                                               scale_log2e, n_splits, scratch, tickets, stream);

@@ -71,6 +71,11 @@ __device__ __forceinline__ void at_mbar_arrive(uint64_t* bar) {
 // SLEEP: pause between tries (for the loader, which runs ahead and whose polls would only take
 // issue slots from the softmax warps); the others poll in a short loop, since every hand-over
 // between the MMA thread and the softmax warps is on the critical path of a tile.
+// The limit in clock ticks (set by ni_attention_prefill_tc_set_wait), and a switch for the tests: with
+// it the softmax warps wait once more at the end, for a phase that nothing completes.
+__constant__ long long at_wait_limit = 2000000000LL;
+__constant__ int at_extra_wait = 0;
+
 template <bool SLEEP>
 __device__ __forceinline__ bool at_wait_impl(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* error, int code) {
     const uint32_t addr = at_smem(bar);
@@ -88,7 +93,7 @@ __device__ __forceinline__ bool at_wait_impl(uint64_t* bar, uint32_t parity, vol
             if (*abort_flag) return false;
             const long long now = clock64();
             if (start == 0) start = now;
-            if (now - start > 2000000000LL) {
+            if (now - start > at_wait_limit) {
                 *abort_flag = 1;
                 atomicExch(error, code);
                 return false;
@@ -612,6 +617,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
             }
         }
+        if (at_extra_wait)                                     // tests: a phase that never completes
+            at_wait(&o_done[s], (uint32_t)n_tiles & 1u, abort_flag, p.error, AT_ERR_SOFTMAX);
     }
     at_fence_before();
     __syncthreads();
@@ -625,6 +632,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 typedef CUresult (*AtEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// ticks: how long a wait inside the kernel may last, in clock ticks (<= 0: the default of about a
+// second); extra_wait != 0: the softmax warps wait once more for a phase that never completes (for
+// the test of the give-up path).  Holds for the current device until set again.
+NI_EXPORT int ni_attention_prefill_tc_set_wait(long long ticks, int extra_wait) {
+    if (ticks <= 0) ticks = 2000000000LL;
+    cudaError_t e = cudaMemcpyToSymbol(at_wait_limit, &ticks, sizeof(ticks));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(at_extra_wait, &extra_wait, sizeof(extra_wait));
+    return e == cudaSuccess ? NI_OK : (int)e;
+}
 
 static AtEncodeTiledFn at_encode_tiled() {
     static AtEncodeTiledFn fn = nullptr;

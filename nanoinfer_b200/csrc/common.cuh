@@ -23,6 +23,20 @@
         return e__ == cudaSuccess ? NI_OK : (int)e__;  \
     } while (0)
 
+// Streaming multiprocessors of the current device (asked once per device; 148 on a B200).
+// Grid sizes and work splits are derived from it, never from a literal.
+static inline int ni_sm_count() {
+    static int cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (cached[dev] <= 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
 template <typename T> __device__ __forceinline__ float ni_to_float(T v);
 template <> __device__ __forceinline__ float ni_to_float<float>(float v) { return v; }
 template <> __device__ __forceinline__ float ni_to_float<__nv_bfloat16>(__nv_bfloat16 v) {

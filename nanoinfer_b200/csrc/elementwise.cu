@@ -170,7 +170,7 @@ NI_EXPORT int ni_residual_add(float* h, const void* delta, int delta_dtype, long
     if (n <= 0) return NI_OK;
     const int threads = 256;
     long long blocks = (n + threads - 1) / threads;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > ni_sm_count() * 16) blocks = ni_sm_count() * 16;
     if (delta_dtype == NI_DTYPE_F32)
         residual_add_kernel<float><<<(int)blocks, threads, 0, stream>>>(h, (const float*)delta, (size_t)n);
     else if (delta_dtype == NI_DTYPE_BF16)
@@ -228,7 +228,7 @@ NI_EXPORT int ni_swiglu_blocked(const void* gate_up, void* out, int dtype, int n
     if (inter <= 0 || inter % 8) return NI_ERR_BAD_ARGUMENT;
     const int threads = 256;
     long long blocks = ((long long)n_tokens * (inter / 8) + threads - 1) / threads;
-    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (blocks > ni_sm_count() * 32) blocks = ni_sm_count() * 32;
     if (dtype == NI_DTYPE_F32)
         swiglu_blocked_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, n_tokens, inter);
     else if (dtype == NI_DTYPE_BF16)
@@ -245,7 +245,7 @@ NI_EXPORT int ni_swiglu(const void* gate_up, void* out, int dtype, int n_tokens,
     if (inter <= 0) return NI_ERR_BAD_ARGUMENT;
     const int threads = 256;
     long long blocks = ((long long)n_tokens * inter + threads - 1) / threads;
-    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (blocks > ni_sm_count() * 32) blocks = ni_sm_count() * 32;
     if (dtype == NI_DTYPE_F32)
         swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, n_tokens, inter);
     else if (dtype == NI_DTYPE_BF16)

@@ -53,6 +53,12 @@ __device__ __forceinline__ void sw_mbar_expect_tx(uint64_t* bar, uint32_t bytes)
 __device__ __forceinline__ void sw_mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(sw_smem(bar)) : "memory");
 }
+// How long a wait on an mbarrier may last, in clock ticks (about a second), and a switch for the
+// tests: with it the epilogue warps wait once more at the end, for a phase that nothing completes.
+// Set by ni_gemm_swap_tc_set_wait.
+__constant__ long long sw_wait_limit = 2000000000LL;
+__constant__ int sw_extra_wait = 0;
+
 __device__ __forceinline__ bool sw_wait(uint64_t* bar, uint32_t parity, int* error, int code) {
     const uint32_t addr = sw_smem(bar);
     long long start = 0;
@@ -67,7 +73,7 @@ __device__ __forceinline__ bool sw_wait(uint64_t* bar, uint32_t parity, int* err
         if ((iter & 1023) == 1023) {
             const long long now = clock64();
             if (start == 0) start = now;
-            if (now - start > 2000000000LL) {
+            if (now - start > sw_wait_limit) {
                 atomicExch(error, code);
                 return false;
             }
@@ -362,6 +368,7 @@ gemm_swap_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 asm volatile("bar.sync 1, 128;\n" ::: "memory");   // last_flag is read before it is written again
             }
         }
+        if (sw_extra_wait) sw_wait(&acc_full[acc], acc_phase, p.error, SW_ERR_EPILOGUE);   // tests: a phase that never completes
     }
     sw_fence_before();
     __syncthreads();
@@ -389,6 +396,16 @@ static SwEncodeTiledFn sw_encode_tiled() {
     return fn;
 }
 
+// ticks: how long a wait inside the kernel may last, in clock ticks (<= 0: the default of about a
+// second); extra_wait != 0: the epilogue warps wait once more for a phase that never completes (for
+// the test of the give-up path).  Holds for the current device until set again.
+NI_EXPORT int ni_gemm_swap_tc_set_wait(long long ticks, int extra_wait) {
+    if (ticks <= 0) ticks = 2000000000LL;
+    cudaError_t e = cudaMemcpyToSymbol(sw_wait_limit, &ticks, sizeof(ticks));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(sw_extra_wait, &extra_wait, sizeof(extra_wait));
+    return e == cudaSuccess ? NI_OK : (int)e;
+}
+
 static int sw_make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
     SwEncodeTiledFn enc = sw_encode_tiled();
     if (!enc) return NI_ERR_BAD_ARGUMENT;
@@ -402,15 +419,7 @@ static int sw_make_map(CUtensorMap* map, const void* ptr, int rows, int K, int b
     return r == CUDA_SUCCESS ? NI_OK : NI_ERR_BAD_ARGUMENT;
 }
 
-static int sw_n_sms() {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    }
-    return n;
-}
+static int sw_n_sms() { return ni_sm_count(); }
 
 template <int BT, int MODE>
 static int launch_sw_mode(const CUtensorMap& mw, const CUtensorMap& mx, const SwParams& p, cudaStream_t stream) {

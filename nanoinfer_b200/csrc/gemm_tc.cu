@@ -48,7 +48,13 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(tc_smem(bar)) : "memory");
 }
-// Waits for the phase with the given parity; false if the wait ran out (about two seconds).
+// How long a wait on an mbarrier may last, in clock ticks (about two seconds), and a switch for the
+// tests: with it the epilogue warps wait once more at the end, for a phase that nothing completes, so
+// that a wait runs out, the kernel records it and returns.  Set by ni_gemm_tc_set_wait.
+__constant__ long long tc_wait_limit = 4000000000LL;
+__constant__ int tc_extra_wait = 0;
+
+// Waits for the phase with the given parity; false if the wait ran out.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = tc_smem(bar);
     const long long start = clock64();
@@ -60,7 +66,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
             "selp.b32 %0, 1, 0, p;\n}\n"
             : "=r"(done) : "r"(addr), "r"(parity) : "memory");
         if (done) return true;
-        if (clock64() - start > 4000000000LL) return false;
+        if (clock64() - start > tc_wait_limit) return false;
     }
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -292,6 +298,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             mbar_arrive(&acc_empty[acc]);
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
+        if (tc_extra_wait && !mbar_wait(&acc_full[acc], acc_phase))     // tests: a phase that never completes
+            atomicExch(p.error, TC_ERR_TIMEOUT_EPILOGUE);
     }
     tc_fence_before();
     __syncthreads();
@@ -350,6 +358,16 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
     const int grid = tiles < n_sms ? tiles : n_sms;
     gemm_tc_kernel<BN, STAGES><<<grid, TC_THREADS, smem, stream>>>(ma, mb, p);
     NI_RETURN_LAUNCH_STATUS();
+}
+
+// ticks: how long a wait inside the kernel may last, in clock ticks (<= 0: the default of about two
+// seconds); extra_wait != 0: the epilogue warps wait once more for a phase that never completes (for
+// the test of the give-up path).  Holds for the current device until set again.
+NI_EXPORT int ni_gemm_tc_set_wait(long long ticks, int extra_wait) {
+    if (ticks <= 0) ticks = 4000000000LL;
+    cudaError_t e = cudaMemcpyToSymbol(tc_wait_limit, &ticks, sizeof(ticks));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(tc_extra_wait, &extra_wait, sizeof(extra_wait));
+    return e == cudaSuccess ? NI_OK : (int)e;
 }
 
 // a: bf16 [M, K]; b: bf16 [N, K]; K a multiple of 8; both 16-byte aligned.  mode 0 store bf16 [M, N],

@@ -329,7 +329,7 @@ static int dispatch_gemv(const GemvParams& p, bool norm, cudaStream_t stream) {
     if (p.K <= 0 || p.mode < 0 || p.mode > GV_ROPE_KV) return NI_ERR_BAD_ARGUMENT;
     if (p.M > 16 || p.K % 8) return NI_ERR_UNSUPPORTED_SIZE;
     // 16 rows per tile unless that leaves SMs idle; the fused epilogues need whole 16-row tiles
-    const bool rn16 = p.mode >= GV_SWIGLU || (p.N + 15) / 16 >= 2 * 148;
+    const bool rn16 = p.mode >= GV_SWIGLU || (p.N + 15) / 16 >= 2 * ni_sm_count();
     if (p.mode == GV_SWIGLU && p.N % 16) return NI_ERR_UNSUPPORTED_SIZE;
     if (p.mode == GV_ROPE_KV && (p.head_dim % 16 || p.rotary_dim % 2 ||
                                  p.N != (p.n_q_heads + 2 * p.n_kv_heads) * p.head_dim))
@@ -345,7 +345,7 @@ static int dispatch_gemv(const GemvParams& p, bool norm, cudaStream_t stream) {
     int tpb = 1;
     if (keep) {
         const int tiles = (p.N + (rn16 ? 16 : 8) - 1) / (rn16 ? 16 : 8);
-        const int blocks = ((one && unroll == 4) ? 2 : 1) * 148;
+        const int blocks = ((one && unroll == 4) ? 2 : 1) * ni_sm_count();
         tpb = (tiles + blocks - 1) / blocks;
         if (tpb < 1) tpb = 1;
     }

@@ -577,6 +577,22 @@ NI_HOST_EXPORT int ni_sched_commit(void* s, long long id, int finished) {
     }
     return kOk;
 }
+// Ends a request in any state as failed (a device error made its cache contents worthless, or the
+// caller gives it up): it leaves the running list or the waiting queue, its pages and slot are given
+// back, tokens on the way are forgotten.  Returns 1 if it was alive, 0 if it had ended before.
+NI_HOST_EXPORT int ni_sched_abort(void* s, long long id) {
+    auto* sc = static_cast<Scheduler*>(s);
+    auto it = sc->reqs.find(id);
+    if (it == sc->reqs.end()) return kErrArgument;
+    SchedRequest& r = it->second;
+    if (r.state == kFinished || r.state == kFailed) return 0;
+    if (r.state == kRunning) sc->drop(id);
+    else sc->waiting.erase(std::remove(sc->waiting.begin(), sc->waiting.end(), id), sc->waiting.end());
+    r.state = kFailed;
+    r.n_pending = 0;
+    ++sc->n_finished;
+    return 1;
+}
 NI_HOST_EXPORT int ni_sched_can_continue(void* s, const long long* prev, int n_prev) {
     return static_cast<Scheduler*>(s)->can_continue(prev, n_prev) ? 1 : 0;
 }

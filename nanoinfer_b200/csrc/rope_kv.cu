@@ -195,7 +195,7 @@ NI_EXPORT int ni_rope_kv_write(const void* qkv, int dtype, void* q_out, void* k_
     if (interleaved && head_dim % 8 == 0) {
         const int items = (n_q_heads + 2 * n_kv_heads) * (head_dim / 8);
         const int threads = items >= 512 ? 256 : (items >= 256 ? 128 : 64);      // about four chunks per thread
-        const int blocks = n_tokens < 148 * 16 ? n_tokens : 148 * 16;
+        const int blocks = n_tokens < ni_sm_count() * 16 ? n_tokens : ni_sm_count() * 16;
 #define LAUNCHV(T)                                                                                     \
     rope_kv_write_vec_kernel<T><<<blocks, threads, rotary_dim * sizeof(float), stream>>>(               \
         (const T*)qkv, (T*)q_out, (T*)k_pages, (T*)v_pages, positions, seq_of_token, block_table,     \

@@ -49,6 +49,8 @@ class _InFlight:
     ids: Optional[torch.Tensor]              # the sampled ids where the sampler left them
     host: Optional[torch.Tensor] = None      # their copy on the host (pinned when ids are on a GPU)
     ready: Optional["torch.cuda.Event"] = None
+    error: Optional[torch.Tensor] = None     # the device's error word as it stood after this step, on the host
+    epoch: int = 0                           # how many device errors the engine had seen when this step was launched
 
 
 class Engine:
@@ -67,8 +69,10 @@ class Engine:
         self._running = False
         self.num_steps = 0
         self._inflight: Optional[_InFlight] = None
-        self._pinned: List[torch.Tensor] = []       # two buffers for sampled ids, used in turn
+        self._pinned: List[torch.Tensor] = []       # two buffers for sampled ids (+ the error word), used in turn
         self._pinned_next = 0
+        self._device_error: Optional[Exception] = None
+        self._error_epoch = 0
 
     @classmethod
     def from_model_dir(cls, model_dir: str, config: Optional[EngineConfig] = None, **overrides) -> "Engine":
@@ -161,6 +165,10 @@ class Engine:
         if launched is not None and not self._may_stay_in_flight(launched):
             outputs += self._collect(launched)
             self._inflight = None
+        if self._device_error is not None:
+            err, self._device_error = self._device_error, None
+            self.last_outputs = outputs        # what was booked before the error is not lost
+            raise err
         return outputs
 
     def _may_stay_in_flight(self, step: _InFlight) -> bool:
@@ -190,24 +198,33 @@ class Engine:
             logits = self.runner.step(entries, device_tokens=feed.ids)
         else:
             logits = self.runner.step(entries)
-        step = _InFlight(batch, emitting, None)
+        step = _InFlight(batch, emitting, None, epoch=self._error_epoch)
         if emitting:
             step.ids = self.sampler.sample(
                 logits, [r.sampling_params for r in emitting], [r.seed for r in emitting],
                 [len(r.generated_tokens) + r.num_pending for r in emitting], [r.generated_tokens for r in emitting])
+            # the error word of the device rides with the ids: a kernel that gave up a bounded wait
+            # during this step (or an earlier one that emitted nothing) is seen when they are read
+            word = getattr(self.runner, "error_word", None)
+            n = len(emitting)
             if step.ids.is_cuda:
                 if not self._pinned:
-                    cap = max(self.config.max_batch_size, len(emitting))
+                    cap = max(self.config.max_batch_size, n) + 1
                     self._pinned = [torch.empty(cap, dtype=torch.int32, pin_memory=True) for _ in range(2)]
-                if len(emitting) > self._pinned[0].numel():
-                    self._pinned = [torch.empty(2 * len(emitting), dtype=torch.int32, pin_memory=True) for _ in range(2)]
-                step.host = self._pinned[self._pinned_next][:len(emitting)]
+                if n + 1 > self._pinned[0].numel():
+                    self._pinned = [torch.empty(2 * n + 1, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+                buf = self._pinned[self._pinned_next]
                 self._pinned_next ^= 1
+                step.host = buf[:n]
                 step.host.copy_(step.ids, non_blocking=True)
+                if word is not None:
+                    step.error = buf[n:n + 1]
+                    step.error.copy_(word, non_blocking=True)
                 step.ready = torch.cuda.Event()
                 step.ready.record()
             else:
                 step.host = step.ids
+                step.error = word
         self.scheduler.advance(batch, emitting)
         self.num_steps += 1
         return step
@@ -218,12 +235,35 @@ class Engine:
             return []
         if step.ready is not None:
             step.ready.synchronize()
+        if step.epoch != self._error_epoch:
+            return []          # launched before a device error was seen: its requests have failed already
+        code = int(step.error[0]) if step.error is not None else 0
+        if code:
+            self._fail_running(code)
+            return []
         sampled: Dict[int, int] = {}
         for req, tok in zip(step.emitting, step.host.tolist()):
             if not req.is_finished() and req.num_pending > 0:      # else: it ended meanwhile
                 sampled[req.request_id] = int(tok)
         done = {r.request_id for r in self.scheduler.commit(sampled)}
         return [StepOutput(rid, tok, rid in done) for rid, tok in sampled.items()]
+
+    def _fail_running(self, code: int) -> None:
+        """A kernel gave up a bounded wait: what the steps since the last check computed and wrote
+        into the cache is not to be trusted.  Every running request fails with reason
+        "device_error" (pages and slots given back); waiting requests are untouched and the engine
+        goes on.  step() raises a KernelError once the books are in order."""
+        from ..kernels import ops
+        word = getattr(self.runner, "error_word", None)
+        if word is not None:
+            word.zero_()
+        for req in self.scheduler.running_requests():
+            self.scheduler.abort(req, "device_error")
+        self._error_epoch += 1
+        if self._device_error is None:
+            self._device_error = ops.KernelError(
+                f"a kernel gave up waiting ({ops.describe_device_error(code)}); the running requests "
+                f"have failed with reason 'device_error', the engine can go on")
 
     def run(self) -> None:
         """Step until no request is waiting or running (or stop() is called)."""

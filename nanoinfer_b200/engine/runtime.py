@@ -83,8 +83,10 @@ class Runtime:
         batch is small (SwiGLU at up to 32 rows: 14.6 us against 12.5 + 3.9)."""
         if self.dtype != torch.bfloat16 or not ops.SKINNY_ROWS < n_rows <= ops.SWAP_MAX_ROWS or k % 8:
             return False
+        if ops.gemm_swap_scratch(n_rows, n_out, k) != 0:
+            return False          # the kernel would split K: the callers here pass no scratch
         tiles = -(-n_out // 128)
-        if tiles >= 4 * 148:
+        if tiles >= 4 * ops.sm_count(self.device):
             return True
         return fused and tiles >= 100 and n_rows <= 32
 

@@ -139,6 +139,17 @@ class Scheduler:
                 finished.append(req)
         return finished
 
+    def abort(self, req: InferenceRequest, reason: str) -> bool:
+        """End a request as failed, whatever its state; its pages and slot are given back.
+        Returns False if it had ended before."""
+        if self._lib.ni_sched_abort(self._h, req.request_id) != 1:
+            return False
+        req.fail(reason)
+        return True
+
+    def running_requests(self) -> List[InferenceRequest]:
+        return [r for r in self.requests.values() if r._ended is None and self.request_field(r.request_id, 0) == 1]
+
     def update_after_step(self, batch: ScheduledBatch, sampled: Dict[int, int]) -> List[InferenceRequest]:
         """advance + commit in one call, for a step whose tokens are read at once."""
         self.advance(batch, [req for req, _ in batch.entries if req.request_id in sampled])

@@ -193,6 +193,7 @@ class ModelRunner:
                 src = self.caches[run.cache_of]
                 self.caches[r] = CacheView(group=src.group, k_pages=src.k_pages, v_pages=src.v_pages,
                                            state=src.state, writable=False)
+        self.error_word = ops.error_word(self.rt.device)   # non-zero once a kernel gave up a bounded wait
         self.use_graphs = True
         self.h2d_bytes = 0            # bytes of step metadata copied to the device so far
         self.max_graph_batch = 256

@@ -54,17 +54,21 @@ _SIGNATURES = {
     "attention_prefill_tc": {
         "ni_attention_prefill_tc": [_P, _P, _P, _P, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P],
         "ni_attention_prefill_tc_supports": [_I, _I, _I, _I],
+        "ni_attention_prefill_tc_set_wait": [_LL, _I],
     },
     "gemm_swap_tc": {
         "ni_gemm_swap_tc": [_P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
         "ni_gemm_swap_tc_splits": [_I, _I, _I],
         "ni_gemm_swap_tc_scratch": [_I, _I, _I],
+        "ni_gemm_swap_tc_set_wait": [_LL, _I],
     },
     "gemm_tc2": {
         "ni_gemm_tc2": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
+        "ni_gemm_tc2_set_wait": [_LL, _I],
     },
     "gemm_tc": {
         "ni_gemm_tc": [_P, _P, _P, _I, _I, _I, _I, _P, _P],
+        "ni_gemm_tc_set_wait": [_LL, _I],
     },
     "sampling": {
         "ni_argmax": [_P, _P, _I, _I, _P, _P],
@@ -108,6 +112,18 @@ def preload(modules) -> None:
         load(m)
 
 
+_sm_counts: Dict[int, int] = {}
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of the device (148 on a B200); every work split asks here."""
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index or 0
+    n = _sm_counts.get(idx)
+    if n is None:
+        n = _sm_counts[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return n
+
+
 _launches = 0
 
 
@@ -124,6 +140,14 @@ def _check(code: int, what: str) -> None:
     if code < 0:
         raise KernelError(f"{what}: {_ERRORS.get(code, f'error {code}')}")
     raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def _check_plain(code: int, what: str) -> None:
+    """As _check, for calls that launch nothing."""
+    if code < 0:
+        raise KernelError(f"{what}: {_ERRORS.get(code, f'error {code}')}")
+    if code > 0:
+        raise KernelError(f"{what}: CUDA error {code}")
 
 
 def _stream() -> int:
@@ -383,25 +407,68 @@ def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
 
 _error_words: Dict[torch.device, torch.Tensor] = {}
 
+# What the codes in the error word stand for (each kernel writes its own when a bounded wait runs out).
+DEVICE_ERROR_CODES = {
+    1: "tensor-core product (gemm_tc / gemm_tc2): the loader gave up waiting for a free stage",
+    2: "tensor-core product (gemm_tc / gemm_tc2): the MMA issuer gave up waiting",
+    3: "tensor-core product (gemm_tc / gemm_tc2): the epilogue gave up waiting for an accumulator",
+    11: "tensor-core prefill attention: the loader gave up waiting",
+    12: "tensor-core prefill attention: the MMA issuer gave up waiting",
+    13: "tensor-core prefill attention: the softmax warps gave up waiting",
+    21: "swapped-operand product (gemm_swap_tc): the loader gave up waiting",
+    22: "swapped-operand product (gemm_swap_tc): the MMA issuer gave up waiting",
+    23: "swapped-operand product (gemm_swap_tc): the epilogue gave up waiting",
+    31: "fused decode step (decode_fused): a grid barrier was not reached by every block in time",
+    32: "fused decode step (decode_fused): the weight loader gave up waiting for a free stage",
+    33: "fused decode step (decode_fused): a consumer gave up waiting for its weights",
+}
 
-def _error_word(device: torch.device) -> torch.Tensor:
+
+def error_word(device) -> torch.Tensor:
+    """The device's error word: int32 [1], zero unless a kernel recorded that one of its bounded
+    waits ran out.  The engine copies it to the host with every step's sampled ids."""
+    device = torch.device(device)
+    if device.index is None:
+        device = torch.device(device.type, torch.cuda.current_device())
     w = _error_words.get(device)
     if w is None:
         w = _error_words[device] = torch.zeros(1, dtype=torch.int32, device=device)
     return w
 
 
+_error_word = error_word
+
+
+def describe_device_error(code: int) -> str:
+    return f"code {code}: {DEVICE_ERROR_CODES.get(code, 'unknown kernel')}"
+
+
 def check_device_errors(device=None) -> None:
-    """Raise if a kernel recorded that one of its bounded waits ran out (synchronises)."""
+    """Raise if a kernel recorded that one of its bounded waits ran out (synchronises), and
+    clear the record."""
     for dev, w in _error_words.items():
         if device is not None and dev != torch.device(device):
             continue
         code = int(w.item())
         if code:
             w.zero_()
-            raise KernelError(f"a kernel on {dev} gave up waiting (code {code}: 1 = loader, 2 = MMA issuer, "
-                              f"3 = epilogue of the tensor-core product; 21-23 the same of the swapped-operand product; 11 = loader, 12 = MMA issuer, "
-                              f"13 = softmax of the tensor-core prefill attention)")
+            raise KernelError(f"a kernel on {dev} gave up waiting ({describe_device_error(code)}); "
+                              f"the results of that step are not valid")
+
+
+_WAIT_SETTERS = {"gemm_tc": "ni_gemm_tc_set_wait", "gemm_tc2": "ni_gemm_tc2_set_wait",
+                 "gemm_swap_tc": "ni_gemm_swap_tc_set_wait",
+                 "attention_prefill_tc": "ni_attention_prefill_tc_set_wait"}
+
+
+def set_wait_limit(module: str, ticks: int = 0, extra_wait: bool = False) -> None:
+    """How long a wait inside the module's kernels may last, in clock ticks (0: the default of one
+    to two seconds).  ``extra_wait`` makes the kernels wait once more at their end for something
+    that never comes - the way the tests make a bounded wait run out."""
+    if module not in _WAIT_SETTERS:
+        raise KernelError(f"module '{module}' has no bounded waits to set")
+    _check_plain(getattr(load(module), _WAIT_SETTERS[module])(int(ticks), 1 if extra_wait else 0),
+                 f"set_wait_limit({module})")
 
 
 def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, mode: int, kernel: Optional[str] = None,
@@ -498,7 +565,7 @@ DECODE_BLOCKS_PER_SM = 4
 DECODE_FRESH_KEYS = 2
 
 
-def decode_splits(n_items: int, n_kv_heads: int, head_dim: int, max_kv_len: int) -> int:
+def decode_splits(n_items: int, n_kv_heads: int, head_dim: int, max_kv_len: int, n_sms: Optional[int] = None) -> int:
     """How many blocks share one (token, kv head): as many as fill the GPU once (three blocks of
     the split kernel are resident per SM; a second wave costs more than longer blocks), each with
     at least 384 keys of the longest context - 256 when there are few pairs, whose blocks are
@@ -508,9 +575,11 @@ def decode_splits(n_items: int, n_kv_heads: int, head_dim: int, max_kv_len: int)
     More pairs than the GPU holds at once: one lean block per pair with heads of 64 (four of
     those fit an SM); with heads of 128 (three per SM) the count, up to 4, that fills the last
     wave best (512 pairs: 58 % of two waves unsplit, 87 % of four waves in three parts)."""
+    if n_sms is None:
+        n_sms = sm_count()
     pairs = max(1, n_items * n_kv_heads)
     chunks = -(-max_kv_len // 64)                 # the kernel cuts a context into 64-key chunks
-    slots = 148 * 3
+    slots = n_sms * 3
     if head_dim > 64 and pairs > slots:
         best, best_fill = 1, 0.0
         for s in range(1, 5):
@@ -521,10 +590,10 @@ def decode_splits(n_items: int, n_kv_heads: int, head_dim: int, max_kv_len: int)
                 best, best_fill = s, fill
         per_split = -(-chunks // best)
         return max(1, -(-chunks // per_split))
-    if (148 * DECODE_BLOCKS_PER_SM) // pairs <= 1:
+    if (n_sms * DECODE_BLOCKS_PER_SM) // pairs <= 1:
         return 1                                  # large batch: one lean block per pair
-    if pairs > 148 and head_dim <= 64:            # more than one pair per SM: lean blocks, four per SM
-        slots = 148 * DECODE_BLOCKS_PER_SM
+    if pairs > n_sms and head_dim <= 64:          # more than one pair per SM: lean blocks, four per SM
+        slots = n_sms * DECODE_BLOCKS_PER_SM
     fill = slots // pairs
     keys_per_split = 256 if pairs <= 16 else 384
     target = max(1, min(64, fill, -(-max_kv_len // keys_per_split)))

@@ -11,7 +11,7 @@ from nanoinfer_b200.kernels import ops
 def test_decode_splits_are_bounded_and_leave_no_empty_split(head_dim):
     for n_items, n_kv, ctx in itertools.product([1, 2, 3, 8, 16, 19, 24, 32, 37, 40, 56, 64, 96, 128, 300],
                                                 [1, 2, 8], [1, 63, 64, 65, 500, 2112, 3072, 4096, 16384, 131072]):
-        s = ops.decode_splits(n_items, n_kv, head_dim, ctx)
+        s = ops.decode_splits(n_items, n_kv, head_dim, ctx, n_sms=148)
         assert 1 <= s <= 64
         chunks = -(-ctx // 64)
         assert s <= chunks                                  # a split holds at least one 64-key chunk
@@ -23,17 +23,17 @@ def test_decode_splits_are_bounded_and_leave_no_empty_split(head_dim):
 
 def test_decode_splits_follow_the_resident_blocks():
     # few pairs: as many fat blocks as fit at three per SM, of at least 256 / 384 keys
-    assert ops.decode_splits(1, 8, 64, 3072) == 12
-    assert ops.decode_splits(8, 8, 64, 3072) == 6
-    assert 8 * 8 * ops.decode_splits(8, 8, 64, 131072) <= 3 * 148
+    assert ops.decode_splits(1, 8, 64, 3072, n_sms=148) == 12
+    assert ops.decode_splits(8, 8, 64, 3072, n_sms=148) == 6
+    assert 8 * 8 * ops.decode_splits(8, 8, 64, 131072, n_sms=148) <= 3 * 148
     # middle batches of 64-wide heads: lean blocks, four per SM
-    assert ops.decode_splits(32, 8, 64, 3072) == 2 and 32 * 8 * 2 <= 4 * 148
-    assert ops.decode_splits(24, 8, 64, 3072) == 3
+    assert ops.decode_splits(32, 8, 64, 3072, n_sms=148) == 2 and 32 * 8 * 2 <= 4 * 148
+    assert ops.decode_splits(24, 8, 64, 3072, n_sms=148) == 3
     # large batches: one block per pair with heads of 64; with heads of 128 the last wave is filled
-    assert ops.decode_splits(64, 8, 64, 3072) == 1
-    assert ops.decode_splits(64, 8, 128, 7168) == 4
-    assert ops.decode_splits(64, 8, 128, 300) == 1           # too short to split
-    assert ops.decode_splits(32, 8, 128, 3072) == 1          # three per SM: 256 blocks are one wave
+    assert ops.decode_splits(64, 8, 64, 3072, n_sms=148) == 1
+    assert ops.decode_splits(64, 8, 128, 7168, n_sms=148) == 4
+    assert ops.decode_splits(64, 8, 128, 300, n_sms=148) == 1           # too short to split
+    assert ops.decode_splits(32, 8, 128, 3072, n_sms=148) == 1          # three per SM: 256 blocks are one wave
 
 
 def test_tensor_core_prefill_attention_cases():

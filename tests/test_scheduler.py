@@ -205,3 +205,37 @@ def test_overlap_can_be_switched_off():
     assert [o.request_id for o in eng.step()] == [a]
     eng.run()
     assert runner.fed_steps == 0 and eng.get_request_result(a) == expected_continuation([1, 2, 3], 5, 50)
+
+
+@pytest.mark.parametrize("overlap", [False, True])
+def test_a_device_error_word_fails_the_running_requests_and_the_engine_goes_on(overlap):
+    """The runner's error word (set by a kernel that gave up a bounded wait) is read with every
+    step's sampled ids: the step raises, the running requests fail and give back what they hold,
+    a waiting request is untouched, and after the word is cleared the engine serves on."""
+    import torch
+    from nanoinfer_b200.kernels.ops import KernelError
+    runner = FakeFeedingRunner(num_pages=64, max_tokens=128) if overlap else FakeRunner(num_pages=64, max_tokens=128)
+    runner.error_word = torch.zeros(1, dtype=torch.int32)
+    eng, _ = make(runner, max_sequences=2, overlap_steps=overlap)
+    a = eng.add_request([1, 2, 3], 10)
+    b = eng.add_request([4, 5], 10)
+    c = eng.add_request([7, 7, 7], 6)                 # waits: only two requests run at once
+    for _ in range(3):
+        eng.step()
+    assert eng.get_request(c).state == RequestState.WAITING
+    runner.error_word[0] = 13                          # "a kernel gave up" during the step that comes next
+    with pytest.raises(KernelError, match="code 13.*softmax"):
+        for _ in range(3):
+            eng.step()
+    assert int(runner.error_word[0]) == 0              # cleared, so that later steps are judged on their own
+    for rid in (a, b):
+        assert eng.get_request(rid).state == RequestState.FAILED
+        assert eng.get_request(rid).finish_reason == "device_error"
+    assert eng.get_request(c).state in (RequestState.WAITING, RequestState.RUNNING)   # admitted after the error at the earliest
+    eng.run()                                          # no second report; the waiting request is served
+    assert eng.get_request_result(c) == expected_continuation([7, 7, 7], 6, 50)
+    d = eng.add_request([1, 2, 3], 4)
+    eng.run()
+    assert eng.get_request_result(d) == expected_continuation([1, 2, 3], 4, 50)
+    runner.cache.check_consistency()
+    assert runner.cache.num_free_pages() == 64 and runner.cache.num_free_slots == 4
