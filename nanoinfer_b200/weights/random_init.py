@@ -11,7 +11,7 @@ from __future__ import annotations
 import hashlib
 import json
 import os
-from typing import Any, Dict, Iterator, Tuple
+from typing import Any, Dict, Iterator, Optional, Tuple
 
 import torch
 
@@ -25,8 +25,12 @@ def _tensor_seed(seed: int, name: str) -> int:
     return int.from_bytes(h[:8], "little") & ((1 << 63) - 1)
 
 
-def random_tensors(config, seed: int, std: float = 0.02,
-                   dtype: torch.dtype = torch.bfloat16) -> Iterator[Tuple[str, torch.Tensor]]:
+def random_tensors(config, seed: int, std: float = 0.02, dtype: torch.dtype = torch.bfloat16,
+                   slot_std: Optional[Dict[str, float]] = None) -> Iterator[Tuple[str, torch.Tensor]]:
+    """``slot_std``: another standard deviation for the weights of some slots, by slot name (for
+    instance {"q": 0.14, "k": 0.14} gives a model whose attention is peaked instead of nearly
+    uniform; the values drawn are the same, scaled)."""
+    slot_std = slot_std or {}
     for p in tensor_plan(config):
         if p.init == "ones":
             yield p.name, torch.ones(p.shape, dtype=dtype)
@@ -35,15 +39,15 @@ def random_tensors(config, seed: int, std: float = 0.02,
         else:
             g = torch.Generator(device="cpu")
             g.manual_seed(_tensor_seed(seed, p.name))
-            yield p.name, (torch.randn(p.shape, generator=g, dtype=torch.float32) * std).to(dtype)
+            yield p.name, (torch.randn(p.shape, generator=g, dtype=torch.float32) * slot_std.get(p.slot, std)).to(dtype)
 
 
 def write_random_model(model_dir: str, raw_config: Dict[str, Any], seed: int, std: float = 0.02,
-                       dtype: torch.dtype = torch.bfloat16) -> None:
+                       dtype: torch.dtype = torch.bfloat16, slot_std: Optional[Dict[str, float]] = None) -> None:
     """Create ``model_dir`` with config.json (``raw_config`` as given) and model.safetensors."""
     config = registry.config_from_dict(raw_config)
     os.makedirs(model_dir, exist_ok=True)
     with open(os.path.join(model_dir, "config.json"), "w", encoding="utf-8") as f:
         json.dump(raw_config, f, indent=1, sort_keys=True)
     write_safetensors(os.path.join(model_dir, "model.safetensors"),
-                      random_tensors(config, seed, std, dtype))
+                      random_tensors(config, seed, std, dtype, slot_std))

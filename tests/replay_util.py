@@ -87,6 +87,61 @@ def mixed(requests, max_live=4, prefill_sizes=(5, 2, 13, 3, 24, 2), tail=6, seed
     return steps
 
 
+def wide(requests, n_live, tail=8, joiners=2, per_prefill_step=6):
+    """Many requests decoding together.  ``requests`` holds 2 * n_live + joiners requests:
+    a first group of ``n_live`` is prefilled (several whole prompts per step), then decodes its
+    last ``tail`` tokens together, one step of n_live single tokens after the other; beside some of
+    those steps the ``joiners`` bring their prompts in portions and then decode along.  When the
+    first group has ended, a second group of n_live takes over its pages (its prompts run beside
+    the joiners' single tokens) and decodes together with the joiners."""
+    items = list(requests.items())
+    assert len(items) == 2 * n_live + joiners
+    first, late, second = items[:n_live], items[n_live:n_live + joiners], items[n_live + joiners:]
+    fed = {rid: 0 for rid, _ in items}
+    steps = []
+
+    def portion(rid, toks, n):
+        a = fed[rid]
+        fed[rid] = a + n
+        return {"id": rid, "tokens": toks[a:a + n], "want": list(range(n))}
+
+    def push(entries):
+        end = [e["id"] for e in entries if fed[e["id"]] == len(requests[e["id"]])]
+        steps.append({"step": len(steps), "entries": entries, "end": end})
+
+    def prefill(group, beside=()):
+        for at in range(0, len(group), per_prefill_step):
+            entries = [portion(rid, toks, len(toks) - tail) for rid, toks in group[at:at + per_prefill_step]]
+            entries += [portion(rid, toks, 1) for rid, toks in beside if fed[rid] < len(toks)]
+            push(entries)
+
+    def decode(group, others):
+        """All of ``group`` one token per step until it ends; ``others`` bring portions of 2..9
+        tokens in every second step until only their tail is left, then single tokens."""
+        k = 0
+        while any(fed[rid] < len(toks) for rid, toks in group):
+            entries = [portion(rid, toks, 1) for rid, toks in group if fed[rid] < len(toks)]
+            for j, (rid, toks) in enumerate(others):
+                left = len(toks) - fed[rid]
+                if left <= 0:
+                    continue
+                if left > tail:
+                    if k % 2 == j % 2:
+                        entries.append(portion(rid, toks, min(2 + (3 * k + 5 * j) % 8, left - tail)))
+                else:
+                    entries.append(portion(rid, toks, 1))
+            push(entries)
+            k += 1
+
+    prefill(first)
+    decode(first, late)
+    prefill(second, beside=late)
+    decode(second, late)
+    decode([x for x in late if fed[x[0]] < len(x[1])], [])
+    assert all(fed[rid] == len(toks) for rid, toks in items)
+    return steps
+
+
 def max_live_tokens(steps, round_to=64):
     """The most tokens live requests hold at any time, each rounded up to ``round_to``."""
     held, peak = {}, 0

@@ -23,6 +23,8 @@ SETUP = {
     "b": (8, [1, 7, 40, 90, 130, 300, 47]),
     "c": (16, [3, 48, 250, 611, 97]),
     "d": (16, [2, 129, 700, 65, 310]),
+    "ds": (16, [2, 129, 700, 65, 310]),       # D untied, peaked attention
+    "e": (16, [3, 130, 515, 66, 300]),        # heads of 128 in groups of three, peaked attention
 }
 CUTS = {"whole": ru.whole, "tail": ru.tail_by_token, "ragged": ru.ragged, "mixed": ru.mixed}
 
@@ -45,7 +47,7 @@ def _plain(plain_cache, key, model_dir):
     return plain_cache[key]
 
 
-def _runner(model_dir, dtype, page, steps):
+def _runner(model_dir, dtype, page, steps, max_requests=4):
     from nanoinfer_b200.config import load_config
     from nanoinfer_b200.engine import ModelRunner
     from nanoinfer_b200.weights import load_weights
@@ -53,12 +55,27 @@ def _runner(model_dir, dtype, page, steps):
     # exactly as many pages as the trace needs at its fullest (requests rounded up to 64)
     num_pages = ru.max_live_tokens(steps, 64) // page
     return ModelRunner(cfg, load_weights(model_dir, cfg), dtype=dtype, page_size=page,
-                       num_pages=num_pages, max_requests=4)
+                       num_pages=num_pages, max_requests=max_requests)
+
+
+class _Spy:
+    """Counts the calls of one function of nanoinfer_b200.kernels.ops and keeps what ``note``
+    extracts from each call's arguments; the function itself runs unchanged."""
+
+    def __init__(self, monkeypatch, name, note):
+        from nanoinfer_b200.kernels import ops
+        self.seen = []
+        inner = getattr(ops, name)
+
+        def wrapper(*args, **kw):
+            self.seen.append(note(*args, **kw))
+            return inner(*args, **kw)
+        monkeypatch.setattr(ops, name, wrapper)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("cut", ["whole", "tail", "ragged", "mixed"])
-@pytest.mark.parametrize("key", ["a", "b", "c", "d"])
+@pytest.mark.parametrize("key", ["a", "b", "c", "d", "ds", "e"])
 def test_replay_matches_plain(model_dirs, plain_cache, key, cut, dtype):
     raw, reqs, want = _plain(plain_cache, key, model_dirs[key])
     steps = CUTS[cut](reqs)
@@ -68,6 +85,65 @@ def test_replay_matches_plain(model_dirs, plain_cache, key, cut, dtype):
     ru.compare(got, want, dtype, label=f"{key}/{cut}/{dtype}")
     runner.cache.check_consistency()
     assert runner.cache.num_free_pages(0) == runner.cache.pools[0].num_pages
+
+
+def _wide_requests(raw, n_live, tail, seed):
+    import random
+    rng = random.Random(seed)
+    lens = [rng.randint(tail + 2, tail + 50) for _ in range(n_live)] + [tail + 18, tail + 27] + \
+           [rng.randint(tail + 2, tail + 50) for _ in range(n_live)]
+    return {f"w{i}": random_tokens(raw["vocab_size"], n, seed * 1000 + i) for i, n in enumerate(lens)}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_live", [12, 33, 64])
+@pytest.mark.parametrize("key", ["ds", "e"])
+def test_wide_decode_batches_match_plain(model_dirs, monkeypatch, key, n_live, dtype):
+    """12, 33 and 64 requests decoding together, prompt portions of others beside them in some
+    steps, a second group that takes over the first group's pages: with more than eight rows every
+    projection leaves the skinny kernel for the library product (or the swapped-operand kernel) with
+    stand-alone norm, rotary and activation kernels, and the decode attention runs with many rows.
+    Logits at every position against the plain implementation, and a check that those routes ran."""
+    raw, w = load_plain(model_dirs[key])
+    tail = 12
+    reqs = _wide_requests(raw, n_live, tail, seed=n_live)
+    steps = ru.wide(reqs, n_live, tail=tail)
+    assert sum(1 for s in steps if len(s["entries"]) == n_live and all(len(e["tokens"]) == 1 for e in s["entries"])) >= tail
+    decode_rows = _Spy(monkeypatch, "attention_decode", lambda *a, **k: a[5])          # n_items
+    library_rows = _Spy(monkeypatch, "linear_bf16", lambda x, *a, **k: x.shape[0])
+    plain_rows = _Spy(monkeypatch, "attention_generic", lambda q, *a, **k: q.shape[0])
+    runner = _runner(model_dirs[key], dtype, 16, steps, max_requests=n_live + 2)
+    got = ru.run_trace(runner, steps)
+    assert len(got) == sum(len(t) for t in reqs.values())
+    ru.compare(got, ru.plain_logits(raw, w, reqs), dtype, label=f"wide/{key}/{n_live}/{dtype}")
+    runner.cache.check_consistency()
+    assert runner.cache.num_free_pages(0) == runner.cache.pools[0].num_pages
+    if dtype == "bfloat16":
+        assert max(decode_rows.seen) >= n_live, "the split-K decode attention never saw the whole batch"
+        assert max(library_rows.seen) >= n_live, "no projection of the whole batch went to the library product"
+        assert n_live in runner._graphs, "steps of n_live single tokens are expected to be captured and replayed"
+    else:
+        assert max(plain_rows.seen) >= n_live
+
+
+def test_wide_outputs_take_the_swapped_operand_product(model_dirs, monkeypatch):
+    """A vocabulary and a feed-forward wide enough that, at 9 to 32 rows, the output projection and
+    the gate/up projection go to the swapped-operand tcgen05 kernel (one thin layer, so the plain
+    implementation stays quick)."""
+    from nanoinfer_b200.kernels import ops
+    raw, w = load_plain(model_dirs["f"])
+    n_live, tail = 12, 6
+    reqs = _wide_requests(raw, n_live, tail, seed=5)
+    steps = ru.wide(reqs, n_live, tail=tail)
+    swapped = _Spy(monkeypatch, "gemm_swap_tc", lambda x, w_, out, mode, *a, **k: (x.shape[0], mode))
+    runner = _runner(model_dirs["f"], "bfloat16", 16, steps, max_requests=n_live + 2)
+    got = ru.run_trace(runner, steps)
+    ru.compare(got, ru.plain_logits(raw, w, reqs), "bfloat16", label="wide/f")
+    ops.check_device_errors()
+    modes = {m for _, m in swapped.seen}
+    assert ops.STORE_F32 in modes, "the output projection over the vocabulary did not take the swapped-operand kernel"
+    assert ops.SWIGLU_BF16 in modes, "the gate/up projection did not take the swapped-operand kernel"
+    assert max(r for r, _ in swapped.seen) >= n_live
 
 
 def test_repeated_portion_shapes_are_replayed_from_a_graph(model_dirs, plain_cache):
@@ -112,7 +188,7 @@ def test_repeated_portion_shapes_are_replayed_from_a_graph(model_dirs, plain_cac
     assert runner.cache.num_free_pages(0) == runner.cache.pools[0].num_pages
 
 
-@pytest.mark.parametrize("key", ["a", "b"])
+@pytest.mark.parametrize("key", ["a", "b", "e"])
 def test_cuts_agree_bitwise_in_float32(model_dirs, plain_cache, key):
     """The 32-bit path fixes the order of every sum, so the cut cannot change a single bit."""
     raw, reqs, _ = _plain(plain_cache, key, model_dirs[key])
@@ -220,3 +296,38 @@ def test_benchmark_layer_sizes(tmp_path_factory, dtype, shape):
     ru.compare(got, want, dtype, label=f"layer-sizes-{shape}/{dtype}")
     from nanoinfer_b200.kernels import ops
     ops.check_device_errors()
+
+
+@pytest.mark.parametrize("key", ["ds", "e"])
+def test_a_wrong_page_breaks_the_bfloat16_bound(model_dirs, key):
+    """The bfloat16 tolerances must bite: with one entry of one request's block table pointing at
+    another request's page (a valid page of the pool, injected on the host), the logits of the next
+    decoded token have to fall outside them.  The same steps with the true table pass.  (Models with
+    peaked attention: with the near-uniform attention of N(0, 0.02) projections sixteen wrong keys
+    among a hundred would move the logits by less than bfloat16 rounding does.)"""
+    raw, w = load_plain(model_dirs[key])
+    reqs = {"x": random_tokens(raw["vocab_size"], 100, 31), "y": random_tokens(raw["vocab_size"], 90, 32)}
+    want = ru.plain_logits(raw, w, reqs)
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": reqs["x"][:99], "want": []}], "end": []},
+             {"step": 1, "entries": [{"id": "y", "tokens": reqs["y"], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "x", "tokens": reqs["x"][99:], "want": [0]}], "end": ["x", "y"]}]
+    for wrong in (False, True):
+        runner = _runner(model_dirs[key], "bfloat16", 16, steps)
+        if wrong:
+            true_rows = runner.cache.table_rows
+
+            def swapped(group, slots, width=None, true_rows=true_rows, cache=runner.cache):
+                rows = true_rows(group, slots, width).copy()
+                if cache.has("x") and cache.has("y") and cache.length("x") == 100:
+                    for i, s in enumerate(slots):
+                        if s == cache.slot("x"):
+                            rows[i, 2] = true_rows(group, [cache.slot("y")], width)[0, 2]   # tokens 32..47 of the other request
+                return rows
+            runner.cache.table_rows = swapped
+        got = ru.run_trace(runner, steps)
+        assert list(got) == [("x", 99)]
+        if wrong:
+            with pytest.raises(AssertionError):
+                ru.compare(got, want, "bfloat16", label="wrong page")
+        else:
+            ru.compare(got, want, "bfloat16", label="true pages")

@@ -67,3 +67,19 @@ def test_attention_window_and_causality():
     # causality: changing a later key does not change an earlier output
     k2 = k.clone(); k2[7] += 1.0
     torch.testing.assert_close(plain.attention(q, k2, v, 0.25)[:7], full[:7])
+
+
+def test_the_smoke_check_computes_what_the_plain_implementation_computes(tmp_path):
+    """__graft_entry__.smoke() carries its own short restatement of the formulas; it must agree
+    with the plain implementation of these tests."""
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import __graft_entry__ as entry
+    from helpers import load_plain, random_tokens
+    from nanoinfer_b200.weights import write_random_model
+    raw = dict(entry.SMOKE_CONFIG, tie_word_embeddings=False)
+    d = str(tmp_path / "m")
+    write_random_model(d, raw, seed=0, slot_std={"q": 0.15, "k": 0.15})
+    raw_read, w = load_plain(d)
+    toks = random_tokens(raw["vocab_size"], 37, 1)
+    torch.testing.assert_close(entry._plain_logits(raw, w, toks), plain.forward(raw_read, w, toks), rtol=1e-5, atol=1e-5)

@@ -4,8 +4,16 @@ A and B differ in every size and option: layers, width, head counts and grouping
 size, feed-forward width, vocabulary, rope theta and scaling, eps, tied or untied output.
 C has sizes that are no power of two and a head size of 48.  D has the head size (64) and
 grouping (4 query heads per key/value head) that the split-K decode kernel takes, and a width
-that is not heads x head size.
+that is not heads x head size.  E has heads of 128 in an odd group of three query heads per
+key/value head (what the 3B size of the family has), an untied output and sizes that are no power
+of two.  F is one thin layer under a vocabulary and a feed-forward wide enough for the routes that
+only large output sizes take (the swapped-operand tensor-core product).
+
+SHARP: standard deviations for the query and key projections that make the attention scores O(1)
+instead of O(0.05), so that the softmax is peaked: a key that is lost, or read from the wrong
+page, moves the logits by far more than bfloat16 rounding does.
 """
+import math
 TINY_A = {
     "architectures": ["LlamaForCausalLM"],
     "hidden_size": 64, "intermediate_size": 192, "num_hidden_layers": 2,
@@ -44,3 +52,28 @@ TINY_D = {
                      "high_freq_factor": 4.0, "original_max_position_embeddings": 128},
     "tie_word_embeddings": True, "hidden_act": "silu",
 }
+TINY_E = {
+    "architectures": ["LlamaForCausalLM"],
+    "hidden_size": 192, "intermediate_size": 328, "num_hidden_layers": 2,
+    "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 128,
+    "vocab_size": 777, "max_position_embeddings": 2048, "rms_norm_eps": 1e-6,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 512},
+    "tie_word_embeddings": False, "hidden_act": "silu",
+}
+TINY_F = {
+    "architectures": ["LlamaForCausalLM"],
+    "hidden_size": 128, "intermediate_size": 6400, "num_hidden_layers": 1,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64,
+    "vocab_size": 76000, "max_position_embeddings": 512, "rms_norm_eps": 1e-5,
+    "rope_theta": 10000.0, "rope_scaling": None, "tie_word_embeddings": True, "hidden_act": "silu",
+}
+# D with an untied output: greedy continuations of a tied random model repeat the last token
+TINY_D_UNTIED = dict(TINY_D, tie_word_embeddings=False)
+
+
+def sharp(raw):
+    """slot_std for write_random_model: scores q.k / sqrt(hd) with a standard deviation of about 3."""
+    s = math.sqrt(3.0 / raw["hidden_size"])
+    return {"q": s, "k": s}
