@@ -3,8 +3,11 @@ function per part.  It shares no code with the package: it reads the config.json
 dictionary itself and takes weights as {safetensors name: tensor}.
 
 Written from the reference's formulas; every function cites where the reference computes
-the same thing (paths relative to the reference project).  It rests on
-tests/golden/ for its agreement with the reference's own model code (tools/model.py).
+the same thing (paths relative to the reference project).  Its agreement with the reference rests
+on tests/golden/: whole-model logits of the reference's own Python model (tools/model.py;
+test_plain_vs_golden.py), and outputs of the reference's own C++ CPU kernels, compiled unchanged,
+for what that model lacks - the llama3 frequency rule and sin/cos table, the rotation of adjacent
+pairs, attention over a paged cache and of a portion in mid-sequence (test_reference_kernels.py).
 
 Deliberate difference from the reference: its attention softmax divides by (sum + 1e-6)
 (src/op/kernels/cpu/prefill_attention_kernel.cpp:133); this one divides by the sum.

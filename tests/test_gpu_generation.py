@@ -101,7 +101,7 @@ def test_few_pages_force_preemption_and_tokens_stay_the_same(model_dirs, key, pa
     for p, o in zip(prompts, outs):
         assert len(o) == 40
         want = plain.greedy_generate(raw, w, p, 40)
-        _varied(want[:16])
+        _varied(want)
         if dtype == "float32":
             assert o == want
         else:
@@ -139,14 +139,14 @@ def test_sampled_generation_survives_preemption(model_dirs):
 
 def test_stop_token_from_config_ends_generation(model_dirs):
     from nanoinfer_b200 import Engine, SamplingParams
-    raw, w = load_plain(model_dirs["bs"])
+    raw, w = load_plain(model_dirs["ds"])
     prompt = random_tokens(raw["vocab_size"], 9, 3)
     free_run = plain.greedy_generate(raw, w, prompt, 12)
     _varied(free_run)
     stop = free_run[6]
     first = free_run.index(stop)
     assert first >= 2, "the stop token must not be the first token either"
-    eng = Engine.from_model_dir(model_dirs["bs"], dtype="float32", block_size=8)
+    eng = Engine.from_model_dir(model_dirs["ds"], dtype="float32")
     eng.stop_token_ids = (stop,)
     out = eng.generate([prompt], max_new_tokens=12, sampling_params=SamplingParams.greedy())[0]
     assert out == free_run[:first + 1]
@@ -197,11 +197,11 @@ def test_overlapped_steps_change_no_token(model_dirs, dtype):
 
 
 def test_command_line(model_dirs, tmp_path):
-    raw, w = load_plain(model_dirs["bs"])
+    raw, w = load_plain(model_dirs["ds"])
     prompt = random_tokens(raw["vocab_size"], 11, 4)
     proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "nanoinfer"), "generate", "--model",
-                           model_dirs["bs"], "--dtype", "float32", "--prompt-ids", ",".join(map(str, prompt)),
-                           "--max-new-tokens", "8", "--temperature", "0", "--block-size", "8"],
+                           model_dirs["ds"], "--dtype", "float32", "--prompt-ids", ",".join(map(str, prompt)),
+                           "--max-new-tokens", "8", "--temperature", "0"],
                           capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stderr[-2000:]
     rec = json.loads(proc.stdout.splitlines()[0])
