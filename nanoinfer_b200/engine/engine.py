@@ -92,7 +92,8 @@ class Engine:
         cfg = config or EngineConfig()
         runner = ModelRunner(model_config, weights, dtype=cfg.dtype, page_size=cfg.block_size,
                              num_pages=cfg.num_cache_blocks, max_requests=cfg.max_sequences,
-                             max_tokens_per_request=cfg.max_model_len, device=cfg.device)
+                             max_tokens_per_request=cfg.max_model_len,
+                             max_portion_tokens=min(cfg.prefill_chunk_size, cfg.max_num_batched_tokens), device=cfg.device)
         sampler = Sampler(model_config.vocab_size, runner.rt.device)
         return cls(runner, sampler, cfg, stop_token_ids=model_config.eos_token_ids)
 

@@ -22,7 +22,7 @@ import torch
 
 from ..cache import CacheManager, GroupSpec, OutOfPages
 from ..config.model_config import ModelConfig
-from ..parts.base import PagedKVNeed, StateNeed
+from ..parts.base import PagedKVNeed, PagedNeed, StateNeed, StepPlan, planes_of
 from .model import DecoderModel
 from .request import PENDING_TOKEN
 from .runtime import Runtime
@@ -43,12 +43,27 @@ class StepEntry:
 
 @dataclass
 class CacheView:
-    """What a mixer sees of the cache for one layer run."""
+    """What a mixer sees of the cache for one layer run: the page tensors of its planes by name
+    (``k_pages`` / ``v_pages`` are the planes "k" and "v"), or its state tensor."""
     group: int = -1
-    k_pages: Optional[torch.Tensor] = None
-    v_pages: Optional[torch.Tensor] = None
+    pages: Dict[str, torch.Tensor] = field(default_factory=dict)
     state: Optional[torch.Tensor] = None
     writable: bool = True
+
+    @property
+    def k_pages(self) -> Optional[torch.Tensor]:
+        return self.pages.get("k")
+
+    @property
+    def v_pages(self) -> Optional[torch.Tensor]:
+        return self.pages.get("v")
+
+
+@dataclass
+class DevicePlan:
+    """A part's StepPlan after the upload: its arrays as int32 device tensors, its integers."""
+    arrays: Dict[str, torch.Tensor]
+    scalars: Dict[str, int]
 
 
 @dataclass
@@ -58,7 +73,10 @@ class StepContext:
     tokens, positions, seq_of_token: int32 [T];  cu_q: int32 [B+1] token offsets per
     request;  kv_len: int32 [B] cached length after this step;  slots: int32 [B] state slot
     per request;  logit_rows: int32 [R];  block_tables[g]: int32 [B, W] of group g.
-    The host_* fields hold the same numbers for decisions made on the host.
+    The host_* fields hold the same numbers for decisions made on the host (empty in a step
+    that is replayed from a graph).  decode_only: every request brings exactly one token.
+    plans: what the parts' own plan_step hooks returned for this step, by the class that defines
+    the hook; a part reads its own with plan_of(self).
     """
     n_tokens: int
     n_seqs: int
@@ -76,22 +94,36 @@ class StepContext:
     host_slots: List[int] = field(default_factory=list)
     max_q_len: int = 0
     max_kv_len: int = 0
-    # How attention splits the step: requests with at most SHORT_PORTION tokens are handled
-    # token by token (dec_tokens: their token indices), longer portions in tiles of
-    # ATTENTION_TILE query rows (tile_seq / tile_row0, heaviest first; long_tokens: their token
-    # indices).  decode_only: every request has exactly one token (then the lists are unused,
-    # so that a captured step does not depend on them).
     decode_only: bool = False
-    n_dec: int = 0
-    dec_tokens: Optional[torch.Tensor] = None
-    n_tiles: int = 0
-    tile_seq: Optional[torch.Tensor] = None
-    tile_row0: Optional[torch.Tensor] = None
-    long_tokens: Optional[torch.Tensor] = None
+    plans: Dict[type, DevicePlan] = field(default_factory=dict)
+
+    def plan_of(self, part) -> DevicePlan:
+        owner = plan_owner(type(part))
+        if owner is None or owner not in self.plans:
+            raise StepError(f"{type(part).__name__} has no plan in this step (no plan_step hook, or the "
+                            f"context was built without it)")
+        return self.plans[owner]
 
 
-SHORT_PORTION = 2        # at most kernels.ops.DECODE_FRESH_KEYS (checked below)
-ATTENTION_TILE = 128     # = kernels.ops.PREFILL_TILE_ROWS
+def plan_owner(cls) -> Optional[type]:
+    """The class in ``cls``'s ancestry that defines plan_step (one plan per such class and step)."""
+    for c in cls.__mro__:
+        if "plan_step" in c.__dict__:
+            return c
+    return None
+
+
+def upload_plans(parts, q_lens: Sequence[int], starts: Sequence[int], device) -> Dict[type, DevicePlan]:
+    """The plans of the given parts for one step, each array copied to the device on its own (for
+    contexts built by hand; the runner packs them into its single metadata copy instead)."""
+    out: Dict[type, DevicePlan] = {}
+    for part in parts:
+        owner = plan_owner(type(part))
+        if owner is not None and owner not in out:
+            plan = owner.plan_step(list(q_lens), list(starts))
+            out[owner] = DevicePlan({k: torch.from_numpy(np.ascontiguousarray(v, dtype=np.int32)).to(device)
+                                     for k, v in plan.arrays.items()}, dict(plan.scalars))
+    return out
 
 
 def reserve_entries(cache: CacheManager, entries: Sequence[StepEntry], admit) -> List[int]:
@@ -143,8 +175,13 @@ def _round_up(n: int, m: int) -> int:
 
 class ModelRunner:
     def __init__(self, config: ModelConfig, weights: Dict[str, torch.Tensor], *, dtype,
-                 page_size: int = 16, num_pages: int = 1024, max_requests: int = 8,
-                 max_tokens_per_request: Optional[int] = None, device: str = "cuda:0") -> None:
+                 page_size: int = 16, num_pages=1024, max_requests: int = 8,
+                 max_tokens_per_request: Optional[int] = None, max_portion_tokens: Optional[int] = None,
+                 device: str = "cuda:0") -> None:
+        """``num_pages``: pages of every cache group's pool, or one count per group (in the order
+        the groups first appear in the schedule).  With one count, a windowed group gets no more
+        pages than its requests can ever hold at once, if ``max_portion_tokens`` (the most tokens
+        a request brings in one step) is given: max_requests * (window + portion) tokens."""
         from .runtime import parse_dtype
         self.config = config
         self.rt = Runtime(device=torch.device(device), dtype=parse_dtype(dtype), page_size=page_size)
@@ -154,21 +191,21 @@ class ModelRunner:
         ops.preload(common + (["gemm_f32"] if self.rt.dtype == torch.float32 else
                               ["gemv_bf16", "gemm_tc", "gemm_tc2", "gemm_swap_tc", "attention_prefill", "attention_prefill_tc", "attention_decode"]))
         self.model = DecoderModel(config, weights, self.rt)
-        if max_tokens_per_request is None:
-            max_tokens_per_request = min(config.max_position_embeddings, num_pages * page_size)
-        self.max_tokens_per_request = min(max_tokens_per_request, config.max_position_embeddings)
 
         # cache groups: one per distinct need among the runs that own a cache
         needs = self.model.cache_needs()
+        group_keys: List[tuple] = []
         group_specs: List[GroupSpec] = []
         self.caches: List[Optional[CacheView]] = [None] * len(needs)
         self._state_runs: List[int] = []
         for r, need in enumerate(needs):
-            if isinstance(need, PagedKVNeed):
-                spec = GroupSpec(need.num_kv_heads, need.head_dim, need.window)
-                if spec not in group_specs:
-                    group_specs.append(spec)
-                self.caches[r] = CacheView(group=group_specs.index(spec))
+            if isinstance(need, (PagedKVNeed, PagedNeed)):
+                key = (planes_of(need), need.window)
+                if key not in group_keys:
+                    group_keys.append(key)
+                    kv = isinstance(need, PagedKVNeed)
+                    group_specs.append(GroupSpec(need.num_kv_heads if kv else 0, need.head_dim if kv else 0, need.window))
+                self.caches[r] = CacheView(group=group_keys.index(key))
             elif isinstance(need, StateNeed):
                 self.caches[r] = CacheView()
                 self._state_runs.append(r)
@@ -176,23 +213,38 @@ class ModelRunner:
                 raise StepError(f"run {r}: unknown cache need {need!r}")
         if not group_specs:
             group_specs.append(GroupSpec(0, 0, None))  # bookkeeping of lengths only
-        self.cache = CacheManager(group_specs, [num_pages] * len(group_specs), page_size,
-                                  max_requests, self.max_tokens_per_request)
+        pages_per_group = self._pages_per_group(num_pages, group_specs, page_size, max_requests, max_portion_tokens)
+        if max_tokens_per_request is None:
+            full = [n for n, g in zip(pages_per_group, group_specs) if g.window is None] or pages_per_group
+            max_tokens_per_request = min(config.max_position_embeddings, min(full) * page_size)
+        self.max_tokens_per_request = min(max_tokens_per_request, config.max_position_embeddings)
+        self.cache = CacheManager(group_specs, pages_per_group, page_size, max_requests, self.max_tokens_per_request)
         rt = self.rt
         for r, need in enumerate(needs):
             view = self.caches[r]
-            if isinstance(need, PagedKVNeed):
-                shape = (num_pages, need.num_kv_heads, page_size, need.head_dim)
-                view.k_pages = torch.zeros(shape, dtype=rt.dtype, device=rt.device)
-                view.v_pages = torch.zeros(shape, dtype=rt.dtype, device=rt.device)
+            if isinstance(need, (PagedKVNeed, PagedNeed)):
+                n_pages = pages_per_group[view.group]
+                for name, row in planes_of(need):
+                    shape = (n_pages,) + tuple(row[:-1]) + (page_size, row[-1])
+                    view.pages[name] = torch.zeros(shape, dtype=rt.dtype, device=rt.device)
             elif isinstance(need, StateNeed):
                 dt = rt.dtype if need.dtype == "compute" else getattr(torch, need.dtype)
                 view.state = torch.zeros((max_requests,) + tuple(need.shape), dtype=dt, device=rt.device)
         for r, run in enumerate(config.schedule):
             if run.cache_of is not None:
                 src = self.caches[run.cache_of]
-                self.caches[r] = CacheView(group=src.group, k_pages=src.k_pages, v_pages=src.v_pages,
-                                           state=src.state, writable=False)
+                self.caches[r] = CacheView(group=src.group, pages=src.pages, state=src.state, writable=False)
+        # hooks of the parts: who plans its own work per step, and what may be captured into a graph
+        parts = [p for b in self.model.blocks for p in (getattr(b, "mixer", None), getattr(b, "feed_forward", None))
+                 if p is not None]
+        self.planners: List[type] = []
+        for part in parts:
+            owner = plan_owner(type(part))
+            if owner is not None and owner not in self.planners:
+                self.planners.append(owner)
+        safety = {getattr(p, "graph_safe", "none") for p in parts}
+        self.decode_graphs_ok = safety <= {"decode", "all"}
+        self.portion_graphs_ok = safety <= {"all"}
         self.error_word = ops.error_word(self.rt.device)   # non-zero once a kernel gave up a bounded wait
         self.use_graphs = True
         self.h2d_bytes = 0            # bytes of step metadata copied to the device so far
@@ -214,6 +266,23 @@ class ModelRunner:
         self._pinned_events: List[torch.cuda.Event] = []
         self._pinned_next = 0
         self._dev_meta: Optional[torch.Tensor] = None
+
+    @staticmethod
+    def _pages_per_group(num_pages, group_specs, page_size, max_requests, max_portion_tokens) -> List[int]:
+        if not isinstance(num_pages, int):
+            counts = [int(n) for n in num_pages]
+            if len(counts) != len(group_specs):
+                raise StepError(f"{len(counts)} page counts for {len(group_specs)} cache groups")
+            return counts
+        counts = []
+        for g in group_specs:
+            n = num_pages
+            if g.window is not None and max_portion_tokens is not None:
+                # a request holds its window, the portion being appended, and two partly used pages
+                per_request = -(-(g.window + max_portion_tokens) // page_size) + 2
+                n = min(n, max_requests * per_request)
+            counts.append(n)
+        return counts
 
     # ---- metadata -------------------------------------------------------------------------
     def _upload(self, host: np.ndarray) -> torch.Tensor:
@@ -268,12 +337,13 @@ class ModelRunner:
             self.caches[r].state[slot].zero_()
         return slot
 
+    N_FIXED = 7      # tokens, positions, request of each token, row offsets, kv lengths, slots, logit rows
+
     def _layout(self, entries: Sequence[StepEntry], starts: Sequence[int], full_width: bool):
         """The step's metadata as host arrays, in the order they lie in one buffer: tokens,
-        positions, request of each token, row offsets, kv lengths, slots, logit rows, tokens of
-        short portions, tokens of long portions, attention tiles (request, first row), block
-        tables per group.  ``full_width``: tables at the cache's full width (what a captured
-        graph needs) instead of the width this step uses."""
+        positions, request of each token, row offsets, kv lengths, slots, logit rows, block tables
+        per group, then the arrays of the parts' own plans.  ``full_width``: tables at the cache's
+        full width (what a captured graph needs) instead of the width this step uses."""
         cache = self.cache
         q_lens = [len(e.tokens) for e in entries]
         kv_lens = [s + q for s, q in zip(starts, q_lens)]
@@ -287,51 +357,49 @@ class ModelRunner:
         rows = [int(cu_q[i]) + int(w) for i, e in enumerate(entries) for w in e.want]
         width = cache.table_width if full_width else max(1, -(-max(kv_lens) // cache.page_size))
         tables = [cache.table_rows(g, slots, width).reshape(-1) for g in range(len(cache.groups))]
-        dec, long_tok, tiles = [], [], []
-        for i, ql in enumerate(q_lens):
-            if ql <= SHORT_PORTION:
-                dec.extend(range(int(cu_q[i]), int(cu_q[i]) + ql))
-            else:
-                long_tok.extend(range(int(cu_q[i]), int(cu_q[i]) + ql))
-                tiles.extend((starts[i] + r0, i, r0) for r0 in range(0, ql, ATTENTION_TILE))
-        tiles.sort(key=lambda x: -x[0])      # most keys first
+        plans = [owner.plan_step(q_lens, list(starts)) for owner in self.planners]
         parts = [tokens, positions, seq_of_token, cu_q, np.asarray(kv_lens, dtype=np.int32),
-                 np.asarray(slots, dtype=np.int32), np.asarray(rows, dtype=np.int32),
-                 np.asarray(dec, dtype=np.int32), np.asarray(long_tok, dtype=np.int32),
-                 np.asarray([x[1] for x in tiles], dtype=np.int32),
-                 np.asarray([x[2] for x in tiles], dtype=np.int32)] + tables
+                 np.asarray(slots, dtype=np.int32), np.asarray(rows, dtype=np.int32)] + tables
+        for plan in plans:
+            parts += [np.asarray(a, dtype=np.int32) for a in plan.arrays.values()]
         offsets, total = [], 0
         for p in parts:
             offsets.append(total)
             total += _round_up(max(p.size, 1), 4)
-        return parts, offsets, total, q_lens, kv_lens, slots, width
+        return parts, offsets, total, q_lens, kv_lens, slots, width, plans
 
-    def _context(self, dev: torch.Tensor, parts, offsets, q_lens, kv_lens, slots, width, max_kv_len) -> StepContext:
+    def _context(self, dev: torch.Tensor, parts, offsets, q_lens, kv_lens, slots, width, max_kv_len, plans) -> StepContext:
         """Views of the uploaded buffer ``dev`` as a StepContext."""
-        n_fixed, n_seqs = 11, len(q_lens)
+        n_seqs, n_groups = len(q_lens), len(self.cache.groups)
 
         def view(i):
             return dev[offsets[i]:offsets[i] + parts[i].size]
 
+        at = self.N_FIXED + n_groups
+        device_plans: Dict[type, DevicePlan] = {}
+        for owner, plan in zip(self.planners, plans):
+            arrays = {}
+            for name in plan.arrays:
+                arrays[name] = view(at)
+                at += 1
+            device_plans[owner] = DevicePlan(arrays, dict(plan.scalars))
         return StepContext(
             n_tokens=sum(q_lens), n_seqs=n_seqs, n_logit_rows=parts[6].size, tokens=view(0),
             positions=view(1), seq_of_token=view(2), cu_q=view(3), kv_len=view(4), slots=view(5),
             logit_rows=view(6),
-            block_tables=[view(n_fixed + g).view(n_seqs, width) for g in range(len(self.cache.groups))],
+            block_tables=[view(self.N_FIXED + g).view(n_seqs, width) for g in range(n_groups)],
             host_q_lens=q_lens, host_kv_lens=kv_lens, host_slots=slots, max_q_len=max(q_lens),
-            max_kv_len=max_kv_len, decode_only=all(q == 1 for q in q_lens), n_dec=parts[7].size,
-            dec_tokens=view(7), long_tokens=view(8), n_tiles=parts[9].size, tile_seq=view(9),
-            tile_row0=view(10))
+            max_kv_len=max_kv_len, decode_only=all(q == 1 for q in q_lens), plans=device_plans)
 
     def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
         """Take pages for the entries' tokens and upload the step's metadata."""
         starts = reserve_entries(self.cache, entries, self.admit)
-        parts, offsets, total, q_lens, kv_lens, slots, width = self._layout(entries, starts, full_width=False)
+        parts, offsets, total, q_lens, kv_lens, slots, width, plans = self._layout(entries, starts, full_width=False)
         host = np.zeros(total, dtype=np.int32)
         for o, p in zip(offsets, parts):
             host[o:o + p.size] = p
         dev = self._upload(host)
-        return self._context(dev, parts, offsets, q_lens, kv_lens, slots, width, max(kv_lens))
+        return self._context(dev, parts, offsets, q_lens, kv_lens, slots, width, max(kv_lens), plans)
 
     # ---- the step -------------------------------------------------------------------------
     def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -357,10 +425,10 @@ class ModelRunner:
 
     # ---- decode steps as CUDA graphs ------------------------------------------------------
     def _graphable(self, entries: Sequence[StepEntry]) -> bool:
-        """A step of single tokens that all want their logits, for a model whose layers keep
-        nothing but pages between steps (replaying a page write is harmless; replaying a
-        state update is not), can be captured once per batch size and replayed."""
-        return (self.use_graphs and not self._state_runs and len(entries) <= self.max_graph_batch
+        """A step of single tokens that all want their logits can be captured once per batch size
+        and replayed, if every mixer and feed-forward of the model says that its forward finds
+        what changes between steps in device memory (graph_safe)."""
+        return (self.use_graphs and self.decode_graphs_ok and len(entries) <= self.max_graph_batch
                 and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries))
 
     # ---- steps with prompt portions as CUDA graphs -------------------------------------------
@@ -369,7 +437,7 @@ class ModelRunner:
         rows it wants (everything else is metadata in device memory), so a shape that comes back -
         the same portion size step after step while a prompt is cut into portions - is captured at
         its ``portion_graph_after``-th appearance and replayed from then on."""
-        if not self.use_graphs or self._state_runs or self.rt.dtype != torch.bfloat16:
+        if not self.use_graphs or not self.portion_graphs_ok or self.rt.dtype != torch.bfloat16:
             return False
         sig = tuple((len(e.tokens), len(e.want)) for e in entries)
         if sig in self._portion_graphs:
@@ -403,7 +471,7 @@ class ModelRunner:
     def can_feed_device_tokens(self, n: int) -> bool:
         """True if the next step of ``n`` single tokens can take its tokens from a device tensor
         (it then runs as a replayed graph, whose token buffer they are copied into)."""
-        return (self.use_graphs and not self._state_runs and 0 < n <= self.max_graph_batch
+        return (self.use_graphs and self.decode_graphs_ok and 0 < n <= self.max_graph_batch
                 and self._decode_graph_due(n, count=False))
 
     def _decode_graph(self, n: int) -> "_DecodeGraph":
@@ -419,8 +487,8 @@ class ModelRunner:
         ``last_tokens[i]`` is the token of request i that has not been run yet.  Pages for all
         steps are taken up front.  Returns int32 [n_steps, len(requests)] on the device; the
         token that the last step samples is returned but not yet run."""
-        if self._state_runs:
-            raise StepError("device-side decoding needs a model without per-request state")
+        if not self.decode_graphs_ok:
+            raise StepError("device-side decoding needs a model whose parts can be captured into a graph")
         for r in requests:
             self.cache.append(r, n_steps)
         n = len(requests)
@@ -435,9 +503,6 @@ class ModelRunner:
 
 
 from ..kernels import ops  # noqa: E402  (after the classes above: no import cycle)
-
-if SHORT_PORTION > ops.DECODE_FRESH_KEYS:
-    raise ImportError("SHORT_PORTION exceeds the keys that the decode-attention kernel fetches late")
 
 
 class _quiet_collector:
@@ -471,7 +536,7 @@ class _PortionGraph:
 
     def run(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> torch.Tensor:
         runner = self.runner
-        parts, offsets, total, q_lens, kv_lens, slots, width = runner._layout(entries, starts, full_width=True)
+        parts, offsets, total, q_lens, kv_lens, slots, width, plans = runner._layout(entries, starts, full_width=True)
         if self.host is None:
             self.host = torch.zeros(total, dtype=torch.int32, pin_memory=True)
             self.host_np = self.host.numpy()
@@ -485,12 +550,17 @@ class _PortionGraph:
         self.copy_pending = True
         runner.h2d_bytes += total * 4
         if self.graph is None:
-            ctx = runner._context(self.dev, parts, offsets, q_lens, kv_lens, slots, width, runner.max_tokens_per_request)
-            runner.model.forward(ctx, runner.caches)        # eager first: loads what is missing, sizes the workspaces
+            ctx = runner._context(self.dev, parts, offsets, q_lens, kv_lens, slots, width,
+                                  runner.max_tokens_per_request, plans)
+            ctx.host_q_lens, ctx.host_kv_lens, ctx.host_slots = [], [], []     # a replay has no host numbers
+            # This step runs eagerly (which also loads what is missing and sizes the workspaces);
+            # the same launches are then captured for the steps to come.  Every step's kernels run once.
+            logits = runner.model.forward(ctx, runner.caches)
             torch.cuda.synchronize()
             self.graph = torch.cuda.CUDAGraph()
             with _quiet_collector(), torch.cuda.graph(self.graph):
                 self.logits = runner.model.forward(ctx, runner.caches)
+            return logits
         self.graph.replay()
         return self.logits
 
@@ -509,11 +579,21 @@ class _DecodeGraph:
         cache = runner.cache
         self.width = cache.table_width
         n_groups = len(cache.groups)
-        sizes = [n, n, n, n + 1, n, n, n] + [n * self.width] * n_groups
-        self.offsets, total = [], 0
-        for sz in sizes:
-            self.offsets.append(total)
-            total += _round_up(sz, 4)
+        # the parts' plans for n single tokens: sizes are fixed by the step's shape, contents are
+        # refreshed with the positions (a plan may order its work by cached length)
+        plans = [owner.plan_step([1] * n, [0] * n) for owner in runner.planners]
+        self.plan_sizes = [[np.asarray(a).size for a in plan.arrays.values()] for plan in plans]
+        flat_plan_sizes = [sz for ps in self.plan_sizes for sz in ps]
+        # what changes every step comes first (one small copy): tokens, positions, request of each
+        # token, row offsets, kv lengths, plan arrays; then slots, logit rows and the block tables
+        names = ["tokens", "positions", "seq_of_token", "cu_q", "kv_len"] + [f"plan{i}" for i in range(len(flat_plan_sizes))] + \
+                ["slots", "logit_rows"] + [f"table{g}" for g in range(n_groups)]
+        sizes = [n, n, n, n + 1, n] + flat_plan_sizes + [n, n] + [n * self.width] * n_groups
+        self.off, total = {}, 0
+        for name, sz in zip(names, sizes):
+            self.off[name] = total
+            total += _round_up(max(sz, 1), 4)
+        self.small = self.off["slots"]
         dev = runner.rt.device
         self.host = torch.zeros(total, dtype=torch.int32, pin_memory=True)
         self.host_np = self.host.numpy()
@@ -522,20 +602,29 @@ class _DecodeGraph:
         self.copy_pending = False
         self.last_ids: Optional[list] = None     # requests and table version of the last full refresh
         self.last_version = -1
-        o = self.offsets
-        self.host_np[o[2]:o[2] + n] = np.arange(n)            # seq_of_token
-        self.host_np[o[3]:o[3] + n + 1] = np.arange(n + 1)    # cu_q
-        self.host_np[o[6]:o[6] + n] = np.arange(n)            # logit rows: all
+        o = self.off
+        self.host_np[o["seq_of_token"]:o["seq_of_token"] + n] = np.arange(n)
+        self.host_np[o["cu_q"]:o["cu_q"] + n + 1] = np.arange(n + 1)
+        self.host_np[o["logit_rows"]:o["logit_rows"] + n] = np.arange(n)            # all rows are wanted
 
-        def view(i, sz):
-            return self.dev[o[i]:o[i] + sz]
+        def view(name, sz):
+            return self.dev[o[name]:o[name] + sz]
 
+        at = 0
+        device_plans: Dict[type, DevicePlan] = {}
+        for owner, plan in zip(runner.planners, plans):
+            arrays = {}
+            for name, a in plan.arrays.items():
+                arrays[name] = view(f"plan{at}", np.asarray(a).size)
+                at += 1
+            device_plans[owner] = DevicePlan(arrays, dict(plan.scalars))
+        self.has_plan_arrays = any(sz > 0 for sz in flat_plan_sizes)
         self.ctx = StepContext(
-            n_tokens=n, n_seqs=n, n_logit_rows=n, tokens=view(0, n), positions=view(1, n),
-            seq_of_token=view(2, n), cu_q=view(3, n + 1), kv_len=view(4, n), slots=view(5, n),
-            logit_rows=view(6, n),
-            block_tables=[view(7 + g, n * self.width).view(n, self.width) for g in range(n_groups)],
-            max_q_len=1, max_kv_len=runner.max_tokens_per_request, decode_only=True)
+            n_tokens=n, n_seqs=n, n_logit_rows=n, tokens=view("tokens", n), positions=view("positions", n),
+            seq_of_token=view("seq_of_token", n), cu_q=view("cu_q", n + 1), kv_len=view("kv_len", n),
+            slots=view("slots", n), logit_rows=view("logit_rows", n),
+            block_tables=[view(f"table{g}", n * self.width).view(n, self.width) for g in range(n_groups)],
+            max_q_len=1, max_kv_len=runner.max_tokens_per_request, decode_only=True, plans=device_plans)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
         self.greedy_graph: Optional[torch.cuda.CUDAGraph] = None
@@ -546,20 +635,30 @@ class _DecodeGraph:
         """Refresh the step's metadata on the device: tokens, positions and lengths every step
         (one small copy); slots and block tables only when a request joined or left or a page
         was taken since the last fill (a second copy)."""
-        n, o, cache = self.n, self.offsets, self.runner.cache
+        n, o, cache = self.n, self.off, self.runner.cache
         if self.copy_pending:
             self.copied.synchronize()
         h = self.host_np
-        h[o[0]:o[0] + n] = [e.tokens[0] for e in entries]
-        h[o[1]:o[1] + n] = starts
-        h[o[4]:o[4] + n] = h[o[1]:o[1] + n] + 1
+        h[o["tokens"]:o["tokens"] + n] = [e.tokens[0] for e in entries]
+        h[o["positions"]:o["positions"] + n] = starts
+        h[o["kv_len"]:o["kv_len"] + n] = h[o["positions"]:o["positions"] + n] + 1
+        if self.has_plan_arrays:          # the parts' plans may depend on the cached lengths
+            at = 0
+            for owner, sizes in zip(self.runner.planners, self.plan_sizes):
+                plan = owner.plan_step([1] * n, list(starts))
+                for a, sz in zip(plan.arrays.values(), sizes):
+                    a = np.asarray(a, dtype=np.int32)
+                    if a.size != sz:
+                        raise StepError(f"{owner.__name__}.plan_step: the size of an array changed with the positions")
+                    h[o[f"plan{at}"]:o[f"plan{at}"] + sz] = a
+                    at += 1
         ids = [e.request for e in entries]
-        small = o[5]                      # tokens, positions, seq_of_token, cu_q, kv_len come first
+        small = self.small
         if ids != self.last_ids or cache.table_version != self.last_version:
             slots = [cache.slot(r) for r in ids]
-            h[o[5]:o[5] + n] = slots
+            h[o["slots"]:o["slots"] + n] = slots
             for g in range(len(cache.groups)):
-                h[o[7 + g]:o[7 + g] + n * self.width] = cache.table_rows(g, slots).reshape(-1)
+                h[o[f"table{g}"]:o[f"table{g}"] + n * self.width] = cache.table_rows(g, slots).reshape(-1)
             self.last_ids, self.last_version = ids, cache.table_version
             self.dev.copy_(self.host, non_blocking=True)
             self.runner.h2d_bytes += self.host.numel() * 4
@@ -569,15 +668,18 @@ class _DecodeGraph:
         self.copied.record(ops.current_stream_object())
         self.copy_pending = True
 
-    def _capture(self) -> None:
+    def _capture(self) -> torch.Tensor:
+        """Runs this step eagerly (which also compiles and loads what is missing and sizes the
+        workspaces) and captures the same launches for the steps to come; returns this step's
+        logits.  Every step's kernels run exactly once, so a part that updates state of its own
+        is not run twice for the step that is captured."""
         runner = self.runner
-        # an eager pass first: compiles and loads what is missing and sizes the workspaces;
-        # it writes the same keys and values that the replay will write again
-        runner.model.forward(self.ctx, runner.caches)
+        logits = runner.model.forward(self.ctx, runner.caches)
         torch.cuda.synchronize()
         self.graph = torch.cuda.CUDAGraph()
         with _quiet_collector(), torch.cuda.graph(self.graph):
             self.logits = runner.model.forward(self.ctx, runner.caches)
+        return logits
 
     def run(self, entries: Sequence[StepEntry], starts: Sequence[int],
             device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -585,16 +687,24 @@ class _DecodeGraph:
         if device_tokens is not None:
             self.ctx.tokens.copy_(device_tokens)      # after the host's copy, before the replay
         if self.graph is None:
-            self._capture()
+            return self._capture()
         self.graph.replay()
         return self.logits
 
     def run_greedy(self, entries: Sequence[StepEntry], starts: Sequence[int], n_steps: int) -> torch.Tensor:
         runner, ctx = self.runner, self.ctx
         self._fill(entries, starts)
+        out = torch.empty(n_steps, self.n, dtype=torch.int32, device=runner.rt.device)
+        first = 0
         if self.greedy_graph is None:
+            # the first step runs eagerly, feedback included; the graph is captured for the others
             self.greedy_out = torch.zeros(self.n, dtype=torch.int32, device=runner.rt.device)
-            ops.argmax(runner.model.forward(ctx, runner.caches), self.greedy_out)   # eager pass first
+            ops.argmax(runner.model.forward(ctx, runner.caches), self.greedy_out)
+            ctx.tokens.copy_(self.greedy_out)
+            ctx.positions.add_(1)
+            ctx.kv_len.add_(1)
+            out[0].copy_(self.greedy_out)
+            first = 1
             torch.cuda.synchronize()
             self.greedy_graph = torch.cuda.CUDAGraph()
             before = ops.launch_count()
@@ -605,8 +715,7 @@ class _DecodeGraph:
                 ctx.positions.add_(1)
                 ctx.kv_len.add_(1)
             self.greedy_launches = ops.launch_count() - before   # this package's kernels per step
-        out = torch.empty(n_steps, self.n, dtype=torch.int32, device=runner.rt.device)
-        for i in range(n_steps):
+        for i in range(first, n_steps):
             self.greedy_graph.replay()
             out[i].copy_(self.greedy_out)
         return out

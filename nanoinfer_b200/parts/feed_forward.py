@@ -36,6 +36,7 @@ class SwiGLU(Part):
         self.w_down = rt.weight(weights["down"])
 
     adds_into_residual = True   # forward() accepts residual= and may add its output there
+    graph_safe = "all"
 
     def can_fuse_norm(self, norm, n_rows: int) -> bool:
         return (self.blocked and self.rt.skinny(n_rows, self.hidden_size) and hasattr(norm, "gain")

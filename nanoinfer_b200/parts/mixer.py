@@ -1,14 +1,15 @@
 """Token mixers.  The one built in is grouped-query attention over the paged cache."""
 from __future__ import annotations
 
-from typing import Dict, Optional
+from typing import Dict, List, Optional
 
+import numpy as np
 import torch
 
 from ..config.model_config import ConfigError
 from ..config.registry import part, register_part
 from ..kernels import ops
-from .base import PagedKVNeed, Part, WeightSlot
+from .base import PagedKVNeed, Part, StepPlan, WeightSlot
 
 
 class PagedAttention(Part):
@@ -58,6 +59,39 @@ class PagedAttention(Part):
         return PagedKVNeed(self.n_kv, self.head_dim, self.window)
 
     adds_into_residual = True   # forward() accepts residual= and may add its output there
+    graph_safe = "all"          # everything that changes between steps is read from device memory
+
+    # How the attention kernels split a step.  Requests that bring at most SHORT_PORTION tokens are
+    # handled token by token by the split-K kernel (which fetches a token's last
+    # ops.DECODE_FRESH_KEYS keys late, after the kernel that writes them); longer portions go to the
+    # flash-style kernels in tiles of TILE_ROWS query rows, the tile with the most keys first.
+    SHORT_PORTION = ops.DECODE_FRESH_KEYS
+    TILE_ROWS = ops.PREFILL_TILE_ROWS
+
+    @staticmethod
+    def plan_step(q_lens: List[int], starts: List[int]) -> StepPlan:
+        """dec_tokens: token indices of the short portions; long_tokens: of the long ones;
+        tile_seq / tile_row0: request and first query row of each tile.  The arrays' sizes follow
+        from q_lens alone; the tiles' order also from the cached lengths."""
+        i32 = np.int32
+        if max(q_lens) == 1:       # single tokens only: the kernels take tokens 0 .. n-1 as they come
+            none = np.zeros(0, dtype=i32)
+            return StepPlan({"dec_tokens": none, "long_tokens": none, "tile_seq": none, "tile_row0": none},
+                            {"n_dec": len(q_lens), "n_tiles": 0})
+        dec, long_tok, tiles = [], [], []
+        at = 0
+        for i, (ql, start) in enumerate(zip(q_lens, starts)):
+            if ql <= PagedAttention.SHORT_PORTION:
+                dec.extend(range(at, at + ql))
+            else:
+                long_tok.extend(range(at, at + ql))
+                tiles.extend((start + r0, i, r0) for r0 in range(0, ql, PagedAttention.TILE_ROWS))
+            at += ql
+        tiles.sort(key=lambda x: -x[0])      # most keys first
+        return StepPlan({"dec_tokens": np.asarray(dec, dtype=i32), "long_tokens": np.asarray(long_tok, dtype=i32),
+                         "tile_seq": np.asarray([t[1] for t in tiles], dtype=i32),
+                         "tile_row0": np.asarray([t[2] for t in tiles], dtype=i32)},
+                        {"n_dec": len(dec), "n_tiles": len(tiles)})
 
     def can_fuse_norm(self, norm, n_rows: int) -> bool:
         """True if forward_fused_norm can take the residual stream itself (few rows, bfloat16)."""
@@ -106,8 +140,9 @@ class PagedAttention(Part):
             return
         decode_ok = self.head_dim in ops.DECODE_HEAD_DIMS and self.n_heads // self.n_kv <= 16
         prefill_ok = self.head_dim % 16 == 0 and self.head_dim <= ops.PREFILL_MAX_HEAD_DIM
-        n_dec = n if ctx.decode_only else ctx.n_dec
-        dec_list = None if ctx.decode_only else ctx.dec_tokens
+        plan = None if ctx.decode_only else ctx.plan_of(self)    # a step of single tokens needs no lists
+        n_dec = n if plan is None else plan.scalars["n_dec"]
+        dec_list = None if plan is None else plan.arrays["dec_tokens"]
         if n_dec > 0:
             if decode_ok:
                 splits = ops.decode_splits(n_dec, self.n_kv, self.head_dim, ctx.max_kv_len)
@@ -119,13 +154,14 @@ class PagedAttention(Part):
             else:
                 ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
                                       table, *common, token_list=dec_list)
-        if not ctx.decode_only and ctx.n_tiles > 0:
+        if plan is not None and plan.scalars["n_tiles"] > 0:
             if prefill_ok:
-                ops.attention_prefill(q, cache.k_pages, cache.v_pages, att, ctx.tile_seq, ctx.tile_row0,
-                                      ctx.n_tiles, ctx.cu_q, ctx.kv_len, table, *common)
+                ops.attention_prefill(q, cache.k_pages, cache.v_pages, att, plan.arrays["tile_seq"],
+                                      plan.arrays["tile_row0"], plan.scalars["n_tiles"], ctx.cu_q, ctx.kv_len, table,
+                                      *common)
             else:
                 ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
-                                      table, *common, token_list=ctx.long_tokens)
+                                      table, *common, token_list=plan.arrays["long_tokens"])
 
 
 def _pairs_adjacent(w: torch.Tensor, n_heads: int, head_dim: int, rotary_dim: int) -> torch.Tensor:

@@ -116,10 +116,11 @@ def test_attention_part_and_block(dtype, window, pairing, hd):
     cm = CacheManager([GroupSpec(n_kv, hd, window)], [8], 8, 2, 64)
     slot = cm.admit("r")
     shape = (8, n_kv, 8, hd)
-    cache = CacheView(group=0, k_pages=torch.zeros(shape, dtype=rt.dtype, device=DEV),
-                      v_pages=torch.zeros(shape, dtype=rt.dtype, device=DEV))
+    cache = CacheView(group=0, pages={"k": torch.zeros(shape, dtype=rt.dtype, device=DEV),
+                                      "v": torch.zeros(shape, dtype=rt.dtype, device=DEV)})
 
     def ctx_for(start, n):
+        from nanoinfer_b200.engine.step import upload_plans
         cm.append("r", n)
         i32 = dict(dtype=torch.int32, device=DEV)
         width = cm.table_width
@@ -130,9 +131,7 @@ def test_attention_part_and_block(dtype, window, pairing, hd):
             slots=torch.tensor([slot], **i32), logit_rows=torch.zeros(0, **i32),
             block_tables=[torch.from_numpy(cm.table_rows(0, [slot], width)).to(DEV)],
             host_q_lens=[n], host_kv_lens=[start + n], host_slots=[slot], max_q_len=n, max_kv_len=start + n,
-            decode_only=(n == 1), n_dec=n if n <= 2 else 0, dec_tokens=torch.arange(n, **i32),
-            n_tiles=0 if n <= 2 else -(-n // 128), tile_seq=torch.zeros(max(1, -(-n // 128)), **i32),
-            tile_row0=torch.arange(0, max(n, 1), 128, **i32), long_tokens=torch.arange(n, **i32))
+            decode_only=(n == 1), plans=upload_plans([mixer], [n], [start], DEV))   # the mixer's own tiling of the step
 
     outs = [mixer.forward(x[:20].to(DEV), ctx_for(0, 20), cache)]
     for t in range(20, T):
@@ -351,9 +350,268 @@ def test_toy_parts_register_build_and_step(tmp_path, dtype):
         # three needs, three kinds of cache: all keys, a window of keys, a state slot
         assert [g.window for g in runner.cache.groups] == [None, TOY_RAW["window"]]
         assert len(runner._state_runs) == 1 and runner.caches[4].writable is False
+        assert not runner.decode_graphs_ok          # the host-side toy mixer declares no graph safety
         got = ru.run_trace(runner, steps)
         assert len(got) == sum(len(t) for t in reqs.values())
         got = {k: v for k, v in got.items() if k[1] < limit[k[0]]}
         ru.compare(got, want, dtype, label=f"toy/{cut.__name__}/{dtype}")
         runner.cache.check_consistency()
         assert all(p.num_free == p.num_pages for p in runner.cache.pools)
+
+
+# ---------------------------------------------------------------------------------------------
+# more toy parts: a plan of the part's own, state under captured graphs, a cache that is not K/V
+# ---------------------------------------------------------------------------------------------
+LATENT = 12
+
+
+def _register_more_toys():
+    import numpy as np
+    from nanoinfer_b200.config import (FeedForwardSpec, LayerRun, LayerSpec, MixerSpec, ModelConfig, NormSpec,
+                                       PositionSpec, register_architecture, register_part)
+    from nanoinfer_b200.parts.base import PagedNeed, Part, StateNeed, StepPlan, WeightSlot
+
+    class ShiftMixer(Part):
+        """y_t = W1 x_t + W2 x_{t-1} (x_{-1} = 0).  The token before a portion's first token comes
+        from the request's state slot.  The part plans its own work: per request, the index of its
+        first and of its last token in the step.  Nothing is decided on the host in forward, so any
+        step may be captured and replayed."""
+        graph_safe = "all"
+
+        @staticmethod
+        def weight_slots(spec, hidden_size):
+            return {"w1": WeightSlot((hidden_size, hidden_size)), "w2": WeightSlot((hidden_size, hidden_size))}
+
+        def __init__(self, spec, hidden_size, weights, rt):
+            super().__init__(spec, hidden_size, weights, rt)
+            self.w1 = weights["w1"].to(rt.device, torch.float32)
+            self.w2 = weights["w2"].to(rt.device, torch.float32)
+
+        def cache_need(self):
+            return StateNeed((self.hidden_size,), "float32")
+
+        @staticmethod
+        def plan_step(q_lens, starts):
+            ends = np.cumsum(q_lens)
+            return StepPlan({"first_token": (ends - np.asarray(q_lens)).astype(np.int32),
+                             "last_token": (ends - 1).astype(np.int32)}, {"n_requests": len(q_lens)})
+
+        def forward(self, x, ctx, cache):
+            plan = ctx.plan_of(self)
+            assert plan.scalars["n_requests"] == ctx.n_seqs
+            xf = x.float()
+            slots = ctx.slots.long()
+            prev = torch.roll(xf, 1, 0)
+            prev.index_copy_(0, plan.arrays["first_token"].long(), cache.state.index_select(0, slots))
+            cache.state.index_copy_(0, slots, xf.index_select(0, plan.arrays["last_token"].long()))
+            return (xf @ self.w1.t() + prev @ self.w2.t()).to(self.rt.dtype)
+
+    class DeviceRunningState(Part):
+        """s_t = DECAY * s_{t-1} + W_in x_t ; y_t = W_out s_t, with the state update of single-token
+        steps done by device-side index operations: such steps may be captured ("decode").  A step
+        that ran twice would decay and add twice."""
+        graph_safe = "decode"
+
+        @staticmethod
+        def weight_slots(spec, hidden_size):
+            return {"w_in": WeightSlot((STATE, hidden_size)), "w_out": WeightSlot((hidden_size, STATE))}
+
+        def __init__(self, spec, hidden_size, weights, rt):
+            super().__init__(spec, hidden_size, weights, rt)
+            self.w_in = weights["w_in"].to(rt.device, torch.float32)
+            self.w_out = weights["w_out"].to(rt.device, torch.float32)
+
+        def cache_need(self):
+            return StateNeed((STATE,), "float32")
+
+        def forward(self, x, ctx, cache):
+            u = x.float() @ self.w_in.t()
+            if ctx.decode_only:
+                slots = ctx.slots.long()
+                s = cache.state.index_select(0, slots) * DECAY + u
+                cache.state.index_copy_(0, slots, s)
+                return (s @ self.w_out.t()).to(self.rt.dtype)
+            y = torch.empty(x.shape[0], self.hidden_size, dtype=torch.float32, device=x.device)
+            at = 0
+            for n, slot in zip(ctx.host_q_lens, ctx.host_slots):
+                s = cache.state[slot]
+                for t in range(at, at + n):
+                    s = DECAY * s + u[t]
+                    y[t] = self.w_out @ s
+                cache.state[slot] = s
+                at += n
+            return y.to(self.rt.dtype)
+
+    class LatentMeanMixer(Part):
+        """Keeps ONE small vector per token in pages (a cache that is not keys and values):
+        c_t = W_c x_t ; y_t = W_o mean(c_0 .. c_t)."""
+
+        @staticmethod
+        def weight_slots(spec, hidden_size):
+            return {"w_c": WeightSlot((LATENT, hidden_size)), "w_o": WeightSlot((hidden_size, LATENT))}
+
+        def __init__(self, spec, hidden_size, weights, rt):
+            super().__init__(spec, hidden_size, weights, rt)
+            self.w_c = weights["w_c"].to(rt.device, torch.float32)
+            self.w_o = weights["w_o"].to(rt.device, torch.float32)
+
+        def cache_need(self):
+            return PagedNeed((("latent", (LATENT,)),), None)
+
+        def forward(self, x, ctx, cache):
+            pages = cache.pages["latent"]                      # [P, page, LATENT]
+            page = pages.shape[1]
+            c = (x.float() @ self.w_c.t()).to(pages.dtype)
+            table = ctx.block_tables[cache.group].cpu()
+            y = torch.empty(x.shape[0], self.hidden_size, dtype=torch.float32, device=x.device)
+            at = 0
+            for i, (n, kv) in enumerate(zip(ctx.host_q_lens, ctx.host_kv_lens)):
+                start = kv - n
+                for t in range(n):
+                    pos = start + t
+                    pages[int(table[i, pos // page]), pos % page] = c[at + t]
+                held = torch.cat([pages[int(table[i, b])] for b in range(-(-kv // page))])[:kv].float()
+                means = held.cumsum(0) / torch.arange(1, kv + 1, device=x.device)[:, None]
+                y[at:at + n] = means[start:] @ self.w_o.t()
+                at += n
+            return y.to(self.rt.dtype)
+
+    register_part("mixer", "toy_shift", ShiftMixer, replace=True)
+    register_part("mixer", "toy_device_state", DeviceRunningState, replace=True)
+    register_part("mixer", "toy_latent_mean", LatentMeanMixer, replace=True)
+
+    def parse(raw):
+        d, hd = raw["width"], raw["head"]
+        norm = NormSpec("rmsnorm", raw["eps"])
+        ffn = FeedForwardSpec("swiglu", raw["ffn"])
+
+        def att(window):
+            return MixerSpec("attention", raw["heads"], raw["kv_heads"], hd, window, 1.0 / math.sqrt(hd),
+                             PositionSpec("rope", 10000.0, hd, "half", None))
+        kinds = {"shift": MixerSpec("toy_shift"), "state": MixerSpec("toy_device_state"),
+                 "latent": MixerSpec("toy_latent_mean"), "attention": att(None), "window": att(raw["window"])}
+        layers = tuple(LayerSpec(kinds[k], ffn, norm, norm) for k in raw["mixers"])
+        return ModelConfig("ToyMixersForTest", d, raw["vocab"], raw["max_pos"], layers,
+                           tuple(LayerRun(i) for i in range(len(layers))), norm, tie_word_embeddings=False)
+
+    def name(scope, slot):
+        return "toy2." + ".".join(str(s) for s in scope) + "." + slot
+
+    register_architecture("ToyMixersForTest", parse, name, replace=True)
+
+
+def _toy2_raw(mixers):
+    return {"architectures": ["ToyMixersForTest"], "width": 64, "head": 16, "heads": 4, "kv_heads": 2, "ffn": 96,
+            "vocab": 210, "max_pos": 512, "eps": 1e-5, "window": 20, "mixers": list(mixers)}
+
+
+def _toy2_plain(raw, w, tokens):
+    d, hd, nq, nkv = raw["width"], raw["head"], raw["heads"], raw["kv_heads"]
+    T = len(tokens)
+    W = {k: v.float() for k, v in w.items()}
+    pos = torch.arange(T)
+    inv_freq = plain.rope_inv_freq(hd, 10000.0, None)
+    h = plain.embedding(W["toy2.embedding.weight"], torch.tensor(tokens))
+    for i, kind in enumerate(raw["mixers"]):
+        p = f"toy2.layer.{i}"
+        x = plain.rms_norm(h, W[f"{p}.mixer_norm.weight"], raw["eps"])
+        if kind == "shift":
+            prev = torch.cat([torch.zeros(1, d), x[:-1]])
+            y = x @ W[f"{p}.mixer.w1"].t() + prev @ W[f"{p}.mixer.w2"].t()
+        elif kind == "state":
+            u = x @ W[f"{p}.mixer.w_in"].t()
+            s, y = torch.zeros(STATE), torch.empty(T, d)
+            for t in range(T):
+                s = DECAY * s + u[t]
+                y[t] = W[f"{p}.mixer.w_out"] @ s
+        elif kind == "latent":
+            c = x @ W[f"{p}.mixer.w_c"].t()
+            y = (c.cumsum(0) / torch.arange(1, T + 1)[:, None]) @ W[f"{p}.mixer.w_o"].t()
+        else:
+            q = plain.rope((x @ W[f"{p}.mixer.q"].t()).view(T, nq, hd), pos, inv_freq, "half")
+            k = plain.rope((x @ W[f"{p}.mixer.k"].t()).view(T, nkv, hd), pos, inv_freq, "half")
+            v = (x @ W[f"{p}.mixer.v"].t()).view(T, nkv, hd)
+            window = raw["window"] if kind == "window" else None
+            y = plain.attention(q, k, v, 1.0 / math.sqrt(hd), window).reshape(T, nq * hd) @ W[f"{p}.mixer.o"].t()
+        h = h + y
+        x = plain.rms_norm(h, W[f"{p}.ffn_norm.weight"], raw["eps"])
+        f = f"{p}.feed_forward"
+        h = h + plain.swiglu_ffn(x, W[f"{f}.gate"], W[f"{f}.up"], W[f"{f}.down"])
+    return plain.rms_norm(h, W["toy2.final_norm.weight"], raw["eps"]) @ W["toy2.lm_head.weight"].t()
+
+
+def _fixed_portions(requests, size, tail):
+    """Portions of one size step after step (they come back, so they are captured), then the last
+    ``tail`` tokens one by one; one request at a time."""
+    steps = []
+    for rid, toks in requests.items():
+        head = max(1, len(toks) - tail)
+        cuts = list(range(0, head, size)) + [head] + list(range(head + 1, len(toks)))
+        for a, b in zip(cuts, cuts[1:] + [len(toks)]):
+            if a < b:
+                steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": toks[a:b], "want": list(range(b - a))}],
+                              "end": [rid] if b == len(toks) else []})
+    return steps
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("mixers,decode_graphs,portion_graphs", [
+    (("shift", "attention"), True, True),                 # own plan + state, every step capturable
+    (("shift", "state", "window"), True, False),          # a state update that must not run twice; decode steps captured
+    (("latent", "attention", "window"), False, False),    # a paged cache that is not K/V; host-side mixer: never captured
+])
+def test_parts_with_plans_state_and_other_caches(tmp_path, mixers, decode_graphs, portion_graphs, dtype):
+    """Parts defined here, with hooks of their own, through the engine's step function, captured
+    graphs included, in all cuts - without a change to the package's files."""
+    from nanoinfer_b200.config import load_config
+    from nanoinfer_b200.engine import ModelRunner
+    from nanoinfer_b200.weights import load_weights, write_random_model
+    _register_more_toys()
+    raw = _toy2_raw(mixers)
+    d = str(tmp_path / "toy2")
+    write_random_model(d, raw, seed=6, std=0.08)
+    cfg = load_config(d)
+    weights = load_weights(d, cfg)
+    reqs = {f"t{i}": random_tokens(raw["vocab"], n, 300 + i) for i, n in enumerate([9, 70, 31, 120])}
+    want = {rid: _toy2_plain(raw, weights, toks) for rid, toks in reqs.items()}
+    for cut in ("fixed", "ragged", "mixed"):
+        steps = {"fixed": lambda r: _fixed_portions(r, 8, 30), "ragged": ru.ragged, "mixed": ru.mixed}[cut](reqs)
+        pages = ru.max_live_tokens(steps, 64) // 8
+        n_groups = len({m for m in mixers if m in ("attention", "window", "latent")})
+        # pools of different sizes: the windowed group needs far fewer pages than the others
+        counts = [pages if m != "window" else max(16, pages // 2) for m in mixers if m in ("attention", "window", "latent")]
+        runner = ModelRunner(cfg, weights, dtype=dtype, page_size=8, num_pages=counts, max_requests=4)
+        assert [p.num_pages for p in runner.cache.pools] == counts and len(counts) == n_groups
+        assert (runner.decode_graphs_ok, runner.portion_graphs_ok) == (decode_graphs, portion_graphs)
+        runner.portion_graph_after = 2
+        got = ru.run_trace(runner, steps)
+        assert len(got) == sum(len(t) for t in reqs.values())
+        ru.compare(got, want, dtype, label=f"toy2/{'+'.join(mixers)}/{cut}/{dtype}")
+        if cut == "fixed":
+            assert bool(runner._graphs) == decode_graphs, "single-token steps: captured exactly when every part allows it"
+            assert bool(runner._portion_graphs) == (portion_graphs and dtype == "bfloat16")
+        runner.cache.check_consistency()
+        assert all(p.num_free == p.num_pages for p in runner.cache.pools)
+
+
+def test_a_windowed_group_gets_a_pool_of_its_own_size(tmp_path):
+    """One page count for the runner: the group that keeps all keys gets it, a windowed group no
+    more than its requests can hold (window + the largest portion, per request)."""
+    from nanoinfer_b200.config import load_config
+    from nanoinfer_b200.engine import ModelRunner
+    from nanoinfer_b200.weights import load_weights, write_random_model
+    _register_more_toys()
+    raw = _toy2_raw(("attention", "window"))
+    d = str(tmp_path / "toy2w")
+    write_random_model(d, raw, seed=7, std=0.08)
+    cfg = load_config(d)
+    weights = load_weights(d, cfg)
+    runner = ModelRunner(cfg, weights, dtype="float32", page_size=8, num_pages=400, max_requests=4, max_portion_tokens=24)
+    full, windowed = runner.cache.pools
+    assert full.num_pages == 400 and windowed.num_pages == 4 * (-(-(20 + 24) // 8) + 2)
+    assert runner.caches[0].k_pages.shape[0] == 400 and runner.caches[1].k_pages.shape[0] == windowed.num_pages
+    reqs = {f"w{i}": random_tokens(raw["vocab"], n, 400 + i) for i, n in enumerate([300, 180, 250, 90])}
+    steps = ru.mixed(reqs, prefill_sizes=(24, 5, 13, 24, 2))
+    got = ru.run_trace(runner, steps)
+    ru.compare(got, {rid: _toy2_plain(raw, weights, toks) for rid, toks in reqs.items()}, "float32", label="window pool")
+    runner.cache.check_consistency()

@@ -42,7 +42,7 @@ def _plain(plain_cache, key, model_dir):
     if key not in plain_cache:
         raw, w = load_plain(model_dir)
         page, lens = SETUP[key]
-        reqs = _requests(raw, lens, seed=ord(key))
+        reqs = _requests(raw, lens, seed=sum(map(ord, key)))
         plain_cache[key] = (raw, reqs, ru.plain_logits(raw, w, reqs))
     return plain_cache[key]
 
@@ -108,7 +108,7 @@ def test_wide_decode_batches_match_plain(model_dirs, monkeypatch, key, n_live, d
     tail = 12
     reqs = _wide_requests(raw, n_live, tail, seed=n_live)
     steps = ru.wide(reqs, n_live, tail=tail)
-    assert sum(1 for s in steps if len(s["entries"]) == n_live and all(len(e["tokens"]) == 1 for e in s["entries"])) >= tail
+    assert sum(1 for s in steps if len(s["entries"]) >= n_live and all(len(e["tokens"]) == 1 for e in s["entries"])) >= tail
     decode_rows = _Spy(monkeypatch, "attention_decode", lambda *a, **k: a[5])          # n_items
     library_rows = _Spy(monkeypatch, "linear_bf16", lambda x, *a, **k: x.shape[0])
     plain_rows = _Spy(monkeypatch, "attention_generic", lambda q, *a, **k: q.shape[0])
@@ -121,7 +121,7 @@ def test_wide_decode_batches_match_plain(model_dirs, monkeypatch, key, n_live, d
     if dtype == "bfloat16":
         assert max(decode_rows.seen) >= n_live, "the split-K decode attention never saw the whole batch"
         assert max(library_rows.seen) >= n_live, "no projection of the whole batch went to the library product"
-        assert n_live in runner._graphs, "steps of n_live single tokens are expected to be captured and replayed"
+        assert any(n >= n_live for n in runner._graphs), "steps of n_live single tokens are expected to be captured and replayed"
     else:
         assert max(plain_rows.seen) >= n_live
 

@@ -9,9 +9,11 @@ key/value head (what the 3B size of the family has), an untied output and sizes 
 of two.  F is one thin layer under a vocabulary and a feed-forward wide enough for the routes that
 only large output sizes take (the swapped-operand tensor-core product).
 
-SHARP: standard deviations for the query and key projections that make the attention scores O(1)
-instead of O(0.05), so that the softmax is peaked: a key that is lost, or read from the wrong
-page, moves the logits by far more than bfloat16 rounding does.
+sharp(): standard deviations for the query and key projections that make the attention scores O(1)
+(standard deviation about 1.5) instead of O(0.05), so that the softmax is peaked: a key that is
+lost, or read from the wrong page, moves the logits by far more than bfloat16 rounding does.
+(Not sharper than that: rounding errors of the scores grow with their size and pass through the
+exponential, and the tolerances of these tests were fixed for scores of this order.)
 """
 import math
 TINY_A = {
@@ -74,6 +76,6 @@ TINY_D_UNTIED = dict(TINY_D, tie_word_embeddings=False)
 
 
 def sharp(raw):
-    """slot_std for write_random_model: scores q.k / sqrt(hd) with a standard deviation of about 3."""
-    s = math.sqrt(3.0 / raw["hidden_size"])
+    """slot_std for write_random_model: scores q.k / sqrt(hd) with a standard deviation of about 1.5."""
+    s = math.sqrt(1.5 / raw["hidden_size"])
     return {"q": s, "k": s}
