@@ -34,6 +34,7 @@ class DecoderModel:
         # (the reference uploads the shared matrix twice, src/model/llama.cpp:576-578,652-657)
         self.lm_head = (self.embedding if config.tie_word_embeddings
                         else rt.weight(by_scope[("lm_head",)]["weight"]))
+        self._fused = False      # the fused decode step: not looked at yet / None (does not apply) / the object
 
     def cache_needs(self) -> List[Optional[object]]:
         """Per schedule entry: what its mixer keeps between steps (None if it reads
@@ -50,6 +51,12 @@ class DecoderModel:
         """Run the step's tokens through every scheduled layer; return FP32 logits
         [len(ctx.logit_rows), vocab] for the wanted rows only."""
         rt, cfg = self.rt, self.config
+        if ctx.decode_only and self._fused is not None:
+            if self._fused is False:
+                from .fused_decode import FusedDecode
+                self._fused = FusedDecode.build(self, caches)
+            if self._fused is not None and self._fused.takes(ctx):
+                return self._fused.run(ctx)      # a step of a few single tokens: one persistent kernel
         h = rt.empty(ctx.n_tokens, cfg.hidden_size, dtype=torch.float32)
         ops.embedding(ctx.tokens, self.embedding, h)
         delta = None

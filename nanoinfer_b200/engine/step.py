@@ -177,19 +177,21 @@ class ModelRunner:
     def __init__(self, config: ModelConfig, weights: Dict[str, torch.Tensor], *, dtype,
                  page_size: int = 16, num_pages=1024, max_requests: int = 8,
                  max_tokens_per_request: Optional[int] = None, max_portion_tokens: Optional[int] = None,
-                 device: str = "cuda:0") -> None:
+                 device: str = "cuda:0", fused_decode: bool = True) -> None:
         """``num_pages``: pages of every cache group's pool, or one count per group (in the order
         the groups first appear in the schedule).  With one count, a windowed group gets no more
         pages than its requests can ever hold at once, if ``max_portion_tokens`` (the most tokens
         a request brings in one step) is given: max_requests * (window + portion) tokens."""
         from .runtime import parse_dtype
         self.config = config
-        self.rt = Runtime(device=torch.device(device), dtype=parse_dtype(dtype), page_size=page_size)
+        self.rt = Runtime(device=torch.device(device), dtype=parse_dtype(dtype), page_size=page_size,
+                          fused_decode=fused_decode)
         # compile (in parallel) and load what this precision needs before the first step
         from ..kernels import ops
         common = ["elementwise", "rope_kv", "attention_generic"]
         ops.preload(common + (["gemm_f32"] if self.rt.dtype == torch.float32 else
-                              ["gemv_bf16", "gemm_tc", "gemm_tc2", "gemm_swap_tc", "attention_prefill", "attention_prefill_tc", "attention_decode"]))
+                              ["gemv_bf16", "gemm_tc", "gemm_tc2", "gemm_swap_tc", "attention_prefill", "attention_prefill_tc", "attention_decode",
+                               "decode_fused"]))
         self.model = DecoderModel(config, weights, self.rt)
 
         # cache groups: one per distinct need among the runs that own a cache

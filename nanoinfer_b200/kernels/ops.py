@@ -70,6 +70,13 @@ _SIGNATURES = {
         "ni_gemm_tc": [_P, _P, _P, _I, _I, _I, _I, _P, _P],
         "ni_gemm_tc_set_wait": [_LL, _I],
     },
+    "decode_fused": {
+        "ni_decode_fused": [_P, _P],
+        "ni_decode_fused_supports": [_I] * 9,
+        "ni_decode_fused_max_rows": [],
+        "ni_decode_fused_max_groups": [],
+        "ni_decode_fused_blocks": [],
+    },
     "sampling": {
         "ni_argmax": [_P, _P, _I, _I, _P, _P],
         "ni_repetition_penalty": [_P, _P, _P, _I, _I, _I, _P],
@@ -702,3 +709,59 @@ def sample(logits, out, temperatures, top_ks, top_ps, seeds, counters) -> None:
         _dev(temperatures, "temperatures", torch.float32), _dev(top_ks, "top_ks", torch.int32),
         _dev(top_ps, "top_ps", torch.float32), _dev(seeds, "seeds", torch.int64),
         _dev(counters, "counters", torch.int64), n, v, _stream()), "sample")
+
+
+# ---- the fused decode step ---------------------------------------------------------------------------
+FUSED_MAX_GROUPS = 4
+
+
+class FusedLayer(ctypes.Structure):
+    """One scheduled layer run of the fused decode kernel (mirrors FdLayer of decode_fused.cu)."""
+    _fields_ = [("w_qkv", _P), ("w_o", _P), ("w_gate_up", _P), ("w_down", _P), ("gain_mixer", _P), ("gain_ffn", _P),
+                ("k_pages", _P), ("v_pages", _P), ("eps_mixer", _F), ("eps_ffn", _F), ("write_cache", _I), ("group", _I)]
+
+
+class FusedParams(ctypes.Structure):
+    """Arguments of the fused decode kernel (mirrors FdParams of decode_fused.cu)."""
+    _fields_ = [("layers", _P), ("inv_freq", _P), ("embedding", _P), ("lm_head", _P), ("gain_final", _P),
+                ("tokens", _P), ("positions", _P), ("seq_of_token", _P), ("logit_rows", _P),
+                ("tables", _P * FUSED_MAX_GROUPS),
+                ("h", _P), ("q", _P), ("att", _P), ("act", _P), ("logits", _P), ("partials", _P), ("tickets", _P),
+                ("barrier", _P), ("error", _P), ("wait_limit", _LL), ("bt_stride", _I * FUSED_MAX_GROUPS),
+                ("n_layers", _I), ("M", _I), ("R", _I), ("d", _I), ("n_q_heads", _I), ("n_kv_heads", _I),
+                ("head_dim", _I), ("rotary_dim", _I), ("inter", _I), ("vocab", _I), ("page_size", _I), ("window", _I),
+                ("scale_log2e", _F), ("eps_final", _F), ("skip_arrive_at", _I)]
+
+
+def decode_fused_lib() -> ctypes.CDLL:
+    lib = load("decode_fused")
+    if not getattr(lib, "_ni_checked", False):
+        for fn, size in (("ni_decode_fused_params_size", ctypes.sizeof(FusedParams)),
+                         ("ni_decode_fused_layer_size", ctypes.sizeof(FusedLayer))):
+            f = getattr(lib, fn)
+            f.restype = ctypes.c_longlong
+            if int(f()) != size:
+                raise KernelError(f"decode_fused: the argument records of the built kernel and of ops.py differ ({fn})")
+        if lib.ni_decode_fused_max_groups() != FUSED_MAX_GROUPS:
+            raise KernelError("decode_fused: FD_MAX_GROUPS of the built kernel differs from ops.FUSED_MAX_GROUPS")
+        lib._ni_checked = True
+    return lib
+
+
+def decode_fused_supports(m: int, d: int, n_q_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int,
+                          inter: int, vocab: int, page_size: int) -> bool:
+    return bool(decode_fused_lib().ni_decode_fused_supports(m, d, n_q_heads, n_kv_heads, head_dim, rotary_dim, inter,
+                                                            vocab, page_size))
+
+
+def decode_fused_partials(m: int, n_kv_heads: int, head_dim: int) -> int:
+    f = decode_fused_lib().ni_decode_fused_partials
+    f.restype = ctypes.c_longlong
+    f.argtypes = [_I, _I, _I]
+    return int(f(m, n_kv_heads, head_dim))
+
+
+def decode_fused(params: FusedParams) -> None:
+    """One decode step of up to 8 single tokens as one persistent kernel (see decode_fused.cu).
+    The caller fills ``params`` with device pointers and sizes; the launch is on the current stream."""
+    _check(decode_fused_lib().ni_decode_fused(ctypes.byref(params), _stream()), "decode_fused")
