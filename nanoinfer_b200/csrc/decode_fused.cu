@@ -6,26 +6,37 @@
 //
 // Why one kernel: at these sizes a decode step is a chain of ~80 products of 3-15 us each, and what
 // it costs is not bandwidth inside the kernels but the ramp and the tail of every one of them.
-// Here the weights of ALL layers are one stream that never stops:
+// Here the weights of ALL layers are one stream:
 //
 //   * one block per SM (cooperative launch), 8 consumer warps + 1 loader warp;
 //   * every weight matrix is cut by rows into one contiguous share per block (+-1 unit, so every
 //     SM streams the same number of bytes); the loader warp walks its block's shares of all
-//     matrices of all layers in order and copies them, 16 rows x 512 columns at a time, with
-//     cp.async.bulk (TMA, no tensor map needed for contiguous row segments) into a ring of shared-
-//     memory stages guarded by mbarriers.  It runs ahead of the consumers by the depth of the ring
-//     (150 KB per SM, 22 MB over the GPU), across layer and phase boundaries: while the consumers
-//     sit at a grid barrier or run attention, the next projections' weights are already landing;
-//   * the consumer warps split a stage's columns, multiply with mma.sync (weights on the 16-row
-//     side, the batch on the 8-wide side, FP32 accumulate), add their partial sums in warp order
-//     through shared memory and run the epilogue (rotary + cache write, residual add, SwiGLU,
-//     logits).  Each output element is owned by one block: no atomics on data, results do not
-//     depend on timing;
+//     matrices of all layers in order and copies them, 8 rows x 2048 columns at a time, one
+//     cp.async.bulk (TMA, no tensor map needed for contiguous row segments) of up to 4 KB per row,
+//     into a ring of shared-memory stages guarded by mbarriers.  It runs ahead of the consumers by
+//     the depth of the ring (128 KB per SM, 19 MB over the GPU), across layer and phase boundaries;
+//   * the consumer warps split a stage's columns, multiply with mma.sync (two stages = the 16 rows
+//     of the A operand, the batch on the 8-wide side, FP32 accumulate), add their partial sums in
+//     warp order through shared memory and run the epilogue (rotary + cache write, residual add,
+//     SwiGLU, logits).  Each output element is owned by one block: no atomics on data, results do
+//     not depend on timing;
 //   * activations pass from phase to phase through global memory (L2) and a grid barrier: a
 //     counter that every block increments and polls (bounded).  Attention runs between two such
 //     barriers on the same blocks: the (token, kv head) pairs' keys are cut into 64-key units, each
 //     block takes a contiguous run of units, partial results of a pair are merged, in order, by
 //     the block that finishes last (atomic ticket, no waiting).
+//
+// Where it stands (1B sizes, context 2,048, time of one step seen by block 0): batch 8: 1.68 ms
+// (projections 0.79, attention 0.48, the 81 grid barriers 0.29, output projection 0.12); batch 1:
+// 1.19 ms - against 0.86 and 0.81 ms for the chain of per-part kernels, so the engine does not use
+// it unless asked (ModelRunner(fused_decode=True)).  What was learned on the way: the copy engine
+// takes about 90 clocks per bulk copy, so 1 KB copies ran the stream at half the HBM rate (the
+// output projection alone: 166 us with 1 KB copies, 95 us with 2 KB, 82 us = HBM rate with 4 KB);
+// the legacy mma.sync pipe delivers one m16n8k16 per ~60 clocks per scheduler here, so with two
+// warps per scheduler the arithmetic (2,000 clocks per 64 KB) is slower than the stream; with nine
+// warps per block a thread gets at most 168 registers (a scheduler's third warp); and a grid barrier
+// costs 1.8-7 us (3.5 on average: two trips to L2 plus the skew of 148 blocks), five per layer,
+// on the consumers' critical path where the ring (2.9 us of stream) cannot hide it.
 //
 // Every wait (grid barrier, ring stages) is bounded in clock ticks; a wait that runs out writes a
 // code to the error word, raises the block's abort flag, the loader waits (bounded) for its copies
@@ -41,14 +52,15 @@
 #define FD_CONSUMER_WARPS 8
 #define FD_CONSUMERS (FD_CONSUMER_WARPS * 32)
 #define FD_THREADS (FD_CONSUMERS + 32)
-#define FD_KT 512                                  // columns of a ring tile
+#define FD_TILE_ROWS 8                             // weight rows of a ring stage
+#define FD_KT 2048                                 // columns of a ring stage: 4 KB per row and copy
 #define FD_ROW_BYTES (FD_KT * 2 + 16)              // padded: ldmatrix rows fall into different banks
-#define FD_STAGE_BYTES (16 * FD_ROW_BYTES)
-#define FD_STAGES 9
+#define FD_STAGE_BYTES (FD_TILE_ROWS * FD_ROW_BYTES)
+#define FD_STAGES 4
 #define FD_RING_BYTES (FD_STAGES * FD_STAGE_BYTES)
 #define FD_WORK_BYTES (68 * 1024)                  // activations of a phase / K and V segments / merge buffer
-#define FD_RED_FLOATS (2 * FD_CONSUMER_WARPS * 16 * 8)
-#define FD_SMEM_BYTES (FD_RING_BYTES + FD_WORK_BYTES + FD_RED_FLOATS * 4 + 512)
+#define FD_RED_FLOATS (2 * FD_CONSUMER_WARPS * 128)
+#define FD_SMEM_BYTES (FD_RING_BYTES + FD_WORK_BYTES + FD_RED_FLOATS * 4 + 1024 + 512)
 #define FD_MAX_ROWS 8
 #define FD_MAX_GROUPS 4
 
@@ -93,6 +105,7 @@ struct FdParams {
     int* tickets;                // attention: M Hkv (zeroed by the kernel)
     unsigned* barrier;           // one word; set to zero before the launch
     int* error;
+    long long* trace;            // optional: block 0 writes the time (ns) at which it passes each phase boundary
     long long wait_limit;        // clock ticks
     int bt_stride[FD_MAX_GROUPS];
     int n_layers, M, R, d, n_q_heads, n_kv_heads, head_dim, rotary_dim, inter, vocab, page_size, window;
@@ -203,9 +216,43 @@ struct FdShared {
     uint64_t* full;          // [FD_STAGES]
     uint64_t* empty;
     float* rstd;             // [8]
+    float* ssq;              // [warps][8] partial sums of squares
+    int* pos;                // [8] the tokens' positions
+    int* seq;                // [8] the tokens' rows of the block tables
+    int* page;               // [groups][8] the page that receives each token's key and value
     volatile int* abort_flag;
     int* flag;               // "this block arrived last" of the attention merge
 };
+
+// Shared memory: the ring, the work area, the reduction buffers, then the small things - among them
+// a copy of the kernel's arguments.  Functions that are not inlined find all of it through these two
+// accessors instead of through references to the kernel's own variables (which would live in local
+// memory, and every use of them would be a load from there).
+extern __shared__ __align__(128) unsigned char fd_smem_raw[];
+#define FD_TAIL_OFFSET (FD_RING_BYTES + FD_WORK_BYTES + FD_RED_FLOATS * 4)
+#define FD_TAIL_BYTES 1024                          // barriers, statistics, positions, pages, flags: 552 bytes used
+#define FD_PARAMS_OFFSET (FD_TAIL_OFFSET + FD_TAIL_BYTES)
+
+__device__ __forceinline__ FdShared fd_shared() {
+    FdShared s;
+    s.ring = fd_smem_raw;
+    s.work = fd_smem_raw + FD_RING_BYTES;
+    s.red = reinterpret_cast<float*>(s.work + FD_WORK_BYTES);
+    unsigned char* tail = fd_smem_raw + FD_TAIL_OFFSET;
+    s.full = reinterpret_cast<uint64_t*>(tail);
+    s.empty = s.full + FD_STAGES;
+    s.rstd = reinterpret_cast<float*>(s.empty + FD_STAGES);
+    s.ssq = s.rstd + 8;
+    s.pos = reinterpret_cast<int*>(s.ssq + FD_CONSUMER_WARPS * 8);
+    s.seq = s.pos + 8;
+    s.page = s.seq + 8;
+    s.abort_flag = reinterpret_cast<volatile int*>(s.page + FD_MAX_GROUPS * 8);
+    s.flag = const_cast<int*>(s.abort_flag) + 1;
+    static_assert(2 * FD_STAGES * 8 + (8 + FD_CONSUMER_WARPS * 8 + 8 + 8 + FD_MAX_GROUPS * 8 + 2) * 4 <= FD_TAIL_BYTES, "tail of the shared memory");
+    static_assert(sizeof(FdParams) <= 512, "room for the arguments' copy");
+    return s;
+}
+__device__ __forceinline__ const FdParams& fd_params() { return *reinterpret_cast<const FdParams*>(fd_smem_raw + FD_PARAMS_OFFSET); }
 
 struct FdRing {              // a consumer's or the loader's place in the ring
     int stage;
@@ -214,24 +261,32 @@ struct FdRing {              // a consumer's or the loader's place in the ring
 };
 
 // ---- the loader warp -------------------------------------------------------------------------------
+// The order in which a block's share of a matrix passes through the ring (the consumers walk the
+// same order): groups of up to 16 rows; within a group the 2048-column tiles one after the other;
+// within a tile the group's first 8 rows, then the rest.  One stage = up to 8 rows of one tile; each
+// row is one bulk copy of up to 4 KB (copies of this size keep the copy engine's request rate, about
+// one per 90 clocks, off the critical path; at 1 KB per copy the stream ran at half the HBM rate).
 __device__ bool fd_load_matrix(const FdParams& p, const FdShared& s, FdRing& ring, const bf16* W, int N, int K, int gran,
                                int lane) {
     int r0, r1;
     fd_rows(N, gran, blockIdx.x, gridDim.x, r0, r1);
     for (int rg = r0; rg < r1; rg += 16) {
-        const int rows = min(16, r1 - rg);
+        const int sg_rows = min(16, r1 - rg);
         for (int k0 = 0; k0 < K; k0 += FD_KT) {
             const int cols = min(FD_KT, K - k0);
-            if (!fd_mbar_wait(&s.empty[ring.stage], ring.phase ^ 1, s.abort_flag, p.wait_limit)) {
-                if (lane == 0 && !*s.abort_flag) { atomicCAS(p.error, 0, FD_ERR_LOADER); *s.abort_flag = 1; }
-                return false;
+            for (int sub = 0; sub * 8 < sg_rows; ++sub) {
+                const int rows = min(8, sg_rows - sub * 8);
+                if (!fd_mbar_wait(&s.empty[ring.stage], ring.phase ^ 1, s.abort_flag, p.wait_limit)) {
+                    if (lane == 0 && !*s.abort_flag) { atomicCAS(p.error, 0, FD_ERR_LOADER); *s.abort_flag = 1; }
+                    return false;
+                }
+                if (lane == 0) fd_mbar_expect_tx(&s.full[ring.stage], (uint32_t)(rows * cols * 2));
+                __syncwarp();
+                if (lane < rows)
+                    fd_bulk_copy(s.ring + (size_t)ring.stage * FD_STAGE_BYTES + lane * FD_ROW_BYTES,
+                                 W + (size_t)(rg + sub * 8 + lane) * K + k0, (uint32_t)(cols * 2), &s.full[ring.stage]);
+                ring.advance();
             }
-            if (lane == 0) fd_mbar_expect_tx(&s.full[ring.stage], (uint32_t)(rows * cols * 2));
-            __syncwarp();
-            if (lane < rows)
-                fd_bulk_copy(s.ring + (size_t)ring.stage * FD_STAGE_BYTES + lane * FD_ROW_BYTES,
-                             W + (size_t)(rg + lane) * K + k0, (uint32_t)(cols * 2), &s.full[ring.stage]);
-            ring.advance();
         }
     }
     return true;
@@ -291,7 +346,105 @@ __device__ void fd_grid_sync(const FdParams& p, const FdShared& s, int& n_passed
 }
 
 // ---- consumers: activations of a phase into shared memory ---------------------------------------------
-// 1 / rms of each of the phase's rows (one warp per row), from the FP32 residual stream.
+// norm(h[rows]) * gain as bfloat16 into the work area, for a projection whose K (= d) fits it in one
+// piece.  All consumer threads share every row (thread j takes the 16-byte pieces j, j + 256, ...),
+// so that all loads of the phase are in flight at once: one trip to L2 instead of one per piece.
+// With d <= 2048 the values stay in registers between the statistics and the scaling; wider rows are
+// read a second time.
+__device__ __noinline__ void fd_act_norm_whole(unsigned char* dst, int stride, const int* rows, int n_rows, const float* gain,
+                                               float eps) {
+    const FdParams& p = fd_params();
+    const FdShared s = fd_shared();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int pieces = p.d / 4;                                  // float4 per row
+    const bool keep = pieces <= 2 * FD_CONSUMERS;
+    float4 v[16];
+    float ss[FD_MAX_ROWS];
+#pragma unroll
+    for (int r = 0; r < FD_MAX_ROWS; ++r) ss[r] = 0.f;
+    if (keep) {
+#pragma unroll
+        for (int r = 0; r < FD_MAX_ROWS; ++r) {
+            const float* src = p.h + (size_t)(r < n_rows ? (rows ? rows[r] : r) : 0) * p.d;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int idx = tid + c * FD_CONSUMERS;
+                v[r * 2 + c] = (r < n_rows && idx < pieces) ? __ldcg(reinterpret_cast<const float4*>(src) + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < FD_MAX_ROWS; ++r)
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const float4 x = v[r * 2 + c];
+                ss[r] += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+            }
+    } else {
+        for (int base = 0; base < pieces; base += 2 * FD_CONSUMERS) {
+#pragma unroll
+            for (int r = 0; r < FD_MAX_ROWS; ++r) {
+                const float* src = p.h + (size_t)(r < n_rows ? (rows ? rows[r] : r) : 0) * p.d;
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int idx = base + tid + c * FD_CONSUMERS;
+                    v[r * 2 + c] = (r < n_rows && idx < pieces) ? __ldcg(reinterpret_cast<const float4*>(src) + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < FD_MAX_ROWS; ++r)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const float4 x = v[r * 2 + c];
+                    ss[r] += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+                }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < FD_MAX_ROWS; ++r) {
+        const float t = ni_warp_sum(ss[r]);
+        if (lane == 0) s.ssq[warp * 8 + r] = t;
+    }
+    fd_bar();
+    float rstd[FD_MAX_ROWS];
+#pragma unroll
+    for (int r = 0; r < FD_MAX_ROWS; ++r) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < FD_CONSUMER_WARPS; ++w) t += s.ssq[w * 8 + r];
+        rstd[r] = rsqrtf(t / (float)p.d + eps);
+    }
+    for (int base = 0; base < pieces; base += 2 * FD_CONSUMERS) {
+        if (!keep) {
+#pragma unroll
+            for (int r = 0; r < FD_MAX_ROWS; ++r) {
+                const float* src = p.h + (size_t)(r < n_rows ? (rows ? rows[r] : r) : 0) * p.d;
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int idx = base + tid + c * FD_CONSUMERS;
+                    v[r * 2 + c] = (r < n_rows && idx < pieces) ? __ldcg(reinterpret_cast<const float4*>(src) + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            const int idx = base + tid + c * FD_CONSUMERS;
+            if (idx < pieces) {
+                const float4 g = *(reinterpret_cast<const float4*>(gain) + idx);
+#pragma unroll
+                for (int r = 0; r < FD_MAX_ROWS; ++r) {
+                    if (r < n_rows) {
+                        const float4 x = v[r * 2 + c];
+                        uint2 o;
+                        o.x = fd_pack2(x.x * rstd[r] * g.x, x.y * rstd[r] * g.y);
+                        o.y = fd_pack2(x.z * rstd[r] * g.z, x.w * rstd[r] * g.w);
+                        *reinterpret_cast<uint2*>(dst + (size_t)r * stride + (size_t)idx * 8) = o;
+                    }
+                }
+            }
+        }
+    }
+}
+// The same piece by piece, for rows too wide for the work area: 1 / rms of every row first (one warp per row).
 __device__ void fd_row_rstd(const FdParams& p, const FdShared& s, const int* rows, int n_rows, float eps, int warp, int lane) {
     if (warp < n_rows) {
         const float* src = p.h + (size_t)(rows ? rows[warp] : warp) * p.d;
@@ -342,117 +495,43 @@ struct FdInput {
 };
 
 // ---- consumers: one projection ---------------------------------------------------------------------
-// A wait that runs out does not change the control flow: the warp records the error, raises the
-// block's abort flag and goes on through the same loops and block barriers without data (every
-// later wait returns at once), so that no warp is ever left alone at a barrier.
-template <int OUT>
-__device__ void fd_project(const FdParams& p, const FdShared& s, FdRing& ring, int& red_buf, const FdInput& in,
-                           const FdLayer* L, int N, int K, int gran) {
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = lane >> 2, t = lane & 3;
-    int r0, r1;
-    fd_rows(N, gran, blockIdx.x, gridDim.x, r0, r1);
-    const int Kc = fd_chunk(K);
-    const bool chunked = Kc < K;
-    const int stride = Kc * 2 + 16;
-    if (in.kind == FD_IN_NORM) {
-        fd_row_rstd(p, s, in.rows, in.n_rows, in.eps, warp, lane);
-        __syncwarp();
-    }
-    int resident = -1;                                        // chunk that lies in the work area
-    for (int rg = r0; rg < r1; rg += 16) {
-        const int rows = min(16, r1 - rg);
-        float c[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int c0 = 0; c0 < K; c0 += Kc) {
-            const int chunk = c0 / Kc, cn = min(Kc, K - c0);
-            unsigned char* act = s.work + (chunked ? (chunk & 1) * 8 * stride : 0);
-            if (chunk != resident) {
-                // (chunked: every warp is past the chunk before last, whose buffer the prefetch overwrites)
-                if (chunked) fd_bar();
-                if (in.kind == FD_IN_NORM) {
-                    fd_act_norm(p, s, act, stride, in.rows, in.n_rows, in.gain, c0, cn, warp, lane);
-                } else {
-                    if (!chunked || resident < 0 || chunk != resident + 1) { fd_act_copy(act, stride, in.src, K, in.n_rows, c0, cn); fd_cp_commit(); }
-                    if (chunked && c0 + Kc < K) {             // the next chunk streams in under this one
-                        fd_act_copy(s.work + ((chunk + 1) & 1) * 8 * stride, stride, in.src, K, in.n_rows, c0 + Kc, min(Kc, K - c0 - Kc));
-                        fd_cp_commit();
-                        fd_cp_wait<1>();
-                    } else {
-                        fd_cp_wait<0>();
-                    }
-                }
-                fd_bar();
-                resident = chunk;
-            }
-            for (int k0 = c0; k0 < c0 + cn; k0 += FD_KT) {
-                const int cols = min(FD_KT, c0 + cn - k0);
-                const bool landed = fd_mbar_wait(&s.full[ring.stage], ring.phase, s.abort_flag, p.wait_limit);
-                if (!landed && lane == 0 && !*s.abort_flag) { atomicCAS(p.error, 0, FD_ERR_CONSUMER); *s.abort_flag = 1; }
-                const int kw = warp * 64;
-                if (landed && kw < cols) {
-                    const int n = min(64, cols - kw);
-                    const uint32_t a_base = fd_smem(s.ring + (size_t)ring.stage * FD_STAGE_BYTES + (lane & 15) * FD_ROW_BYTES) +
-                                            (kw + (lane >> 4) * 8) * 2;
-                    const uint32_t b_base = fd_smem(act + (size_t)(lane & 7) * stride) + ((k0 - c0) + kw + ((lane >> 3) & 1) * 8) * 2;
-                    int kk = 0;
-#pragma unroll 4
-                    for (; kk + 16 <= n; kk += 16) {
-                        uint32_t a[4], b[2];
-                        fd_ldsm_x4(a, a_base + kk * 2);
-                        fd_ldsm_x2(b, b_base + kk * 2);
-                        fd_mma16(c, a, b[0], b[1]);
-                    }
-                    if (kk < n) {                             // K = 8 (mod 16): one step of eight columns
-                        uint32_t a[2], b;
-                        fd_ldsm_x2(a, fd_smem(s.ring + (size_t)ring.stage * FD_STAGE_BYTES + (lane & 15) * FD_ROW_BYTES) + (kw + kk) * 2);
-                        fd_ldsm_x1(b, fd_smem(act + (size_t)(lane & 7) * stride) + ((k0 - c0) + kw + kk) * 2);
-                        fd_mma8(c, a[0], a[1], b);
-                    }
-                }
-                __syncwarp();
-                if (lane == 0) fd_mbar_arrive(&s.empty[ring.stage]);
-                ring.advance();
-            }
-        }
-        // ---- the warps' partial sums meet in shared memory; added in warp order ----
-        float* red = s.red + red_buf * (FD_CONSUMER_WARPS * 128);
-        red_buf ^= 1;
-        float* mine = red + warp * 128;
-        mine[g * 8 + 2 * t] = c[0];
-        mine[g * 8 + 2 * t + 1] = c[1];
-        mine[(g + 8) * 8 + 2 * t] = c[2];
-        mine[(g + 8) * 8 + 2 * t + 1] = c[3];
-        fd_bar();
-        auto total = [&](int row, int tok) {
+// The epilogue of a group of up to 16 weight rows: the warps' partial sums (in `red`) are added in warp
+// order and go where the projection's kind says.  A function of its own, so that what it needs in
+// registers (rotary angles, page addresses) does not weigh on the loop that streams the weights.
+__device__ __noinline__ void fd_epilogue(const int OUT, const FdLayer* L, const float* red, int rg, int sg_rows) {
+    const FdParams& p = fd_params();
+    const FdShared s = fd_shared();
+    const int tid = threadIdx.x;
+        auto total = [&](int row, int tok) {                  // row: 0 .. 15 within the group
             float v = 0.f;
 #pragma unroll
-            for (int w = 0; w < FD_CONSUMER_WARPS; ++w) v += red[w * 128 + row * 8 + tok];
+            for (int w = 0; w < FD_CONSUMER_WARPS; ++w) v += red[w * 128 + (row >> 3) * 64 + tok * 8 + (row & 7)];
             return v;
         };
         if (OUT == FD_OUT_QKV) {
             if (tid < 64) {
                 const int row = 2 * (tid >> 3), tok = tid & 7;
-                if (row < rows && tok < p.M) {
+                if (row < sg_rows && tok < p.M) {
                     float v0 = total(row, tok), v1 = total(row + 1, tok);
-                    const int n = rg + row, hd = p.head_dim;
+                    const int n_row = rg + row, hd = p.head_dim;
                     const int q_dim = p.n_q_heads * hd, kv_dim = p.n_kv_heads * hd;
-                    const int pos = p.positions[tok];
-                    const int dh = n % hd;
-                    if (n < q_dim + kv_dim && dh < p.rotary_dim) {
+                    const int pos = s.pos[tok];
+                    const int dh = n_row % hd;
+                    if (n_row < q_dim + kv_dim && dh < p.rotary_dim) {
                         float sn, cs;
                         sincosf((float)pos * p.inv_freq[dh >> 1], &sn, &cs);
                         const float a = v0 * cs - v1 * sn, b = v0 * sn + v1 * cs;
                         v0 = a;
                         v1 = b;
                     }
-                    if (n < q_dim) {
-                        *reinterpret_cast<uint32_t*>(p.q + (size_t)tok * q_dim + n) = fd_pack2(v0, v1);
+                    if (n_row < q_dim) {
+                        *reinterpret_cast<uint32_t*>(p.q + (size_t)tok * q_dim + n_row) = fd_pack2(v0, v1);
                     } else if (L->write_cache) {
-                        const int kv = n - q_dim;
+                        const int kv = n_row - q_dim;
                         const bool is_v = kv >= kv_dim;
                         const int idx = is_v ? kv - kv_dim : kv;
                         const int head = idx / hd;
-                        const int page = p.tables[L->group][(size_t)p.seq_of_token[tok] * p.bt_stride[L->group] + pos / p.page_size];
+                        const int page = s.page[L->group * 8 + tok];
                         const size_t off = (((size_t)page * p.n_kv_heads + head) * p.page_size + pos % p.page_size) * hd + dh;
                         *reinterpret_cast<uint32_t*>((is_v ? L->v_pages : L->k_pages) + off) = fd_pack2(v0, v1);
                     }
@@ -461,7 +540,7 @@ __device__ void fd_project(const FdParams& p, const FdShared& s, FdRing& ring, i
         } else if (OUT == FD_OUT_ADD) {
             if (tid < 128) {
                 const int tok = tid >> 4, row = tid & 15;
-                if (row < rows && tok < p.M) {
+                if (row < sg_rows && tok < p.M) {
                     float* dst = p.h + (size_t)tok * p.d + rg + row;
                     *dst = __ldcg(dst) + total(row, tok);
                 }
@@ -477,10 +556,173 @@ __device__ void fd_project(const FdParams& p, const FdShared& s, FdRing& ring, i
         } else {
             if (tid < 128) {
                 const int tok = tid >> 4, row = tid & 15;
-                if (row < rows && tok < p.R) p.logits[(size_t)tok * p.vocab + rg + row] = total(row, tok);
+                if (row < sg_rows && tok < p.R) p.logits[(size_t)tok * p.vocab + rg + row] = total(row, tok);
             }
         }
+}
+
+// A warp's share of a group's stages when it is narrower than 256 columns (K is not a multiple of 2048: the
+// last tile of a row, or a small model): steps of 16 columns and at most one of 8, activations read
+// from shared memory as they are needed.  x_base / w0_base / w1_base: this lane's row of the
+// activations / of the group's first and second stage (0: there is none), at the warp's first column.
+__device__ __noinline__ void fd_narrow_tile(float c[4], uint32_t x_base, uint32_t w0_base, uint32_t w1_base, int n, int lane) {
+    int kk = 0;
+    for (; kk + 16 <= n; kk += 16) {
+        uint32_t lo[2], hi[2] = {0u, 0u}, x[2];
+        fd_ldsm_x2(lo, w0_base + (kk + ((lane >> 3) & 1) * 8) * 2);
+        if (w1_base) fd_ldsm_x2(hi, w1_base + (kk + ((lane >> 3) & 1) * 8) * 2);
+        fd_ldsm_x2(x, x_base + (kk + ((lane >> 3) & 1) * 8) * 2);
+        const uint32_t a[4] = {lo[0], hi[0], lo[1], hi[1]};
+        fd_mma16(c, a, x[0], x[1]);
     }
+    if (kk < n) {
+        uint32_t lo, hi = 0u, x;
+        fd_ldsm_x1(lo, w0_base + kk * 2);
+        if (w1_base) fd_ldsm_x1(hi, w1_base + kk * 2);
+        fd_ldsm_x1(x, x_base + kk * 2);
+        fd_mma8(c, lo, hi, x);
+    }
+}
+
+// A wait that runs out does not change the control flow: the warp records the error, raises the
+// block's abort flag and goes on through the same loops and block barriers without data (every
+// later wait returns at once), so that no warp is ever left alone at a barrier.
+//
+// The weights are the A operand of the MMA (a group's two 8-row stages are the halves of its 16
+// rows), the batch its 8 columns.  The 8 warps split a stage's columns, 256 each; a warp's activation
+// fragments for its columns of the current tile stay in registers (for K <= 2048: for the whole
+// phase), so shared memory carries the weights only.  (The legacy mma.sync pipe is slow on this
+// part: with the weights as the 8-wide operand, twice as many MMAs, the arithmetic took longer
+// than the stream - 4,900 clocks per 32 KB stage.)
+//
+// One function for all four projections (the epilogue is chosen at run time): the hot loop exists
+// once in the instruction cache, and it is short - the general code for tiles narrower than a
+// warp's 256 columns (odd sizes) is kept out of it.
+struct FdConsumer {          // what a consumer thread carries from projection to projection
+    FdRing ring;
+    int red_buf;
+};
+
+__device__ __noinline__ FdConsumer fd_project(const int OUT, FdConsumer state, const FdInput in, const FdLayer* L, int N, int K,
+                                              int gran) {
+    const FdParams& p = fd_params();
+    const FdShared s = fd_shared();
+    FdRing ring = state.ring;
+    int red_buf = state.red_buf;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    int r0, r1;
+    fd_rows(N, gran, blockIdx.x, gridDim.x, r0, r1);
+    const int Kc = fd_chunk(K);
+    const bool chunked = Kc < K;                              // then Kc == FD_KT: a chunk is a tile
+    const int stride = Kc * 2 + 16;
+    int resident = -1;                                        // chunk that lies in the work area
+    if (in.kind == FD_IN_NORM) {
+        if (!chunked) {                                       // the usual case: the whole normalised rows, loaded at once
+            fd_act_norm_whole(s.work, stride, in.rows, in.n_rows, in.gain, in.eps);
+            fd_bar();
+            resident = 0;
+        } else {
+            fd_row_rstd(p, s, in.rows, in.n_rows, in.eps, warp, lane);
+            __syncwarp();
+        }
+    }
+    uint32_t af[16][2];                                       // A fragments of this warp's 256 columns of a tile
+    int frag_k0 = -1;
+    const int kw = warp * 256;
+    for (int rg = r0; rg < r1; rg += 16) {
+        const int sg_rows = min(16, r1 - rg);
+        float c[2][4];                                        // two chains (even and odd steps) of the same 16 rows x 8 tokens
+#pragma unroll
+        for (int j = 0; j < 2; ++j) c[j][0] = c[j][1] = c[j][2] = c[j][3] = 0.f;
+        for (int k0 = 0; k0 < K; k0 += FD_KT) {
+            const int cols = min(FD_KT, K - k0);
+            const int chunk = chunked ? k0 / FD_KT : 0, c0 = chunked ? k0 : 0;
+            unsigned char* act = s.work + (chunked ? (chunk & 1) * 8 * stride : 0);
+            if (chunk != resident) {
+                // (chunked: every warp is past the chunk before last, whose buffer the prefetch overwrites)
+                if (chunked) fd_bar();
+                if (in.kind == FD_IN_NORM) {
+                    fd_act_norm(p, s, act, stride, in.rows, in.n_rows, in.gain, c0, cols, warp, lane);
+                } else {
+                    if (!chunked || resident < 0 || chunk != resident + 1) {
+                        fd_act_copy(act, stride, in.src, K, in.n_rows, c0, chunked ? cols : K);
+                        fd_cp_commit();
+                    }
+                    if (chunked && k0 + FD_KT < K) {          // the next chunk streams in under this one
+                        fd_act_copy(s.work + ((chunk + 1) & 1) * 8 * stride, stride, in.src, K, in.n_rows, k0 + FD_KT,
+                                    min(FD_KT, K - k0 - FD_KT));
+                        fd_cp_commit();
+                        fd_cp_wait<1>();
+                    } else {
+                        fd_cp_wait<0>();
+                    }
+                }
+                fd_bar();
+                resident = chunk;
+                frag_k0 = -1;
+            }
+            const int n = min(256, cols - kw);                // this warp's columns of the tile (may be <= 0)
+            const bool whole = n == 256;
+            const uint32_t a_base = fd_smem(act + (size_t)(lane & 7) * stride) + ((k0 - c0) + kw) * 2;
+            if (whole && frag_k0 != k0) {
+                frag_k0 = k0;
+#pragma unroll
+                for (int i2 = 0; i2 < 8; ++i2) {
+                    uint32_t r[4];
+                    fd_ldsm_x4(r, a_base + (i2 * 32 + (lane >> 3) * 8) * 2);
+                    af[2 * i2][0] = r[0]; af[2 * i2][1] = r[1]; af[2 * i2 + 1][0] = r[2]; af[2 * i2 + 1][1] = r[3];
+                }
+            }
+            // The group's two 8-row stages of this tile are the two halves of the MMA's 16 rows.
+            const bool two = sg_rows > 8;
+            const int st0 = ring.stage;
+            bool landed = fd_mbar_wait(&s.full[st0], ring.phase, s.abort_flag, p.wait_limit);
+            ring.advance();
+            const int st1 = ring.stage;
+            if (two) {
+                landed = fd_mbar_wait(&s.full[st1], ring.phase, s.abort_flag, p.wait_limit) && landed;
+                ring.advance();
+            }
+            if (!landed && lane == 0 && !*s.abort_flag) { atomicCAS(p.error, 0, FD_ERR_CONSUMER); *s.abort_flag = 1; }
+            const uint32_t w0_row = fd_smem(s.ring + (size_t)st0 * FD_STAGE_BYTES + (lane & 7) * FD_ROW_BYTES) + kw * 2;
+            const uint32_t w1_row = fd_smem(s.ring + (size_t)st1 * FD_STAGE_BYTES + (lane & 7) * FD_ROW_BYTES) + kw * 2;
+            if (landed && whole) {
+#pragma unroll
+                for (int i2 = 0; i2 < 8; ++i2) {
+                    uint32_t lo[4], hi[4] = {0u, 0u, 0u, 0u};
+                    fd_ldsm_x4(lo, w0_row + (i2 * 32 + (lane >> 3) * 8) * 2);
+                    if (two) fd_ldsm_x4(hi, w1_row + (i2 * 32 + (lane >> 3) * 8) * 2);
+                    const uint32_t a0[4] = {lo[0], hi[0], lo[1], hi[1]};
+                    const uint32_t a1[4] = {lo[2], hi[2], lo[3], hi[3]};
+                    fd_mma16(c[0], a0, af[2 * i2][0], af[2 * i2][1]);
+                    fd_mma16(c[1], a1, af[2 * i2 + 1][0], af[2 * i2 + 1][1]);
+                }
+            } else if (landed && n > 0) {
+                fd_narrow_tile(c[0], a_base, w0_row, two ? w1_row : 0u, n, lane);
+            }
+            __syncwarp();
+            if (lane == 0) {
+                fd_mbar_arrive(&s.empty[st0]);
+                if (two) fd_mbar_arrive(&s.empty[st1]);
+            }
+        }
+        // ---- the warps' partial sums meet in shared memory; added in warp order ----
+        // c[sub][0..1]: token g, weight rows 2t and 2t + 1 of the group's rows sub * 8 ..
+        float* red = s.red + red_buf * (FD_CONSUMER_WARPS * 128);
+        red_buf ^= 1;
+        float* mine = red + warp * 128;
+        // rows g (first stage) and g + 8 (second stage) of the group, tokens 2t and 2t + 1
+        mine[2 * t * 8 + g] = c[0][0] + c[1][0];
+        mine[(2 * t + 1) * 8 + g] = c[0][1] + c[1][1];
+        mine[64 + 2 * t * 8 + g] = c[0][2] + c[1][2];
+        mine[64 + (2 * t + 1) * 8 + g] = c[0][3] + c[1][3];
+        fd_bar();
+        fd_epilogue(OUT, L, red, rg, sg_rows);
+    }
+    state.ring = ring;
+    state.red_buf = red_buf;
+    return state;
 }
 
 // ---- consumers: attention of the step's tokens over the paged cache ------------------------------------
@@ -496,15 +738,17 @@ template <int HD> __device__ __forceinline__ int fd_sw(int row, int piece) {
 template <int HD>
 __device__ void fd_attend_range(const FdParams& p, const FdShared& s, const FdLayer& L, int tok, int kvh, int k_begin, int k_end,
                                 bool final_result, float* record) {
-    constexpr int SEG = HD == 64 ? 128 : 64;      // keys per buffer
+    constexpr int SEG = 4096 / HD;                 // keys per buffer: K and V of a segment are 8 KB each
+    constexpr int NBUF = 4;                        // three segments in flight while one is used
     constexpr int MW = SEG / 16;                   // warps that do the arithmetic (16 keys each per segment)
     constexpr int CH = HD / 8, KS = HD / 16, NT_O = HD / 8;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     bf16* sQ = reinterpret_cast<bf16*>(s.work);                       // [16][HD]
-    bf16* sKV = sQ + 16 * HD;                                         // 2 x (K [SEG][HD] + V [SEG][HD])
+    bf16* sKV = sQ + 16 * HD;                                         // NBUF x (K [SEG][HD] + V [SEG][HD])
+    static_assert((16 + NBUF * 2 * SEG) * HD * 2 <= FD_WORK_BYTES, "attention buffers");
     const int G = p.n_q_heads / p.n_kv_heads;
-    const int* table = p.tables[L.group] + (size_t)p.seq_of_token[tok] * p.bt_stride[L.group];
+    const int* table = p.tables[L.group] + (size_t)s.seq[tok] * p.bt_stride[L.group];
     const int page_size = p.page_size;
 
     float o[NT_O][4];
@@ -519,6 +763,7 @@ __device__ void fd_attend_range(const FdParams& p, const FdShared& s, const FdLa
         bf16* sK = sKV + (size_t)buf * 2 * SEG * HD;
         bf16* sV = sK + SEG * HD;
         constexpr int ITERS = SEG * CH / FD_CONSUMERS;
+        static_assert(ITERS * FD_CONSUMERS == SEG * CH, "segment pieces per thread");
         int page[ITERS];
 #pragma unroll
         for (int it = 0; it < ITERS; ++it) {                          // all look-ups first, then all copies
@@ -540,43 +785,55 @@ __device__ void fd_attend_range(const FdParams& p, const FdShared& s, const FdLa
         }
     };
 
-    request(k_begin, 0);
+    const int n_segs = (k_end - k_begin + SEG - 1) / SEG;
     for (int idx = tid; idx < 16 * CH; idx += FD_CONSUMERS) {
         const int r = idx / CH, c = idx - r * CH;
         bf16* dst = sQ + fd_sw<HD>(r, c);
         if (r < G) fd_cp16(dst, p.q + ((size_t)tok * p.n_q_heads + (size_t)kvh * G + r) * HD + c * 8);
         else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
     }
-    fd_cp_commit();
+#pragma unroll
+    for (int i = 0; i < NBUF - 1; ++i) {                              // (a group may be empty: the counting stays the same)
+        if (i < n_segs) request(k_begin + i * SEG, i);
+        fd_cp_commit();
+    }
 
-    int buf = 0;
-    for (int seg0 = k_begin; seg0 < k_end; seg0 += SEG, buf ^= 1) {
+    for (int i = 0; i < n_segs; ++i) {
+        const int seg0 = k_begin + i * SEG;
+        const int buf = i % NBUF;
         const int seg_keys = min(SEG, k_end - seg0);
         const int rows = ((seg_keys + 15) / 16) * 16;
         const bf16* sK = sKV + (size_t)buf * 2 * SEG * HD;
         const bf16* sV = sK + SEG * HD;
-        if (seg0 + SEG < k_end) request(seg0 + SEG, buf ^ 1);
+        if (i + NBUF - 1 < n_segs) request(seg0 + (NBUF - 1) * SEG, (i + NBUF - 1) % NBUF);
         fd_cp_commit();
-        fd_cp_wait<1>();
+        fd_cp_wait<NBUF - 1>();                                       // segment i (and Q) have landed
         fd_bar();
-        if (seg0 == k_begin) {
+        if (i == 0) {
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks)
                 fd_ldsm_x4(qa[ks], fd_smem(sQ + fd_sw<HD>((lane & 7) + 8 * ((lane >> 3) & 1), 2 * ks + (lane >> 4))));
         }
         const int w0 = warp * 16;                                    // this warp's keys of the segment
         if (warp < MW && w0 < seg_keys) {
-            float sc[2][4];
+            float sc[2][4], sc2[2][4];                               // two chains per tile: an MMA's result takes long to come back
 #pragma unroll
-            for (int j = 0; j < 2; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+            for (int j = 0; j < 2; ++j) {
+                sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+                sc2[j][0] = sc2[j][1] = sc2[j][2] = sc2[j][3] = 0.f;
+            }
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {
                 uint32_t b[4];
                 const int mi = lane >> 3;
                 fd_ldsm_x4(b, fd_smem(sK + fd_sw<HD>(w0 + (lane & 7) + 8 * (mi >> 1), 2 * ks + (mi & 1))));
-                fd_mma16(sc[0], qa[ks], b[0], b[1]);
-                fd_mma16(sc[1], qa[ks], b[2], b[3]);
+                fd_mma16((ks & 1) ? sc2[0] : sc[0], qa[ks], b[0], b[1]);
+                fd_mma16((ks & 1) ? sc2[1] : sc[1], qa[ks], b[2], b[3]);
             }
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sc[j][e] += sc2[j][e];
             float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
@@ -670,7 +927,10 @@ __device__ void fd_attend_range(const FdParams& p, const FdShared& s, const FdLa
 }
 
 template <int HD>
-__device__ void fd_attention(const FdParams& p, const FdShared& s, const FdLayer& L) {
+__device__ __noinline__ void fd_attention(const FdLayer* layer) {
+    const FdParams& p = fd_params();
+    const FdShared s = fd_shared();
+    const FdLayer& L = *layer;
     const int tid = threadIdx.x;
     const int nb = gridDim.x, b = blockIdx.x;
     const int G = p.n_q_heads / p.n_kv_heads;
@@ -678,7 +938,7 @@ __device__ void fd_attention(const FdParams& p, const FdShared& s, const FdLayer
     int chunks[FD_MAX_ROWS], lo[FD_MAX_ROWS];
     long long U = 0;
     for (int i = 0; i < p.M; ++i) {
-        const int pos = p.positions[i];
+        const int pos = s.pos[i];
         lo[i] = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
         chunks[i] = (pos + 1 - lo[i] + 63) / 64;
         U += (long long)chunks[i] * p.n_kv_heads;
@@ -692,7 +952,7 @@ __device__ void fd_attention(const FdParams& p, const FdShared& s, const FdLayer
             if (pu1 <= u_begin || pu0 >= u_end) continue;
             const int pair = i * p.n_kv_heads + kvh;
             const int cb = (int)(max(pu0, u_begin) - pu0), ce = (int)(min(pu1, u_end) - pu0);
-            const int pos = p.positions[i];
+            const int pos = s.pos[i];
             const int k_begin = lo[i] + cb * 64, k_end = min(pos + 1, lo[i] + ce * 64);
             const int first = block_of(pu0), last = block_of(pu1 - 1);
             const int n_seg = last - first + 1;
@@ -750,34 +1010,48 @@ __device__ void fd_attention(const FdParams& p, const FdShared& s, const FdLayer
     }
 }
 
-// ---- the kernel --------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(FD_THREADS, 1) decode_fused_kernel(const __grid_constant__ FdParams p) {
-    extern __shared__ __align__(128) unsigned char fd_smem_raw[];
-    FdShared s;
-    s.ring = fd_smem_raw;
-    s.work = fd_smem_raw + FD_RING_BYTES;
-    s.red = reinterpret_cast<float*>(s.work + FD_WORK_BYTES);
-    unsigned char* tail = reinterpret_cast<unsigned char*>(s.red + FD_RED_FLOATS);
-    s.full = reinterpret_cast<uint64_t*>(tail);
-    s.empty = s.full + FD_STAGES;
-    s.rstd = reinterpret_cast<float*>(s.empty + FD_STAGES);
-    s.abort_flag = reinterpret_cast<volatile int*>(s.rstd + 8);
-    s.flag = const_cast<int*>(s.abort_flag) + 1;
+__device__ __forceinline__ void fd_trace(const FdParams& p, int& n) {
+    if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+        long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        p.trace[n] = t;
+    }
+    ++n;
+}
 
+// ---- the kernel --------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(FD_THREADS, 1) decode_fused_kernel(const __grid_constant__ FdParams kernel_params) {
+    const FdShared s = fd_shared();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    {   // the arguments' copy in shared memory
+        const int* src = reinterpret_cast<const int*>(&kernel_params);
+        int* dst = reinterpret_cast<int*>(fd_smem_raw + FD_PARAMS_OFFSET);
+        for (int i = tid; i < (int)(sizeof(FdParams) / 4); i += FD_THREADS) dst[i] = src[i];
+    }
+    const FdParams& p = fd_params();
     if (tid == 0) {
         for (int i = 0; i < FD_STAGES; ++i) { fd_mbar_init(&s.full[i], 1); fd_mbar_init(&s.empty[i], FD_CONSUMER_WARPS); }
         *s.abort_flag = 0;
         *s.flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
+    if (tid < FD_MAX_ROWS) {                                      // what every phase asks of the step's tokens
+        const bool live = tid < kernel_params.M;
+        const int pos = live ? kernel_params.positions[tid] : 0, seq = live ? kernel_params.seq_of_token[tid] : 0;
+        s.pos[tid] = pos;
+        s.seq[tid] = seq;
+        for (int g = 0; g < FD_MAX_GROUPS; ++g)
+            s.page[g * 8 + tid] = (live && kernel_params.tables[g] != nullptr)
+                                      ? kernel_params.tables[g][(size_t)seq * kernel_params.bt_stride[g] + pos / kernel_params.page_size] : 0;
+    }
     __syncthreads();
 
     if (warp == FD_CONSUMER_WARPS) {
         fd_loader(p, s, lane);
     } else {
-        FdRing ring = {0, 0};
-        int red_buf = 0, n_passed = 0;
+        FdConsumer st;
+        st.ring.stage = 0; st.ring.phase = 0; st.red_buf = 0;
+        int n_passed = 0;
         const int qkv_rows = (p.n_q_heads + 2 * p.n_kv_heads) * p.head_dim, q_dim = p.n_q_heads * p.head_dim;
         // embedding: row i of the residual stream by block i (mod blocks)
         for (int i = blockIdx.x; i < p.M; i += gridDim.x) {
@@ -794,29 +1068,43 @@ __global__ void __launch_bounds__(FD_THREADS, 1) decode_fused_kernel(const __gri
         }
         // the attention merge's tickets start from zero whatever an earlier launch that gave up left there
         if (blockIdx.x == 0) for (int i = tid; i < p.M * p.n_kv_heads; i += FD_CONSUMERS) p.tickets[i] = 0;
+        int n_trace = 0;
+        fd_trace(p, n_trace);
         fd_grid_sync(p, s, n_passed);
+        fd_trace(p, n_trace);
         for (int l = 0; l < p.n_layers; ++l) {
             const FdLayer* L = p.layers + l;
             FdInput in;
             in.kind = FD_IN_NORM; in.src = nullptr; in.rows = nullptr; in.gain = L->gain_mixer; in.eps = L->eps_mixer; in.n_rows = p.M;
-            fd_project<FD_OUT_QKV>(p, s, ring, red_buf, in, L, qkv_rows, p.d, 2);
+            st = fd_project(FD_OUT_QKV, st, in, L, qkv_rows, p.d, 2);
+            fd_trace(p, n_trace);
             fd_grid_sync(p, s, n_passed);
-            if (p.head_dim == 64) fd_attention<64>(p, s, *L); else fd_attention<128>(p, s, *L);
+            fd_trace(p, n_trace);
+            if (p.head_dim == 64) fd_attention<64>(L); else fd_attention<128>(L);
+            fd_trace(p, n_trace);
             fd_grid_sync(p, s, n_passed);
+            fd_trace(p, n_trace);
             in.kind = FD_IN_BF16; in.src = p.att;
-            fd_project<FD_OUT_ADD>(p, s, ring, red_buf, in, L, p.d, q_dim, 1);
+            st = fd_project(FD_OUT_ADD, st, in, L, p.d, q_dim, 1);
+            fd_trace(p, n_trace);
             fd_grid_sync(p, s, n_passed);
+            fd_trace(p, n_trace);
             in.kind = FD_IN_NORM; in.src = nullptr; in.gain = L->gain_ffn; in.eps = L->eps_ffn;
-            fd_project<FD_OUT_SWIGLU>(p, s, ring, red_buf, in, L, 2 * p.inter, p.d, 16);
+            st = fd_project(FD_OUT_SWIGLU, st, in, L, 2 * p.inter, p.d, 16);
+            fd_trace(p, n_trace);
             fd_grid_sync(p, s, n_passed);
+            fd_trace(p, n_trace);
             in.kind = FD_IN_BF16; in.src = p.act;
-            fd_project<FD_OUT_ADD>(p, s, ring, red_buf, in, L, p.d, p.inter, 1);
+            st = fd_project(FD_OUT_ADD, st, in, L, p.d, p.inter, 1);
+            fd_trace(p, n_trace);
             fd_grid_sync(p, s, n_passed);
+            fd_trace(p, n_trace);
         }
         if (p.R > 0) {
             FdInput in;
             in.kind = FD_IN_NORM; in.src = nullptr; in.rows = p.logit_rows; in.gain = p.gain_final; in.eps = p.eps_final; in.n_rows = p.R;
-            fd_project<FD_OUT_LOGITS>(p, s, ring, red_buf, in, nullptr, p.vocab, p.d, 1);
+            st = fd_project(FD_OUT_LOGITS, st, in, nullptr, p.vocab, p.d, 1);
+            fd_trace(p, n_trace);
         }
     }
     __syncthreads();
@@ -842,6 +1130,17 @@ NI_EXPORT int ni_decode_fused_supports(int M, int d, int n_q_heads, int n_kv_hea
 // Floats of `partials` and ints of `tickets` the attention merge needs.
 NI_EXPORT long long ni_decode_fused_partials(int M, int n_kv_heads, int head_dim) {
     return (long long)(ni_sm_count() + M * n_kv_heads) * 16 * (head_dim + 2);
+}
+
+// Blocks of the kernel that fit one SM at once (1 is what the launch needs; 0: it cannot be launched
+// here), or a negative CUDA error code.
+NI_EXPORT int ni_decode_fused_occupancy() {
+    cudaError_t e = cudaFuncSetAttribute(decode_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FD_SMEM_BYTES);
+    if (e != cudaSuccess) return -(int)e;
+    int per_sm = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_fused_kernel, FD_THREADS, FD_SMEM_BYTES);
+    if (e != cudaSuccess) return -(int)e;
+    return per_sm;
 }
 
 NI_EXPORT int ni_decode_fused(const FdParams* hp, cudaStream_t stream) {

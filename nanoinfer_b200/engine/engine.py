@@ -32,6 +32,7 @@ class EngineConfig:
     dtype: str = "bfloat16"
     device: str = "cuda:0"
     overlap_steps: bool = True          # launch a decode step before the previous step's tokens are read
+    fused_decode: bool = False          # small decode steps as one persistent kernel (see ModelRunner)
 
 
 @dataclass
@@ -93,7 +94,8 @@ class Engine:
         runner = ModelRunner(model_config, weights, dtype=cfg.dtype, page_size=cfg.block_size,
                              num_pages=cfg.num_cache_blocks, max_requests=cfg.max_sequences,
                              max_tokens_per_request=cfg.max_model_len,
-                             max_portion_tokens=min(cfg.prefill_chunk_size, cfg.max_num_batched_tokens), device=cfg.device)
+                             max_portion_tokens=min(cfg.prefill_chunk_size, cfg.max_num_batched_tokens), device=cfg.device,
+                             fused_decode=cfg.fused_decode)
         sampler = Sampler(model_config.vocab_size, runner.rt.device)
         return cls(runner, sampler, cfg, stop_token_ids=model_config.eos_token_ids)
 

@@ -33,7 +33,7 @@ class Runtime:
     device: torch.device
     dtype: torch.dtype
     page_size: int
-    fused_decode: bool = True     # steps of up to 8 single tokens as one persistent kernel, where the model allows
+    fused_decode: bool = False    # steps of up to 8 single tokens as ONE persistent kernel (slower than the chain of kernels so far)
 
     def __post_init__(self) -> None:
         self._workspaces = {}

@@ -727,7 +727,7 @@ class FusedParams(ctypes.Structure):
                 ("tokens", _P), ("positions", _P), ("seq_of_token", _P), ("logit_rows", _P),
                 ("tables", _P * FUSED_MAX_GROUPS),
                 ("h", _P), ("q", _P), ("att", _P), ("act", _P), ("logits", _P), ("partials", _P), ("tickets", _P),
-                ("barrier", _P), ("error", _P), ("wait_limit", _LL), ("bt_stride", _I * FUSED_MAX_GROUPS),
+                ("barrier", _P), ("error", _P), ("trace", _P), ("wait_limit", _LL), ("bt_stride", _I * FUSED_MAX_GROUPS),
                 ("n_layers", _I), ("M", _I), ("R", _I), ("d", _I), ("n_q_heads", _I), ("n_kv_heads", _I),
                 ("head_dim", _I), ("rotary_dim", _I), ("inter", _I), ("vocab", _I), ("page_size", _I), ("window", _I),
                 ("scale_log2e", _F), ("eps_final", _F), ("skip_arrive_at", _I)]
