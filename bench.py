@@ -260,7 +260,7 @@ def run_ours(args):
     assert produced == args.batch * K, f"end-to-end run produced {produced} tokens, expected {args.batch * K}"
     e2e = {"value": round(produced / e2e_s, 1), "unit": "tok/s", "ms_per_step": round(e2e_s / K * 1e3, 4),
            "h2d_bytes_per_step": int((runner.h2d_bytes + getattr(engine.sampler, "h2d_bytes", 0)) / K),
-           "d2h_bytes_per_step": 4 * args.batch}
+           "d2h_bytes_per_step": 4 * args.batch + 4}          # the sampled ids and the device's error word
 
     out = {
         "metric": "decode_tokens_per_second", "value": round(value, 1), "unit": "tok/s", "n_gpus": 1,
@@ -382,8 +382,10 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference is a CMake C++/CUDA project without setup.py or pyproject.toml "
-                          "(pip: 'not installable') and its build downloads its dependencies; nothing to run offline"}))
+                          "the reference is a CMake C++/CUDA project without setup.py or pyproject.toml (pip: 'not "
+                          "installable'); its engine (include/nanoinfer/model/model.h, op/encode.h) needs sentencepiece, "
+                          "abseil, re2, glog and armadillo, which its build downloads and this machine does not have, and "
+                          "Engine::add_request takes text that it tokenises with a tokenizer file no offline source provides"}))
         return 0
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")

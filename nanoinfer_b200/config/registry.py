@@ -10,7 +10,10 @@ Adding an architecture = one ``register_architecture`` call with
   * ``parse_config(raw: dict) -> ModelConfig``: reads the architecture's own keys;
   * ``tensor_name(scope: tuple, slot: str) -> str``: the safetensors name of a part's
     weight slot.  Scopes are ("embedding",), ("lm_head",), ("final_norm",) and
-    ("layer", i, "mixer" | "feed_forward" | "mixer_norm" | "ffn_norm").
+    ("layer", i, "mixer" | "feed_forward" | "mixer_norm" | "ffn_norm");
+  * optionally ``ignored_tensors``: name patterns (fnmatch) of tensors that exporters of this
+    architecture store beside the weights and that nothing reads (buffers such as a rotary
+    table); the loader passes over them instead of reporting them as unexpected.
 Adding a mixer / feed-forward / norm / position encoding / block arrangement = one
 ``register_part(category, kind, cls)`` call; the class contract is given in
 ``nanoinfer_b200.parts.base``.
@@ -30,16 +33,17 @@ class Architecture:
     name: str
     parse_config: Callable[[Dict[str, Any]], ModelConfig]
     tensor_name: Callable[[Tuple, str], str]
+    ignored_tensors: Tuple[str, ...] = ()
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
 _PARTS: Dict[str, Dict[str, type]] = {c: {} for c in PART_CATEGORIES}
 
 
-def register_architecture(name: str, parse_config, tensor_name, *, replace: bool = False) -> None:
+def register_architecture(name: str, parse_config, tensor_name, *, ignored_tensors=(), replace: bool = False) -> None:
     if name in _ARCHITECTURES and not replace:
         raise ConfigError(f"architecture '{name}' is already registered")
-    _ARCHITECTURES[name] = Architecture(name, parse_config, tensor_name)
+    _ARCHITECTURES[name] = Architecture(name, parse_config, tensor_name, tuple(ignored_tensors))
 
 
 def architecture(name: str) -> Architecture:

@@ -47,6 +47,8 @@ _SIGNATURES = {
     "attention_decode": {
         "ni_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P],
         "ni_attention_decode_fresh_keys": [],
+        # the variant whose scratch lies in the library's own image (attention_decode_noalloc.h)
+        "ni_attention_decode_noalloc": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     },
     "attention_prefill": {
         "ni_attention_prefill": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],

@@ -135,4 +135,5 @@ def tensor_name(scope: Tuple, slot: str) -> str:
     raise ConfigError(f"{NAME}: no tensor name for scope {scope} slot '{slot}'")
 
 
-register_architecture(NAME, parse_config, tensor_name, replace=True)
+# Older exports of this architecture store each layer's rotary frequency buffer beside the weights.
+register_architecture(NAME, parse_config, tensor_name, ignored_tensors=("*.rotary_emb.inv_freq",), replace=True)

@@ -10,6 +10,7 @@ and can only check counts afterwards (src/model/llama.cpp:727-764).
 """
 from __future__ import annotations
 
+from fnmatch import fnmatchcase
 from typing import Dict, List
 
 import torch
@@ -49,12 +50,14 @@ def check_tensors(model_dir: str, config: ModelConfig, found: Dict[str, tuple]) 
     """Compare {name: shape} of a folder with the configuration's plan; raise WeightError."""
     plan = {p.name: p for p in tensor_plan(config)}
     missing = [n for n in plan if n not in found]
+    from ..config import registry
+    arch = registry.architecture(config.architecture)
     allowed_extra = set()
     if config.tie_word_embeddings:
         # a tied model may still store its output projection; it is not read
-        from ..config import registry
-        allowed_extra.add(registry.architecture(config.architecture).tensor_name(("lm_head",), "weight"))
-    unexpected = [n for n in found if n not in plan and n not in allowed_extra]
+        allowed_extra.add(arch.tensor_name(("lm_head",), "weight"))
+    unexpected = [n for n in found if n not in plan and n not in allowed_extra
+                  and not any(fnmatchcase(n, pat) for pat in arch.ignored_tensors)]
     wrong = [(n, plan[n].shape, found[n]) for n in plan if n in found and tuple(found[n]) != plan[n].shape]
     if missing or unexpected or wrong:
         raise WeightError(model_dir, sorted(missing), sorted(unexpected), sorted(wrong))

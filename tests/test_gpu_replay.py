@@ -331,3 +331,45 @@ def test_a_wrong_page_breaks_the_bfloat16_bound(model_dirs, key):
                 ru.compare(got, want, "bfloat16", label="wrong page")
         else:
             ru.compare(got, want, "bfloat16", label="true pages")
+
+
+@pytest.mark.slow
+def test_full_size_model_in_float32_all_cuts(tmp_path_factory):
+    """All 16 layers of the 1B configuration (the package's own config.json of that size, random
+    weights) in true 32-bit: three requests through the four cuts with reused pages.  Logits at every
+    position against the plain implementation, the cuts bitwise equal among themselves, and a greedy
+    continuation equal to the plain one.  (About 5 GB of weights on the host and on the device; the
+    plain implementation runs ~1.5 TFLOP on the CPU.)"""
+    from nanoinfer_b200.config import preset
+    from nanoinfer_b200.weights import write_random_model
+    import plain_llama as plain
+    raw = preset("llama-3.2-1b")
+    assert raw["num_hidden_layers"] == 16 and raw["vocab_size"] == 128256
+    d = str(tmp_path_factory.mktemp("full_size") / "m")
+    s = (1.5 / raw["hidden_size"]) ** 0.5
+    write_random_model(d, raw, seed=9, slot_std={"q": s, "k": s})
+    raw_read, w = load_plain(d)
+    reqs = {"p": random_tokens(raw["vocab_size"], 280, 1), "q": random_tokens(raw["vocab_size"], 130, 2),
+            "r": random_tokens(raw["vocab_size"], 75, 3)}
+    want = ru.plain_logits(raw_read, w, reqs)
+    results = {}
+    for cut, fn in CUTS.items():
+        steps = fn(reqs) if cut != "mixed" else ru.mixed(reqs, max_live=2)     # two live: the third takes over freed pages
+        runner = _runner(d, "float32", 16, steps)
+        got = ru.run_trace(runner, steps)
+        assert len(got) == sum(len(t) for t in reqs.values())
+        ru.compare(got, want, "float32", label=f"1b/{cut}/float32")
+        results[cut] = got
+        runner.cache.check_consistency()
+        del runner
+        torch.cuda.empty_cache()
+    for cut in ("tail", "ragged", "mixed"):
+        for k, row in results["whole"].items():
+            assert torch.equal(row, results[cut][k]), f"1b: {cut} differs from whole at {k}"
+    # greedy continuation: the engine's tokens are the plain implementation's
+    from nanoinfer_b200 import Engine, SamplingParams
+    prompt = reqs["r"][:20]
+    eng = Engine.from_model_dir(d, dtype="float32", block_size=16, num_cache_blocks=16, max_sequences=2)
+    eng.stop_token_ids = ()
+    assert eng.generate([prompt], max_new_tokens=5, sampling_params=SamplingParams.greedy())[0] == \
+        plain.greedy_generate(raw_read, w, prompt, 5)

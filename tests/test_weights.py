@@ -128,3 +128,24 @@ def test_sharded_folder(tmp_path):
     write_safetensors(os.path.join(d, "model-00002-of-00002.safetensors"), tensors[7:])
     w = load_weights(d, cfg)
     assert all(torch.equal(w[n], t) for n, t in tensors)
+
+
+def test_buffers_that_exporters_store_beside_the_weights_are_passed_over(tmp_path):
+    """Older exports of the architecture carry model.layers.N.self_attn.rotary_emb.inv_freq: the
+    architecture declares the pattern, the loader neither reads nor reports such tensors - while any
+    other stray tensor is still an error."""
+    d = str(tmp_path / "m")
+    cfg = config_from_dict(TINY_A)
+    tensors = dict(random_tensors(cfg, 0))
+    extra = {f"model.layers.{i}.self_attn.rotary_emb.inv_freq": torch.ones(8) for i in range(2)}
+    os.makedirs(d)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(TINY_A, f)
+    write_safetensors(os.path.join(d, "model.safetensors"), list({**tensors, **extra}.items()))
+    w = load_weights(d, load_config(d))
+    assert set(w) == set(tensors)
+    write_safetensors(os.path.join(d, "model.safetensors"),
+                      list({**tensors, **extra, "model.layers.0.self_attn.stray": torch.ones(3)}.items()))
+    with pytest.raises(WeightError) as err:
+        load_weights(d, load_config(d))
+    assert err.value.unexpected == ["model.layers.0.self_attn.stray"]

@@ -27,11 +27,14 @@ ERR_STATIC_SCRATCH_TOO_SMALL = -4
 
 
 def _symbol():
-    from nanoinfer_b200.kernels import build
+    """The exported C symbol itself, from a handle of its own on the built library (the argument
+    types are the ones the package registers for it, checked here against a second declaration)."""
+    from nanoinfer_b200.kernels import build, ops
     lib = ctypes.CDLL(build.ensure_built(["attention_decode"])["attention_decode"])
     fn = lib.ni_attention_decode_noalloc
     fn.argtypes = [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P]
     fn.restype = _I
+    assert ops._SIGNATURES["attention_decode"]["ni_attention_decode_noalloc"] == fn.argtypes
     return fn
 
 
@@ -92,3 +95,73 @@ def test_noalloc_entry_point_refuses_what_its_arrays_cannot_hold():
     assert rc == ERR_STATIC_SCRATCH_TOO_SMALL
     torch.cuda.synchronize()
     assert torch.all(out == 3.0)        # nothing was launched
+
+
+@pytest.mark.parametrize("n_q,n_kv,hd,page,window,listed", [(24, 8, 128, 16, None, False), (32, 8, 64, 16, 200, False),
+                                                             (8, 2, 128, 8, 77, True), (32, 8, 64, 16, None, True)])
+def test_noalloc_entry_point_with_wide_heads_windows_and_token_lists(n_q, n_kv, hd, page, window, listed):
+    """The other kernel variants behind the same entry point: heads of 128, a window of recent keys,
+    and a list that picks some of the step's tokens - again two calls in a row."""
+    from nanoinfer_b200.kernels import ops
+    fn = _symbol()
+    stream = torch.cuda.current_stream().cuda_stream
+    for seed, lens, n_splits in [(4, [300, 17, 700, 64, 129], 4), (5, [90, 513, 33, 256, 2], 2)]:
+        q, k_pages, v_pages, positions, seq_of, table = _case(seed, lens, n_q, n_kv, hd, page)
+        picked = torch.tensor([3, 0, 4], dtype=torch.int32, device=DEV) if listed else None
+        n = picked.numel() if listed else q.shape[0]
+        scale = 1.0 / math.sqrt(hd)
+        want = torch.full_like(q, 2.0)
+        scratch = torch.empty(n * n_q * n_splits * (hd + 2), dtype=torch.float32, device=DEV)
+        tickets = torch.zeros(n * n_kv, dtype=torch.int32, device=DEV)
+        ops.attention_decode(q, k_pages, v_pages, want, picked, n, positions, seq_of, table, n_q, n_kv, hd, page,
+                             window, scale, n_splits, scratch, tickets)
+        got = torch.full_like(q, 2.0)
+        rc = fn(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), got.data_ptr(),
+                picked.data_ptr() if listed else None, n, positions.data_ptr(), seq_of.data_ptr(), table.data_ptr(),
+                table.shape[1], n_q, n_kv, hd, page, window or 0, scale, n_splits, stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+        torch.testing.assert_close(got.float(), want.float(), rtol=8e-3, atol=4e-3)
+        assert torch.equal(got, want)
+        if listed:
+            assert torch.all(got[1] == 2.0) and torch.all(got[2] == 2.0)     # tokens that were not picked stay untouched
+
+
+def test_noalloc_entry_point_at_and_beyond_its_limits():
+    """A call that needs exactly the arrays' size runs; one float more, or one ticket more, is refused."""
+    from nanoinfer_b200.kernels import ops
+    fn = _symbol()
+    stream = torch.cuda.current_stream().cuda_stream
+    # 4 tokens x 32 heads x 124 splits x 66 floats = 1,047,552 <= 2^20 < the same with 125 splits
+    n_q, n_kv, hd, page = 32, 8, 64, 16
+    lens = [8000, 7990, 8100, 64]
+    q, k_pages, v_pages, positions, seq_of, table = _case(6, lens, n_q, n_kv, hd, page)
+    n = len(lens)
+    for n_splits, fits in ((124, True), (125, False)):
+        assert (n * n_q * n_splits * (hd + 2) <= MAX_PARTIAL_FLOATS) == fits
+        out = torch.full_like(q, 3.0)
+        rc = fn(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), None, n, positions.data_ptr(),
+                seq_of.data_ptr(), table.data_ptr(), table.shape[1], n_q, n_kv, hd, page, 0, 0.125, n_splits, stream)
+        torch.cuda.synchronize()
+        if fits:
+            assert rc == 0
+            want = torch.zeros_like(q)
+            scratch = torch.empty(n * n_q * n_splits * (hd + 2), dtype=torch.float32, device=DEV)
+            tickets = torch.zeros(n * n_kv, dtype=torch.int32, device=DEV)
+            ops.attention_decode(q, k_pages, v_pages, want, None, n, positions, seq_of, table, n_q, n_kv, hd, page,
+                                 None, 0.125, n_splits, scratch, tickets)
+            torch.cuda.synchronize()
+            assert torch.equal(out, want)
+        else:
+            assert rc == ERR_STATIC_SCRATCH_TOO_SMALL and torch.all(out == 3.0)
+    # tickets: 513 tokens x 8 kv heads = 4,104 > 4,096 (the floats would fit: 513 x 32 x 66 x 1 split)
+    n_big = 513
+    assert n_big * n_kv > MAX_TICKETS and n_big * n_q * (hd + 2) <= MAX_PARTIAL_FLOATS
+    qb = torch.zeros(n_big, n_q * hd, dtype=torch.bfloat16, device=DEV)
+    out = torch.full_like(qb, 3.0)
+    i32 = dict(dtype=torch.int32, device=DEV)
+    rc = fn(qb.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), None, n_big,
+            torch.zeros(n_big, **i32).data_ptr(), torch.zeros(n_big, **i32).data_ptr(), table.data_ptr(), table.shape[1],
+            n_q, n_kv, hd, page, 0, 0.125, 1, stream)
+    torch.cuda.synchronize()
+    assert rc == ERR_STATIC_SCRATCH_TOO_SMALL and torch.all(out == 3.0)
