@@ -7,11 +7,16 @@
 // A block is persistent and warp-specialised like gemm_tc.cu: warp 0 drives TMA through a deep
 // ring of stages (16 KB of weights + the matching activation columns each), warp 1 issues the MMAs
 // (warp-uniform loop, elected lane), warps 2-5 read the accumulator from tensor memory (two
-// accumulators alternate).  A work unit is (128 weight rows, a slice of K): projections with few
-// weight rows are split along K so that every SM streams.  Split sums are combined WITHOUT waiting
-// and in a fixed order: every unit stores its partial tile, the unit that arrives last at the
-// tile's ticket adds the partials split by split and runs the epilogue - so the result does not
-// depend on timing.
+// accumulators alternate).  A work unit is (128 weight rows, a slice of K).  A projection with few
+// weight rows (2,048 rows are 16 tiles for 148 SMs) is split along K over the blocks of a THREAD-
+// BLOCK CLUSTER (up to 8): every block multiplies its slice, leaves its partial tile in its own
+// shared memory, and after a cluster barrier each block adds, in block order, all partial tiles
+// for ITS share of the batch rows - read through distributed shared memory - and runs the
+// epilogue.  No global scratch, no atomics, a fixed order of sums.
+//
+// The kernel is launched with programmatic stream serialisation: a block requests its first
+// stages of WEIGHTS (which depend on nothing) before griddepcontrol.wait and the activations after
+// it, so the weight stream of a projection starts under the tail of the kernel before it.
 //
 // Epilogues (a thread owns one weight row = one output column of every batch row): store
 // bfloat16 | store FP32 | add into the FP32 residual stream | SwiGLU over the blocked gate/up
@@ -31,7 +36,7 @@
 
 #define SW_BK 64
 #define SW_ROWS 128            // weight rows per tile
-#define SW_THREADS 192
+#define SW_THREADS 320           // loader, MMA issuer, 8 epilogue warps: two per quarter of the lanes, half the batch columns each
 
 #define SW_STORE_BF16 0
 #define SW_STORE_F32 1
@@ -130,13 +135,30 @@ __device__ __forceinline__ void sw_ld8(uint32_t taddr, uint32_t r[8]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
 
+__device__ __forceinline__ void sw_pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void sw_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
+__device__ __forceinline__ void sw_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ uint32_t sw_cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+// Stores a float at the same shared-memory offset in block `rank` of this cluster.
+__device__ __forceinline__ void sw_st_cluster(const float* mine, uint32_t rank, float v) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(sw_smem(mine)), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(remote), "f"(v) : "memory");
+}
+
 struct SwParams {
     void* out;
     int M, N, K, mode;
-    int splits;               // slices of K per tile of weight rows
-    float* partials;          // splits > 1: [tiles][splits][BT][128] FP32
-    int* tickets;             // splits > 1: [tiles], zero on entry, left zero
+    int splits;               // slices of K per tile of weight rows = blocks of a cluster
     int* error;
+    long long* trace;         // optional: block 0 stamps the time (ns) of its milestones here
     // SW_ROPE_KV
     const int* positions;
     const int* seq_of_token;
@@ -163,7 +185,7 @@ __device__ __forceinline__ void sw_epilogue(const SwParams& p, int n, int m, flo
         const float up = __shfl_down_sync(0xffffffffu, v, 8);
         if (ok && (n & 8) == 0)
             reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * (p.N >> 1) + ((n >> 4) << 3) + (n & 7)] =
-                __float2bfloat16_rn((v / (1.0f + expf(-v))) * up);
+                __float2bfloat16_rn(__fdividef(v, 1.0f + __expf(-v)) * up);
     } else {  // SW_ROPE_KV: rows 2i and 2i + 1 are a rotary pair
         const float other = __shfl_xor_sync(0xffffffffu, v, 1);
         if (!ok) return;
@@ -191,7 +213,15 @@ __device__ __forceinline__ void sw_epilogue(const SwParams& p, int n, int m, flo
 }
 
 // Stages of the ring: as many as fit shared memory, since bytes in flight set the streaming rate.
-template <int BT> struct SwStages { static constexpr int value = BT <= 32 ? 10 : (BT <= 64 ? 8 : 6); };
+__device__ __forceinline__ void sw_stamp(const SwParams& p, int i) {
+    if (p.trace != nullptr && blockIdx.x == 0) {
+        long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        p.trace[i] = t;
+    }
+}
+
+template <int BT> struct SwStages { static constexpr int value = BT <= 32 ? 10 : (BT <= 64 ? 7 : 4); };
 
 template <int BT, int MODE>
 __global__ void __launch_bounds__(SW_THREADS, 1)
@@ -204,23 +234,24 @@ gemm_swap_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     uint8_t* base = reinterpret_cast<uint8_t*>(((uintptr_t)sw_smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* sA = base;
     uint8_t* sB = base + SW_STAGES * A_BYTES;
-    uint64_t* full = reinterpret_cast<uint64_t*>(sB + SW_STAGES * B_BYTES);
+    float* slots = reinterpret_cast<float*>(sB + SW_STAGES * B_BYTES);     // split sums: [slices][rows owned][128] FP32, <= BT rows in all
+    uint64_t* full = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(slots) + (BT + 8) * SW_ROWS * 4);
     uint64_t* empty = full + SW_STAGES;
     uint64_t* acc_full = empty + SW_STAGES;
     uint64_t* acc_empty = acc_full + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
-    int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);
+    int* pre_kb = reinterpret_cast<int*>(tmem_slot + 1);       // [SW_STAGES] k-blocks whose weights were requested ahead
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) sw_stamp(p, 0);
     const int k_blocks = (p.K + SW_BK - 1) / SW_BK;
     const int tiles = (p.N + SW_ROWS - 1) / SW_ROWS;
-    const int splits = p.splits;
+    const int splits = p.splits;                    // > 1: one unit per block, the tile's units form a cluster
     const int n_units = tiles * splits;
-    const int kb_per_split = (k_blocks + splits - 1) / splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < SW_STAGES; ++s) { sw_mbar_init(&full[s], 1); sw_mbar_init(&empty[s], 1); }
-        for (int a = 0; a < 2; ++a) { sw_mbar_init(&acc_full[a], 1); sw_mbar_init(&acc_empty[a], 128); }
+        for (int a = 0; a < 2; ++a) { sw_mbar_init(&acc_full[a], 1); sw_mbar_init(&acc_empty[a], 256); }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_w) : "memory");
         asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_x) : "memory");
@@ -234,28 +265,45 @@ gemm_swap_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     __syncthreads();
     sw_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    sw_pdl_launch_dependents();                     // the kernel after this one may begin its own prologue
+    if (splits > 1) sw_cluster_sync();              // every block of the cluster runs: its shared memory may be stored into
+    if (threadIdx.x == 0) sw_stamp(p, 1);
 
     if (warp == 0) {
         // ---- TMA producer ----
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
-            bool ok = true;
+            bool ok = true, released = false;
+            int issued = 0;                         // loads of this block so far
             for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
                 const int tile = unit / splits, split = unit - tile * splits;
-                const int kb0 = split * kb_per_split, kb1 = min(k_blocks, kb0 + kb_per_split);   // (never empty: host)
+                const int kb0 = k_blocks * split / splits, kb1 = k_blocks * (split + 1) / splits;   // (never empty: splits <= k_blocks)
                 // Every block needs the same activation columns for a k-block.  Blocks therefore walk
                 // their slice of K from different starting points (a fixed function of the tile), or
                 // they would all ask the same few L2 lines for them at the same moment.
                 const int span = kb1 - kb0, start = (tile * 5) % span;
                 for (int i = 0; i < span; ++i) {
                     const int kb = kb0 + (start + i < span ? start + i : start + i - span);
+                    if (!released && issued == SW_STAGES) {
+                        // The ring is full of weights, which depend on nothing.  Now wait for the kernel
+                        // before this one, whose results the activations are, and send them after.
+                        sw_pdl_wait();
+                        released = true;
+                        for (int j = 0; j < SW_STAGES; ++j) sw_tma_2d(sB + j * B_BYTES, &map_x, pre_kb[j] * SW_BK, 0, &full[j]);
+                    }
                     if (!sw_wait(&empty[stage], phase ^ 1, p.error, SW_ERR_PRODUCER)) { ok = false; break; }
                     sw_mbar_expect_tx(&full[stage], A_BYTES + B_BYTES);
                     sw_tma_2d(sA + stage * A_BYTES, &map_w, kb * SW_BK, tile * SW_ROWS, &full[stage]);
-                    sw_tma_2d(sB + stage * B_BYTES, &map_x, kb * SW_BK, 0, &full[stage]);
+                    if (released) sw_tma_2d(sB + stage * B_BYTES, &map_x, kb * SW_BK, 0, &full[stage]);
+                    else pre_kb[issued] = kb;
+                    ++issued;
                     if (++stage == SW_STAGES) { stage = 0; phase ^= 1; }
                 }
+            }
+            if (!released) {                        // fewer loads than stages: all weights are on their way
+                sw_pdl_wait();
+                for (int j = 0; j < issued; ++j) sw_tma_2d(sB + j * B_BYTES, &map_x, pre_kb[j] * SW_BK, 0, &full[j]);
             }
         }
     } else if (warp == 1) {
@@ -270,7 +318,7 @@ gemm_swap_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         bool ok = true;
         for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
             const int tile = unit / splits, split = unit - tile * splits;
-            const int kb0 = split * kb_per_split, kb1 = min(k_blocks, kb0 + kb_per_split);
+            const int kb0 = k_blocks * split / splits, kb1 = k_blocks * (split + 1) / splits;
             if (!__all_sync(0xffffffffu, sw_wait(&acc_empty[acc], acc_phase ^ 1, p.error, SW_ERR_MMA))) break;
             sw_fence_after();
             const uint32_t tmem_d = tmem_base + acc * BT;
@@ -294,25 +342,28 @@ gemm_swap_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
         __syncwarp();
     } else {
-        // ---- epilogue: warps 2..5, each its own quarter of the 128 weight rows ----
+        // ---- epilogue: warps 2..9; a warp reads the lanes of its quarter (warp & 3, as tensor memory
+        // demands), and of the two warps of a quarter each takes half of the batch columns ----
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int row = quarter * 32 + lane;               // weight row within the tile
+        const int c_lo = half * (BT / 2), c_hi = c_lo + BT / 2;
         int acc = 0;
         uint32_t acc_phase = 0;
+        sw_pdl_wait();                                      // the epilogues read and write what earlier kernels wrote
         for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x) {
-            const int tile = unit / splits, split = unit - tile * splits;
-            const bool has_work = true;                     // the host cuts K so that no slice is empty
+            const int tile = unit / splits;
             const int n = tile * SW_ROWS + row;
-            if (has_work) {
-                if (!__all_sync(0xffffffffu, sw_wait(&acc_full[acc], acc_phase, p.error, SW_ERR_EPILOGUE))) break;
-                sw_fence_after();
-            }
+            if (threadIdx.x == 64) sw_stamp(p, 2);
+            if (!__all_sync(0xffffffffu, sw_wait(&acc_full[acc], acc_phase, p.error, SW_ERR_EPILOGUE))) break;
+            sw_fence_after();
+            if (threadIdx.x == 64) sw_stamp(p, 3);
             const uint32_t t_acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BT;
             // (Short loop bodies: a tile's epilogue code runs once per tile, so it has to stay small
             // enough for the instruction cache - fully unrolled it was the kernel's largest cost.)
             if (splits == 1) {
 #pragma unroll 1
-                for (int c0 = 0; c0 < BT && c0 < p.M; c0 += 8) {
+                for (int c0 = c_lo; c0 < c_hi && c0 < p.M; c0 += 8) {
                     uint32_t v[8];
                     sw_ld8(t_acc + c0, v);
 #pragma unroll
@@ -320,56 +371,54 @@ gemm_swap_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         if (c0 + c < p.M) sw_epilogue<MODE>(p, n, c0 + c, __uint_as_float(v[c]), lane);   // (uniform over the warp)
                 }
             } else {
-                // this slice's partial tile: [BT][128] FP32, one coalesced row of 128 per batch row
-                float* mine = p.partials + ((size_t)(tile * splits + split) * BT) * SW_ROWS + row;
+                // This slice's partial sums go straight to the block that owns the batch row (block r of
+                // the cluster owns rows r * per .. ), into slot [slice][row of that block][128] of ITS
+                // shared memory, a region apart from the ring (which a neighbour's MMAs may still be
+                // reading).  Stores to a neighbour's shared memory do not make the storing thread wait;
+                // loads from it, tried first, did: 64 round trips per thread.
+                const int per = (p.M + splits - 1) / splits;
+                const uint32_t me = sw_cluster_rank();
+                float* dst = slots + (size_t)me * per * SW_ROWS + row;
+                int owner = c_lo / per, local = c_lo - owner * per;      // of batch row c_lo; advanced without dividing
 #pragma unroll 1
-                for (int c0 = 0; c0 < BT && c0 < p.M; c0 += 8) {
+                for (int c0 = c_lo; c0 < c_hi && c0 < p.M; c0 += 8) {
                     uint32_t v[8];
                     sw_ld8(t_acc + c0, v);
 #pragma unroll
-                    for (int c = 0; c < 8; ++c)
-                        if (c0 + c < p.M) mine[(size_t)(c0 + c) * SW_ROWS] = __uint_as_float(v[c]);
-                }
-            }
-            if (has_work) {
-                sw_fence_before();
-                sw_mbar_arrive(&acc_empty[acc]);
-                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
-            }
-            if (splits > 1) {
-                // whoever arrives last at the tile's ticket adds the partial tiles in slice order
-                __threadfence();
-                asm volatile("bar.sync 1, 128;\n" ::: "memory");
-                if (warp == 2 && lane == 0) {
-                    const int t = atomicAdd(p.tickets + tile, 1);
-                    const int last = t == splits - 1;
-                    if (last) p.tickets[tile] = 0;
-                    *last_flag = last;
-                }
-                asm volatile("bar.sync 1, 128;\n" ::: "memory");
-                if (*last_flag) {
-                    __threadfence();
-                    const float* part = p.partials + ((size_t)tile * splits * BT) * SW_ROWS + row;
-#pragma unroll 1
-                    for (int m0 = 0; m0 < p.M; m0 += 8) {      // eight batch rows at a time: their loads overlap
-                        float s[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) s[j] = 0.f;
-                        for (int sp = 0; sp < splits; ++sp) {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                if (m0 + j < p.M) s[j] += __ldcg(part + ((size_t)sp * BT + m0 + j) * SW_ROWS);
-                        }
-#pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            if (m0 + j < p.M) sw_epilogue<MODE>(p, n, m0 + j, s[j], lane);
+                    for (int c = 0; c < 8; ++c) {
+                        if (c0 + c < p.M) sw_st_cluster(dst + local * SW_ROWS, (uint32_t)owner, __uint_as_float(v[c]));
+                        if (++local == per) { local = 0; ++owner; }
                     }
                 }
-                asm volatile("bar.sync 1, 128;\n" ::: "memory");   // last_flag is read before it is written again
             }
+            sw_fence_before();
+            sw_mbar_arrive(&acc_empty[acc]);
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            if (threadIdx.x == 64) sw_stamp(p, 4);
         }
         if (sw_extra_wait) sw_wait(&acc_full[acc], acc_phase, p.error, SW_ERR_EPILOGUE);   // tests: a phase that never completes
     }
+    if (splits > 1) {
+        // ---- the slices' partial sums are added, in slice order, by the block that owns the batch row ----
+        sw_cluster_sync();                                  // all partial sums have arrived in their owners' slots
+        if (threadIdx.x == 64) sw_stamp(p, 5);
+        if (warp >= 2) {
+            const int quarter = warp & 3, half = (warp - 2) >> 2;
+            const int row = quarter * 32 + lane;
+            const int n = (blockIdx.x / splits) * SW_ROWS + row;
+            const int per = (p.M + splits - 1) / splits;
+            const int me = (int)sw_cluster_rank();
+            const float* mine = slots + row;
+#pragma unroll 1
+            for (int l = half; l < per && me * per + l < p.M; l += 2) {     // the quarter's two warps take rows in turn
+                float v = 0.f;
+                for (int sp = 0; sp < splits; ++sp) v += mine[((size_t)sp * per + l) * SW_ROWS];
+                sw_epilogue<MODE>(p, n, me * per + l, v, lane);
+            }
+        }
+        // (nothing remote is touched after the barrier above: the blocks may leave one by one)
+    }
+    if (threadIdx.x == 64) sw_stamp(p, 6);
     sw_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -406,6 +455,11 @@ NI_EXPORT int ni_gemm_swap_tc_set_wait(long long ticks, int extra_wait) {
     return e == cudaSuccess ? NI_OK : (int)e;
 }
 
+static long long* sw_trace_ptr = nullptr;
+// For looking at where a launch's time goes: block 0 writes the time of its milestones (start, set-up
+// done, epilogue starts waiting, accumulator complete, accumulator read, sums arrived, end) to ptr.
+NI_EXPORT void ni_gemm_swap_tc_set_trace(long long* ptr) { sw_trace_ptr = ptr; }
+
 static int sw_make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
     SwEncodeTiledFn enc = sw_encode_tiled();
     if (!enc) return NI_ERR_BAD_ARGUMENT;
@@ -423,7 +477,9 @@ static int sw_n_sms() { return ni_sm_count(); }
 
 template <int BT, int MODE>
 static int launch_sw_mode(const CUtensorMap& mw, const CUtensorMap& mx, const SwParams& p, cudaStream_t stream) {
-    constexpr size_t smem = 1024 + (size_t)SwStages<BT>::value * (SW_ROWS * SW_BK * 2 + BT * SW_BK * 2) + 256;
+    constexpr size_t smem = 1024 + (size_t)SwStages<BT>::value * (SW_ROWS * SW_BK * 2 + BT * SW_BK * 2) +
+                            (size_t)(BT + 8) * SW_ROWS * 4 + 256;
+    static_assert(smem <= 232448, "shared memory of the swapped-operand product");
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_swap_tc_kernel<BT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -431,9 +487,28 @@ static int launch_sw_mode(const CUtensorMap& mw, const CUtensorMap& mx, const Sw
         configured = true;
     }
     const int units = ((p.N + SW_ROWS - 1) / SW_ROWS) * p.splits;
-    const int grid = units < sw_n_sms() ? units : sw_n_sms();
-    gemm_swap_tc_kernel<BT, MODE><<<grid, SW_THREADS, smem, stream>>>(mw, mx, p);
-    NI_RETURN_LAUNCH_STATUS();
+    // split: one unit per block, a tile's units are one cluster; whole tiles: persistent blocks
+    const int grid = p.splits > 1 ? units : (units < sw_n_sms() ? units : sw_n_sms());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(SW_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    int n_attr = 1;
+    if (p.splits > 1) {
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = p.splits;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = 1;
+        n_attr = 2;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n_attr;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_swap_tc_kernel<BT, MODE>, mw, mx, p);
+    return e == cudaSuccess ? NI_OK : (int)e;
 }
 
 template <int BT>
@@ -447,29 +522,25 @@ static int launch_sw(const CUtensorMap& mw, const CUtensorMap& mx, const SwParam
     }
 }
 
-// How many slices of K a product is cut into (so that about every SM has a unit), and the FP32
-// words of scratch that the slices need.  1 slice needs no scratch.
+// How many slices of K a product is cut into - the blocks of one cluster per tile of 128 weight rows -
+// so that about every SM has a unit: 1 when whole tiles already keep three quarters of the SMs busy,
+// else up to 8 (the portable cluster size), never more than there are 64-column blocks of K.
 NI_EXPORT int ni_gemm_swap_tc_splits(int M, int N, int K) {
     const int tiles = (N + SW_ROWS - 1) / SW_ROWS;
     const int k_blocks = (K + SW_BK - 1) / SW_BK;
+    if (tiles * 4 >= sw_n_sms() * 3) return 1;
     int splits = sw_n_sms() / tiles;
-    if (splits > k_blocks / 2) splits = k_blocks / 2;     // at least two k-blocks per slice
-    if (splits > 16) splits = 16;
-    if (splits < 1) splits = 1;
-    const int per = (k_blocks + splits - 1) / splits;
-    return (k_blocks + per - 1) / per;                    // no empty slice
+    if (splits > 8) splits = 8;
+    if (splits > k_blocks) splits = k_blocks;
+    return splits < 1 ? 1 : splits;
 }
-NI_EXPORT long long ni_gemm_swap_tc_scratch(int M, int N, int K) {
-    const int splits = ni_gemm_swap_tc_splits(M, N, K);
-    if (splits == 1) return 0;
-    const int bt = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
-    return (long long)((N + SW_ROWS - 1) / SW_ROWS) * splits * bt * SW_ROWS;
-}
+// Global scratch the product needs: none (the slices of K meet in the cluster's shared memory).
+NI_EXPORT long long ni_gemm_swap_tc_scratch(int M, int N, int K) { return 0; }
 
 // x: bf16 [M, K], 9 <= M <= 128 (fewer rows work too); w: bf16 [N, K]; K a multiple of 8; 16-byte aligned.
 // mode 0 store bf16 [M, N], 1 store FP32, 2 add into FP32 [M, N], 3 SwiGLU over blocked rows -> bf16
 // [M, N / 2], 4 rotary encoding + paged K/V write of a fused QKV projection (out = q, bf16 [M, Hq * hd]).
-// partials: FP32 scratch of ni_gemm_swap_tc_scratch words; tickets: one zero int per 128 weight rows.
+// partials, tickets: unused (kept in the signature; earlier versions combined the slices of K through them).
 NI_EXPORT int ni_gemm_swap_tc(const void* x, const void* w, void* out, int M, int N, int K, int mode, float* partials,
                               int* tickets, const int* positions, const int* seq_of_token, const int* block_table,
                               int bt_stride, const float* inv_freq, void* k_pages, void* v_pages, int n_q_heads,
@@ -484,8 +555,8 @@ NI_EXPORT int ni_gemm_swap_tc(const void* x, const void* w, void* out, int M, in
     SwParams p = {};
     p.out = out; p.M = M; p.N = N; p.K = K; p.mode = mode; p.error = error;
     p.splits = ni_gemm_swap_tc_splits(M, N, K);
-    if (p.splits > 1 && (partials == nullptr || tickets == nullptr)) return NI_ERR_BAD_ARGUMENT;
-    p.partials = partials; p.tickets = tickets;
+    p.trace = sw_trace_ptr;
+    (void)partials; (void)tickets;
     p.positions = positions; p.seq_of_token = seq_of_token; p.block_table = block_table; p.inv_freq = inv_freq;
     p.k_pages = (__nv_bfloat16*)k_pages; p.v_pages = (__nv_bfloat16*)v_pages; p.bt_stride = bt_stride;
     p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim; p.rotary_dim = rotary_dim;

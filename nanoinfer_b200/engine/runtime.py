@@ -36,6 +36,9 @@ class Runtime:
     fused_decode: bool = False    # steps of up to 8 single tokens as ONE persistent kernel (slower than the chain of kernels so far)
 
     def __post_init__(self) -> None:
+        import os
+        if os.environ.get("NANOINFER_B200_MID_BATCH"):          # for measurements: which projections take the swapped kernel
+            self.mid_batch_mask = int(os.environ["NANOINFER_B200_MID_BATCH"])
         self._workspaces = {}
         self._retired = []
         ops.require_cuda()
@@ -76,20 +79,26 @@ class Runtime:
         bandwidth kernel (and so may carry fused prologues and epilogues)."""
         return self.dtype == torch.bfloat16 and 0 < n_rows <= ops.SKINNY_ROWS and k % 8 == 0
 
+    # Which projections of a step of 9 .. 128 rows go to the package's swapped-operand tcgen05 kernel
+    # (with their neighbours fused into its epilogue) instead of the library product followed by
+    # separate element-wise kernels.
+    MID_QKV, MID_OUT, MID_GATE_UP, MID_DOWN, MID_HEAD = 1, 2, 4, 8, 16
+    mid_batch_mask: int = MID_HEAD
+
+    def mid_batch(self, n_rows: int, k: int, which: int) -> bool:
+        """True if projection ``which`` (one of the MID_* bits) of n_rows rows with inner size k
+        takes the swapped-operand kernel."""
+        return (self.dtype == torch.bfloat16 and ops.SKINNY_ROWS < n_rows <= ops.SWAP_MAX_ROWS and k % 8 == 0
+                and bool(self.mid_batch_mask & which))
+
     def swapped_gemm(self, n_rows: int, n_out: int, k: int, fused: bool = False) -> bool:
-        """True if a product of 9..128 rows goes to the package's swapped-operand tcgen05 kernel:
-        where K need not be split (enough weight rows to give every SM a tile) and either the
-        blocks stream several tiles each (an output projection over a vocabulary: 5.9 TB/s of
-        weights against 5.7 for the library product) or a fused epilogue saves a launch and the
-        batch is small (SwiGLU at up to 32 rows: 14.6 us against 12.5 + 3.9)."""
+        """True if a plain product of 9..128 rows goes to the package's swapped-operand tcgen05 kernel:
+        an output projection over a vocabulary (blocks stream several tiles each: 5.9 TB/s of weights
+        against 5.7 for the library product)."""
         if self.dtype != torch.bfloat16 or not ops.SKINNY_ROWS < n_rows <= ops.SWAP_MAX_ROWS or k % 8:
             return False
-        if ops.gemm_swap_scratch(n_rows, n_out, k) != 0:
-            return False          # the kernel would split K: the callers here pass no scratch
         tiles = -(-n_out // 128)
-        if tiles >= 4 * ops.sm_count(self.device):
-            return True
-        return fused and tiles >= 100 and n_rows <= 32
+        return tiles >= 4 * ops.sm_count(self.device) and bool(self.mid_batch_mask & self.MID_HEAD)
 
     def tensor_core_gemm(self, n_rows: int, k: int) -> bool:
         """True if a product with this many rows goes to the package's tcgen05 kernel (where

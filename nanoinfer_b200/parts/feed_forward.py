@@ -50,11 +50,14 @@ class SwiGLU(Part):
             ops.gemv_bf16(x, self.w_gate_up, act, ops.SWIGLU_BF16)     # activation in the epilogue
         elif self.blocked and rt.tensor_core_gemm(n, self.hidden_size):
             ops.gemm_tc(x, self.w_gate_up, act, ops.SWIGLU_BF16)       # tcgen05 product, activation fused
-        elif self.blocked and rt.swapped_gemm(n, 2 * self.inter, self.hidden_size, fused=True):
+        elif self.blocked and rt.mid_batch(n, self.hidden_size, rt.MID_GATE_UP):
             ops.gemm_swap_tc(x, self.w_gate_up, act, ops.SWIGLU_BF16)  # weights on the tile's lanes, activation fused
         else:
             gate_up = rt.linear(x, self.w_gate_up)
             ops.swiglu(gate_up, act, blocked=self.blocked)
+        if residual is not None and rt.mid_batch(n, self.inter, rt.MID_DOWN):
+            ops.gemm_swap_tc(act, self.w_down, residual, ops.ADD_F32)
+            return None
         return rt.linear(act, self.w_down, residual=residual)
 
     def forward_fused_norm(self, h: torch.Tensor, norm, ctx, residual=None):

@@ -117,12 +117,21 @@ class PagedAttention(Part):
             ops.gemv_qkv_rope(x, gain, eps, self.w_qkv, q, k_pages, v_pages, ctx.positions, ctx.seq_of_token,
                               table, pos.inv_freq, self.n_heads, self.n_kv, self.head_dim, pos.rotary_dim,
                               rt.page_size)
+        elif rt.mid_batch(n, self.hidden_size, rt.MID_QKV) and self.head_dim % 2 == 0:
+            # a middle batch: projection on the tensor cores with the weights on the tile's lanes,
+            # rotation and cache write in its epilogue
+            ops.gemm_swap_tc(x, self.w_qkv, q, ops.ROPE_KV,
+                             rope=(ctx.positions, ctx.seq_of_token, table, pos.inv_freq, k_pages, v_pages, self.n_heads,
+                                   self.n_kv, self.head_dim, pos.rotary_dim, rt.page_size))
         else:
             qkv = rt.linear(x, self.w_qkv)
             ops.rope_kv_write(qkv, q, k_pages, v_pages, ctx.positions, ctx.seq_of_token, table, pos.inv_freq,
                               self.n_heads, self.n_kv, self.head_dim, pos.rotary_dim, True, rt.page_size)
         att = rt.empty(n, self.n_heads * self.head_dim)
         self._attend(q, cache, att, ctx, table)
+        if residual is not None and rt.mid_batch(n, self.n_heads * self.head_dim, rt.MID_OUT):
+            ops.gemm_swap_tc(att, self.w_o, residual, ops.ADD_F32)       # added into the residual stream in the epilogue
+            return None
         return rt.linear(att, self.w_o, residual=residual)
 
     def _attend(self, q, cache, att, ctx, table) -> None:

@@ -19,31 +19,54 @@ from typing import Dict, List, Optional, Sequence
 
 import torch
 
+# The precision the plain implementation computes in.  float32 is what the reference computes in;
+# float64 serves as the exact value when the rounding of a 32-bit computation itself is what a test
+# measures (at the full model size, where sums of 8,192 terms through 16 layers no longer agree to
+# 1e-4 between two correct 32-bit implementations that add in different orders).
+DTYPE = torch.float32
+
+
+class precision:
+    """with plain.precision(torch.float64): ... - compute in another precision for a while."""
+
+    def __init__(self, dtype):
+        self.dtype = dtype
+
+    def __enter__(self):
+        global DTYPE
+        self.before, DTYPE = DTYPE, self.dtype
+
+    def __exit__(self, *exc):
+        global DTYPE
+        DTYPE = self.before
+        return False
+
 
 def embedding(table: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
     """h[t] = E[tok[t]]  (src/op/kernels/cpu/embedding_kernel.cpp:30-50)."""
-    return table.float()[tokens.long()]
+    return table.to(DTYPE)[tokens.long()]
 
 
 def rms_norm(x: torch.Tensor, gain: torch.Tensor, eps: float) -> torch.Tensor:
     """y = x * rsqrt(mean(x^2) + eps) * g, eps inside the root
     (src/op/kernels/cuda/rmsnorm_kernel.cu:49-104, line 79; tools/model.py:34-39)."""
-    x = x.float()
+    x = x.to(DTYPE)
     inv = torch.rsqrt(x.pow(2).mean(dim=-1, keepdim=True) + eps)
-    return (x * inv) * gain.float()
+    return (x * inv) * gain.to(DTYPE)
 
 
 def rope_inv_freq(rotary_dim: int, theta: float, scaling: Optional[dict]) -> torch.Tensor:
     """Inverse frequencies with the optional llama3 rule, FP32 throughout
     (src/op/kernels/cpu/rope_kernel.cpp:117-139)."""
-    idx = torch.arange(0, rotary_dim, 2, dtype=torch.float32)
-    freq = 1.0 / torch.pow(torch.tensor(theta, dtype=torch.float32), idx / rotary_dim)
+    f32 = torch.float32        # frequencies and angles are 32-bit numbers by definition, whatever DTYPE is
+    idx = torch.arange(0, rotary_dim, 2, dtype=f32)
+    freq = 1.0 / torch.pow(torch.tensor(theta, dtype=f32), idx / rotary_dim)
     if scaling is not None and scaling.get("rope_type", scaling.get("type")) == "llama3":
-        factor = torch.tensor(float(scaling["factor"]), dtype=torch.float32)
-        low = torch.tensor(float(scaling["low_freq_factor"]), dtype=torch.float32)
-        high = torch.tensor(float(scaling["high_freq_factor"]), dtype=torch.float32)
-        orig = torch.tensor(float(scaling["original_max_position_embeddings"]), dtype=torch.float32)
-        wavelen = torch.tensor(2.0 * math.pi, dtype=torch.float32) / freq
+        factor = torch.tensor(float(scaling["factor"]), dtype=f32)
+        low = torch.tensor(float(scaling["low_freq_factor"]), dtype=f32)
+        high = torch.tensor(float(scaling["high_freq_factor"]), dtype=f32)
+        orig = torch.tensor(float(scaling["original_max_position_embeddings"]), dtype=f32)
+        wavelen = torch.tensor(2.0 * math.pi, dtype=f32) / freq
         smooth = (orig / wavelen - low) / (high - low)
         blended = (1.0 - smooth) * freq / factor + smooth * freq
         freq = torch.where(wavelen >= orig / low, freq / factor,
@@ -56,9 +79,9 @@ def rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor, pairi
     "interleaved": pairs (2i, 2i+1) (src/op/kernels/cpu/rope_kernel.cpp:68-93);
     "half": pairs (i, i + rot/2), the same rotation for projection rows in the
     safetensors order (the exporter's permutation, tools/export_llama3.py:571-583)."""
-    x = x.float()
+    x = x.to(DTYPE)
     rot = inv_freq.numel() * 2
-    angle = positions.float()[:, None] * inv_freq.float()[None, :]      # [T, rot/2]
+    angle = (positions.to(torch.float32)[:, None] * inv_freq.to(torch.float32)[None, :]).to(DTYPE)   # [T, rot/2], FP32 product
     cos, sin = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
     out = x.clone()
     if pairing == "interleaved":
@@ -84,7 +107,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
     T, hq, hd = q.shape
     hkv = k.shape[1]
     rep = hq // hkv
-    q, k, v = q.float(), k.float(), v.float()
+    q, k, v = q.to(DTYPE), k.to(DTYPE), v.to(DTYPE)
     out = torch.empty_like(q)
     i = torch.arange(T)
     mask = i[None, :] <= i[:, None]
@@ -104,23 +127,23 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
 def swiglu_ffn(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
     """down(silu(gate(x)) * up(x)), silu(g) = g / (1 + exp(-g))
     (src/model/llama.cpp:364-379, src/op/kernels/cpu/swiglu_kernel.cpp:25-40)."""
-    x = x.float()
-    g = x @ w_gate.float().t()
-    u = x @ w_up.float().t()
-    return ((g / (1.0 + torch.exp(-g))) * u) @ w_down.float().t()
+    x = x.to(DTYPE)
+    g = x @ w_gate.to(DTYPE).t()
+    u = x @ w_up.to(DTYPE).t()
+    return ((g / (1.0 + torch.exp(-g))) * u) @ w_down.to(DTYPE).t()
 
 
 def attention_block(x, w, prefix, n_heads, n_kv, hd, positions, inv_freq, pairing, scale, window=None):
     """QKV projections, RoPE on q and k, attention, output projection
     (src/model/llama.cpp:327-356)."""
     T = x.shape[0]
-    q = (x @ w[f"{prefix}.q_proj.weight"].float().t()).view(T, n_heads, hd)
-    k = (x @ w[f"{prefix}.k_proj.weight"].float().t()).view(T, n_kv, hd)
-    v = (x @ w[f"{prefix}.v_proj.weight"].float().t()).view(T, n_kv, hd)
+    q = (x @ w[f"{prefix}.q_proj.weight"].to(DTYPE).t()).view(T, n_heads, hd)
+    k = (x @ w[f"{prefix}.k_proj.weight"].to(DTYPE).t()).view(T, n_kv, hd)
+    v = (x @ w[f"{prefix}.v_proj.weight"].to(DTYPE).t()).view(T, n_kv, hd)
     q = rope(q, positions, inv_freq, pairing)
     k = rope(k, positions, inv_freq, pairing)
     o = attention(q, k, v, scale, window).reshape(T, n_heads * hd)
-    return o @ w[f"{prefix}.o_proj.weight"].float().t()
+    return o @ w[f"{prefix}.o_proj.weight"].to(DTYPE).t()
 
 
 def forward(raw: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int]) -> torch.Tensor:
@@ -147,7 +170,7 @@ def forward(raw: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int]) -> tor
                            w[f"{p}.mlp.down_proj.weight"])
     h = rms_norm(h, w["model.norm.weight"], eps)
     head = w["model.embed_tokens.weight"] if raw.get("tie_word_embeddings", False) else w["lm_head.weight"]
-    return h @ head.float().t()
+    return h @ head.to(DTYPE).t()
 
 
 def greedy_generate(raw: dict, w: Dict[str, torch.Tensor], prompt: Sequence[int], n_new: int) -> List[int]:

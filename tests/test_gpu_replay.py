@@ -351,14 +351,29 @@ def test_full_size_model_in_float32_all_cuts(tmp_path_factory):
     raw_read, w = load_plain(d)
     reqs = {"p": random_tokens(raw["vocab_size"], 280, 1), "q": random_tokens(raw["vocab_size"], 130, 2),
             "r": random_tokens(raw["vocab_size"], 75, 3)}
-    want = ru.plain_logits(raw_read, w, reqs)
+    # At this size two correct 32-bit computations that add in different orders no longer agree to the
+    # 1e-4 of the small models (sums of 8,192 terms, 16 layers).  The yardstick is therefore the
+    # plain implementation itself: its 32-bit result against its 64-bit result is how far a 32-bit
+    # computation of this model is from the exact one; the engine may be no further than a small
+    # multiple of that, at any logit of any position.
+    want32 = ru.plain_logits(raw_read, w, reqs)
+    with plain.precision(torch.float64):
+        want64 = ru.plain_logits(raw_read, w, reqs)
+    plain_error = max((want32[r].double() - want64[r]).abs().max().item() for r in reqs)
+    scale = max(want64[r].abs().max().item() for r in reqs)
+    assert plain_error < 1e-4 * scale, "the 32-bit plain implementation itself is off"
     results = {}
     for cut, fn in CUTS.items():
         steps = fn(reqs) if cut != "mixed" else ru.mixed(reqs, max_live=2)     # two live: the third takes over freed pages
         runner = _runner(d, "float32", 16, steps)
         got = ru.run_trace(runner, steps)
         assert len(got) == sum(len(t) for t in reqs.values())
-        ru.compare(got, want, "float32", label=f"1b/{cut}/float32")
+        engine_error = max((row.double() - want64[rid][pos]).abs().max().item() for (rid, pos), row in got.items())
+        # (The engine adds each dot product's terms one after the other in ascending order, so that no
+        # cut can change a bit; the CPU library adds 16 lanes side by side.  One chain of 8,192 terms
+        # rounds about sqrt(16) = 4 times as much as 16 chains of 512: measured 4.2.  Twice that is allowed.)
+        assert engine_error <= 8.0 * plain_error, \
+            f"1b/{cut}: engine {engine_error:.3g} from the exact logits, the plain 32-bit computation {plain_error:.3g}"
         results[cut] = got
         runner.cache.check_consistency()
         del runner

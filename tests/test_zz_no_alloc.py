@@ -154,14 +154,14 @@ def test_noalloc_entry_point_at_and_beyond_its_limits():
             assert torch.equal(out, want)
         else:
             assert rc == ERR_STATIC_SCRATCH_TOO_SMALL and torch.all(out == 3.0)
-    # tickets: 513 tokens x 8 kv heads = 4,104 > 4,096 (the floats would fit: 513 x 32 x 66 x 1 split)
-    n_big = 513
-    assert n_big * n_kv > MAX_TICKETS and n_big * n_q * (hd + 2) <= MAX_PARTIAL_FLOATS
-    qb = torch.zeros(n_big, n_q * hd, dtype=torch.bfloat16, device=DEV)
+    # tickets: 513 tokens x 8 kv heads = 4,104 > 4,096, while the floats fit (513 x 8 heads x 66 x 1 split)
+    n_big, few_q = 513, 8
+    assert n_big * n_kv > MAX_TICKETS and n_big * few_q * (hd + 2) <= MAX_PARTIAL_FLOATS
+    qb = torch.zeros(n_big, few_q * hd, dtype=torch.bfloat16, device=DEV)
     out = torch.full_like(qb, 3.0)
     i32 = dict(dtype=torch.int32, device=DEV)
     rc = fn(qb.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), None, n_big,
             torch.zeros(n_big, **i32).data_ptr(), torch.zeros(n_big, **i32).data_ptr(), table.data_ptr(), table.shape[1],
-            n_q, n_kv, hd, page, 0, 0.125, 1, stream)
+            few_q, n_kv, hd, page, 0, 0.125, 1, stream)
     torch.cuda.synchronize()
     assert rc == ERR_STATIC_SCRATCH_TOO_SMALL and torch.all(out == 3.0)
