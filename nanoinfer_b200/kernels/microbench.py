@@ -4,6 +4,8 @@
     python -m nanoinfer_b200.kernels.microbench gemm_swap --m 64 --n 16384 --k 2048 --mode swiglu
     python -m nanoinfer_b200.kernels.microbench attention_decode --batch 8 --context 3072
     python -m nanoinfer_b200.kernels.microbench attention_prefill --tokens 2048 --kernel tc
+    python -m nanoinfer_b200.kernels.microbench gemm_swap --m 64 --n 2048 --k 2048 --mode add --milestones
+    python -m nanoinfer_b200.kernels.microbench decode_fused --batch 8 --context 2048
 
 Each case runs its kernel over several distinct copies of its inputs in turn (together
 larger than the L2 cache, so every run reads from HBM), times it with CUDA events after
@@ -106,6 +108,20 @@ def gemm_swap(args) -> None:
     ops.check_device_errors()
     ref = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
     us_lib = _time([lambda w=w: torch.matmul(x, w.t(), out=ref) for w in ws], args.iters)
+    if args.milestones:
+        import ctypes
+        lib = ops.load("gemm_swap_tc")
+        lib.ni_gemm_swap_tc_set_trace.argtypes = [ctypes.c_void_p]
+        lib.ni_gemm_swap_tc_set_trace.restype = None
+        stamps = torch.zeros(16, dtype=torch.int64, device=DEV)
+        lib.ni_gemm_swap_tc_set_trace(stamps.data_ptr())
+        ops.gemm_swap_tc(x, ws[-1], out, mode, scratch, tickets)
+        torch.cuda.synchronize()
+        lib.ni_gemm_swap_tc_set_trace(None)
+        t = stamps.cpu().tolist()
+        names = ["set-up done", "epilogue waits", "accumulator complete", "accumulator read (sums sent)", "sums arrived", "end"]
+        print("  one launch, block 0, microseconds after its start: " +
+              "; ".join(f"{nm} {(t[i + 1] - t[0]) / 1e3:.2f}" for i, nm in enumerate(names) if t[i + 1] > 0))
     print(f"gemm_swap m={m} n={n} k={k} mode={args.mode}: {us:.2f} us, {w_bytes / us / 1e3:.0f} GB/s of weights "
           f"(library product, plain store: {us_lib:.2f} us, {w_bytes / us_lib / 1e3:.0f} GB/s; {copies} weight copies in turn)")
 
@@ -158,6 +174,67 @@ def attention_prefill(args) -> None:
           f"{flops / us / 1e6:.0f} TFLOP/s (causal)")
 
 
+def decode_fused(args) -> None:
+    """One decode step of the whole model as ONE persistent kernel (csrc/decode_fused.cu) against the
+    same step as the chain of per-part kernels, and where the fused kernel's time goes: block 0 stamps
+    the time at every phase boundary."""
+    from ..config import config_from_dict, preset
+    from ..engine import ModelRunner, StepEntry
+    from ..weights import tensor_plan
+    raw = dict(preset(args.shape))
+    if args.layers:
+        raw["num_hidden_layers"] = args.layers
+    config = config_from_dict(raw)
+    g = torch.Generator(device=DEV).manual_seed(0)
+    weights = {p.name: (torch.ones(p.shape, dtype=torch.bfloat16, device=DEV) if p.init == "ones" else
+                        (torch.randn(p.shape, generator=g, device=DEV, dtype=torch.float32) * 0.02).to(torch.bfloat16))
+               for p in tensor_plan(config)}
+    batch, ctx_len, page = args.batch, args.context, 16
+    cpu = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, raw["vocab_size"], (ctx_len,), generator=cpu).tolist() for _ in range(batch)]
+    results = {}
+    for fused in (False, True):
+        runner = ModelRunner(config, weights, dtype="bfloat16", page_size=page, num_pages=batch * (ctx_len // page + 8) + 8,
+                             max_requests=batch, max_tokens_per_request=ctx_len + 256, fused_decode=fused)
+        last = []
+        for r, toks in enumerate(prompts):
+            last.append(int(torch.argmax(runner.step([StepEntry(r, toks, [ctx_len - 1])])[0])))
+        n = args.iters
+        toks = runner.greedy_decode_on_device(list(range(batch)), last, 4)       # captures the step
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        toks = runner.greedy_decode_on_device(list(range(batch)), toks[-1].tolist(), n)
+        b.record()
+        torch.cuda.synchronize()
+        ops.check_device_errors()
+        results[fused] = a.elapsed_time(b) / n
+        if fused:
+            f = runner.model._fused
+            stamps = torch.zeros(4096, dtype=torch.int64, device=DEV)
+            f.params.trace = stamps.data_ptr()
+            runner.use_graphs = False
+            runner.step([StepEntry(r, [int(t)], [0]) for r, t in enumerate(toks[-1].tolist())])
+            torch.cuda.synchronize()
+            f.params.trace = None
+            layers = raw["num_hidden_layers"]
+            names = ["embedding", "barrier"]
+            for _ in range(layers):
+                names += ["qkv", "barrier", "attention", "barrier", "output", "barrier", "gate/up", "barrier", "down", "barrier"]
+            names += ["vocabulary"]
+            t = stamps.cpu().tolist()[:len(names)]
+            total = {}
+            for i in range(1, len(names)):
+                total.setdefault(names[i], []).append((t[i] - t[i - 1]) / 1e3)
+            print(f"fused kernel, one step seen by block 0: {(t[-1] - t[0]) / 1e3:.0f} us")
+            for k, v in total.items():
+                print(f"  {k:10s} {len(v):3d} x {sum(v) / len(v):7.2f} us = {sum(v):8.1f} us")
+        del runner
+        torch.cuda.empty_cache()
+    print(f"decode step, batch {batch}, context {ctx_len}, {raw['num_hidden_layers']} layers of {args.shape}: "
+          f"chain of kernels {results[False]:.3f} ms, fused kernel {results[True]:.3f} ms")
+
+
 def main() -> None:
     ops.require_cuda()
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -183,7 +260,14 @@ def main() -> None:
     p.add_argument("--n", type=int, default=16384)
     p.add_argument("--k", type=int, default=2048)
     p.add_argument("--mode", default="bf16", choices=["bf16", "f32", "add", "swiglu"])
+    p.add_argument("--milestones", action="store_true", help="also print block 0's timeline of one launch")
     p.set_defaults(fn=gemm_swap)
+    p = sub.add_parser("decode_fused")
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--context", type=int, default=2048)
+    p.add_argument("--shape", default="llama-3.2-1b")
+    p.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has")
+    p.set_defaults(fn=decode_fused)
     for name, fn in (("attention_decode", attention_decode), ("attention_prefill", attention_prefill)):
         p = sub.add_parser(name)
         p.add_argument("--batch", type=int, default=8)
