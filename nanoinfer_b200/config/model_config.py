@@ -15,7 +15,7 @@ from __future__ import annotations
 
 import json
 import os
-from dataclasses import dataclass, field
+from dataclasses import dataclass, field, replace
 from typing import Any, Dict, Optional, Tuple
 
 
@@ -95,6 +95,33 @@ class FeedForwardSpec:
 
 
 @dataclass(frozen=True)
+class EmbeddingSpec:
+    """How token ids become rows of the residual stream.  kind "table": row ``id`` of a
+    [vocab, hidden] matrix (src/op/kernels/cuda/embedding_kernel.cu:7-31).  ``vocab_size`` 0 means
+    the model's; ``extra`` carries constants of other kinds."""
+    kind: str = "table"
+    vocab_size: int = 0
+    extra: Tuple[Tuple[str, Any], ...] = ()
+
+    def extra_dict(self) -> Dict[str, Any]:
+        return dict(self.extra)
+
+
+@dataclass(frozen=True)
+class HeadSpec:
+    """How the residual stream's wanted rows become logits.  kind "linear": final norm, then a
+    product with a [vocab, hidden] matrix (src/model/llama.cpp:381-389); ``tied``: that matrix is
+    the embedding's table and the head stores none of its own."""
+    kind: str = "linear"
+    vocab_size: int = 0
+    tied: bool = False
+    extra: Tuple[Tuple[str, Any], ...] = ()
+
+    def extra_dict(self) -> Dict[str, Any]:
+        return dict(self.extra)
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One layer: how mixer, feed-forward and norms are arranged, and their specs.
 
@@ -134,10 +161,21 @@ class ModelConfig:
     bos_token_id: Optional[int] = None
     eos_token_ids: Tuple[int, ...] = ()
     raw: Tuple[Tuple[str, Any], ...] = ()
+    embedding: EmbeddingSpec = field(default_factory=EmbeddingSpec)
+    head: HeadSpec = field(default_factory=HeadSpec)
 
     @property
     def num_layers(self) -> int:
         return len(self.layers)
+
+    def embedding_spec(self) -> EmbeddingSpec:
+        """The embedding's spec with the model's vocabulary filled in."""
+        return replace(self.embedding, vocab_size=self.embedding.vocab_size or self.vocab_size)
+
+    def head_spec(self) -> HeadSpec:
+        """The head's spec with the model's vocabulary and ``tie_word_embeddings`` filled in."""
+        return replace(self.head, vocab_size=self.head.vocab_size or self.vocab_size,
+                       tied=self.head.tied or self.tie_word_embeddings)
 
     def validate(self) -> None:
         if self.hidden_size <= 0 or self.vocab_size <= 0:

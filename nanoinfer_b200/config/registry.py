@@ -25,7 +25,7 @@ from typing import Any, Callable, Dict, Tuple
 
 from .model_config import ConfigError, ModelConfig, read_config_json
 
-PART_CATEGORIES = ("mixer", "feed_forward", "norm", "position", "arrangement")
+PART_CATEGORIES = ("mixer", "feed_forward", "norm", "position", "arrangement", "embedding", "head")
 
 
 @dataclass(frozen=True)

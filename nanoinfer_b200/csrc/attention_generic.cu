@@ -3,6 +3,8 @@
 // softmax in FP32.  Prompt portions and single decoded tokens are the same case: a
 // token at position p sees keys [max(0, p - window + 1), p] of its own request.  An optional
 // token list restricts the launch to some of the step's tokens (n_tokens = its length).
+// An optional slope per query head adds slope * (key position - query position) to the scaled
+// score: a position encoding that acts on the scores instead of rotating queries and keys.
 //
 // The result of a token depends only on its own keys and their order, never on how the
 // step was cut or what else is in the batch, so this kernel is the FP32 path's attention
@@ -24,7 +26,8 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
                                          const int* __restrict__ seq_of_token,
                                          const int* __restrict__ block_table, int bt_stride,
                                          int n_tokens, int n_q_heads, int n_kv_heads, int head_dim,
-                                         int page_size, int window, float scale) {
+                                         int page_size, int window, float scale,
+                                         const float* __restrict__ head_slopes) {
     const int warps_per_block = blockDim.x >> 5;
     const long long item = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
     if (item >= (long long)n_tokens * n_q_heads) return;
@@ -36,6 +39,7 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
     const int pos = positions[t];
     const int* table = block_table + (size_t)seq_of_token[t] * bt_stride;
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const float slope = head_slopes ? head_slopes[head] : 0.f;
 
     float qr[ATT_MAX_REGS], acc[ATT_MAX_REGS];
     const T* qrow = q + ((size_t)t * n_q_heads + head) * head_dim;
@@ -58,7 +62,7 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
             if (dim < head_dim) dot += qr[r] * ni_to_float(krow[dim]);
         }
         dot = ni_warp_sum(dot);
-        const float s = dot * scale;
+        const float s = dot * scale + slope * (float)(j - pos);
         const float m_new = fmaxf(m, s);
         const float corr = expf(m - m_new);  // exp(-inf) = 0 on the first key
         const float p = expf(s - m_new);
@@ -83,7 +87,8 @@ NI_EXPORT int ni_attention_generic(const void* q, int dtype, const void* k_pages
                                    const void* v_pages, void* out, const int* token_list,
                                    const int* positions, const int* seq_of_token, const int* block_table, int bt_stride,
                                    int n_tokens, int n_q_heads, int n_kv_heads, int head_dim,
-                                   int page_size, int window, float scale, cudaStream_t stream) {
+                                   int page_size, int window, float scale, const float* head_slopes,
+                                   cudaStream_t stream) {
     if (n_tokens <= 0) return NI_OK;
     if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads || head_dim <= 0 || page_size <= 0)
         return NI_ERR_BAD_ARGUMENT;
@@ -96,7 +101,7 @@ NI_EXPORT int ni_attention_generic(const void* q, int dtype, const void* k_pages
     attention_generic_kernel<T><<<(int)blocks, warps * 32, 0, stream>>>(                            \
         (const T*)q, (const T*)k_pages, (const T*)v_pages, (T*)out, token_list, positions,         \
         seq_of_token,                                                                               \
-        block_table, bt_stride, n_tokens, n_q_heads, n_kv_heads, head_dim, page_size, window, scale)
+        block_table, bt_stride, n_tokens, n_q_heads, n_kv_heads, head_dim, page_size, window, scale, head_slopes)
     if (dtype == NI_DTYPE_F32) LAUNCH(float);
     else if (dtype == NI_DTYPE_BF16) LAUNCH(__nv_bfloat16);
     else return NI_ERR_BAD_ARGUMENT;

@@ -17,6 +17,8 @@ import torch
 
 from ..kernels import ops
 from ..parts.block import PreNormBlock
+from ..parts.embedding import TableEmbedding
+from ..parts.head import LinearHead
 from ..parts.feed_forward import SwiGLU
 from ..parts.mixer import PagedAttention
 from ..parts.norm import RMSNorm
@@ -34,7 +36,9 @@ class FusedDecode:
         rt, cfg = model.rt, model.config
         if rt.dtype != torch.bfloat16 or not getattr(rt, "fused_decode", True):
             return None
-        if not isinstance(model.final_norm, RMSNorm) or not cfg.schedule:
+        if type(model.final_norm) is not RMSNorm or not cfg.schedule:
+            return None
+        if type(model.embedding) is not TableEmbedding or type(model.head) is not LinearHead:
             return None
         blocks = [model.blocks[run.layer] for run in cfg.schedule]
         for b in blocks:
@@ -50,6 +54,8 @@ class FusedDecode:
             if not same or b.feed_forward.inter != blocks[0].feed_forward.inter:
                 return None
             if m.position.rotary_dim > 0 and not torch.equal(m.position.inv_freq, first.position.inv_freq):
+                return None
+            if getattr(m.position, "head_slopes", None) is not None:
                 return None
         groups = {c.group for c in caches if c is not None}
         if any(c is None or c.k_pages is None for c in caches) or max(groups) >= ops.FUSED_MAX_GROUPS:
@@ -88,7 +94,7 @@ class FusedDecode:
         self.error = ops.error_word(dev)
         p = self.params = ops.FusedParams()
         p.layers, p.inv_freq = self.layers.data_ptr(), mixer.position.inv_freq.data_ptr()
-        p.embedding, p.lm_head = model.embedding.data_ptr(), model.lm_head.data_ptr()
+        p.embedding, p.lm_head = model.embedding.table.data_ptr(), model.head.weight.data_ptr()
         p.gain_final, p.eps_final = model.final_norm.gain.data_ptr(), model.final_norm.eps
         p.h, p.q, p.att, p.act, p.logits = (t.data_ptr() for t in (self.h, self.q, self.att, self.act, self.logits))
         p.partials, p.tickets, p.barrier, p.error = (t.data_ptr() for t in (self.partials, self.tickets, self.barrier, self.error))

@@ -9,7 +9,6 @@ import torch
 
 from ..config import registry
 from ..config.model_config import ModelConfig
-from ..kernels import ops
 from ..weights.plan import tensor_plan
 
 
@@ -23,17 +22,22 @@ class DecoderModel:
             if p.name not in weights:
                 raise KeyError(f"weight '{p.name}' is missing")
             by_scope.setdefault(p.scope, {})[p.slot] = weights[p.name]
-        self.embedding = rt.weight(by_scope[("embedding",)]["weight"])
+        emb = config.embedding_spec()
+        self.embedding = registry.part("embedding", emb.kind)(emb, d, by_scope.get(("embedding",), {}), rt)
         self.blocks = []
         for i, layer in enumerate(config.layers):
             cls = registry.part("arrangement", layer.arrangement)
             self.blocks.append(cls(layer, d, lambda what, i=i: by_scope.get(("layer", i, what), {}), rt))
         self.final_norm = registry.part("norm", config.final_norm.kind)(
             config.final_norm, d, by_scope.get(("final_norm",), {}), rt)
-        # a tied output projection is the embedding table itself: one device copy
-        # (the reference uploads the shared matrix twice, src/model/llama.cpp:576-578,652-657)
-        self.lm_head = (self.embedding if config.tie_word_embeddings
-                        else rt.weight(by_scope[("lm_head",)]["weight"]))
+        head = config.head_spec()
+        head_weights = dict(by_scope.get(("lm_head",), {}))
+        if head.tied:
+            table = getattr(self.embedding, "table", None)
+            if table is None:
+                raise ValueError(f"a tied head needs an embedding with a table; '{emb.kind}' has none")
+            head_weights["weight"] = table      # the embedding's own device copy
+        self.head = registry.part("head", head.kind)(head, d, head_weights, rt)
         self._fused = False      # the fused decode step: not looked at yet / None (does not apply) / the object
 
     def cache_needs(self) -> List[Optional[object]]:
@@ -58,18 +62,8 @@ class DecoderModel:
             if self._fused is not None and self._fused.takes(ctx):
                 return self._fused.run(ctx)      # a step of a few single tokens: one persistent kernel
         h = rt.empty(ctx.n_tokens, cfg.hidden_size, dtype=torch.float32)
-        ops.embedding(ctx.tokens, self.embedding, h)
+        self.embedding.forward(ctx.tokens, h)
         delta = None
         for r, run in enumerate(cfg.schedule):
             delta = self.blocks[run.layer].forward(h, delta, ctx, caches[r])
-        if ctx.n_logit_rows == 0:
-            return rt.empty(0, cfg.vocab_size, dtype=torch.float32)
-        norm = self.final_norm
-        if (delta is None and rt.skinny(ctx.n_logit_rows, cfg.hidden_size) and hasattr(norm, "gain")
-                and hasattr(norm, "eps")):
-            # few rows: final norm, row selection and output projection in one launch
-            logits = rt.empty(ctx.n_logit_rows, cfg.vocab_size, dtype=torch.float32)
-            ops.gemv_norm_bf16(h, norm.gain, norm.eps, ctx.logit_rows, self.lm_head, logits, ops.STORE_F32)
-            return logits
-        x = norm.forward(h, delta, rows=ctx.logit_rows)
-        return rt.linear(x, self.lm_head, out_dtype=torch.float32)
+        return self.head.forward(h, delta, self.final_norm, ctx)

@@ -242,7 +242,7 @@ class ModelRunner:
                 self.caches[r] = CacheView(group=src.group, pages=src.pages, state=src.state, writable=False)
         # hooks of the parts: who plans its own work per step, and what may be captured into a graph
         parts = [p for b in self.model.blocks for p in (getattr(b, "mixer", None), getattr(b, "feed_forward", None))
-                 if p is not None]
+                 if p is not None] + [self.model.embedding, self.model.head]
         self.planners: List[type] = []
         for part in parts:
             owner = plan_owner(type(part))

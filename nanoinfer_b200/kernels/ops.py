@@ -34,7 +34,7 @@ _SIGNATURES = {
         "ni_rope_kv_write": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     },
     "attention_generic": {
-        "ni_attention_generic": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P],
+        "ni_attention_generic": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P],
     },
     "gemm_f32": {
         "ni_gemm_f32": [_P, _P, _P, _I, _I, _I, _P],
@@ -280,9 +280,12 @@ def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
                       out: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
                       block_table: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int,
                       page_size: int, window: Optional[int], scale: float,
-                      token_list: Optional[torch.Tensor] = None) -> None:
+                      token_list: Optional[torch.Tensor] = None, head_slopes: Optional[torch.Tensor] = None) -> None:
     """The plain attention kernel (any dtype, any head size up to 256).  ``token_list``
-    int32 [n] restricts it to those tokens of the step."""
+    int32 [n] restricts it to those tokens of the step.  ``head_slopes`` float32 [Hq] adds
+    slope[h] * (key position - query position) to the scaled scores of head h."""
+    if head_slopes is not None and head_slopes.numel() != n_q_heads:
+        raise KernelError("attention: one slope per query head")
     n = q.shape[0]
     if q.shape != (n, n_q_heads * head_dim) or out.shape != q.shape:
         raise KernelError("attention: q and out must be [T, Hq * head_dim]")
@@ -296,7 +299,8 @@ def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         _dev(positions, "positions", torch.int32),
         _dev(seq_of_token, "seq_of_token", torch.int32), _dev(block_table, "block_table", torch.int32),
         block_table.shape[1], n if token_list is None else token_list.numel(), n_q_heads, n_kv_heads, head_dim, page_size,
-        int(window) if window else 0, float(scale), _stream()), "attention_generic")
+        int(window) if window else 0, float(scale),
+        _dev(head_slopes, "head_slopes", torch.float32) if head_slopes is not None else None, _stream()), "attention_generic")
 
 
 def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:

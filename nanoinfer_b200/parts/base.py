@@ -24,7 +24,15 @@ FeedForward     forward(x, ctx) -> y [T, d]
                 is called with ``residual=h`` as well and may add its output into h itself
                 and return None (a fused epilogue).
 
-Two optional hooks, on mixers and feed-forwards alike:
+Embedding       forward(tokens, h) -> None
+                    tokens int32 [T] on the device; fills the FP32 residual stream h [T, d].
+                    ``table`` (optional attribute): its [vocab, d] matrix on the device, which a
+                    tied head is handed as its "weight".
+Head            forward(h, delta, norm, ctx) -> FP32 logits [ctx.n_logit_rows, vocab]
+                    for rows ctx.logit_rows of h (+ delta, still pending); ``norm`` is the model's
+                    final norm.  Its spec says ``tied``; then weight_slots is empty.
+
+Two optional hooks, on mixers, feed-forwards, embeddings and heads alike:
 
 plan_step       a static method plan_step(q_lens, starts) -> StepPlan.  Called once per step and
                 per class that defines it, on the host, with every entry's number of tokens and

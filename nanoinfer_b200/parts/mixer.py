@@ -143,9 +143,12 @@ class PagedAttention(Part):
         rt = self.rt
         common = (self.n_heads, self.n_kv, self.head_dim, rt.page_size, self.window, self.scale)
         n = q.shape[0]
-        if rt.dtype != torch.bfloat16:
+        slopes = getattr(self.position, "head_slopes", None)
+        if rt.dtype != torch.bfloat16 or slopes is not None:
+            # float32, or a position encoding that acts on the scores (a bias slope[h] * (k_pos - q_pos)):
+            # the plain kernel takes both; the tensor-core kernels know rotations only
             ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
-                                  table, *common)
+                                  table, *common, head_slopes=slopes)
             return
         decode_ok = self.head_dim in ops.DECODE_HEAD_DIMS and self.n_heads // self.n_kv <= 16
         prefill_ok = self.head_dim % 16 == 0 and self.head_dim <= ops.PREFILL_MAX_HEAD_DIM

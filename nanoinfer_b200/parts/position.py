@@ -40,7 +40,13 @@ def rope_inverse_frequencies(rotary_dim: int, theta: float, scaling) -> np.ndarr
 
 
 class RotaryEncoding(Part):
-    """Rotary encoding: holds inv_freq [rotary_dim/2] FP32 on the device and the pairing."""
+    """Rotary encoding: holds inv_freq [rotary_dim/2] FP32 on the device and the pairing.
+
+    What a mixer reads from ANY position encoding: ``rotary_dim`` (0: nothing is rotated), ``inv_freq``,
+    ``interleaved``, and ``head_slopes`` - None, or float32 [num_heads] on the device: the encoding adds
+    slope[h] * (key position - query position) to the scaled attention scores of head h (then the mixer
+    uses the plain attention kernel, which takes such a bias, in either precision)."""
+    head_slopes = None
 
     def __init__(self, spec, hidden_size, weights, rt) -> None:
         super().__init__(spec, hidden_size, weights, rt)
@@ -58,6 +64,7 @@ class RotaryEncoding(Part):
 
 class NoEncoding(Part):
     """No position encoding: queries and keys are used as projected."""
+    head_slopes = None
 
     def __init__(self, spec, hidden_size, weights, rt) -> None:
         super().__init__(spec, hidden_size, weights, rt)

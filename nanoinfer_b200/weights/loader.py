@@ -53,7 +53,7 @@ def check_tensors(model_dir: str, config: ModelConfig, found: Dict[str, tuple]) 
     from ..config import registry
     arch = registry.architecture(config.architecture)
     allowed_extra = set()
-    if config.tie_word_embeddings:
+    if config.head_spec().tied:
         # a tied model may still store its output projection; it is not read
         allowed_extra.add(arch.tensor_name(("lm_head",), "weight"))
     unexpected = [n for n in found if n not in plan and n not in allowed_extra

@@ -32,8 +32,8 @@ def tensor_plan(config: ModelConfig) -> List[PlannedTensor]:
             plan.append(PlannedTensor(arch.tensor_name(scope, slot), tuple(ws.shape), ws.init,
                                       scope, slot))
 
-    from ..parts.base import WeightSlot
-    add(("embedding",), {"weight": WeightSlot((config.vocab_size, d))})
+    emb = config.embedding_spec()
+    add(("embedding",), registry.part("embedding", emb.kind).weight_slots(emb, d))
     for i, layer in enumerate(config.layers):
         add(("layer", i, "mixer_norm"),
             registry.part("norm", layer.mixer_norm.kind).weight_slots(layer.mixer_norm, d))
@@ -45,8 +45,8 @@ def tensor_plan(config: ModelConfig) -> List[PlannedTensor]:
             registry.part("feed_forward", layer.feed_forward.kind).weight_slots(layer.feed_forward, d))
     add(("final_norm",),
         registry.part("norm", config.final_norm.kind).weight_slots(config.final_norm, d))
-    if not config.tie_word_embeddings:
-        add(("lm_head",), {"weight": WeightSlot((config.vocab_size, d))})
+    head = config.head_spec()
+    add(("lm_head",), registry.part("head", head.kind).weight_slots(head, d))
     names = [p.name for p in plan]
     if len(set(names)) != len(names):
         dup = sorted({n for n in names if names.count(n) > 1})

@@ -139,6 +139,46 @@ def test_attention_generic(dtype, n_q, n_kv, hd, page, window):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_q,n_kv,hd,page,window", [(6, 2, 48, 4, None), (5, 1, 80, 16, 33)])
+def test_attention_generic_with_a_slope_per_head(dtype, n_q, n_kv, hd, page, window):
+    """score = q.k * scale + slope[h] * (key position - query position), over pages, for a span of
+    queries in the middle of a sequence; the plain side is written out here."""
+    from nanoinfer_b200.kernels import ops
+    lens = [150, 9]
+    table, k_pages, v_pages, ks, vs = _paged_setup(lens, n_kv, hd, page, dtype, seed=hd + 1)
+    spans = [(90, 150), (8, 9)]
+    g = torch.Generator().manual_seed(6)
+    qs = [torch.randn(t, n_q, hd, generator=g).to(dtype) for t in lens]
+    slopes = torch.rand(n_q, generator=g) * 0.5
+    q = torch.cat([qs[s][a:b] for s, (a, b) in enumerate(spans)]).reshape(-1, n_q * hd)
+    positions = torch.cat([torch.arange(a, b) for a, b in spans]).int()
+    seq_of = torch.cat([torch.full((b - a,), s) for s, (a, b) in enumerate(spans)]).int()
+    out = torch.empty_like(q).to(DEV)
+    scale = 1.0 / math.sqrt(hd)
+    ops.attention_generic(q.to(DEV), k_pages.to(DEV), v_pages.to(DEV), out, positions.to(DEV),
+                          seq_of.to(DEV), table.to(DEV), n_q, n_kv, hd, page, window, scale,
+                          head_slopes=slopes.to(DEV))
+    want = []
+    for s, (a, b) in enumerate(spans):
+        t = lens[s]
+        i = torch.arange(t)
+        mask = i[None, :] <= i[:, None]
+        if window is not None:
+            mask &= i[None, :] > i[:, None] - window
+        o = torch.empty(t, n_q, hd)
+        for h in range(n_q):
+            kh, vh = ks[s][:, h // (n_q // n_kv)].float(), vs[s][:, h // (n_q // n_kv)].float()
+            sc = (qs[s][:, h].float() @ kh.t()) * scale + slopes[h] * (i[None, :] - i[:, None]).float()
+            o[:, h] = torch.softmax(sc.masked_fill(~mask, float("-inf")), dim=-1) @ vh
+        want.append(o[a:b])
+    torch.testing.assert_close(out.cpu().float(), torch.cat(want).reshape(-1, n_q * hd), **_tol(dtype))
+    with pytest.raises(ops.KernelError, match="one slope per query head"):
+        ops.attention_generic(q.to(DEV), k_pages.to(DEV), v_pages.to(DEV), out, positions.to(DEV),
+                              seq_of.to(DEV), table.to(DEV), n_q, n_kv, hd, page, window, scale,
+                              head_slopes=slopes[:-1].to(DEV))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("pairing", ["half", "interleaved"])
 @pytest.mark.parametrize("n_q,n_kv,hd,rot,page", [(4, 2, 16, 16, 16), (3, 1, 32, 32, 8), (6, 3, 48, 32, 4),
                                                   (5, 5, 80, 80, 16)])

@@ -160,6 +160,81 @@ def test_attention_part_and_block(dtype, window, pairing, hd):
     _close(h.cpu(), want_h, dtype)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window,hd,n_q,n_kv", [(None, 32, 4, 2), (7, 48, 3, 1)])
+def test_a_position_encoding_that_biases_the_scores(dtype, window, hd, n_q, n_kv):
+    """Another kind of position encoding, defined and registered here: nothing is rotated; head h
+    adds -BIAS_BASE^-(h+1) * (query position - key position) to its scaled scores.  The mixer
+    reads the slopes from its encoding and hands them to the attention kernel; a portion and
+    single tokens give what the whole sequence gives.  The slope of head 0 is made large, so
+    that each of its rows is the value of its own position: a bias that was dropped, or had the
+    wrong sign, would average the values instead."""
+    from nanoinfer_b200.cache import CacheManager, GroupSpec
+    from nanoinfer_b200.config import MixerSpec, PositionSpec, part, register_part
+    from nanoinfer_b200.engine.step import CacheView, StepContext, upload_plans
+    from nanoinfer_b200.parts.position import NoEncoding
+    BIAS_BASE, STEEP = 2.0, 40.0
+
+    class LinearScoreBias(NoEncoding):
+        def __init__(self, spec, hidden_size, weights, rt):
+            super().__init__(spec, hidden_size, weights, rt)
+            slopes = [STEEP] + [BIAS_BASE ** -(h + 1) for h in range(1, n_q)]
+            self.head_slopes = torch.tensor(slopes, dtype=torch.float32, device=rt.device)
+
+    register_part("position", "toy_linear_score_bias", LinearScoreBias, replace=True)
+    rt = _runtime(dtype, page=8)
+    d, T, cut = 72, 41, 26
+    g = torch.Generator().manual_seed(hd)
+    spec = MixerSpec("attention", n_q, n_kv, hd, window, 1.0 / math.sqrt(hd),
+                     PositionSpec("toy_linear_score_bias", 10000.0, 0, "half", None))
+    names = {"q": (n_q * hd, d), "k": (n_kv * hd, d), "v": (n_kv * hd, d), "o": (d, n_q * hd)}
+    w = {k: (torch.randn(s, generator=g) * 0.1).to(torch.bfloat16) for k, s in names.items()}
+    mixer = part("mixer", "attention")(spec, d, w, rt)
+    x = torch.randn(T, d, generator=g).to(rt.dtype)
+
+    # plain: the same projections, scores with the bias, whole sequence
+    with plain.precision(torch.float32):
+        xf = x.float()
+        q = (xf @ w["q"].float().t()).view(T, n_q, hd)
+        k = (xf @ w["k"].float().t()).view(T, n_kv, hd)
+        v = (xf @ w["v"].float().t()).view(T, n_kv, hd)
+        i = torch.arange(T)
+        mask = i[None, :] <= i[:, None]
+        if window is not None:
+            mask &= i[None, :] > i[:, None] - window
+        att = torch.empty(T, n_q, hd)
+        slopes = mixer.position.head_slopes.cpu()
+        for h in range(n_q):
+            kh, vh = k[:, h // (n_q // n_kv)], v[:, h // (n_q // n_kv)]
+            sc = (q[:, h] @ kh.t()) * spec.softmax_scale + slopes[h] * (i[None, :] - i[:, None]).float()
+            att[:, h] = torch.softmax(sc.masked_fill(~mask, float("-inf")), dim=-1) @ vh
+        want = att.reshape(T, n_q * hd) @ w["o"].float().t()
+        assert torch.allclose(att[:, 0], v[:, 0], atol=1e-6)          # the steep head sees itself alone
+
+    cm = CacheManager([GroupSpec(n_kv, hd, window)], [8], 8, 2, 64)
+    slot = cm.admit("r")
+    shape = (8, n_kv, 8, hd)
+    cache = CacheView(group=0, pages={"k": torch.zeros(shape, dtype=rt.dtype, device=DEV),
+                                      "v": torch.zeros(shape, dtype=rt.dtype, device=DEV)})
+
+    def ctx_for(start, n):
+        cm.append("r", n)
+        i32 = dict(dtype=torch.int32, device=DEV)
+        return StepContext(
+            n_tokens=n, n_seqs=1, n_logit_rows=0, tokens=torch.zeros(n, **i32),
+            positions=torch.arange(start, start + n, **i32), seq_of_token=torch.zeros(n, **i32),
+            cu_q=torch.tensor([0, n], **i32), kv_len=torch.tensor([start + n], **i32),
+            slots=torch.tensor([slot], **i32), logit_rows=torch.zeros(0, **i32),
+            block_tables=[torch.from_numpy(cm.table_rows(0, [slot], cm.table_width)).to(DEV)],
+            host_q_lens=[n], host_kv_lens=[start + n], host_slots=[slot], max_q_len=n, max_kv_len=start + n,
+            decode_only=(n == 1), plans=upload_plans([mixer], [n], [start], DEV))
+
+    outs = [mixer.forward(x[:cut].to(DEV), ctx_for(0, cut), cache)]
+    for t in range(cut, T):
+        outs.append(mixer.forward(x[t:t + 1].to(DEV), ctx_for(t, 1), cache))
+    _close(torch.cat(outs).cpu().float(), want, dtype)
+
+
 # ---------------------------------------------------------------------------------------------
 # toy parts, defined in the test
 # ---------------------------------------------------------------------------------------------
@@ -367,9 +442,11 @@ LATENT = 12
 
 def _register_more_toys():
     import numpy as np
-    from nanoinfer_b200.config import (FeedForwardSpec, LayerRun, LayerSpec, MixerSpec, ModelConfig, NormSpec,
-                                       PositionSpec, register_architecture, register_part)
+    from nanoinfer_b200.config import (EmbeddingSpec, FeedForwardSpec, HeadSpec, LayerRun, LayerSpec, MixerSpec,
+                                       ModelConfig, NormSpec, PositionSpec, register_architecture, register_part)
     from nanoinfer_b200.parts.base import PagedNeed, Part, StateNeed, StepPlan, WeightSlot
+    from nanoinfer_b200.parts.embedding import TableEmbedding
+    from nanoinfer_b200.parts.head import LinearHead
 
     class ShiftMixer(Part):
         """y_t = W1 x_t + W2 x_{t-1} (x_{-1} = 0).  The token before a portion's first token comes
@@ -476,6 +553,31 @@ def _register_more_toys():
                 at += n
             return y.to(self.rt.dtype)
 
+    class ScaledTable(TableEmbedding):
+        """Rows of the table times EMBED_SCALE (a constant of its spec)."""
+
+        def __init__(self, spec, hidden_size, weights, rt):
+            super().__init__(spec, hidden_size, weights, rt)
+            self.factor = float(spec.extra_dict()["scale"])
+
+        def forward(self, tokens, h):
+            super().forward(tokens, h)
+            h.mul_(self.factor)
+
+    class SoftCapHead(LinearHead):
+        """cap * tanh(logits / cap) over the linear head's logits; here with a matrix of its own
+        even when the model's configuration ties the head (its spec is not tied)."""
+
+        def __init__(self, spec, hidden_size, weights, rt):
+            super().__init__(spec, hidden_size, weights, rt)
+            self.cap = float(spec.extra_dict()["cap"])
+
+        def forward(self, h, delta, norm, ctx):
+            logits = super().forward(h, delta, norm, ctx)
+            return torch.tanh(logits / self.cap) * self.cap
+
+    register_part("embedding", "toy_scaled_table", ScaledTable, replace=True)
+    register_part("head", "toy_soft_cap", SoftCapHead, replace=True)
     register_part("mixer", "toy_shift", ShiftMixer, replace=True)
     register_part("mixer", "toy_device_state", DeviceRunningState, replace=True)
     register_part("mixer", "toy_latent_mean", LatentMeanMixer, replace=True)
@@ -491,8 +593,13 @@ def _register_more_toys():
         kinds = {"shift": MixerSpec("toy_shift"), "state": MixerSpec("toy_device_state"),
                  "latent": MixerSpec("toy_latent_mean"), "attention": att(None), "window": att(raw["window"])}
         layers = tuple(LayerSpec(kinds[k], ffn, norm, norm) for k in raw["mixers"])
+        ends = {}
+        if raw.get("embed_scale") is not None:
+            ends["embedding"] = EmbeddingSpec("toy_scaled_table", extra=(("scale", raw["embed_scale"]),))
+        if raw.get("soft_cap") is not None:
+            ends["head"] = HeadSpec("toy_soft_cap", extra=(("cap", raw["soft_cap"]),))
         return ModelConfig("ToyMixersForTest", d, raw["vocab"], raw["max_pos"], layers,
-                           tuple(LayerRun(i) for i in range(len(layers))), norm, tie_word_embeddings=False)
+                           tuple(LayerRun(i) for i in range(len(layers))), norm, tie_word_embeddings=False, **ends)
 
     def name(scope, slot):
         return "toy2." + ".".join(str(s) for s in scope) + "." + slot
@@ -511,7 +618,7 @@ def _toy2_plain(raw, w, tokens):
     W = {k: v.float() for k, v in w.items()}
     pos = torch.arange(T)
     inv_freq = plain.rope_inv_freq(hd, 10000.0, None)
-    h = plain.embedding(W["toy2.embedding.weight"], torch.tensor(tokens))
+    h = plain.embedding(W["toy2.embedding.weight"], torch.tensor(tokens)) * (raw.get("embed_scale") or 1.0)
     for i, kind in enumerate(raw["mixers"]):
         p = f"toy2.layer.{i}"
         x = plain.rms_norm(h, W[f"{p}.mixer_norm.weight"], raw["eps"])
@@ -537,7 +644,9 @@ def _toy2_plain(raw, w, tokens):
         x = plain.rms_norm(h, W[f"{p}.ffn_norm.weight"], raw["eps"])
         f = f"{p}.feed_forward"
         h = h + plain.swiglu_ffn(x, W[f"{f}.gate"], W[f"{f}.up"], W[f"{f}.down"])
-    return plain.rms_norm(h, W["toy2.final_norm.weight"], raw["eps"]) @ W["toy2.lm_head.weight"].t()
+    logits = plain.rms_norm(h, W["toy2.final_norm.weight"], raw["eps"]) @ W["toy2.lm_head.weight"].t()
+    cap = raw.get("soft_cap")
+    return logits if cap is None else torch.tanh(logits / cap) * cap
 
 
 def _fixed_portions(requests, size, tail):
@@ -592,6 +701,32 @@ def test_parts_with_plans_state_and_other_caches(tmp_path, mixers, decode_graphs
             assert bool(runner._portion_graphs) == (portion_graphs and dtype == "bfloat16")
         runner.cache.check_consistency()
         assert all(p.num_free == p.num_pages for p in runner.cache.pools)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_another_embedding_and_another_head(tmp_path, dtype):
+    """The two ends of the model are registered parts as well: an embedding that scales its rows
+    and a head that caps its logits, defined here, in a model whose steps are captured too."""
+    from nanoinfer_b200.config import load_config
+    from nanoinfer_b200.engine import ModelRunner
+    from nanoinfer_b200.weights import load_weights, write_random_model
+    _register_more_toys()
+    raw = dict(_toy2_raw(("attention", "window")), embed_scale=3.0, soft_cap=2.0)
+    d = str(tmp_path / "toy2e")
+    write_random_model(d, raw, seed=8, std=0.08)
+    cfg = load_config(d)
+    weights = load_weights(d, cfg)
+    reqs = {f"e{i}": random_tokens(raw["vocab"], n, 500 + i) for i, n in enumerate([40, 75, 21])}
+    want = {rid: _toy2_plain(raw, weights, toks) for rid, toks in reqs.items()}
+    assert max(w.abs().max().item() for w in want.values()) > 0.8 * raw["soft_cap"], "the cap must bite"
+    for cut in (ru.tail_by_token, ru.mixed):
+        steps = cut(reqs)
+        runner = ModelRunner(cfg, weights, dtype=dtype, page_size=8, num_pages=ru.max_live_tokens(steps, 64) // 8,
+                             max_requests=4)
+        assert type(runner.model.embedding).__name__ == "ScaledTable" and type(runner.model.head).__name__ == "SoftCapHead"
+        assert runner.decode_graphs_ok
+        ru.compare(ru.run_trace(runner, steps), want, dtype, label=f"toy ends/{cut.__name__}/{dtype}")
+        assert runner._graphs
 
 
 def test_a_windowed_group_gets_a_pool_of_its_own_size(tmp_path):

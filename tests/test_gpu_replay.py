@@ -126,10 +126,14 @@ def test_wide_decode_batches_match_plain(model_dirs, monkeypatch, key, n_live, d
         assert max(plain_rows.seen) >= n_live
 
 
-def test_wide_outputs_take_the_swapped_operand_product(model_dirs, monkeypatch):
-    """A vocabulary and a feed-forward wide enough that, at 9 to 32 rows, the output projection and
-    the gate/up projection go to the swapped-operand tcgen05 kernel (one thin layer, so the plain
-    implementation stays quick)."""
+@pytest.mark.parametrize("every_projection", [False, True])
+def test_wide_outputs_take_the_swapped_operand_product(model_dirs, monkeypatch, every_projection):
+    """A vocabulary wide enough that, at 9 to 128 rows, the output projection goes to the
+    swapped-operand tcgen05 kernel (one thin layer, so the plain implementation stays quick).  With
+    every projection routed there (an option; the library product is the default for the layers'
+    own projections), each of its fused epilogues - rotation and cache write, addition into the
+    residual stream, the gated activation - serves the same logits."""
+    from nanoinfer_b200.engine.runtime import Runtime
     from nanoinfer_b200.kernels import ops
     raw, w = load_plain(model_dirs["f"])
     n_live, tail = 12, 6
@@ -137,12 +141,16 @@ def test_wide_outputs_take_the_swapped_operand_product(model_dirs, monkeypatch):
     steps = ru.wide(reqs, n_live, tail=tail)
     swapped = _Spy(monkeypatch, "gemm_swap_tc", lambda x, w_, out, mode, *a, **k: (x.shape[0], mode))
     runner = _runner(model_dirs["f"], "bfloat16", 16, steps, max_requests=n_live + 2)
+    if every_projection:
+        runner.rt.mid_batch_mask = (Runtime.MID_QKV | Runtime.MID_OUT | Runtime.MID_GATE_UP | Runtime.MID_DOWN
+                                    | Runtime.MID_HEAD)
     got = ru.run_trace(runner, steps)
     ru.compare(got, ru.plain_logits(raw, w, reqs), "bfloat16", label="wide/f")
     ops.check_device_errors()
     modes = {m for _, m in swapped.seen}
     assert ops.STORE_F32 in modes, "the output projection over the vocabulary did not take the swapped-operand kernel"
-    assert ops.SWIGLU_BF16 in modes, "the gate/up projection did not take the swapped-operand kernel"
+    layer_modes = {ops.ROPE_KV, ops.ADD_F32, ops.SWIGLU_BF16}
+    assert (layer_modes <= modes) if every_projection else not (layer_modes & modes)
     assert max(r for r, _ in swapped.seen) >= n_live
 
 
