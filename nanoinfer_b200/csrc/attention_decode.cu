@@ -73,6 +73,20 @@ template <int HD> __device__ __forceinline__ int dec_sw(int row, int chunk) {
     return row * HD + ((chunk ^ (row & MASK)) << 3);
 }
 
+// One warp's share of a request to bring [p, p + bytes) into L2 (p 16-byte aligned, bytes a multiple of 16).
+__device__ __forceinline__ void dec_warm(const unsigned char* p, unsigned long long bytes) {
+    if (!bytes) return;
+    const unsigned int n_blocks = gridDim.x * gridDim.y * gridDim.z;
+    const unsigned int bid = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    constexpr unsigned int PIECE = 8192;
+    const unsigned int n_pieces = (unsigned int)((bytes + PIECE - 1) / PIECE);
+    for (unsigned int i = bid + (threadIdx.x & 31) * n_blocks; i < n_pieces; i += 32 * n_blocks) {
+        const unsigned long long off = (unsigned long long)i * PIECE;
+        const unsigned int sz = bytes - off < PIECE ? (unsigned int)(bytes - off) : PIECE;
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(p + off), "r"(sz) : "memory");
+    }
+}
+
 // HD: head size (64 or 128).  SEG: keys a block holds in shared memory at a time (64 per warp
 // pass).  Scratch per (token, q head, split): HD + 2 floats.
 template <int HD, int SEG>
@@ -83,7 +97,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
                         int bt_stride, int n_q_heads, int n_kv_heads, int page_size, int window,
                         float scale_log2e, int n_splits, float* __restrict__ scratch,
-                        int* __restrict__ tickets) {
+                        int* __restrict__ tickets, const unsigned char* __restrict__ warm_a, unsigned long long warm_a_bytes,
+                        const unsigned char* __restrict__ warm_b, unsigned long long warm_b_bytes) {
+    // Weights that the kernels after this one will read (the caller's hint, up to two regions): asked
+    // into L2 now, in pieces dealt over the blocks, while this kernel - which waits on latencies
+    // more than on bandwidth - leaves the memory system room.  Nothing here depends on the kernel before.
+    if (threadIdx.x >= (DEC_WARPS - 1) * 32) dec_warm(warm_a, warm_a_bytes);
     constexpr int CH = HD / 8;       // 16-byte chunks per row
     constexpr int KS = HD / 16;      // k-steps over the head size
     constexpr int NT_O = HD / 8;     // output column tiles
@@ -281,6 +300,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         sm_o[warp][g][d] = o[j][0]; sm_o[warp][g][d + 1] = o[j][1];
         sm_o[warp][g + 8][d] = o[j][2]; sm_o[warp][g + 8][d + 1] = o[j][3];
     }
+    // the block's own stream has ended: the second region is asked for under the merges (here, where
+    // the accumulators are no longer live, it costs the kernel no registers)
+    if (threadIdx.x >= (DEC_WARPS - 1) * 32) dec_warm(warm_b, warm_b_bytes);
     __syncthreads();
     const size_t rec = HD + 2;
     for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
@@ -356,7 +378,9 @@ template <int HD, int SEG>
 static int launch_decode(const void* q, const void* k_pages, const void* v_pages, void* out, const int* token_list,
                          int n_items, const int* positions, const int* seq_of_token, const int* block_table,
                          int bt_stride, int n_q_heads, int n_kv_heads, int page_size, int window,
-                         float scale_log2e, int n_splits, float* scratch, int* tickets, cudaStream_t stream) {
+                         float scale_log2e, int n_splits, float* scratch, int* tickets, const void* warm_a,
+                         unsigned long long warm_a_bytes, const void* warm_b, unsigned long long warm_b_bytes,
+                         cudaStream_t stream) {
     const size_t smem = (size_t)(16 + 4 * SEG) * HD * sizeof(__nv_bfloat16);
     static bool configured = false;
     if (!configured) {
@@ -379,7 +403,8 @@ static int launch_decode(const void* q, const void* k_pages, const void* v_pages
                                        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
                                        (__nv_bfloat16*)out, token_list, positions, seq_of_token, block_table,
                                        bt_stride, n_q_heads, n_kv_heads, page_size, window, scale_log2e, n_splits,
-                                       scratch, tickets);
+                                       scratch, tickets, (const unsigned char*)warm_a, warm_a_bytes,
+                                       (const unsigned char*)warm_b, warm_b_bytes);
     return e == cudaSuccess ? NI_OK : (int)e;
 }
 
@@ -392,8 +417,11 @@ NI_EXPORT int ni_attention_decode(const void* q, const void* k_pages, const void
                                   const int* seq_of_token, const int* block_table, int bt_stride,
                                   int n_q_heads, int n_kv_heads, int head_dim, int page_size, int window,
                                   float scale, int n_splits, float* scratch, int* tickets,
-                                  cudaStream_t stream) {
+                                  const void* warm_a, long long warm_a_bytes, const void* warm_b,
+                                  long long warm_b_bytes, cudaStream_t stream) {
     if (n_items <= 0) return NI_OK;
+    if (warm_a_bytes < 0 || (warm_a_bytes & 15) || (warm_a_bytes && (!warm_a || ((uintptr_t)warm_a & 15)))) return NI_ERR_BAD_ARGUMENT;
+    if (warm_b_bytes < 0 || (warm_b_bytes & 15) || (warm_b_bytes && (!warm_b || ((uintptr_t)warm_b & 15)))) return NI_ERR_BAD_ARGUMENT;
     if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads || page_size <= 0 || n_splits <= 0 ||
         n_splits > 65535 || n_kv_heads > 65535)
         return NI_ERR_BAD_ARGUMENT;
@@ -407,14 +435,17 @@ NI_EXPORT int ni_attention_decode(const void* q, const void* k_pages, const void
             if ((long long)n_items * n_kv_heads * n_splits <= 3LL * ni_sm_count())
                 return launch_decode<64, 128>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
                                               block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
-                                              scale_log2e, n_splits, scratch, tickets, stream);
+                                              scale_log2e, n_splits, scratch, tickets, warm_a, (unsigned long long)warm_a_bytes, warm_b,
+                                              (unsigned long long)warm_b_bytes, stream);
             return launch_decode<64, 64>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
                                           block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
-                                          scale_log2e, n_splits, scratch, tickets, stream);
+                                          scale_log2e, n_splits, scratch, tickets, warm_a, (unsigned long long)warm_a_bytes, warm_b,
+                                              (unsigned long long)warm_b_bytes, stream);
         case 128:
             return launch_decode<128, 64>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
                                            block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
-                                           scale_log2e, n_splits, scratch, tickets, stream);
+                                           scale_log2e, n_splits, scratch, tickets, warm_a, (unsigned long long)warm_a_bytes, warm_b,
+                                              (unsigned long long)warm_b_bytes, stream);
         default: return NI_ERR_UNSUPPORTED_SIZE;
     }
 }
@@ -462,5 +493,5 @@ NI_EXPORT int ni_attention_decode_noalloc(const void* q, const void* k_pages, co
     if (e != cudaSuccess) return (int)e;
     return ni_attention_decode(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
                                block_table, bt_stride, n_q_heads, n_kv_heads, head_dim, page_size, window,
-                               scale, n_splits, noalloc_partials_addr[dev], noalloc_tickets_addr[dev], stream);
+                               scale, n_splits, noalloc_partials_addr[dev], noalloc_tickets_addr[dev], nullptr, 0, nullptr, 0, stream);
 }

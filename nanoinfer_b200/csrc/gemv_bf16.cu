@@ -52,6 +52,10 @@ struct GemvParams {
     __nv_bfloat16* k_pages;
     __nv_bfloat16* v_pages;
     int bt_stride, n_q_heads, n_kv_heads, head_dim, rotary_dim, page_size, write_cache;
+    // optional: bytes that kernels after this one read (weights), asked into L2 once this block has
+    // issued its own last loads - they fill the gap between this kernel's tail and the next one's start
+    const unsigned char* warm;
+    unsigned long long warm_bytes;
 };
 
 __device__ __forceinline__ void gv_mma(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -73,6 +77,18 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
+
+// This block's share of the request to bring [p.warm, +p.warm_bytes) into L2, issued by one warp
+// (addresses and sizes are multiples of 16 bytes).
+__device__ __forceinline__ void gv_warm(const GemvParams& p) {
+    constexpr unsigned int PIECE = 8192;
+    const unsigned int n_pieces = (unsigned int)((p.warm_bytes + PIECE - 1) / PIECE);
+    for (unsigned int i = blockIdx.x + (threadIdx.x & 31) * gridDim.x; i < n_pieces; i += 32 * gridDim.x) {
+        const unsigned long long off = (unsigned long long)i * PIECE;
+        const unsigned int sz = p.warm_bytes - off < PIECE ? (unsigned int)(p.warm_bytes - off) : PIECE;
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(p.warm + off), "r"(sz) : "memory");
+    }
+}
 
 // Builds the B fragment (8 activations of one batch row at k .. k+7) and, with the norm fused,
 // adds their squares to ssq.
@@ -97,7 +113,10 @@ __device__ __forceinline__ uint4 load_x8(const void* xrow, const float* gain8, i
 // registers and the block walks `tiles_per_block` consecutive row tiles with them, so that
 // activations are read and normalised once per block, not once per 16 weight rows (U = 4 for K
 // <= 2048 with two blocks per SM; U = 6 and 8 for K up to 3072 and 4096 with one).
-template <int RN, int NT, bool NORM, bool KEEP, int U>
+// WARM: the kernel ends with its share of the request for p.warm (a variant of its own: the mere
+// presence of that code after the loop made the gate/up kernel, which runs at its register limit,
+// 6 % slower, whether or not it ran).
+template <int RN, int NT, bool NORM, bool KEEP, int U, bool WARM>
 __global__ void __launch_bounds__(GV_WARPS * 32, (NT == 1 && U <= 4) ? 2 : 1) gemv_bf16_kernel(const GemvParams p, int tiles_per_block) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -219,7 +238,6 @@ __global__ void __launch_bounds__(GV_WARPS * 32, (NT == 1 && U <= 4) ? 2 : 1) ge
             }
         }
         if (!waited) { pdl_wait(); waited = true; }   // a warp without work must not run ahead either
-
         // partial sums of the 8 warps -> shared memory -> summed in warp order
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
@@ -305,10 +323,11 @@ __global__ void __launch_bounds__(GV_WARPS * 32, (NT == 1 && U <= 4) ? 2 : 1) ge
         }
     }
     if (!waited) pdl_wait();
+    if (WARM && warp == GV_WARPS - 1) gv_warm(p);
 }
 
-template <int RN, int NT, bool NORM, bool KEEP, int U>
-static int launch_gemv(const GemvParams& p, int tiles_per_block, cudaStream_t stream) {
+template <int RN, int NT, bool NORM, bool KEEP, int U, bool WARM>
+static int launch_gemv_w(const GemvParams& p, int tiles_per_block, cudaStream_t stream) {
     const int tiles = (p.N + RN - 1) / RN;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((tiles + tiles_per_block - 1) / tiles_per_block);
@@ -320,8 +339,15 @@ static int launch_gemv(const GemvParams& p, int tiles_per_block, cudaStream_t st
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_bf16_kernel<RN, NT, NORM, KEEP, U>, p, tiles_per_block);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_bf16_kernel<RN, NT, NORM, KEEP, U, WARM>, p, tiles_per_block);
     return e == cudaSuccess ? NI_OK : (int)e;
+}
+
+template <int RN, int NT, bool NORM, bool KEEP, int U>
+static int launch_gemv(const GemvParams& p, int tiles_per_block, cudaStream_t stream) {
+    // the variant that warms L2 exists for batches of up to 8 rows (single-token steps use no other)
+    if (NT == 1 && p.warm_bytes) return launch_gemv_w<RN, NT, NORM, KEEP, U, NT == 1>(p, tiles_per_block, stream);
+    return launch_gemv_w<RN, NT, NORM, KEEP, U, false>(p, tiles_per_block, stream);
 }
 
 static int dispatch_gemv(const GemvParams& p, bool norm, cudaStream_t stream) {
@@ -375,19 +401,26 @@ static int dispatch_gemv(const GemvParams& p, bool norm, cudaStream_t stream) {
 }
 
 // x bf16 [M, K].  mode: 0 store bf16 [M, N], 1 store FP32, 2 add into FP32, 3 SwiGLU -> bf16 [M, N / 2].
+static bool gv_warm_ok(const void* warm, long long bytes) {
+    return bytes >= 0 && !(bytes & 15) && (bytes == 0 || (warm && !((uintptr_t)warm & 15)));
+}
+
 NI_EXPORT int ni_gemv_bf16(const void* x, const void* w, void* out, int M, int N, int K, int mode,
-                           cudaStream_t stream) {
-    if (mode == GV_ROPE_KV) return NI_ERR_BAD_ARGUMENT;
+                           const void* warm, long long warm_bytes, cudaStream_t stream) {
+    if (mode == GV_ROPE_KV || !gv_warm_ok(warm, warm_bytes)) return NI_ERR_BAD_ARGUMENT;
     GemvParams p = {};
+    p.warm = (const unsigned char*)warm; p.warm_bytes = (unsigned long long)warm_bytes;
     p.x = x; p.w = (const __nv_bfloat16*)w; p.out = out; p.M = M; p.N = N; p.K = K; p.mode = mode;
     return dispatch_gemv(p, false, stream);
 }
 
 // h FP32 [*, K] with RMSNorm fused: y = (norm(h[rows]) * gain) . w^T.  rows may be null (rows 0..M-1).
 NI_EXPORT int ni_gemv_norm_bf16(const float* h, const float* gain, float eps, const int* rows, const void* w,
-                                void* out, int M, int N, int K, int mode, cudaStream_t stream) {
-    if (mode == GV_ROPE_KV) return NI_ERR_BAD_ARGUMENT;
+                                void* out, int M, int N, int K, int mode, const void* warm, long long warm_bytes,
+                                cudaStream_t stream) {
+    if (mode == GV_ROPE_KV || !gv_warm_ok(warm, warm_bytes)) return NI_ERR_BAD_ARGUMENT;
     GemvParams p = {};
+    p.warm = (const unsigned char*)warm; p.warm_bytes = (unsigned long long)warm_bytes;
     p.x = h; p.gain = gain; p.eps = eps; p.rows = rows; p.w = (const __nv_bfloat16*)w; p.out = out;
     p.M = M; p.N = N; p.K = K; p.mode = mode;
     return dispatch_gemv(p, true, stream);
@@ -401,8 +434,10 @@ NI_EXPORT int ni_gemv_qkv_rope(const void* x, const float* gain, float eps, cons
                                void* k_pages, void* v_pages, const int* positions, const int* seq_of_token,
                                const int* block_table, int bt_stride, const float* inv_freq, int M, int K,
                                int n_q_heads, int n_kv_heads, int head_dim, int rotary_dim, int page_size,
-                               int write_cache, cudaStream_t stream) {
+                               int write_cache, const void* warm, long long warm_bytes, cudaStream_t stream) {
+    if (!gv_warm_ok(warm, warm_bytes)) return NI_ERR_BAD_ARGUMENT;
     GemvParams p = {};
+    p.warm = (const unsigned char*)warm; p.warm_bytes = (unsigned long long)warm_bytes;
     p.x = x; p.gain = gain; p.eps = eps; p.w = (const __nv_bfloat16*)w; p.out = q_out;
     p.M = M; p.N = (n_q_heads + 2 * n_kv_heads) * head_dim; p.K = K; p.mode = GV_ROPE_KV;
     p.positions = positions; p.seq_of_token = seq_of_token; p.block_table = block_table; p.bt_stride = bt_stride;

@@ -38,6 +38,10 @@ class DecoderModel:
                 raise ValueError(f"a tied head needs an embedding with a table; '{emb.kind}' has none")
             head_weights["weight"] = table      # the embedding's own device copy
         self.head = registry.part("head", head.kind)(head, d, head_weights, rt)
+        # per scheduled run: the matrices read after it (the next run's, then the head's)
+        order = [tuple(getattr(self.blocks[run.layer], "weights_in_order", tuple)()) for run in config.schedule]
+        order.append(tuple(self.head.weights_in_order()))
+        self._read_after = [order[r + 1] for r in range(len(config.schedule))]
         self._fused = False      # the fused decode step: not looked at yet / None (does not apply) / the object
 
     def cache_needs(self) -> List[Optional[object]]:
@@ -65,5 +69,7 @@ class DecoderModel:
         self.embedding.forward(ctx.tokens, h)
         delta = None
         for r, run in enumerate(cfg.schedule):
+            ctx.read_after = self._read_after[r]
             delta = self.blocks[run.layer].forward(h, delta, ctx, caches[r])
+        ctx.read_after = ()
         return self.head.forward(h, delta, self.final_norm, ctx)

@@ -39,6 +39,9 @@ class Runtime:
         import os
         if os.environ.get("NANOINFER_B200_MID_BATCH"):          # for measurements: which projections take the swapped kernel
             self.mid_batch_mask = int(os.environ["NANOINFER_B200_MID_BATCH"])
+        if os.environ.get("NANOINFER_B200_WARM"):               # for measurements: "<product KiB>,<attention KiB>"
+            a, b, c = os.environ["NANOINFER_B200_WARM"].split(",")
+            self.warm_bytes, self.warm_attention_bytes, self.warm_mask = int(a) << 10, int(b) << 10, int(c)
         self._workspaces = {}
         self._retired = []
         ops.require_cuda()
@@ -56,12 +59,49 @@ class Runtime:
     def empty(self, *shape, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         return torch.empty(shape, device=self.device, dtype=dtype or self.dtype)
 
+    # Asking weights into L2 ahead of their kernel (single-token steps).  A kernel of a few
+    # microseconds leaves the memory system idle while its last blocks merge and write and the next
+    # kernel's blocks start.  The decode attention therefore asks for its output projection when it
+    # starts and, once a block's own stream has ended, for the first warm_attention_bytes of the matrix
+    # after that (a third of that for a lone token, whose attention is over too soon for more); the
+    # output projection goes on from there for warm_bytes.  Measured on the 1B sizes at context 2,048
+    # (ms per step, without / with): batch 1 0.801 / 0.791, 2 0.836 / 0.814, 4 0.854 / 0.829,
+    # 8 0.865 / 0.838.  More does not help (32 MiB: 0.842; 40 MiB: 0.848), nor does the same request at
+    # the end of gate/up (for the down projection: 0.855 - that kernel runs at its register limit and
+    # is 6 % slower with the code in it) or of the down projection (for the next layer: 0.842).
+    warm_bytes: int = 12 << 20
+    warm_attention_bytes: int = 24 << 20
+    warm_mask: int = 1          # which products ask: 1 a mixer's output projection, 2 gate/up, 4 down
+
+    def warm(self, tensor, first: int, nbytes: Optional[int] = None, which: int = 0):
+        """A hint (tensor, first byte, bytes) for a kernel's ``warm`` argument, or None."""
+        nbytes = self.warm_bytes if nbytes is None else nbytes
+        if which and not self.warm_mask & which:
+            return None
+        return (tensor, first, nbytes) if nbytes > 0 and tensor is not None else None
+
+    def warm_after(self, ctx, skip: int = 0, which: int = 0):
+        """The hint for the matrix that is read after the running part (ctx.read_after)."""
+        nxt = ctx.read_after[0] if ctx is not None and ctx.read_after else None
+        return self.warm(nxt, skip, which=which)
+
+    def warm_attention(self, w_out, ctx):
+        """The decode attention's two hints: its own output projection, the head of what follows."""
+        if not ctx.decode_only or (self.warm_bytes <= 0 and self.warm_attention_bytes <= 0):
+            return ()
+        nxt = ctx.read_after[0] if ctx.read_after else None
+        return (self.warm(w_out, 0, w_out.numel() * w_out.element_size()), self.warm(nxt, 0, self.attention_share(ctx)))
+
+    def attention_share(self, ctx) -> int:
+        """How much of the matrix after its output projection the decode attention of this step asks for."""
+        return self.warm_attention_bytes // 3 if ctx.n_tokens == 1 else self.warm_attention_bytes
+
     def linear(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-               residual: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+               residual: Optional[torch.Tensor] = None, warm=None) -> Optional[torch.Tensor]:
         """y[M, N] = x[M, K] . w[N, K]^T.  ``out_dtype`` float32 asks for FP32 results
         (logits); the default is the compute dtype.  With ``residual`` (the FP32 residual
         stream) the kernel MAY add the product into it and return None; otherwise the product
-        is returned and the caller adds it."""
+        is returned and the caller adds it.  ``warm``: a hint that the skinny kernel takes (see warm())."""
         m, n = x.shape[0], w.shape[0]
         out_dtype = out_dtype or self.dtype
         if self.dtype == torch.float32:
@@ -72,7 +112,7 @@ class Runtime:
             out = self.empty(m, n, dtype=out_dtype)
             ops.gemm_swap_tc(x, w, out, ops.STORE_BF16 if out_dtype == torch.bfloat16 else ops.STORE_F32)
             return out
-        return ops.linear_bf16(x, w, out_dtype, residual)
+        return ops.linear_bf16(x, w, out_dtype, residual, warm)
 
     def skinny(self, n_rows: int, k: int) -> bool:
         """True if a product of n_rows activations with inner size k goes to the package's own

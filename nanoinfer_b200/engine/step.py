@@ -77,6 +77,9 @@ class StepContext:
     that is replayed from a graph).  decode_only: every request brings exactly one token.
     plans: what the parts' own plan_step hooks returned for this step, by the class that defines
     the hook; a part reads its own with plan_of(self).
+    read_after: the weight matrices that will be read after the part that is running, in order
+    (set by the model and the arrangement as they go); a part whose kernels leave the memory system
+    room may ask the head of them into L2 (``Runtime.warm``).
     """
     n_tokens: int
     n_seqs: int
@@ -96,6 +99,7 @@ class StepContext:
     max_kv_len: int = 0
     decode_only: bool = False
     plans: Dict[type, DevicePlan] = field(default_factory=dict)
+    read_after: tuple = ()
 
     def plan_of(self, part) -> DevicePlan:
         owner = plan_owner(type(part))

@@ -40,12 +40,12 @@ _SIGNATURES = {
         "ni_gemm_f32": [_P, _P, _P, _I, _I, _I, _P],
     },
     "gemv_bf16": {
-        "ni_gemv_bf16": [_P, _P, _P, _I, _I, _I, _I, _P],
-        "ni_gemv_norm_bf16": [_P, _P, _F, _P, _P, _P, _I, _I, _I, _I, _P],
-        "ni_gemv_qkv_rope": [_P, _P, _F, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+        "ni_gemv_bf16": [_P, _P, _P, _I, _I, _I, _I, _P, _LL, _P],
+        "ni_gemv_norm_bf16": [_P, _P, _F, _P, _P, _P, _I, _I, _I, _I, _P, _LL, _P],
+        "ni_gemv_qkv_rope": [_P, _P, _F, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _LL, _P],
     },
     "attention_decode": {
-        "ni_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P],
+        "ni_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _LL, _P, _LL, _P],
         "ni_attention_decode_fresh_keys": [],
         # the variant whose scratch lies in the library's own image (attention_decode_noalloc.h)
         "ni_attention_decode_noalloc": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
@@ -336,19 +336,34 @@ def _gemv_check(m: int, n: int, k: int, w: torch.Tensor, out: torch.Tensor, mode
             raise KernelError(f"{what}: out must be {want} [M, N]")
 
 
-def gemv_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int) -> None:
+def warm_region(warm) -> tuple:
+    """(address, bytes) of a hint ``(tensor, first byte, bytes)`` - a stretch of a tensor that a
+    kernel asks into L2 on its way - cut to the tensor and to multiples of 16 bytes; (None, 0) for None."""
+    if warm is None:
+        return None, 0
+    t, first, nbytes = warm
+    size = t.numel() * t.element_size()
+    first = min(max(int(first), 0), size) & ~15
+    nbytes = min(int(nbytes), size - first) & ~15
+    if nbytes <= 0 or not t.is_cuda or (t.data_ptr() + first) % 16:
+        return None, 0
+    return t.data_ptr() + first, nbytes
+
+
+def gemv_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, warm=None) -> None:
     """x[M, K] . w[N, K]^T for M <= 16, K % 8 == 0.  mode STORE_BF16 / STORE_F32: out[M, N] =;
     ADD_F32: out[M, N] +=; SWIGLU_BF16: w's rows in blocks of 8 gate + 8 up rows,
-    out[M, N/2] = silu(gate) * up."""
+    out[M, N/2] = silu(gate) * up.  ``warm`` (tensor, first byte, bytes): weights of the kernels
+    after this one, asked into L2 when this kernel's own loads have been issued."""
     m, k = x.shape
     n = w.shape[0]
     _gemv_check(m, n, k, w, out, mode, "gemv_bf16")
     _check(load("gemv_bf16").ni_gemv_bf16(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16),
-                                          _dev(out, "out"), m, n, k, mode, _stream()), "gemv_bf16")
+                                          _dev(out, "out"), m, n, k, mode, *warm_region(warm), _stream()), "gemv_bf16")
 
 
 def gemv_norm_bf16(h: torch.Tensor, gain: torch.Tensor, eps: float, rows: Optional[torch.Tensor],
-                   w: torch.Tensor, out: torch.Tensor, mode: int) -> None:
+                   w: torch.Tensor, out: torch.Tensor, mode: int, warm=None) -> None:
     """The same product with RMSNorm fused in front: x = norm(h[rows]) * gain, h float32
     [*, K] (the residual stream), rows int32 [M] or None for rows 0..M-1."""
     k = h.shape[1]
@@ -360,14 +375,14 @@ def gemv_norm_bf16(h: torch.Tensor, gain: torch.Tensor, eps: float, rows: Option
     _check(load("gemv_bf16").ni_gemv_norm_bf16(
         _dev(h, "h", torch.float32), _dev(gain, "gain", torch.float32), float(eps),
         _dev(rows, "rows", torch.int32) if rows is not None else None, _dev(w, "w", torch.bfloat16),
-        _dev(out, "out"), m, n, k, mode, _stream()), "gemv_norm_bf16")
+        _dev(out, "out"), m, n, k, mode, *warm_region(warm), _stream()), "gemv_norm_bf16")
 
 
 def gemv_qkv_rope(x: torch.Tensor, gain: Optional[torch.Tensor], eps: float, w: torch.Tensor,
                   q_out: torch.Tensor, k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
                   positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
                   inv_freq: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int,
-                  page_size: int) -> None:
+                  page_size: int, warm=None) -> None:
     """Fused QKV projection of at most 16 single tokens: optional RMSNorm in front (x float32
     residual stream and ``gain`` given) or bfloat16 activations (gain None); rotary encoding of
     adjacent pairs and the paged K/V write behind.  q -> q_out bf16 [M, Hq hd]."""
@@ -389,11 +404,11 @@ def gemv_qkv_rope(x: torch.Tensor, gain: Optional[torch.Tensor], eps: float, w: 
         _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
         _dev(block_table, "block_table", torch.int32), block_table.shape[1],
         _dev(inv_freq, "inv_freq", torch.float32), m, k, n_q_heads, n_kv_heads, head_dim, rotary_dim,
-        page_size, 1 if write else 0, _stream()), "gemv_qkv_rope")
+        page_size, 1 if write else 0, *warm_region(warm), _stream()), "gemv_qkv_rope")
 
 
 def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
-                residual: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+                residual: Optional[torch.Tensor] = None, warm=None) -> Optional[torch.Tensor]:
     """y = x . w^T for bfloat16 operands with FP32 accumulation.
 
     Up to SKINNY_ROWS rows (decode): the package's own bandwidth kernel; with ``residual`` (float32
@@ -408,10 +423,10 @@ def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
     m, k = x.shape
     if m <= SKINNY_ROWS and k % 8 == 0:
         if residual is not None:
-            gemv_bf16(x, w, residual, ADD_F32)
+            gemv_bf16(x, w, residual, ADD_F32, warm)
             return None
         out = torch.empty(m, w.shape[0], dtype=out_dtype, device=x.device)
-        gemv_bf16(x, w, out, STORE_BF16 if out_dtype == torch.bfloat16 else STORE_F32)
+        gemv_bf16(x, w, out, STORE_BF16 if out_dtype == torch.bfloat16 else STORE_F32, warm)
         return out
     if out_dtype == torch.bfloat16:
         return torch.matmul(x, w.t())
@@ -620,10 +635,13 @@ PREFILL_TILE_ROWS = 128      # query rows per block of the flash-style kernel
 
 def attention_decode(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token, block_table,
                      n_q_heads, n_kv_heads, head_dim, page_size, window, scale, n_splits, scratch,
-                     tickets) -> None:
+                     tickets, warm=()) -> None:
     """Split-K attention of single query tokens (bfloat16).  ``token_list`` int32 [n_items] or
     None for tokens 0..n_items-1.  scratch: float32, at least n_items * Hq * n_splits *
-    (head_dim + 2); tickets: int32 zeros, at least n_items * Hkv (left zero by the kernel)."""
+    (head_dim + 2); tickets: int32 zeros, at least n_items * Hkv (left zero by the kernel).
+    ``warm``: up to two (tensor, first byte, bytes) (weights that the kernels after it read): the
+    kernel asks the first stretch into L2 when it starts, the second when its own stream has ended."""
+    regions = [v for w_ in (list(warm) + [None, None])[:2] for v in warm_region(w_)]
     if head_dim not in DECODE_HEAD_DIMS or n_q_heads // n_kv_heads > 16:
         raise KernelError(f"attention_decode: head_dim {head_dim} / group {n_q_heads // n_kv_heads} not supported")
     if scratch.numel() < n_items * n_q_heads * n_splits * (head_dim + 2) or tickets.numel() < n_items * n_kv_heads:
@@ -635,8 +653,8 @@ def attention_decode(q, k_pages, v_pages, out, token_list, n_items, positions, s
         _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
         _dev(block_table, "block_table", torch.int32), block_table.shape[1], n_q_heads, n_kv_heads,
         head_dim, page_size, int(window) if window else 0, float(scale), n_splits,
-        _dev(scratch, "scratch", torch.float32), _dev(tickets, "tickets", torch.int32), _stream()),
-        "attention_decode")
+        _dev(scratch, "scratch", torch.float32), _dev(tickets, "tickets", torch.int32),
+        *regions, _stream()), "attention_decode")
 
 
 def attention_prefill_tc_supports(n_q_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> bool:

@@ -120,6 +120,11 @@ class Part:
     def weight_slots(spec, hidden_size: int) -> Dict[str, WeightSlot]:
         return {}
 
+    def weights_in_order(self) -> tuple:
+        """The part's large weight matrices on the device, in the order its kernels read them
+        (what the parts before it may ask into L2 ahead of time); () if it has none."""
+        return ()
+
     def __init__(self, spec, hidden_size: int, weights: Dict[str, "object"], rt) -> None:
         self.spec = spec
         self.hidden_size = hidden_size

@@ -28,9 +28,27 @@ class PreNormBlock:
         self.feed_forward = part("feed_forward", layer_spec.feed_forward.kind)(
             layer_spec.feed_forward, hidden_size, weights_of("feed_forward"), rt)
 
+    def weights_in_order(self) -> tuple:
+        return tuple(getattr(self.mixer, "weights_in_order", tuple)()) + tuple(getattr(self.feed_forward, "weights_in_order", tuple)())
+
     def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], ctx, cache) -> torch.Tensor:
         n = h.shape[0]
         mixer, ffn = self.mixer, self.feed_forward
+        after = ctx.read_after                       # what runs after this block
+        ctx.read_after = tuple(getattr(ffn, "weights_in_order", tuple)()) + tuple(after)   # ... after the mixer
+        try:
+            a = self._mix(h, delta, ctx, cache, n)
+        finally:
+            ctx.read_after = after
+        if a is None and _fuses(ffn, self.ffn_norm, n):
+            return ffn.forward_fused_norm(h, self.ffn_norm, ctx, residual=h)
+        x = self.ffn_norm.forward(h, a)
+        if getattr(ffn, "adds_into_residual", False):
+            return ffn.forward(x, ctx, residual=h)
+        return ffn.forward(x, ctx)
+
+    def _mix(self, h, delta, ctx, cache, n):
+        mixer = self.mixer
         if delta is None and _fuses(mixer, self.mixer_norm, n):
             a = mixer.forward_fused_norm(h, self.mixer_norm, ctx, cache, residual=h)
         else:
@@ -39,12 +57,7 @@ class PreNormBlock:
                 a = mixer.forward(x, ctx, cache, residual=h)     # may add in place and return None
             else:
                 a = mixer.forward(x, ctx, cache)
-        if a is None and _fuses(ffn, self.ffn_norm, n):
-            return ffn.forward_fused_norm(h, self.ffn_norm, ctx, residual=h)
-        x = self.ffn_norm.forward(h, a)
-        if getattr(ffn, "adds_into_residual", False):
-            return ffn.forward(x, ctx, residual=h)
-        return ffn.forward(x, ctx)
+        return a
 
 
 def _fuses(part_obj, norm, n_rows: int) -> bool:

@@ -38,6 +38,9 @@ class SwiGLU(Part):
     adds_into_residual = True   # forward() accepts residual= and may add its output there
     graph_safe = "all"
 
+    def weights_in_order(self) -> tuple:
+        return (self.w_gate_up, self.w_down)
+
     def can_fuse_norm(self, norm, n_rows: int) -> bool:
         return (self.blocked and self.rt.skinny(n_rows, self.hidden_size) and hasattr(norm, "gain")
                 and hasattr(norm, "eps"))
@@ -47,7 +50,8 @@ class SwiGLU(Part):
         n = x.shape[0]
         act = rt.empty(n, self.inter)
         if self.blocked and rt.skinny(n, self.hidden_size):
-            ops.gemv_bf16(x, self.w_gate_up, act, ops.SWIGLU_BF16)     # activation in the epilogue
+            ops.gemv_bf16(x, self.w_gate_up, act, ops.SWIGLU_BF16,     # activation in the epilogue
+                          warm=rt.warm(self.w_down, 0, which=2))
         elif self.blocked and rt.tensor_core_gemm(n, self.hidden_size):
             ops.gemm_tc(x, self.w_gate_up, act, ops.SWIGLU_BF16)       # tcgen05 product, activation fused
         elif self.blocked and rt.mid_batch(n, self.hidden_size, rt.MID_GATE_UP):
@@ -58,14 +62,15 @@ class SwiGLU(Part):
         if residual is not None and rt.mid_batch(n, self.inter, rt.MID_DOWN):
             ops.gemm_swap_tc(act, self.w_down, residual, ops.ADD_F32)
             return None
-        return rt.linear(act, self.w_down, residual=residual)
+        return rt.linear(act, self.w_down, residual=residual, warm=rt.warm_after(ctx, which=4))
 
     def forward_fused_norm(self, h: torch.Tensor, norm, ctx, residual=None):
         """As forward, with x = norm(h): norm, projection and activation in one launch."""
         rt = self.rt
         act = rt.empty(h.shape[0], self.inter)
-        ops.gemv_norm_bf16(h, norm.gain, norm.eps, None, self.w_gate_up, act, ops.SWIGLU_BF16)
-        return rt.linear(act, self.w_down, residual=residual)
+        ops.gemv_norm_bf16(h, norm.gain, norm.eps, None, self.w_gate_up, act, ops.SWIGLU_BF16,
+                           warm=rt.warm(self.w_down, 0, which=2))
+        return rt.linear(act, self.w_down, residual=residual, warm=rt.warm_after(ctx, which=4))
 
 
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)

@@ -25,6 +25,9 @@ class LinearHead(Part):
         self.vocab_size = spec.vocab_size
         self.weight = rt.weight(weights["weight"])     # already on the device when it is the embedding's table
 
+    def weights_in_order(self) -> tuple:
+        return (self.weight,)
+
     def forward(self, h, delta, norm, ctx) -> torch.Tensor:
         """h FP32 [T, hidden] with ``delta`` still to be added (or None); returns FP32 logits
         [ctx.n_logit_rows, vocab] for rows ctx.logit_rows."""

@@ -58,6 +58,9 @@ class PagedAttention(Part):
     def cache_need(self):
         return PagedKVNeed(self.n_kv, self.head_dim, self.window)
 
+    def weights_in_order(self) -> tuple:
+        return (self.w_qkv, self.w_o)
+
     adds_into_residual = True   # forward() accepts residual= and may add its output there
     graph_safe = "all"          # everything that changes between steps is read from device memory
 
@@ -132,7 +135,8 @@ class PagedAttention(Part):
         if residual is not None and rt.mid_batch(n, self.n_heads * self.head_dim, rt.MID_OUT):
             ops.gemm_swap_tc(att, self.w_o, residual, ops.ADD_F32)       # added into the residual stream in the epilogue
             return None
-        return rt.linear(att, self.w_o, residual=residual)
+        # the attention kernel asked for the head of the next matrix; this one goes on from there
+        return rt.linear(att, self.w_o, residual=residual, warm=rt.warm_after(ctx, skip=rt.attention_share(ctx), which=1) if ctx.decode_only else None)
 
     def _attend(self, q, cache, att, ctx, table) -> None:
         """Attention of every token of the step over its own request's pages.
@@ -162,7 +166,8 @@ class PagedAttention(Part):
                                        n_dec * self.n_heads * splits * (self.head_dim + 2), torch.float32)
                 tickets = rt.workspace("attention_decode_tickets", n_dec * self.n_kv, torch.int32, zero=True)
                 ops.attention_decode(q, cache.k_pages, cache.v_pages, att, dec_list, n_dec, ctx.positions,
-                                     ctx.seq_of_token, table, *common, splits, scratch, tickets)
+                                     ctx.seq_of_token, table, *common, splits, scratch, tickets,
+                                     warm=rt.warm_attention(self.w_o, ctx))
             else:
                 ops.attention_generic(q, cache.k_pages, cache.v_pages, att, ctx.positions, ctx.seq_of_token,
                                       table, *common, token_list=dec_list)

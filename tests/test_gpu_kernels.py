@@ -247,6 +247,40 @@ def test_gemv_bf16(m, n, k, mode):
         assert torch.equal(one[0], out[m - 1])
 
 
+def test_a_request_to_warm_l2_changes_no_result():
+    """The skinny products and the decode attention may be handed a stretch of memory to ask into
+    L2 on their way (weights that later kernels read).  Results are the same bit for bit, for
+    stretches of any size and offset (cut to the tensor and to 16 bytes); nothing is written there."""
+    from nanoinfer_b200.kernels import ops
+    later = _randn(300, 1000, dtype=torch.bfloat16, seed=9)             # 600,000 bytes: no multiple of a piece
+    keep = later.clone()
+    x = _randn(5, 2048, dtype=torch.bfloat16, seed=1)
+    w = _randn(264, 2048, dtype=torch.bfloat16, seed=2, scale=0.05)
+    plain_out = torch.empty(5, 264, dtype=torch.float32, device=DEV)
+    ops.gemv_bf16(x, w, plain_out, ops.STORE_F32)
+    for hint in [(later, 0, 1 << 30), (later, 4096 + 8, 100_000), (later, 599_000, 5000), (later, 10**7, 64), None]:
+        out = torch.empty_like(plain_out)
+        ops.gemv_bf16(x, w, out, ops.STORE_F32, warm=hint)
+        assert torch.equal(out, plain_out)
+    assert ops.warm_region((later, 8, 100)) == (later.data_ptr(), 96)      # first byte and size cut to 16 bytes
+    assert ops.warm_region((later, 600_000, 64)) == (None, 0) and ops.warm_region(None) == (None, 0)
+    # the decode attention takes two stretches
+    lens = [300, 40]
+    spans = [(t - 1, t) for t in lens]
+    table, k_pages, v_pages, ks, vs, qs, q, positions, seq_of = _attention_case(lens, spans, 8, 2, 64, 16, 77)
+    outs = []
+    for hints in [(), ((later, 0, 1 << 30), (w, 0, 1 << 20)), ((later, 16, 48), None)]:
+        out = torch.zeros_like(q).to(DEV)
+        scratch = torch.empty(2 * 8 * 3 * 66, dtype=torch.float32, device=DEV)
+        tickets = torch.zeros(4, dtype=torch.int32, device=DEV)
+        ops.attention_decode(q.to(DEV), k_pages.to(DEV), v_pages.to(DEV), out, None, 2, positions.to(DEV), seq_of.to(DEV),
+                             table.to(DEV), 8, 2, 64, 16, None, 0.125, 3, scratch, tickets, warm=hints)
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    torch.cuda.synchronize()
+    assert torch.equal(later, keep)
+
+
 def test_gemv_refuses_what_it_cannot_take():
     from nanoinfer_b200.kernels import ops
     x = _randn(17, 64, dtype=torch.bfloat16)
