@@ -198,7 +198,7 @@ class ModelRunner:
         from ..kernels import ops
         common = ["elementwise", "rope_kv", "attention_generic"]
         ops.preload(common + (["gemm_f32"] if self.rt.dtype == torch.float32 else
-                              ["gemv_bf16", "gemm_tc", "gemm_tc2", "gemm_swap_tc", "attention_prefill", "attention_prefill_tc", "attention_decode"]
+                              ["gemv_bf16", "gemv_ksplit", "gemm_tc", "gemm_tc2", "gemm_swap_tc", "attention_prefill", "attention_prefill_tc", "attention_decode"]
                               + (["decode_fused"] if fused_decode else [])))
         self.model = DecoderModel(config, weights, self.rt)
 

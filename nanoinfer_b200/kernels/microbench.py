@@ -60,10 +60,12 @@ def gemv(args) -> None:
         out = torch.zeros(m, n, dtype=torch.bfloat16 if mode == ops.STORE_BF16 else torch.float32, device=DEV)
     if args.norm:
         fns = [lambda w=w: ops.gemv_norm_bf16(h, gain, 1e-5, None, w, out, mode) for w in ws]
+    elif args.ksplit:
+        fns = [lambda w=w: ops.gemv_ksplit(x, w, out, mode) for w in ws]
     else:
         fns = [lambda w=w: ops.gemv_bf16(x, w, out, mode) for w in ws]
     us = _time(fns, args.iters)
-    print(f"gemv m={m} n={n} k={k} mode={args.mode} norm={args.norm}: {us:.2f} us, "
+    print(f"gemv{' (K split over a cluster)' if args.ksplit else ''} m={m} n={n} k={k} mode={args.mode} norm={args.norm}: {us:.2f} us, "
           f"{w_bytes / us / 1e3:.0f} GB/s of weights ({copies} weight copies in turn)")
 
 
@@ -245,6 +247,7 @@ def main() -> None:
     p.add_argument("--k", type=int, default=2048)
     p.add_argument("--mode", default="bf16", choices=["bf16", "f32", "add", "swiglu"])
     p.add_argument("--norm", action="store_true")
+    p.add_argument("--ksplit", action="store_true", help="the cluster split-K kernel (gemv_ksplit.cu) instead of gemv_bf16.cu")
     p.set_defaults(fn=gemv)
     p = sub.add_parser("gemm")
     p.add_argument("--m", type=int, default=2048)

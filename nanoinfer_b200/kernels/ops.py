@@ -44,6 +44,10 @@ _SIGNATURES = {
         "ni_gemv_norm_bf16": [_P, _P, _F, _P, _P, _P, _I, _I, _I, _I, _P, _LL, _P],
         "ni_gemv_qkv_rope": [_P, _P, _F, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _LL, _P],
     },
+    "gemv_ksplit": {
+        "ni_gemv_ksplit": [_P, _P, _P, _I, _I, _I, _I, _P, _LL, _P],
+        "ni_gemv_ksplit_supports": [_I, _I, _I],
+    },
     "attention_decode": {
         "ni_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _LL, _P, _LL, _P],
         "ni_attention_decode_fresh_keys": [],
@@ -362,6 +366,33 @@ def gemv_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, wa
                                           _dev(out, "out"), m, n, k, mode, *warm_region(warm), _stream()), "gemv_bf16")
 
 
+KSPLIT_ROWS = 8          # rows the cluster split-K skinny product takes
+# The engine uses it for 2,048 < K <= 8,192 (2 to 4 slices).  Measured at 8 rows, against gemv_bf16:
+# N 2,048 x K 8,192: 8.5 us against 10.1;  3,072 x 8,192: 11.1 against 16.7;  4,096 x 4,096: 8.5 against 10.2;
+# 3,072 x 3,072: 7.0 against 8.3;  but 4,096 x 14,336 (7 slices: 37 clusters of 7 blocks leave SMs idle): 27.8 against 26.4.
+KSPLIT_MIN_K, KSPLIT_MAX_K = 2049, 8192
+
+
+def gemv_ksplit_supports(m: int, n: int, k: int) -> bool:
+    """True if gemv_ksplit takes the product: up to 8 rows, K a multiple of 8 in 2 to 8 slices of at most 2,048."""
+    return bool(load("gemv_ksplit").ni_gemv_ksplit_supports(m, n, k))
+
+
+def gemv_ksplit(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, warm=None) -> None:
+    """x[M, K] . w[N, K]^T for M <= 8 and a long K, split over the blocks of a cluster (each keeps
+    its slice of the activations in registers; the slices' sums are added in slice order).
+    mode STORE_BF16 / STORE_F32 / ADD_F32 as gemv_bf16."""
+    m, k = x.shape
+    n = w.shape[0]
+    if mode not in (STORE_BF16, STORE_F32, ADD_F32):
+        raise KernelError("gemv_ksplit: mode must be STORE_BF16, STORE_F32 or ADD_F32")
+    _gemv_check(m, n, k, w, out, mode, "gemv_ksplit")
+    if not gemv_ksplit_supports(m, n, k):
+        raise KernelError(f"gemv_ksplit: M={m}, N={n}, K={k} is not supported (up to 8 rows, K in 2 to 8 slices of 2,048)")
+    _check(load("gemv_ksplit").ni_gemv_ksplit(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16),
+                                              _dev(out, "out"), m, n, k, mode, *warm_region(warm), _stream()), "gemv_ksplit")
+
+
 def gemv_norm_bf16(h: torch.Tensor, gain: torch.Tensor, eps: float, rows: Optional[torch.Tensor],
                    w: torch.Tensor, out: torch.Tensor, mode: int, warm=None) -> None:
     """The same product with RMSNorm fused in front: x = norm(h[rows]) * gain, h float32
@@ -422,11 +453,14 @@ def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
         raise KernelError("linear_bf16: operands must be CUDA tensors")
     m, k = x.shape
     if m <= SKINNY_ROWS and k % 8 == 0:
+        # a long contraction: K split over a cluster, activations in registers (else re-read per row tile)
+        product = gemv_ksplit if (m <= KSPLIT_ROWS and KSPLIT_MIN_K <= k <= KSPLIT_MAX_K
+                                  and gemv_ksplit_supports(m, w.shape[0], k)) else gemv_bf16
         if residual is not None:
-            gemv_bf16(x, w, residual, ADD_F32, warm)
+            product(x, w, residual, ADD_F32, warm)
             return None
         out = torch.empty(m, w.shape[0], dtype=out_dtype, device=x.device)
-        gemv_bf16(x, w, out, STORE_BF16 if out_dtype == torch.bfloat16 else STORE_F32, warm)
+        product(x, w, out, STORE_BF16 if out_dtype == torch.bfloat16 else STORE_F32, warm)
         return out
     if out_dtype == torch.bfloat16:
         return torch.matmul(x, w.t())

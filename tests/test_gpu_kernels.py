@@ -247,6 +247,57 @@ def test_gemv_bf16(m, n, k, mode):
         assert torch.equal(one[0], out[m - 1])
 
 
+@pytest.mark.parametrize("mode", ["bf16", "f32", "add"])
+@pytest.mark.parametrize("m,n,k", [(8, 2048, 8192), (3, 200, 4104), (1, 77, 16384), (8, 4096, 14336), (5, 264, 2056),
+                                   (7, 1000, 6152)])
+def test_gemv_with_k_split_over_a_cluster(m, n, k, mode):
+    """Long contractions: 2 to 8 slices of K in the blocks of a cluster, sums added in slice order;
+    sizes with ragged last slices, last k-blocks and last row tiles."""
+    from nanoinfer_b200.kernels import ops
+    assert ops.gemv_ksplit_supports(m, n, k)
+    x = _randn(m, k, dtype=torch.bfloat16, seed=1)
+    w = _randn(n, k, dtype=torch.bfloat16, seed=2, scale=0.05)
+    w[n // 2, k - 8:] = 4.0                      # the very last k-block of a row must be read
+    want = x.cpu().double() @ w.cpu().double().t()
+    if mode == "bf16":
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+        ops.gemv_ksplit(x, w, out, ops.STORE_BF16)
+        torch.testing.assert_close(out.cpu().double(), want, rtol=4e-3, atol=1e-3 * math.sqrt(k / 2048))
+    elif mode == "f32":
+        out = torch.empty(m, n, dtype=torch.float32, device=DEV)
+        ops.gemv_ksplit(x, w, out, ops.STORE_F32)
+        torch.testing.assert_close(out.cpu().double(), want, rtol=1e-5, atol=1e-5 * math.sqrt(k))
+        again = torch.empty_like(out)
+        ops.gemv_ksplit(x, w, again, ops.STORE_F32)
+        assert torch.equal(out, again)           # fixed order of addition
+        if m > 1:                                # a row's result does not depend on the rows beside it
+            one = torch.empty(1, n, dtype=torch.float32, device=DEV)
+            ops.gemv_ksplit(x[m - 1:m].contiguous(), w, one, ops.STORE_F32)
+            assert torch.equal(one[0], out[m - 1])
+    else:
+        h = _randn(m, n, seed=3)
+        out = h.clone()
+        ops.gemv_ksplit(x, w, out, ops.ADD_F32)
+        torch.testing.assert_close(out.cpu().double(), h.cpu().double() + want, rtol=1e-5, atol=1e-5 * math.sqrt(k))
+    ops.check_device_errors()
+
+
+def test_gemv_k_split_refuses_what_it_cannot_take():
+    from nanoinfer_b200.kernels import ops
+    assert not ops.gemv_ksplit_supports(8, 2048, 2048)       # one slice: the other kernel's business
+    assert not ops.gemv_ksplit_supports(9, 2048, 8192)       # more than 8 rows
+    assert not ops.gemv_ksplit_supports(8, 2048, 8 * 2048 + 64)   # more than 8 slices
+    assert not ops.gemv_ksplit_supports(4, 128256, 8192)     # too many row tiles per cluster for its shared memory
+    with pytest.raises(ops.KernelError, match="not supported"):
+        ops.gemv_ksplit(_randn(8, 2048, dtype=torch.bfloat16), _randn(64, 2048, dtype=torch.bfloat16),
+                        torch.empty(8, 64, dtype=torch.float32, device=DEV), ops.STORE_F32)
+    # the dispatcher of the engine's products falls back to the streaming kernel there
+    x, w = _randn(4, 8192, dtype=torch.bfloat16, seed=1), _randn(40000, 8192, dtype=torch.bfloat16, seed=2, scale=0.05)
+    if not ops.gemv_ksplit_supports(4, 40000, 8192):
+        out = ops.linear_bf16(x, w, torch.float32)
+        torch.testing.assert_close(out.cpu().double(), x.cpu().double() @ w.cpu().double().t(), rtol=1e-5, atol=1e-3)
+
+
 def test_a_request_to_warm_l2_changes_no_result():
     """The skinny products and the decode attention may be handed a stretch of memory to ask into
     L2 on their way (weights that later kernels read).  Results are the same bit for bit, for
