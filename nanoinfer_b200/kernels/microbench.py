@@ -143,13 +143,14 @@ def attention_decode(args) -> None:
     positions = torch.full((b,), ctx - 1, dtype=torch.int32, device=DEV)
     seq_of = torch.arange(b, dtype=torch.int32, device=DEV)
     splits = args.splits or ops.decode_splits(b, hkv, hd, ctx)
+    ops.attention_decode_cluster_merge(not args.scratch_merge)
     scratch = torch.empty(b * hq * splits * (hd + 2), dtype=torch.float32, device=DEV)
     tickets = torch.zeros(b * hkv, dtype=torch.int32, device=DEV)
     fns = [lambda kc=kc, vc=vc: ops.attention_decode(q, kc, vc, out, None, b, positions, seq_of, table, hq, hkv, hd,
                                                      page, None, 1.0 / math.sqrt(hd), splits, scratch, tickets)
            for kc, vc in caches]
     us = _time(fns, args.iters)
-    print(f"attention_decode batch={b} context={ctx} heads={hq}/{hkv} hd={hd} page={page} splits={splits}: "
+    print(f"attention_decode{' (merge through scratch)' if args.scratch_merge else ''} batch={b} context={ctx} heads={hq}/{hkv} hd={hd} page={page} splits={splits}: "
           f"{us:.2f} us, {kv_bytes / us / 1e3:.0f} GB/s of cache")
 
 
@@ -282,6 +283,8 @@ def main() -> None:
         p.add_argument("--page", type=int, default=16)
         p.add_argument("--splits", type=int, default=0)
         p.add_argument("--kernel", default=None, choices=["tc", "mma"], help="prefill: insist on one kernel")
+        p.add_argument("--scratch-merge", action="store_true",
+                       help="decode: merge the splits through global scratch and tickets, not inside a cluster")
         p.set_defaults(fn=fn)
     for sp in sub.choices.values():
         sp.add_argument("--iters", type=int, default=200)

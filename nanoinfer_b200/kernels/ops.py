@@ -51,6 +51,7 @@ _SIGNATURES = {
     "attention_decode": {
         "ni_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _LL, _P, _LL, _P],
         "ni_attention_decode_fresh_keys": [],
+        "ni_attention_decode_set_cluster_merge": [_I],
         # the variant whose scratch lies in the library's own image (attention_decode_noalloc.h)
         "ni_attention_decode_noalloc": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     },
@@ -112,6 +113,9 @@ def load(module: str) -> ctypes.CDLL:
             f = getattr(lib, fn)
             f.argtypes = argtypes
             f.restype = _I
+        import os
+        if module == "attention_decode" and os.environ.get("NANOINFER_B200_SCRATCH_MERGE"):
+            lib.ni_attention_decode_set_cluster_merge(0)
         if module == "attention_decode" and lib.ni_attention_decode_fresh_keys() != DECODE_FRESH_KEYS:
             raise KernelError("attention_decode: DEC_FRESH_KEYS of the built kernel differs from ops.DECODE_FRESH_KEYS")
         _libs[module] = lib
@@ -665,6 +669,12 @@ def decode_splits(n_items: int, n_kv_heads: int, head_dim: int, max_kv_len: int,
 
 PREFILL_MAX_HEAD_DIM = 128
 PREFILL_TILE_ROWS = 128      # query rows per block of the flash-style kernel
+
+
+def attention_decode_cluster_merge(on: bool) -> None:
+    """Whether the splits of a (token, kv head) merge inside a thread-block cluster where they can
+    (the default) or always through the scratch buffer and the tickets."""
+    _check_plain(load("attention_decode").ni_attention_decode_set_cluster_merge(1 if on else 0), "attention_decode")
 
 
 def attention_decode(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token, block_table,

@@ -373,8 +373,12 @@ def _attention_case(lens, spans, n_q, n_kv, hd, page, seed, far_key=None):
 @pytest.mark.parametrize("n_splits", [1, 3, 7])
 @pytest.mark.parametrize("n_q,n_kv,hd,page,window", [(32, 8, 64, 16, None), (8, 8, 64, 8, None), (24, 8, 128, 16, None),
                                                       (16, 1, 64, 4, 100), (6, 2, 128, 32, 33), (16, 2, 64, 16, None)])
-def test_attention_decode(n_q, n_kv, hd, page, window, n_splits):
+@pytest.mark.parametrize("cluster", [True, False])
+def test_attention_decode(n_q, n_kv, hd, page, window, n_splits, cluster):
+    """``cluster``: the splits merge inside a thread-block cluster where the kernel can (2 to 8 splits
+    whose partial results fit its shared memory), else through the scratch and the tickets; off: always the latter."""
     from nanoinfer_b200.kernels import ops
+    ops.attention_decode_cluster_merge(cluster)
     lens = [700, 1, 33, 257]
     spans = [(t - 1, t) for t in lens]          # the last token of each sequence
     far = (0, 5) if window is None else None    # a far key among hundreds must be found
@@ -400,6 +404,7 @@ def test_attention_decode(n_q, n_kv, hd, page, window, n_splits):
     ops.attention_decode(q.to(DEV), k_pages.to(DEV), v_pages.to(DEV), out2, pick, 2, *args)
     assert torch.equal(out2[0], out[0]) and torch.equal(out2[2], out[2])
     assert torch.all(out2[1] == 9.0) and torch.all(out2[3] == 9.0)
+    ops.attention_decode_cluster_merge(True)
 
 
 @pytest.mark.parametrize("n_q,n_kv,hd,page,window", [(4, 2, 16, 16, None), (3, 1, 32, 8, None), (6, 3, 48, 4, 70),
