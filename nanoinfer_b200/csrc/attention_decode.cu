@@ -16,7 +16,7 @@
 //
 // The splits of a (token, kv head) merge in one of two ways.  Through global memory: partial
 // results to a scratch buffer, a fence, an atomic ticket, and the last arrival reads them back.
-// Or, with 2 to 8 splits, as a thread-block cluster (template parameter CL): partial results
+// Or, with 2 to 8 splits (up to 16 where the blocks are few), as a thread-block cluster (template parameter CL): partial results
 // written into the first block's shared memory, one cluster barrier, merged there - about 1.5 us
 // less per launch (batch 8, context 3,072: 17.0 -> 15.3 us).
 //
@@ -426,6 +426,10 @@ static int launch_decode_cl(const void* q, const void* k_pages, const void* v_pa
         cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, SEG, CL>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
+        if (CL) {   // clusters of 9 to 16 blocks (a lone request's many splits) are beyond the portable size
+            e = cudaFuncSetAttribute(attention_decode_kernel<HD, SEG, CL>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            if (e != cudaSuccess) return (int)e;
+        }
         configured = smem;
     }
     cudaLaunchConfig_t cfg = {};
@@ -472,7 +476,7 @@ static int launch_decode(const void* q, const void* k_pages, const void* v_pages
                          cudaStream_t stream) {
     const size_t slot_bytes = (size_t)n_splits * (n_q_heads / n_kv_heads) * (HD + 2) * sizeof(float);
     const bool few_blocks = (long long)n_items * n_kv_heads * n_splits <= 2LL * ni_sm_count() && slot_bytes <= 65536;
-    if (dec_cluster_merge && n_splits >= 2 && n_splits <= 8 && (slot_bytes <= DEC_CLUSTER_SLOT_BYTES || few_blocks))
+    if (dec_cluster_merge && n_splits >= 2 && ((n_splits <= 8 && slot_bytes <= DEC_CLUSTER_SLOT_BYTES) || (n_splits <= 16 && few_blocks)))
         return launch_decode_cl<HD, SEG, true>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
                                                block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
                                                scale_log2e, n_splits, scratch, tickets, warm_a, warm_a_bytes, warm_b,

@@ -370,7 +370,7 @@ def _attention_case(lens, spans, n_q, n_kv, hd, page, seed, far_key=None):
     return table, k_pages, v_pages, ks, vs, qs, q, positions, seq_of
 
 
-@pytest.mark.parametrize("n_splits", [1, 3, 7])
+@pytest.mark.parametrize("n_splits", [1, 3, 7, 12])     # 12: a cluster beyond the portable size where the blocks are few
 @pytest.mark.parametrize("n_q,n_kv,hd,page,window", [(32, 8, 64, 16, None), (8, 8, 64, 8, None), (24, 8, 128, 16, None),
                                                       (16, 1, 64, 4, 100), (6, 2, 128, 32, 33), (16, 2, 64, 16, None)])
 @pytest.mark.parametrize("cluster", [True, False])
