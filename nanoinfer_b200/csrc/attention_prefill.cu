@@ -74,9 +74,12 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     __nv_bfloat16* sK = sQ + PF_BM * HD;          // 2 stages
     __nv_bfloat16* sV = sK + 2 * PF_BN * HD;      // 2 stages
 
-    const int seq = tile_seq[blockIdx.x];
-    const int row0 = tile_row0[blockIdx.x];       // first query row of the tile within the portion
-    const int head = blockIdx.y;
+    // blocks are numbered tile-major (all heads of the tile with the most keys first): the hardware
+    // hands them out in that order, longest job first over the whole launch
+    const int tile_index = blockIdx.x / n_q_heads;
+    const int seq = tile_seq[tile_index];
+    const int row0 = tile_row0[tile_index];       // first query row of the tile within the portion
+    const int head = blockIdx.x - tile_index * n_q_heads;
     const int kvh = head / (n_q_heads / n_kv_heads);
     const int tok0 = cu_q[seq];
     const int q_len = cu_q[seq + 1] - tok0;
@@ -264,7 +267,9 @@ template <int HD> static int launch_prefill(const void* q, const void* k_pages, 
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(n_tiles, n_q_heads);
+    const long long blocks = (long long)n_tiles * n_q_heads;
+    if (blocks > 0x7fffffffLL) return NI_ERR_UNSUPPORTED_SIZE;
+    dim3 grid((unsigned)blocks);
     attention_prefill_kernel<HD><<<grid, PF_WARPS * 32, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
         (__nv_bfloat16*)out, tile_seq, tile_row0, cu_q, kv_len, block_table, bt_stride, n_q_heads,
@@ -280,7 +285,7 @@ NI_EXPORT int ni_attention_prefill(const void* q, const void* k_pages, const voi
                                    int n_kv_heads, int head_dim, int page_size, int window, float scale,
                                    cudaStream_t stream) {
     if (n_tiles <= 0) return NI_OK;
-    if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads || page_size <= 0 || n_q_heads > 65535)
+    if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads || page_size <= 0)
         return NI_ERR_BAD_ARGUMENT;
     const float sl = scale * 1.4426950408889634f;
 #define GO(HD) return launch_prefill<HD>(q, k_pages, v_pages, out, tile_seq, tile_row0, n_tiles, cu_q, kv_len, \

@@ -261,8 +261,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     // ---- the tile's place ----
-    const int seq = p.tile_seq[blockIdx.x];
-    const int row0 = p.tile_row0[blockIdx.x];
+    // Blocks are numbered tile-major: all head pairs of the tile with the most keys first, then all
+    // of the next one.  The hardware hands blocks out in the order of their numbers, so this is
+    // "longest job first" over the whole launch (with the tiles on the grid's fast axis every head
+    // pair's light tiles came before the next pair's heavy ones: 2,048 tokens took 25 tile-times
+    // of the heaviest block's 16, against 16 to 18 this way).
+    const int pairs = p.n_kv_heads * ((p.n_q_heads / p.n_kv_heads + 1) / 2);
+    const int tile_index = blockIdx.x / pairs, pair_index = blockIdx.x - tile_index * pairs;
+    const int seq = p.tile_seq[tile_index];
+    const int row0 = p.tile_row0[tile_index];
     const int q_begin = p.cu_q[seq];
     const int q_len = p.cu_q[seq + 1] - q_begin;
     const int kvl = p.kv_len[seq];
@@ -277,8 +284,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // block of an odd group has one head left: its second stream runs that head again, so that
     // the streams' hand-offs stay as they are, and stores nothing.
     const int blocks_per_kv = (G + 1) / 2;
-    const int kvh = blockIdx.y / blocks_per_kv;
-    const int first = 2 * (blockIdx.y - kvh * blocks_per_kv);
+    const int kvh = pair_index / blocks_per_kv;
+    const int first = 2 * (pair_index - kvh * blocks_per_kv);
     const int head0 = kvh * G + first;
     const int head1 = first + 1 < G ? head0 + 1 : head0;
 
@@ -682,7 +689,9 @@ static int launch_at(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(n_tiles, p.n_kv_heads * ((p.n_q_heads / p.n_kv_heads + 1) / 2));
+    const long long blocks = (long long)n_tiles * p.n_kv_heads * ((p.n_q_heads / p.n_kv_heads + 1) / 2);
+    if (blocks > 0x7fffffffLL) return NI_ERR_UNSUPPORTED_SIZE;
+    dim3 grid((unsigned)blocks);
     attention_prefill_tc_kernel<HD, STAGES><<<grid, AT_THREADS, smem, stream>>>(mq, mk, mv, p);
     NI_RETURN_LAUNCH_STATUS();
 }
@@ -692,7 +701,6 @@ NI_EXPORT int ni_attention_prefill_tc_supports(int n_q_heads, int n_kv_heads, in
     if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads) return 0;
     const int group = n_q_heads / n_kv_heads;
     if (group == 1) return 0;                 // two streams on one head would do every product twice
-    if ((long long)n_kv_heads * ((group + 1) / 2) > 65535) return 0;
     if (head_dim != 64 && head_dim != 128) return 0;
     if (page_size < 8 || page_size > 128 || 128 % page_size) return 0;
     return 1;

@@ -706,7 +706,6 @@ def attention_prefill_tc_supports(n_q_heads: int, n_kv_heads: int, head_dim: int
     query heads per kv head (an odd group's last head shares its block with a silent copy of
     itself), a page size from 8 to 128 that divides 128."""
     return (n_kv_heads > 0 and n_q_heads % n_kv_heads == 0 and n_q_heads // n_kv_heads >= 2
-            and n_kv_heads * ((n_q_heads // n_kv_heads + 1) // 2) <= 65535
             and head_dim in (64, 128) and 8 <= page_size <= 128 and 128 % page_size == 0)
 
 
