@@ -69,6 +69,21 @@ def gemv(args) -> None:
           f"{w_bytes / us / 1e3:.0f} GB/s of weights ({copies} weight copies in turn)")
 
 
+def add_rmsnorm(args) -> None:
+    """Residual add + RMSNorm over [rows, width]: the same buffers again and again (as between two
+    products of a prompt portion, where they lie in L2) or ``--copies`` sets in turn."""
+    t, d = args.rows, args.width
+    g = torch.Generator(device=DEV).manual_seed(0)
+    sets = [(torch.randn(t, d, device=DEV, generator=g), torch.randn(t, d, device=DEV, generator=g).to(torch.bfloat16),
+             torch.empty(t, d, dtype=torch.bfloat16, device=DEV)) for _ in range(args.copies)]
+    gain = torch.ones(d, device=DEV)
+    fns = [lambda h=h, dl=dl, o=o: ops.add_rmsnorm(h, dl, gain, 1e-5, o) for h, dl, o in sets]
+    us = _time(fns, args.iters)
+    nbytes = t * d * (4 + 2 + 4 + 2)
+    print(f"add_rmsnorm rows={t} width={d} copies={args.copies}: {us:.2f} us, {nbytes / us / 1e3:.0f} GB/s "
+          f"(h read and written, delta read, activations written)")
+
+
 def gemm(args) -> None:
     """The tcgen05 product against the library product on the same operands."""
     m, n, k = args.m, args.n, args.k
@@ -250,6 +265,11 @@ def main() -> None:
     p.add_argument("--norm", action="store_true")
     p.add_argument("--ksplit", action="store_true", help="the cluster split-K kernel (gemv_ksplit.cu) instead of gemv_bf16.cu")
     p.set_defaults(fn=gemv)
+    p = sub.add_parser("add_rmsnorm")
+    p.add_argument("--rows", type=int, default=2048)
+    p.add_argument("--width", type=int, default=2048)
+    p.add_argument("--copies", type=int, default=1)
+    p.set_defaults(fn=add_rmsnorm)
     p = sub.add_parser("gemm")
     p.add_argument("--m", type=int, default=2048)
     p.add_argument("--n", type=int, default=16384)

@@ -65,6 +65,35 @@ def test_add_rmsnorm(dtype, d, eps):
     torch.testing.assert_close(out_r.cpu().float(), want[rows.cpu().long()], **_tol(dtype))
 
 
+@pytest.mark.parametrize("d", [512, 1024, 2048, 3072])
+def test_add_rmsnorm_of_many_rows(d):
+    """Many bfloat16 rows of a width that is a multiple of 128 take the warp-per-row kernel; a last
+    block with fewer rows than warps, selected rows, and the same result as the few-row kernel up
+    to the order of the sum of squares."""
+    from nanoinfer_b200.kernels import ops
+    n, eps = 1027, 1e-5
+    h = _randn(n, d, seed=1)
+    delta = _randn(n, d, dtype=torch.bfloat16, seed=2)
+    gain = _randn(d, seed=3) + 1.0
+    want_h = h.cpu() + delta.cpu().float()
+    want = plain.rms_norm(want_h, gain.cpu(), eps)
+    out = torch.empty(n, d, dtype=torch.bfloat16, device=DEV)
+    h1 = h.clone()
+    ops.add_rmsnorm(h1, delta, gain, eps, out)
+    torch.testing.assert_close(h1.cpu(), want_h, rtol=0, atol=0)
+    torch.testing.assert_close(out.cpu().float(), want, **_tol(torch.bfloat16))
+    few = torch.empty(40, d, dtype=torch.bfloat16, device=DEV)
+    h2 = h[:40].clone()
+    ops.add_rmsnorm(h2, delta[:40].contiguous(), gain, eps, few)
+    torch.testing.assert_close(few.float(), out[:40].float(), rtol=8e-3, atol=1e-6)     # one bfloat16 step at most
+    rows = torch.randperm(n, generator=torch.Generator().manual_seed(4))[:1024].int().to(DEV)
+    out_r = torch.empty(1024, d, dtype=torch.bfloat16, device=DEV)
+    h3 = h.clone()
+    ops.add_rmsnorm(h3, delta, gain, eps, out_r, rows)
+    assert torch.equal(h3, h)
+    assert torch.equal(out_r, out[rows.long()])
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("inter", [192, 200, 8200])
 def test_swiglu(dtype, inter):
