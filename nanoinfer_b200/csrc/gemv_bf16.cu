@@ -364,8 +364,9 @@ static int launch_gemv_w(const GemvParams& p, int tiles_per_block, cudaStream_t 
 
 template <int RN, int NT, bool NORM, bool KEEP, int U>
 static int launch_gemv(const GemvParams& p, int tiles_per_block, cudaStream_t stream) {
-    // the variant that warms L2 exists for batches of up to 8 rows (single-token steps use no other)
-    if (NT == 1 && p.warm_bytes) return launch_gemv_w<RN, NT, NORM, KEEP, U, NT == 1>(p, tiles_per_block, stream);
+    // the variant that asks for p.warm exists for up to 8 rows of bfloat16 activations (what the
+    // engine's hints go to: a mixer's output projection, a down projection); elsewhere the hint is dropped
+    if (NT == 1 && !NORM && p.warm_bytes) return launch_gemv_w<RN, NT, NORM, KEEP, U, NT == 1 && !NORM>(p, tiles_per_block, stream);
     return launch_gemv_w<RN, NT, NORM, KEEP, U, false>(p, tiles_per_block, stream);
 }
 

@@ -400,7 +400,8 @@ def gemv_ksplit(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, 
 def gemv_norm_bf16(h: torch.Tensor, gain: torch.Tensor, eps: float, rows: Optional[torch.Tensor],
                    w: torch.Tensor, out: torch.Tensor, mode: int, warm=None) -> None:
     """The same product with RMSNorm fused in front: x = norm(h[rows]) * gain, h float32
-    [*, K] (the residual stream), rows int32 [M] or None for rows 0..M-1."""
+    [*, K] (the residual stream), rows int32 [M] or None for rows 0..M-1.  (``warm`` is accepted
+    and dropped: the kernels with the norm fused run at their register limit and carry no request code.)"""
     k = h.shape[1]
     m = h.shape[0] if rows is None else rows.numel()
     n = w.shape[0]
