@@ -412,6 +412,405 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     }
 }
 
+// ---- the balanced variant: keys dealt evenly over a fixed set of blocks ---------------------------
+//
+// With many (token, kv head) pairs - more than about one per SM - no split count fills the GPU
+// evenly: 256 pairs are 1.7 fat blocks per SM, or 3.5 lean ones in two splits, and requests of
+// different lengths make it worse (every pair is cut into the same number of splits, whatever its
+// length).  Here the grid is fixed: gridDim.x blocks per kv head, three resident per SM in all.
+// For one kv head the keys of all tokens, in 64-key chunks, form one long line, and every block
+// takes an equal stretch of it: the tail of a token that an earlier block began, whole tokens,
+// the head of a token that the next block continues.  A token that lies inside one block is
+// finished there.  A token that spans blocks leaves one partial result per block in a scratch
+// slot (a block has two: one for a stretch that continues a token, one for a stretch that begins
+// one), and the block that arrives last for it (atomic ticket) merges them in the order of the
+// line.  The chunk counts come from the positions on the device (a scan in shared memory by every
+// block), so the launch does not depend on the context lengths and can be replayed from a graph.
+#define DEC_BAL_MAX_ITEMS 1024
+
+template <int HD, int SEG>
+__global__ void __launch_bounds__(DEC_WARPS * 32, 3)
+attention_decode_balanced_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
+                                 const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out,
+                                 const int* __restrict__ token_list, int n_items, const int* __restrict__ positions,
+                                 const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
+                                 int bt_stride, int n_q_heads, int n_kv_heads, int page_size, int window,
+                                 float scale_log2e, float* __restrict__ scratch, int* __restrict__ tickets,
+                                 const unsigned char* __restrict__ warm_a, unsigned long long warm_a_bytes,
+                                 const unsigned char* __restrict__ warm_b, unsigned long long warm_b_bytes) {
+    if (threadIdx.x >= (DEC_WARPS - 1) * 32) dec_warm(warm_a, warm_a_bytes);
+    constexpr int CH = HD / 8;
+    constexpr int KS = HD / 16;
+    constexpr int NT_O = HD / 8;
+    constexpr int WK = SEG / DEC_WARPS;
+    extern __shared__ __align__(128) unsigned char dec_smem[];
+    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(dec_smem);
+    __nv_bfloat16* sKV = sQ + 16 * HD;
+    __shared__ int s_prefix[DEC_BAL_MAX_ITEMS + 1];      // chunks before item i; [n_items] = all chunks
+    __shared__ int s_warp_sum[DEC_WARPS];
+    __shared__ int s_first_item;
+    __shared__ float sm_m[DEC_WARPS][16], sm_l[DEC_WARPS][16];
+    __shared__ int is_last;
+
+    const int kvh = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int G = n_q_heads / n_kv_heads;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
+    const size_t rec = HD + 2;
+
+    // ---- every token's chunk count, and their running sum (step metadata: not written by the kernel before) ----
+    int running = 0;
+    for (int base = 0; base < n_items; base += DEC_WARPS * 32) {
+        const int i = base + threadIdx.x;
+        int c = 0;
+        if (i < n_items) {
+            const int pos = positions[token_list ? token_list[i] : i];
+            const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+            c = (pos + 1 - lo + 63) >> 6;
+        }
+        int incl = c;                                     // inclusive scan inside the warp
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= off) incl += v;
+        }
+        if (lane == 31) s_warp_sum[warp] = incl;
+        __syncthreads();
+        int before = running;
+        for (int w = 0; w < warp; ++w) before += s_warp_sum[w];
+        if (i < n_items) s_prefix[i] = before + incl - c;
+        int all = 0;
+        for (int w = 0; w < DEC_WARPS; ++w) all += s_warp_sum[w];
+        running += all;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) s_prefix[n_items] = running;
+    const int total = running;
+    const int quota = (total + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int g_begin = (int)blockIdx.x * quota;
+    const int g_end = min(total, g_begin + quota);
+    // (asking for old keys before this wait, as the kernel above does, changed nothing here: the scan
+    // already covers the projection's tail)
+    dec_pdl_wait();                                      // the projection has finished: queries and fresh keys are there
+    if (g_begin >= g_end) return;                        // (block-uniform) more blocks than chunks
+    __syncthreads();
+    // the token whose chunks contain g_begin
+    for (int i = threadIdx.x; i < n_items; i += DEC_WARPS * 32)
+        if (s_prefix[i] <= g_begin && g_begin < s_prefix[i + 1]) s_first_item = i;
+    __syncthreads();
+
+    int gpos = g_begin;
+    for (int item = s_first_item; gpos < g_end; ++item) {
+        const int pre = s_prefix[item], c_item = s_prefix[item + 1] - pre;
+        const int c0 = gpos - pre;
+        const int take = min(g_end - gpos, c_item - c0);
+        gpos += take;
+        const int t_idx = token_list ? token_list[item] : item;
+        const int pos = positions[t_idx];
+        const int* table = block_table + (size_t)seq_of_token[t_idx] * bt_stride;
+        const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        const int k_begin = lo + c0 * 64;
+        const int k_end = min(pos + 1, k_begin + take * 64);
+
+        float o[NT_O][4];
+#pragma unroll
+        for (int j = 0; j < NT_O; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+        float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+        uint32_t qa[KS][4];
+
+        auto request = [&](int seg0, int buf) {
+            const int seg_keys = min(SEG, k_end - seg0);
+            const int rows = ((seg_keys + 15) / 16) * 16;
+            __nv_bfloat16* sK = sKV + (size_t)buf * 2 * SEG * HD;
+            __nv_bfloat16* sV = sK + SEG * HD;
+            constexpr int ITERS = SEG * CH / (DEC_WARPS * 32);
+            int page[ITERS];
+#pragma unroll
+            for (int it = 0; it < ITERS; ++it) {
+                const int idx = threadIdx.x + it * DEC_WARPS * 32;
+                const int r = idx / CH;
+                int key = seg0 + r;
+                key = key < k_end ? key : k_end - 1;
+                const int pi = page_shift >= 0 ? key >> page_shift : key / page_size;
+                page[it] = idx < rows * CH ? table[pi] : -1;
+            }
+#pragma unroll
+            for (int it = 0; it < ITERS; ++it) {
+                if (page[it] < 0) continue;
+                const int idx = threadIdx.x + it * DEC_WARPS * 32;
+                const int r = idx / CH, c = idx - r * CH;
+                int key = seg0 + r;
+                key = key < k_end ? key : k_end - 1;
+                const int pi = page_shift >= 0 ? key >> page_shift : key / page_size;
+                const int slot = page_shift >= 0 ? key & (page_size - 1) : key - pi * page_size;
+                const size_t off = (((size_t)page[it] * n_kv_heads + kvh) * page_size + slot) * HD + c * 8;
+                dec_cp_async16(sK + dec_sw<HD>(r, c), k_pages + off);
+                dec_cp_async16(sV + dec_sw<HD>(r, c), v_pages + off);
+            }
+        };
+
+        __syncthreads();      // the buffers and the merge area of the token before are no longer in use
+        request(k_begin, 0);
+        for (int idx = threadIdx.x; idx < 16 * CH; idx += blockDim.x) {
+            const int r = idx / CH, c = idx - r * CH;
+            __nv_bfloat16* dst = sQ + dec_sw<HD>(r, c);
+            if (r < G)
+                dec_cp_async16(dst, q + ((size_t)t_idx * n_q_heads + (size_t)kvh * G + r) * HD + c * 8);
+            else
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+
+        int buf = 0;
+        for (int seg0 = k_begin; seg0 < k_end; seg0 += SEG, buf ^= 1) {
+            const int seg_keys = min(SEG, k_end - seg0);
+            const int rows = ((seg_keys + 15) / 16) * 16;
+            const __nv_bfloat16* sK = sKV + (size_t)buf * 2 * SEG * HD;
+            const __nv_bfloat16* sV = sK + SEG * HD;
+            if (seg0 + SEG < k_end) request(seg0 + SEG, buf ^ 1);
+            asm volatile("cp.async.commit_group;\n" ::);
+            asm volatile("cp.async.wait_group 1;\n" ::);
+            __syncthreads();
+            if (seg0 == k_begin) {
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks)
+                    dec_ldsm_x4(qa[ks], sQ + dec_sw<HD>((lane & 7) + 8 * ((lane >> 3) & 1), 2 * ks + (lane >> 4)));
+            }
+            const int w0 = warp * WK;
+            if (w0 < seg_keys) {
+                float sc[WK / 8][4];
+#pragma unroll
+                for (int j = 0; j < WK / 8; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+#pragma unroll
+                for (int jp = 0; jp < WK / 16; ++jp) {
+                    if (w0 + 16 * jp < rows) {
+#pragma unroll
+                        for (int ks = 0; ks < KS; ++ks) {
+                            uint32_t b[4];
+                            const int mi = lane >> 3;
+                            dec_ldsm_x4(b, sK + dec_sw<HD>(w0 + 16 * jp + (lane & 7) + 8 * (mi >> 1), 2 * ks + (mi & 1)));
+                            mma_bf16_16816(sc[2 * jp], qa[ks], b[0], b[1]);
+                            mma_bf16_16816(sc[2 * jp + 1], qa[ks], b[2], b[3]);
+                        }
+                    }
+                }
+                float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < WK / 8; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const bool ok = w0 + 8 * j + 2 * t + (e & 1) < seg_keys;
+                        sc[j][e] = ok ? sc[j][e] * scale_log2e : -INFINITY;
+                    }
+                    mx0 = fmaxf(mx0, fmaxf(sc[j][0], sc[j][1]));
+                    mx1 = fmaxf(mx1, fmaxf(sc[j][2], sc[j][3]));
+                }
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+                const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+                const float corr0 = dec_exp2(m0 - mn0), corr1 = dec_exp2(m1 - mn1);
+                m0 = mn0; m1 = mn1;
+                float rs0 = 0.f, rs1 = 0.f;
+                uint32_t pa[WK / 16][4];
+#pragma unroll
+                for (int j = 0; j < WK / 8; ++j) {
+                    const __nv_bfloat162 r01 = __floats2bfloat162_rn(dec_exp2(sc[j][0] - mn0), dec_exp2(sc[j][1] - mn0));
+                    const __nv_bfloat162 r23 = __floats2bfloat162_rn(dec_exp2(sc[j][2] - mn1), dec_exp2(sc[j][3] - mn1));
+                    rs0 += __bfloat162float(r01.x) + __bfloat162float(r01.y);
+                    rs1 += __bfloat162float(r23.x) + __bfloat162float(r23.y);
+                    pa[j >> 1][(j & 1) * 2 + 0] = *reinterpret_cast<const uint32_t*>(&r01);
+                    pa[j >> 1][(j & 1) * 2 + 1] = *reinterpret_cast<const uint32_t*>(&r23);
+                }
+                l0 = l0 * corr0 + rs0;
+                l1 = l1 * corr1 + rs1;
+#pragma unroll
+                for (int j = 0; j < NT_O; ++j) {
+                    o[j][0] *= corr0; o[j][1] *= corr0; o[j][2] *= corr1; o[j][3] *= corr1;
+                }
+#pragma unroll
+                for (int ks = 0; ks < WK / 16; ++ks) {
+                    if (w0 + 16 * ks < rows) {
+#pragma unroll
+                        for (int dp = 0; dp < NT_O / 2; ++dp) {
+                            uint32_t b[4];
+                            const int mi = lane >> 3;
+                            dec_ldsm_x4_trans(b, sV + dec_sw<HD>(w0 + 16 * ks + (lane & 7) + 8 * (mi & 1), 2 * dp + (mi >> 1)));
+                            mma_bf16_16816(o[2 * dp], pa[ks], b[0], b[1]);
+                            mma_bf16_16816(o[2 * dp + 1], pa[ks], b[2], b[3]);
+                        }
+                    }
+                }
+            }
+            __syncthreads();
+        }
+        asm volatile("cp.async.wait_group 0;\n" ::);
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+        // ---- merge the block's warps (fixed order) ----
+        __syncthreads();
+        float (*sm_o)[16][HD + 1] = reinterpret_cast<float (*)[16][HD + 1]>(dec_smem);
+        static_assert(sizeof(float) * DEC_WARPS * 16 * (HD + 1) <= sizeof(__nv_bfloat16) * (16 + 4 * SEG) * HD, "merge buffer");
+        if (t == 0) { sm_m[warp][g] = m0; sm_m[warp][g + 8] = m1; sm_l[warp][g] = l0; sm_l[warp][g + 8] = l1; }
+#pragma unroll
+        for (int j = 0; j < NT_O; ++j) {
+            const int d = 8 * j + 2 * t;
+            sm_o[warp][g][d] = o[j][0]; sm_o[warp][g][d + 1] = o[j][1];
+            sm_o[warp][g + 8][d] = o[j][2]; sm_o[warp][g + 8][d + 1] = o[j][3];
+        }
+        __syncthreads();
+        // where this token's stretches lie on the line of blocks
+        const int first_block = pre / quota, last_block = (pre + c_item - 1) / quota;
+        const int n_parts = last_block - first_block + 1;
+        // a block's two slots: 0 for a stretch that continues a token, 1 for one that begins a token
+        float* my_slot = scratch + ((((size_t)kvh * gridDim.x + blockIdx.x) * 2 + (c0 == 0 ? 1 : 0)) * G) * rec;
+        for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+            const int row = idx / HD, d = idx - row * HD;
+            float mm = sm_m[0][row];
+#pragma unroll
+            for (int w = 1; w < DEC_WARPS; ++w) mm = fmaxf(mm, sm_m[w][row]);
+            float acc = 0.f, ll = 0.f;
+#pragma unroll
+            for (int w = 0; w < DEC_WARPS; ++w) {
+                const float f = sm_m[w][row] == -INFINITY ? 0.f : dec_exp2(sm_m[w][row] - mm);
+                acc += sm_o[w][row][d] * f;
+                ll += sm_l[w][row] * f;
+            }
+            if (n_parts == 1) {
+                out[((size_t)t_idx * n_q_heads + (size_t)kvh * G + row) * HD + d] = __float2bfloat16_rn(acc / ll);
+                continue;
+            }
+            float* dst = my_slot + (size_t)row * rec;
+            dst[2 + d] = acc;
+            if (d == 0) { dst[0] = mm; dst[1] = ll; }
+        }
+        if (n_parts == 1) continue;
+        // ---- the last block to arrive for this token merges its stretches, in the order of the line ----
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            int* ticket = tickets + (size_t)item * n_kv_heads + kvh;
+            const int prev = atomicAdd(ticket, 1);
+            is_last = prev == n_parts - 1;
+            if (is_last) *ticket = 0;
+        }
+        __syncthreads();
+        if (!is_last) continue;
+        __threadfence();
+        for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+            const int row = idx / HD, d = idx - row * HD;
+            float mm = -INFINITY, acc = 0.f, ll = 0.f;
+            for (int s0 = 0; s0 < n_parts; s0 += 8) {
+                float ms[8], ls[8], as[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const bool ok = s0 + j < n_parts;
+                    const int part = ok ? s0 + j : s0;
+                    // part 0 began the token in block first_block (slot 1); the others continue it (slot 0)
+                    const float* r = scratch + ((((size_t)kvh * gridDim.x + first_block + part) * 2 + (part == 0 ? 1 : 0)) * G + row) * rec;
+                    ms[j] = __ldcg(r);
+                    ls[j] = __ldcg(r + 1);
+                    as[j] = __ldcg(r + 2 + d);
+                    if (!ok) ms[j] = -INFINITY;
+                }
+                float cm = mm;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) cm = fmaxf(cm, ms[j]);
+                const float f0 = mm == -INFINITY ? 0.f : dec_exp2(mm - cm);
+                acc *= f0;
+                ll *= f0;
+                mm = cm;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float f = ms[j] == -INFINITY ? 0.f : dec_exp2(ms[j] - cm);
+                    acc += as[j] * f;
+                    ll += ls[j] * f;
+                }
+            }
+            out[((size_t)t_idx * n_q_heads + (size_t)kvh * G + row) * HD + d] = __float2bfloat16_rn(acc / ll);
+        }
+    }
+    if (threadIdx.x >= (DEC_WARPS - 1) * 32) dec_warm(warm_b, warm_b_bytes);
+}
+
+// Blocks per kv head of the balanced kernel: three resident per SM, shared among the kv heads.
+static int dec_balanced_blocks(int n_kv_heads) {
+    const int b = (3 * ni_sm_count()) / n_kv_heads;
+    return b < 1 ? 1 : b;
+}
+
+template <int HD, int SEG>
+static int launch_decode_balanced(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                  const int* token_list, int n_items, const int* positions, const int* seq_of_token,
+                                  const int* block_table, int bt_stride, int n_q_heads, int n_kv_heads, int page_size,
+                                  int window, float scale_log2e, float* scratch, int* tickets, const void* warm_a,
+                                  unsigned long long warm_a_bytes, const void* warm_b, unsigned long long warm_b_bytes,
+                                  cudaStream_t stream) {
+    const size_t smem = (size_t)(16 + 4 * SEG) * HD * sizeof(__nv_bfloat16);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_balanced_kernel<HD, SEG>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(dec_balanced_blocks(n_kv_heads), n_kv_heads);
+    cfg.blockDim = dim3(DEC_WARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_balanced_kernel<HD, SEG>, (const __nv_bfloat16*)q,
+                                       (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
+                                       (__nv_bfloat16*)out, token_list, n_items, positions, seq_of_token, block_table,
+                                       bt_stride, n_q_heads, n_kv_heads, page_size, window, scale_log2e, scratch,
+                                       tickets, (const unsigned char*)warm_a, warm_a_bytes, (const unsigned char*)warm_b,
+                                       warm_b_bytes);
+    return e == cudaSuccess ? NI_OK : (int)e;
+}
+
+// Scratch floats of the balanced kernel: two slots per block of G x (head_dim + 2); tickets: n_items * n_kv_heads.
+NI_EXPORT long long ni_attention_decode_balanced_scratch(int n_q_heads, int n_kv_heads, int head_dim) {
+    if (n_kv_heads <= 0 || n_q_heads <= 0) return 0;
+    return 2LL * dec_balanced_blocks(n_kv_heads) * n_kv_heads * (n_q_heads / n_kv_heads) * (head_dim + 2);
+}
+
+NI_EXPORT int ni_attention_decode_balanced(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                           const int* token_list, int n_items, const int* positions,
+                                           const int* seq_of_token, const int* block_table, int bt_stride,
+                                           int n_q_heads, int n_kv_heads, int head_dim, int page_size, int window,
+                                           float scale, float* scratch, int* tickets, const void* warm_a,
+                                           long long warm_a_bytes, const void* warm_b, long long warm_b_bytes,
+                                           cudaStream_t stream) {
+    if (n_items <= 0) return NI_OK;
+    if (n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads || page_size <= 0 || n_kv_heads > 65535)
+        return NI_ERR_BAD_ARGUMENT;
+    if (warm_a_bytes < 0 || (warm_a_bytes & 15) || (warm_a_bytes && (!warm_a || ((uintptr_t)warm_a & 15)))) return NI_ERR_BAD_ARGUMENT;
+    if (warm_b_bytes < 0 || (warm_b_bytes & 15) || (warm_b_bytes && (!warm_b || ((uintptr_t)warm_b & 15)))) return NI_ERR_BAD_ARGUMENT;
+    if (n_q_heads / n_kv_heads > 16 || n_items > DEC_BAL_MAX_ITEMS) return NI_ERR_UNSUPPORTED_SIZE;
+    const float scale_log2e = scale * 1.4426950408889634f;
+    switch (head_dim) {
+        case 64:
+            return launch_decode_balanced<64, 128>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
+                                                   block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
+                                                   scale_log2e, scratch, tickets, warm_a, (unsigned long long)warm_a_bytes,
+                                                   warm_b, (unsigned long long)warm_b_bytes, stream);
+        case 128:
+            return launch_decode_balanced<128, 64>(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token,
+                                                   block_table, bt_stride, n_q_heads, n_kv_heads, page_size, window,
+                                                   scale_log2e, scratch, tickets, warm_a, (unsigned long long)warm_a_bytes,
+                                                   warm_b, (unsigned long long)warm_b_bytes, stream);
+        default: return NI_ERR_UNSUPPORTED_SIZE;
+    }
+}
+
 template <int HD, int SEG, bool CL>
 static int launch_decode_cl(const void* q, const void* k_pages, const void* v_pages, void* out, const int* token_list,
                          int n_items, const int* positions, const int* seq_of_token, const int* block_table,

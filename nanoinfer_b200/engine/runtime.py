@@ -35,6 +35,21 @@ class Runtime:
     page_size: int
     fused_decode: bool = False    # steps of up to 8 single tokens as ONE persistent kernel (slower than the chain of kernels so far)
 
+    # From how many (token, kv head) pairs on a step's single-token attention takes the kernel that
+    # deals the keys evenly over a fixed grid (0: one pair per SM, set when the device is known), and
+    # whether heads of 64 take it too.  Measured in the step (ms per step, split kernel / balanced):
+    # heads of 128: 3B batch 32 3.78 / 3.65, 8B batch 64 at context 6,144 13.62 / 13.27, the continuous
+    # workload (3B, contexts of all lengths) 5.65k / 6.46k generated tokens a second.  Heads of 64 with
+    # equal contexts: batch 24 1.44 / 1.39, but batch 32 1.36 / 1.45 and batch 64 1.76 / 1.85 - there it
+    # only wins when the contexts differ (alone, contexts from a quarter to all of 3,072: batch 32
+    # 37.6 / 33.7 us, batch 64 65.1 / 56.9 us), which a replayed graph cannot know; so it is off for them.
+    balanced_attention_pairs: int = 0
+    balanced_attention_narrow_heads: bool = False
+
+    def balanced_attention(self, n_tokens: int, n_kv_heads: int, head_dim: int) -> bool:
+        return (n_tokens * n_kv_heads > self.balanced_attention_pairs
+                and (head_dim > 64 or self.balanced_attention_narrow_heads))
+
     def __post_init__(self) -> None:
         import os
         if os.environ.get("NANOINFER_B200_MID_BATCH"):          # for measurements: which projections take the swapped kernel
@@ -42,11 +57,16 @@ class Runtime:
         if os.environ.get("NANOINFER_B200_WARM"):               # for measurements: "<product KiB>,<attention KiB>"
             a, b, c = os.environ["NANOINFER_B200_WARM"].split(",")
             self.warm_bytes, self.warm_attention_bytes, self.warm_mask = int(a) << 10, int(b) << 10, int(c)
+        if os.environ.get("NANOINFER_B200_BALANCED"):           # for measurements: "<pairs>,<0|1: heads of 64 too>"
+            a, b = os.environ["NANOINFER_B200_BALANCED"].split(",")
+            self.balanced_attention_pairs, self.balanced_attention_narrow_heads = int(a), bool(int(b))
         self._workspaces = {}
         self._retired = []
         ops.require_cuda()
         if self.device.type != "cuda":
             raise ops.KernelError(f"device {self.device} is not a CUDA device; there is no CPU path")
+        if self.balanced_attention_pairs <= 0:
+            self.balanced_attention_pairs = ops.sm_count(self.device)
 
     def weight(self, t: torch.Tensor) -> torch.Tensor:
         """A matrix weight on the device in the compute dtype."""

@@ -161,11 +161,22 @@ def attention_decode(args) -> None:
     ops.attention_decode_cluster_merge(not args.scratch_merge)
     scratch = torch.empty(b * hq * splits * (hd + 2), dtype=torch.float32, device=DEV)
     tickets = torch.zeros(b * hkv, dtype=torch.int32, device=DEV)
-    fns = [lambda kc=kc, vc=vc: ops.attention_decode(q, kc, vc, out, None, b, positions, seq_of, table, hq, hkv, hd,
-                                                     page, None, 1.0 / math.sqrt(hd), splits, scratch, tickets)
-           for kc, vc in caches]
+    if args.ragged:      # contexts from a quarter of --context to all of it (the cache's bytes are counted as they are read)
+        positions = (torch.linspace(ctx // 4, ctx, b, device=DEV).int() - 1).contiguous()
+        kv_bytes = int(2 * (positions.long() + 1).sum().item() * hkv * hd * 2)
+        splits = args.splits or ops.decode_splits(b, hkv, hd, ctx)
+    if args.balanced:
+        scratch = torch.empty(ops.attention_decode_balanced_scratch(hq, hkv, hd), dtype=torch.float32, device=DEV)
+        fns = [lambda kc=kc, vc=vc: ops.attention_decode_balanced(q, kc, vc, out, None, b, positions, seq_of, table, hq, hkv,
+                                                                  hd, page, None, 1.0 / math.sqrt(hd), scratch, tickets)
+               for kc, vc in caches]
+    else:
+        scratch = torch.empty(b * hq * splits * (hd + 2), dtype=torch.float32, device=DEV)
+        fns = [lambda kc=kc, vc=vc: ops.attention_decode(q, kc, vc, out, None, b, positions, seq_of, table, hq, hkv, hd,
+                                                         page, None, 1.0 / math.sqrt(hd), splits, scratch, tickets)
+               for kc, vc in caches]
     us = _time(fns, args.iters)
-    print(f"attention_decode{' (merge through scratch)' if args.scratch_merge else ''} batch={b} context={ctx} heads={hq}/{hkv} hd={hd} page={page} splits={splits}: "
+    print(f"attention_decode{' (merge through scratch)' if args.scratch_merge else ''}{' (balanced)' if args.balanced else ''}{' ragged' if args.ragged else ''} batch={b} context={ctx} heads={hq}/{hkv} hd={hd} page={page} splits={splits}: "
           f"{us:.2f} us, {kv_bytes / us / 1e3:.0f} GB/s of cache")
 
 
@@ -303,6 +314,8 @@ def main() -> None:
         p.add_argument("--page", type=int, default=16)
         p.add_argument("--splits", type=int, default=0)
         p.add_argument("--kernel", default=None, choices=["tc", "mma"], help="prefill: insist on one kernel")
+        p.add_argument("--balanced", action="store_true", help="decode: the kernel that deals the keys evenly over a fixed grid")
+        p.add_argument("--ragged", action="store_true", help="decode: contexts from a quarter of --context up to it")
         p.add_argument("--scratch-merge", action="store_true",
                        help="decode: merge the splits through global scratch and tickets, not inside a cluster")
         p.set_defaults(fn=fn)

@@ -50,6 +50,7 @@ _SIGNATURES = {
     },
     "attention_decode": {
         "ni_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _LL, _P, _LL, _P],
+        "ni_attention_decode_balanced": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P, _LL, _P, _LL, _P],
         "ni_attention_decode_fresh_keys": [],
         "ni_attention_decode_set_cluster_merge": [_I],
         # the variant whose scratch lies in the library's own image (attention_decode_noalloc.h)
@@ -670,6 +671,41 @@ def decode_splits(n_items: int, n_kv_heads: int, head_dim: int, max_kv_len: int,
 
 PREFILL_MAX_HEAD_DIM = 128
 PREFILL_TILE_ROWS = 128      # query rows per block of the flash-style kernel
+
+
+DECODE_BALANCED_MAX_ITEMS = 1024
+
+
+def attention_decode_balanced_scratch(n_q_heads: int, n_kv_heads: int, head_dim: int) -> int:
+    """Scratch floats that attention_decode_balanced needs (two slots per block; independent of the batch)."""
+    lib = load("attention_decode")
+    lib.ni_attention_decode_balanced_scratch.restype = ctypes.c_longlong
+    lib.ni_attention_decode_balanced_scratch.argtypes = [_I, _I, _I]
+    return int(lib.ni_attention_decode_balanced_scratch(n_q_heads, n_kv_heads, head_dim))
+
+
+def attention_decode_balanced(q, k_pages, v_pages, out, token_list, n_items, positions, seq_of_token, block_table,
+                              n_q_heads, n_kv_heads, head_dim, page_size, window, scale, scratch, tickets, warm=()) -> None:
+    """Attention of single query tokens (bfloat16) with the keys of all tokens dealt evenly over a fixed
+    set of blocks (three per SM): for many tokens, or tokens of very different context lengths.
+    scratch: float32, at least attention_decode_balanced_scratch(...); tickets: int32 zeros, at least
+    n_items * Hkv (left zero by the kernel).  At most DECODE_BALANCED_MAX_ITEMS tokens.  ``warm`` as in
+    attention_decode."""
+    regions = [v for w_ in (list(warm) + [None, None])[:2] for v in warm_region(w_)]
+    if head_dim not in DECODE_HEAD_DIMS or n_q_heads // n_kv_heads > 16 or n_items > DECODE_BALANCED_MAX_ITEMS:
+        raise KernelError(f"attention_decode_balanced: head_dim {head_dim} / group {n_q_heads // n_kv_heads} / "
+                          f"{n_items} tokens not supported")
+    if scratch.numel() < attention_decode_balanced_scratch(n_q_heads, n_kv_heads, head_dim) or tickets.numel() < n_items * n_kv_heads:
+        raise KernelError("attention_decode_balanced: scratch or tickets too small")
+    _check(load("attention_decode").ni_attention_decode_balanced(
+        _dev(q, "q", torch.bfloat16), _dev(k_pages, "k_pages", torch.bfloat16),
+        _dev(v_pages, "v_pages", torch.bfloat16), _dev(out, "out", torch.bfloat16),
+        _dev(token_list, "token_list", torch.int32) if token_list is not None else None, n_items,
+        _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
+        _dev(block_table, "block_table", torch.int32), block_table.shape[1], n_q_heads, n_kv_heads,
+        head_dim, page_size, int(window) if window else 0, float(scale),
+        _dev(scratch, "scratch", torch.float32), _dev(tickets, "tickets", torch.int32), *regions, _stream()),
+        "attention_decode_balanced")
 
 
 def attention_decode_cluster_merge(on: bool) -> None:

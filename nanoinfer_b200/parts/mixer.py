@@ -160,7 +160,15 @@ class PagedAttention(Part):
         n_dec = n if plan is None else plan.scalars["n_dec"]
         dec_list = None if plan is None else plan.arrays["dec_tokens"]
         if n_dec > 0:
-            if decode_ok:
+            if decode_ok and rt.balanced_attention(n_dec, self.n_kv, self.head_dim) and n_dec <= ops.DECODE_BALANCED_MAX_ITEMS:
+                # many tokens: their keys dealt evenly over a fixed set of blocks, whatever their lengths
+                scratch = rt.workspace("attention_decode_balanced_partials",
+                                       ops.attention_decode_balanced_scratch(self.n_heads, self.n_kv, self.head_dim), torch.float32)
+                tickets = rt.workspace("attention_decode_tickets", n_dec * self.n_kv, torch.int32, zero=True)
+                ops.attention_decode_balanced(q, cache.k_pages, cache.v_pages, att, dec_list, n_dec, ctx.positions,
+                                              ctx.seq_of_token, table, *common, scratch, tickets,
+                                              warm=rt.warm_attention(self.w_o, ctx))
+            elif decode_ok:
                 splits = ops.decode_splits(n_dec, self.n_kv, self.head_dim, ctx.max_kv_len)
                 scratch = rt.workspace("attention_decode_partials",
                                        n_dec * self.n_heads * splits * (self.head_dim + 2), torch.float32)

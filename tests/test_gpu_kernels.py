@@ -436,6 +436,45 @@ def test_attention_decode(n_q, n_kv, hd, page, window, n_splits, cluster):
     ops.attention_decode_cluster_merge(True)
 
 
+@pytest.mark.parametrize("n_q,n_kv,hd,page,window", [(32, 8, 64, 16, None), (8, 2, 64, 8, 130), (24, 8, 128, 16, None),
+                                                      (16, 1, 64, 4, None), (6, 2, 128, 32, 77)])
+def test_attention_decode_balanced(n_q, n_kv, hd, page, window):
+    """The kernel that deals the keys of all tokens evenly over a fixed grid: contexts from one key
+    to thousands, so that blocks hold whole tokens, tails, heads, and one token spans many blocks;
+    a far key that must be found; a token list; twice the same result (fixed merge order)."""
+    from nanoinfer_b200.kernels import ops
+    lens = [3000, 1, 33, 257, 64, 65, 700, 2, 128, 1500, 17, 900]
+    spans = [(t - 1, t) for t in lens]
+    far = (0, 5) if window is None else None
+    table, k_pages, v_pages, ks, vs, qs, q, positions, seq_of = _attention_case(lens, spans, n_q, n_kv, hd, page, hd + n_q, far)
+    scale = 1.0 / math.sqrt(hd)
+    n = q.shape[0]
+    scratch = torch.full((ops.attention_decode_balanced_scratch(n_q, n_kv, hd),), float("nan"), dtype=torch.float32, device=DEV)
+    tickets = torch.zeros(n * n_kv, dtype=torch.int32, device=DEV)
+    args = (positions.to(DEV), seq_of.to(DEV), table.to(DEV), n_q, n_kv, hd, page, window, scale, scratch, tickets)
+    out = torch.zeros_like(q).to(DEV)
+    ops.attention_decode_balanced(q.to(DEV), k_pages.to(DEV), v_pages.to(DEV), out, None, n, *args)
+    want = torch.cat([plain.attention(qs[s], ks[s], vs[s], scale, window)[a:b]
+                      for s, (a, b) in enumerate(spans)]).reshape(-1, n_q * hd)
+    torch.testing.assert_close(out.cpu().float(), want, rtol=8e-3, atol=4e-3)
+    assert torch.all(tickets == 0)
+    if far is not None:
+        assert out.cpu().float()[0].mean() > 4.0
+    again = torch.zeros_like(out)
+    ops.attention_decode_balanced(q.to(DEV), k_pages.to(DEV), v_pages.to(DEV), again, None, n, *args)
+    assert torch.equal(again, out)
+    # a token list: those tokens only, in the list's order of work, the others left alone
+    out2 = torch.full_like(out, 9.0)
+    pick = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    ops.attention_decode_balanced(q.to(DEV), k_pages.to(DEV), v_pages.to(DEV), out2, pick, 3, *args)
+    for i in range(n):
+        if i in (6, 0, 3):
+            torch.testing.assert_close(out2[i].float(), out[i].float(), rtol=8e-3, atol=4e-3)   # cut elsewhere: rounding only
+        else:
+            assert torch.all(out2[i] == 9.0)
+    ops.check_device_errors()
+
+
 @pytest.mark.parametrize("n_q,n_kv,hd,page,window", [(4, 2, 16, 16, None), (3, 1, 32, 8, None), (6, 3, 48, 4, 70),
                                                       (32, 8, 64, 16, None), (5, 5, 80, 16, None), (4, 1, 96, 16, 64),
                                                       (2, 2, 112, 8, None), (8, 2, 128, 16, 129)])

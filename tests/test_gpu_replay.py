@@ -126,6 +126,28 @@ def test_wide_decode_batches_match_plain(model_dirs, monkeypatch, key, n_live, d
         assert max(plain_rows.seen) >= n_live
 
 
+@pytest.mark.parametrize("key", ["ds", "e"])
+def test_wide_decode_batches_with_the_balanced_attention(model_dirs, monkeypatch, key):
+    """The same kind of trace with the single-token attention on the kernel that deals all tokens' keys
+    evenly over a fixed grid (the default for wide heads and many tokens; switched on here for these
+    small models): requests of different lengths beside one another, short portions of prompts among
+    the single tokens, pages that come back, steps replayed from graphs."""
+    raw, w = load_plain(model_dirs[key])
+    n_live, tail = 33, 12
+    reqs = _wide_requests(raw, n_live, tail, seed=77)
+    steps = ru.wide(reqs, n_live, tail=tail)
+    balanced_rows = _Spy(monkeypatch, "attention_decode_balanced", lambda *a, **k: a[5])
+    split_rows = _Spy(monkeypatch, "attention_decode", lambda *a, **k: a[5])
+    runner = _runner(model_dirs[key], "bfloat16", 16, steps, max_requests=n_live + 2)
+    runner.rt.balanced_attention_pairs, runner.rt.balanced_attention_narrow_heads = 2, True
+    got = ru.run_trace(runner, steps)
+    assert len(got) == sum(len(t) for t in reqs.values())
+    ru.compare(got, ru.plain_logits(raw, w, reqs), "bfloat16", label=f"balanced/{key}")
+    runner.cache.check_consistency()
+    assert max(balanced_rows.seen) >= n_live and any(n >= n_live for n in runner._graphs)
+    assert all(n * raw["num_key_value_heads"] <= 2 for n in split_rows.seen)     # only the smallest steps took the split kernel
+
+
 @pytest.mark.parametrize("every_projection", [False, True])
 def test_wide_outputs_take_the_swapped_operand_product(model_dirs, monkeypatch, every_projection):
     """A vocabulary wide enough that, at 9 to 128 rows, the output projection goes to the
