@@ -52,6 +52,18 @@ struct GemvParams {
     __nv_bfloat16* k_pages;
     __nv_bfloat16* v_pages;
     int bt_stride, n_q_heads, n_kv_heads, head_dim, rotary_dim, page_size, write_cache;
+    // A norm handed from kernel to kernel (up to 8 rows; template parameter HAND).  Producer (HAND 2,
+    // mode GV_ADD_F32): after out += product it also stores next_x = bf16(out * next_gain) and, per
+    // tile of output columns and row, the sum of out^2 over the tile (next_ssq[tile][8]).  Consumer
+    // (HAND 1; its bfloat16 input is such a next_x): 1/rms of each row from the pre_parts partial
+    // sums, applied to the finished products (a per-row scalar commutes with the product).  Together
+    // they are RMSNorm without a kernel of its own and without the consumer reading the FP32 stream.
+    const float* next_gain;
+    __nv_bfloat16* next_x;
+    float* next_ssq;
+    const float* pre_ssq;
+    int pre_parts;
+    float pre_eps;
     // optional: bytes that kernels after this one read (weights), asked into L2 once this block has
     // issued its own last loads - they fill the gap between this kernel's tail and the next one's start
     const unsigned char* warm;
@@ -116,7 +128,9 @@ __device__ __forceinline__ uint4 load_x8(const void* xrow, const float* gain8, i
 // WARM: the kernel ends with its share of the request for p.warm (a variant of its own: the mere
 // presence of that code after the loop made the gate/up kernel, which runs at its register limit,
 // 6 % slower, whether or not it ran).
-template <int RN, int NT, bool NORM, bool KEEP, int U, bool WARM>
+// HAND: 0, or 1 / 2 for the reader / the writer of a handed-over norm (see GemvParams) - variants of
+// their own for the same reason.
+template <int RN, int NT, bool NORM, bool KEEP, int U, bool WARM, int HAND>
 __global__ void __launch_bounds__(GV_WARPS * 32, (NT == 1 && U <= 4) ? 2 : 1) gemv_bf16_kernel(const GemvParams p, int tiles_per_block, int long_blocks) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -163,6 +177,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32, (NT == 1 && U <= 4) ? 2 : 1) ge
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) ssq[nt] = 0.f;
     bool waited = false;
+    float pre_q = 0.f;      // HAND 1: this lane's share of row `warp`'s partial sums of squares
 
     // This warp's weight fragments of one pass over K (U k-blocks of 64).
     uint4 fa[U][2], fb[U][2];
@@ -210,6 +225,10 @@ __global__ void __launch_bounds__(GV_WARPS * 32, (NT == 1 && U <= 4) ? 2 : 1) ge
                 // everything above reads weights (and the gain) only; what follows depends on the kernel before
                 pdl_wait();
                 waited = true;
+                // a norm prepared by that kernel: this warp's share of its row's partial sums, requested
+                // together with the activations below (its latency hides behind theirs)
+                if (HAND == 1)
+                    for (int i = lane; i < p.pre_parts; i += 32) pre_q += p.pre_ssq[(size_t)i * 8 + warp];
             }
             if (!KEEP || first_tile) {
 #pragma unroll
@@ -245,7 +264,12 @@ __global__ void __launch_bounds__(GV_WARPS * 32, (NT == 1 && U <= 4) ? 2 : 1) ge
                 prefetched = true;
             }
         }
-        if (!waited) { pdl_wait(); waited = true; }   // a warp without work must not run ahead either
+        if (!waited) {                                // a warp without work must not run ahead either
+            pdl_wait();
+            waited = true;
+            if (HAND == 1)
+                for (int i = lane; i < p.pre_parts; i += 32) pre_q += p.pre_ssq[(size_t)i * 8 + warp];
+        }
         // partial sums of the 8 warps -> shared memory -> summed in warp order
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
@@ -270,19 +294,44 @@ __global__ void __launch_bounds__(GV_WARPS * 32, (NT == 1 && U <= 4) ? 2 : 1) ge
             }
             __syncthreads();
         }
+        if (HAND == 1 && first_tile) {
+            // warp w holds row w's partial sums (lanes took them in turn): a fixed shuffle tree adds them up
+            float q = pre_q;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) q += __shfl_xor_sync(0xffffffffu, q, off);
+            if (lane == 0) inv_rms[warp] = 1.0f / sqrtf(q / (float)K + p.pre_eps);
+            __syncthreads();
+        }
         for (int idx = threadIdx.x; idx < NT * 8 * RN; idx += blockDim.x) {
             const int row = idx % RN;                  // weight row within the tile
             const int m = idx / RN;                    // batch row
             float s = 0.f;
 #pragma unroll
             for (int wi = 0; wi < GV_WARPS; ++wi) s += red[wi][m >> 3][row][m & 7];
-            if (NORM) s *= inv_rms[m];
+            if (NORM || HAND == 1) s *= inv_rms[m];
             tile[m][row] = s;
         }
         __syncthreads();
 
         const int mode = p.mode;
-        if (mode <= GV_ADD_F32) {
+        if (HAND == 2) {
+            // the addition, and with it what the next norm needs (see GemvParams); whole warps take part
+            for (int idx = threadIdx.x; idx < 8 * RN; idx += blockDim.x) {
+                const int row = idx % RN, m = idx / RN, n = n0 + row;
+                const bool ok = m < M && n < N;
+                float v = 0.f;
+                if (ok) {
+                    const size_t o = (size_t)m * N + n;
+                    v = reinterpret_cast<float*>(p.out)[o] + tile[m][row];
+                    reinterpret_cast<float*>(p.out)[o] = v;
+                    p.next_x[o] = __float2bfloat16_rn(v * p.next_gain[n]);
+                }
+                float sq = v * v;
+#pragma unroll
+                for (int off = RN / 2; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
+                if (row == 0) p.next_ssq[(size_t)(n0 / RN) * 8 + m] = sq;
+            }
+        } else if (mode <= GV_ADD_F32) {
             for (int idx = threadIdx.x; idx < NT * 8 * RN; idx += blockDim.x) {
                 const int row = idx % RN, m = idx / RN, n = n0 + row;
                 if (m >= M || n >= N) continue;
@@ -335,7 +384,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32, (NT == 1 && U <= 4) ? 2 : 1) ge
     if (WARM && warp == GV_WARPS - 1) gv_warm(p);
 }
 
-template <int RN, int NT, bool NORM, bool KEEP, int U, bool WARM>
+template <int RN, int NT, bool NORM, bool KEEP, int U, bool WARM, int HAND>
 static int launch_gemv_w(const GemvParams& p, int tiles_per_block, cudaStream_t stream) {
     const int tiles = (p.N + RN - 1) / RN;
     // as many blocks as fit the GPU at once (the dispatcher sized tiles_per_block for that), the
@@ -358,16 +407,32 @@ static int launch_gemv_w(const GemvParams& p, int tiles_per_block, cudaStream_t 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_bf16_kernel<RN, NT, NORM, KEEP, U, WARM>, p, tiles_per_block, long_blocks);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_bf16_kernel<RN, NT, NORM, KEEP, U, WARM, HAND>, p, tiles_per_block, long_blocks);
     return e == cudaSuccess ? NI_OK : (int)e;
 }
 
+// True for the template instances that exist with HAND != 0: up to 8 rows of bfloat16 activations kept
+// in registers; the reader with 16-row tiles (gate/up, fused QKV), the writer with K <= 2,048 (longer
+// contractions add through gemv_ksplit.cu).
+template <int RN, int NT, bool NORM, bool KEEP, int U> constexpr bool gv_reads_handoff() { return NT == 1 && !NORM && KEEP && RN == 16; }
+template <int RN, int NT, bool NORM, bool KEEP, int U> constexpr bool gv_writes_handoff() { return NT == 1 && !NORM && KEEP && U == 4; }
+
 template <int RN, int NT, bool NORM, bool KEEP, int U>
 static int launch_gemv(const GemvParams& p, int tiles_per_block, cudaStream_t stream) {
+    if (p.pre_ssq) {
+        if (!gv_reads_handoff<RN, NT, NORM, KEEP, U>()) return NI_ERR_UNSUPPORTED_SIZE;
+        return launch_gemv_w<RN, NT, NORM, KEEP, U, false, gv_reads_handoff<RN, NT, NORM, KEEP, U>() ? 1 : 0>(p, tiles_per_block, stream);
+    }
+    if (p.next_gain) {
+        if (!gv_writes_handoff<RN, NT, NORM, KEEP, U>() || p.mode != GV_ADD_F32) return NI_ERR_UNSUPPORTED_SIZE;
+        constexpr int H = gv_writes_handoff<RN, NT, NORM, KEEP, U>() ? 2 : 0;
+        if (p.warm_bytes) return launch_gemv_w<RN, NT, NORM, KEEP, U, H == 2, H>(p, tiles_per_block, stream);
+        return launch_gemv_w<RN, NT, NORM, KEEP, U, false, H>(p, tiles_per_block, stream);
+    }
     // the variant that asks for p.warm exists for up to 8 rows of bfloat16 activations (what the
     // engine's hints go to: a mixer's output projection, a down projection); elsewhere the hint is dropped
-    if (NT == 1 && !NORM && p.warm_bytes) return launch_gemv_w<RN, NT, NORM, KEEP, U, NT == 1 && !NORM>(p, tiles_per_block, stream);
-    return launch_gemv_w<RN, NT, NORM, KEEP, U, false>(p, tiles_per_block, stream);
+    if (NT == 1 && !NORM && p.warm_bytes) return launch_gemv_w<RN, NT, NORM, KEEP, U, NT == 1 && !NORM, 0>(p, tiles_per_block, stream);
+    return launch_gemv_w<RN, NT, NORM, KEEP, U, false, 0>(p, tiles_per_block, stream);
 }
 
 static int dispatch_gemv(const GemvParams& p, bool norm, cudaStream_t stream) {
@@ -425,10 +490,28 @@ static bool gv_warm_ok(const void* warm, long long bytes) {
     return bytes >= 0 && !(bytes & 15) && (bytes == 0 || (warm && !((uintptr_t)warm & 15)));
 }
 
+// Row tiles of ni_gemv_bf16's output (= partial sums per row that the writer of a handed-over norm stores).
+NI_EXPORT int ni_gemv_bf16_out_tiles(int N, int mode) {
+    const bool rn16 = mode >= GV_SWIGLU || (N + 15) / 16 >= 2 * ni_sm_count();
+    return rn16 ? (N + 15) / 16 : (N + 7) / 8;
+}
+// 1 if ni_gemv_bf16 can write a handed-over norm while adding [M, N] (inner size K) / read one on an input of width K.
+NI_EXPORT int ni_gemv_bf16_writes_handoff(int M, int N, int K) { return M >= 1 && M <= 8 && N >= 1 && K >= 8 && K % 8 == 0 && K <= 64 * GV_WARPS * 4; }
+NI_EXPORT int ni_gemv_bf16_reads_handoff(int M, int K) { return M >= 1 && M <= 8 && K >= 8 && K % 8 == 0 && K <= 64 * GV_WARPS * 8; }
+
+// next_gain / next_x / next_ssq: with mode 2, also prepare the norm that follows (see GemvParams);
+// pre_ssq / pre_parts / pre_eps: x is such a prepared input.  Null pointers switch either off; sizes for
+// which the variant does not exist are refused (-2).
 NI_EXPORT int ni_gemv_bf16(const void* x, const void* w, void* out, int M, int N, int K, int mode,
-                           const void* warm, long long warm_bytes, cudaStream_t stream) {
+                           const void* warm, long long warm_bytes, const float* next_gain, void* next_x,
+                           float* next_ssq, const float* pre_ssq, int pre_parts, float pre_eps, cudaStream_t stream) {
     if (mode == GV_ROPE_KV || !gv_warm_ok(warm, warm_bytes)) return NI_ERR_BAD_ARGUMENT;
+    if (next_gain && (mode != GV_ADD_F32 || !next_x || !next_ssq || pre_ssq)) return NI_ERR_BAD_ARGUMENT;
+    if (pre_ssq && pre_parts <= 0) return NI_ERR_BAD_ARGUMENT;
+    if (pre_ssq && mode != GV_SWIGLU && (N + 15) / 16 < 2 * ni_sm_count()) return NI_ERR_UNSUPPORTED_SIZE;   // (the reader has 16-row tiles)
     GemvParams p = {};
+    p.next_gain = next_gain; p.next_x = (__nv_bfloat16*)next_x; p.next_ssq = next_ssq;
+    p.pre_ssq = pre_ssq; p.pre_parts = pre_parts; p.pre_eps = pre_eps;
     p.warm = (const unsigned char*)warm; p.warm_bytes = (unsigned long long)warm_bytes;
     p.x = x; p.w = (const __nv_bfloat16*)w; p.out = out; p.M = M; p.N = N; p.K = K; p.mode = mode;
     return dispatch_gemv(p, false, stream);
@@ -454,9 +537,12 @@ NI_EXPORT int ni_gemv_qkv_rope(const void* x, const float* gain, float eps, cons
                                void* k_pages, void* v_pages, const int* positions, const int* seq_of_token,
                                const int* block_table, int bt_stride, const float* inv_freq, int M, int K,
                                int n_q_heads, int n_kv_heads, int head_dim, int rotary_dim, int page_size,
-                               int write_cache, const void* warm, long long warm_bytes, cudaStream_t stream) {
+                               int write_cache, const void* warm, long long warm_bytes, const float* pre_ssq,
+                               int pre_parts, float pre_eps, cudaStream_t stream) {
     if (!gv_warm_ok(warm, warm_bytes)) return NI_ERR_BAD_ARGUMENT;
+    if (pre_ssq && (gain != nullptr || pre_parts <= 0)) return NI_ERR_BAD_ARGUMENT;
     GemvParams p = {};
+    p.pre_ssq = pre_ssq; p.pre_parts = pre_parts; p.pre_eps = pre_eps;
     p.warm = (const unsigned char*)warm; p.warm_bytes = (unsigned long long)warm_bytes;
     p.x = x; p.gain = gain; p.eps = eps; p.w = (const __nv_bfloat16*)w; p.out = q_out;
     p.M = M; p.N = (n_q_heads + 2 * n_kv_heads) * head_dim; p.K = K; p.mode = GV_ROPE_KV;

@@ -43,6 +43,11 @@ struct KsParams {
     int splits, slice_blocks, tiles_per_cluster;
     const unsigned char* warm;
     unsigned long long warm_bytes;
+    // with mode KS_ADD_F32: also prepare the norm that follows - next_x = bf16(out * next_gain) and per row
+    // tile and row the sum of out^2 (next_ssq[tile][8]); see gemv_bf16.cu
+    const float* next_gain;
+    __nv_bfloat16* next_x;
+    float* next_ssq;
 };
 
 __device__ __forceinline__ void ks_mma(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -79,7 +84,8 @@ __device__ __forceinline__ void ks_st_cluster(uint32_t addr, float v) {
 
 // RN: weight rows per tile (8 or 16).  WARM: the kernel ends with its share of the request to bring
 // p.warm into L2 (see gemv_bf16.cu).
-template <int RN, bool WARM>
+// NEXT: the adding epilogue also prepares the norm that follows (KsParams::next_*).
+template <int RN, bool WARM, bool NEXT>
 __global__ void __launch_bounds__(KS_WARPS * 32, 2) gemv_ksplit_kernel(const KsParams p) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -181,6 +187,27 @@ __global__ void __launch_bounds__(KS_WARPS * 32, 2) gemv_ksplit_kernel(const KsP
 
     // the first block adds the slices in slice order and writes the result
     const int mode = p.mode;
+    if (NEXT) {
+        // ... and what the next norm needs; whole warps take part (a tile's 8 * RN sums are a multiple of 64 threads)
+        for (int idx = threadIdx.x; idx < tpc * 8 * RN; idx += blockDim.x) {
+            const int ti = idx / (8 * RN), e = idx - ti * (8 * RN);
+            const int row = e % RN, m = e / RN, n = (tile0 + ti) * RN + row;
+            float s = 0.f;
+            for (int r = 0; r < splits; ++r) s += slots[((size_t)r * tpc + ti) * (8 * RN) + e];
+            float v = 0.f;
+            if (m < M && n < N) {
+                const size_t o = (size_t)m * N + n;
+                v = reinterpret_cast<float*>(p.out)[o] + s;
+                reinterpret_cast<float*>(p.out)[o] = v;
+                p.next_x[o] = __float2bfloat16_rn(v * p.next_gain[n]);
+            }
+            float sq = v * v;
+#pragma unroll
+            for (int off = RN / 2; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
+            if (row == 0 && tile0 + ti < n_tiles) p.next_ssq[(size_t)(tile0 + ti) * 8 + m] = sq;
+        }
+        return;
+    }
     for (int idx = threadIdx.x; idx < tpc * 8 * RN; idx += blockDim.x) {
         const int ti = idx / (8 * RN), e = idx - ti * (8 * RN);
         const int row = e % RN, m = e / RN, n = (tile0 + ti) * RN + row;
@@ -221,7 +248,7 @@ static bool ks_plan(int N, int K, KsPlan* plan) {
     return plan->smem <= KS_MAX_SLOT_FLOATS * sizeof(float);
 }
 
-template <int RN, bool WARM>
+template <int RN, bool WARM, bool NEXT>
 static int launch_ksplit(const KsParams& p, const KsPlan& plan, cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(plan.clusters * plan.splits);
@@ -237,7 +264,7 @@ static int launch_ksplit(const KsParams& p, const KsPlan& plan, cudaStream_t str
     attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_ksplit_kernel<RN, WARM>, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_ksplit_kernel<RN, WARM, NEXT>, p);
     return e == cudaSuccess ? NI_OK : (int)e;
 }
 
@@ -248,12 +275,22 @@ NI_EXPORT int ni_gemv_ksplit_supports(int M, int N, int K) {
     return M >= 1 && M <= 8 && N >= 1 && K >= 8 && K % 8 == 0 && ks_plan(N, K, &plan) ? 1 : 0;
 }
 
+// Row tiles of the output for these sizes (= partial sums per row of a handed-over norm), 0 if unsupported.
+NI_EXPORT int ni_gemv_ksplit_out_tiles(int N, int K) {
+    KsPlan plan;
+    if (N < 1 || K < 8 || K % 8 || !ks_plan(N, K, &plan)) return 0;
+    return (N + plan.rn - 1) / plan.rn;
+}
+
 // x bf16 [M, K], w bf16 [N, K].  mode: 0 store bf16 [M, N], 1 store FP32, 2 add into FP32.
 // warm / warm_bytes: optional stretch of memory that the kernel asks into L2 on its way out.
+// next_gain / next_x / next_ssq: with mode 2, also prepare the norm that follows (null: off).
 NI_EXPORT int ni_gemv_ksplit(const void* x, const void* w, void* out, int M, int N, int K, int mode,
-                             const void* warm, long long warm_bytes, cudaStream_t stream) {
+                             const void* warm, long long warm_bytes, const float* next_gain, void* next_x,
+                             float* next_ssq, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return NI_OK;
     if (mode < KS_STORE_BF16 || mode > KS_ADD_F32) return NI_ERR_BAD_ARGUMENT;
+    if (next_gain && (mode != KS_ADD_F32 || !next_x || !next_ssq)) return NI_ERR_BAD_ARGUMENT;
     if (warm_bytes < 0 || (warm_bytes & 15) || (warm_bytes && (!warm || ((uintptr_t)warm & 15)))) return NI_ERR_BAD_ARGUMENT;
     KsPlan plan;
     if (M > 8 || K <= 0 || K % 8 || !ks_plan(N, K, &plan)) return NI_ERR_UNSUPPORTED_SIZE;
@@ -262,10 +299,17 @@ NI_EXPORT int ni_gemv_ksplit(const void* x, const void* w, void* out, int M, int
     p.M = M; p.N = N; p.K = K; p.mode = mode;
     p.splits = plan.splits; p.slice_blocks = plan.slice_blocks; p.tiles_per_cluster = plan.tiles_per_cluster;
     p.warm = (const unsigned char*)warm; p.warm_bytes = (unsigned long long)warm_bytes;
-    if (plan.rn == 16) {
-        if (warm_bytes) return launch_ksplit<16, true>(p, plan, stream);
-        return launch_ksplit<16, false>(p, plan, stream);
-    }
-    if (warm_bytes) return launch_ksplit<8, true>(p, plan, stream);
-    return launch_ksplit<8, false>(p, plan, stream);
+    p.next_gain = next_gain; p.next_x = (__nv_bfloat16*)next_x; p.next_ssq = next_ssq;
+#define KS_GO(RN)                                                                       \
+    do {                                                                                \
+        if (next_gain) {                                                                \
+            if (warm_bytes) return launch_ksplit<RN, true, true>(p, plan, stream);      \
+            return launch_ksplit<RN, false, true>(p, plan, stream);                     \
+        }                                                                               \
+        if (warm_bytes) return launch_ksplit<RN, true, false>(p, plan, stream);         \
+        return launch_ksplit<RN, false, false>(p, plan, stream);                        \
+    } while (0)
+    if (plan.rn == 16) KS_GO(16);
+    KS_GO(8);
+#undef KS_GO
 }

@@ -42,6 +42,10 @@ class DecoderModel:
         order = [tuple(getattr(self.blocks[run.layer], "weights_in_order", tuple)()) for run in config.schedule]
         order.append(tuple(self.head.weights_in_order()))
         self._read_after = [order[r + 1] for r in range(len(config.schedule))]
+        # per scheduled run: the norm that reads the stream after it, if it can come prepared (see
+        # NormHandoff); the head keeps its own fused norm, so the last run hands nothing over
+        firsts = [getattr(self.blocks[run.layer], "first_norm", lambda: None)() for run in config.schedule]
+        self._norm_after = firsts[1:] + [None]
         self._fused = False      # the fused decode step: not looked at yet / None (does not apply) / the object
 
     def cache_needs(self) -> List[Optional[object]]:
@@ -69,7 +73,7 @@ class DecoderModel:
         self.embedding.forward(ctx.tokens, h)
         delta = None
         for r, run in enumerate(cfg.schedule):
-            ctx.read_after = self._read_after[r]
+            ctx.read_after, ctx.norm_after = self._read_after[r], self._norm_after[r]
             delta = self.blocks[run.layer].forward(h, delta, ctx, caches[r])
-        ctx.read_after = ()
+        ctx.read_after, ctx.norm_after = (), None
         return self.head.forward(h, delta, self.final_norm, ctx)

@@ -80,6 +80,8 @@ class StepContext:
     read_after: the weight matrices that will be read after the part that is running, in order
     (set by the model and the arrangement as they go); a part whose kernels leave the memory system
     room may ask the head of them into L2 (``Runtime.warm``).
+    norm_after: the norm part that reads the residual stream after the running block, if it can come
+    prepared by the kernel that last adds into the stream (``ops.NormHandoff``); else None.
     """
     n_tokens: int
     n_seqs: int
@@ -100,6 +102,7 @@ class StepContext:
     decode_only: bool = False
     plans: Dict[type, DevicePlan] = field(default_factory=dict)
     read_after: tuple = ()
+    norm_after: object = None
 
     def plan_of(self, part) -> DevicePlan:
         owner = plan_owner(type(part))

@@ -40,12 +40,16 @@ _SIGNATURES = {
         "ni_gemm_f32": [_P, _P, _P, _I, _I, _I, _P],
     },
     "gemv_bf16": {
-        "ni_gemv_bf16": [_P, _P, _P, _I, _I, _I, _I, _P, _LL, _P],
+        "ni_gemv_bf16": [_P, _P, _P, _I, _I, _I, _I, _P, _LL, _P, _P, _P, _P, _I, _F, _P],
+        "ni_gemv_bf16_out_tiles": [_I, _I],
+        "ni_gemv_bf16_writes_handoff": [_I, _I, _I],
+        "ni_gemv_bf16_reads_handoff": [_I, _I],
         "ni_gemv_norm_bf16": [_P, _P, _F, _P, _P, _P, _I, _I, _I, _I, _P, _LL, _P],
-        "ni_gemv_qkv_rope": [_P, _P, _F, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _LL, _P],
+        "ni_gemv_qkv_rope": [_P, _P, _F, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _LL, _P, _I, _F, _P],
     },
     "gemv_ksplit": {
-        "ni_gemv_ksplit": [_P, _P, _P, _I, _I, _I, _I, _P, _LL, _P],
+        "ni_gemv_ksplit": [_P, _P, _P, _I, _I, _I, _I, _P, _LL, _P, _P, _P, _P],
+        "ni_gemv_ksplit_out_tiles": [_I, _I],
         "ni_gemv_ksplit_supports": [_I, _I, _I],
     },
     "attention_decode": {
@@ -359,16 +363,65 @@ def warm_region(warm) -> tuple:
     return t.data_ptr() + first, nbytes
 
 
-def gemv_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, warm=None) -> None:
+HANDOFF_ROWS = 8      # rows up to which a norm can be handed from the kernel that adds into the stream to its reader
+
+
+class NormHandoff:
+    """A norm prepared by the kernel that last added into the residual stream, for the kernel that
+    reads it (up to HANDOFF_ROWS rows): ``x`` = bfloat16(h * gain) [M, d], ``ssq`` float32
+    [tiles, 8] = per tile of columns and row the sum of h^2, ``eps``.  The reader multiplies its
+    finished products by 1 / sqrt(sum(ssq) / d + eps) per row: together RMSNorm(h) * gain without a
+    kernel of its own.  ``norm`` is the part it stands for."""
+
+    def __init__(self, norm, gain: torch.Tensor, eps: float, rows: int, width: int, tiles: int, device) -> None:
+        self.norm, self.gain, self.eps, self.tiles = norm, gain, float(eps), int(tiles)
+        self.x = torch.empty(rows, width, dtype=torch.bfloat16, device=device)
+        self.ssq = torch.empty(tiles, 8, dtype=torch.float32, device=device)
+
+    def producer_args(self):
+        return _dev(self.gain, "gain", torch.float32), self.x.data_ptr(), self.ssq.data_ptr()
+
+    def reader_args(self):
+        return self.ssq.data_ptr(), self.tiles, self.eps
+
+
+_NO_HANDOFF = (None, None, None)
+_NO_PRE = (None, 0, 0.0)
+
+
+def gemv_out_tiles(m: int, n: int, k: int) -> int:
+    """How many tiles of output columns the skinny product that adds [m, n] into the stream works in
+    (the partial sums per row of a NormHandoff) - of whichever kernel linear_bf16 picks - or 0 if that
+    kernel cannot prepare a norm for these sizes."""
+    if m <= KSPLIT_ROWS and KSPLIT_MIN_K <= k <= KSPLIT_MAX_K and gemv_ksplit_supports(m, n, k):
+        return int(load("gemv_ksplit").ni_gemv_ksplit_out_tiles(n, k))
+    lib = load("gemv_bf16")
+    return int(lib.ni_gemv_bf16_out_tiles(n, ADD_F32)) if lib.ni_gemv_bf16_writes_handoff(m, n, k) else 0
+
+
+def gemv_reads_handoff(m: int, k: int) -> bool:
+    """True if the skinny products can take a prepared norm on an input of m rows and width k."""
+    return bool(load("gemv_bf16").ni_gemv_bf16_reads_handoff(m, k))
+
+
+def gemv_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, warm=None,
+              handoff: Optional["NormHandoff"] = None, pre: Optional["NormHandoff"] = None) -> None:
     """x[M, K] . w[N, K]^T for M <= 16, K % 8 == 0.  mode STORE_BF16 / STORE_F32: out[M, N] =;
     ADD_F32: out[M, N] +=; SWIGLU_BF16: w's rows in blocks of 8 gate + 8 up rows,
     out[M, N/2] = silu(gate) * up.  ``warm`` (tensor, first byte, bytes): weights of the kernels
-    after this one, asked into L2 when this kernel's own loads have been issued."""
+    after this one, asked into L2 when this kernel's own loads have been issued.  ``handoff`` (with
+    ADD_F32, up to 8 rows): also prepare the norm that follows; ``pre``: x is such a prepared input."""
+    if (handoff is not None or pre is not None) and x.shape[0] > HANDOFF_ROWS:
+        raise KernelError("gemv_bf16: a norm is handed over for at most 8 rows")
+    if handoff is not None and (mode != ADD_F32 or handoff.x.shape != out.shape or handoff.tiles != int(load("gemv_bf16").ni_gemv_bf16_out_tiles(w.shape[0], ADD_F32))):
+        raise KernelError("gemv_bf16: the handoff does not fit this product")
     m, k = x.shape
     n = w.shape[0]
     _gemv_check(m, n, k, w, out, mode, "gemv_bf16")
     _check(load("gemv_bf16").ni_gemv_bf16(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16),
-                                          _dev(out, "out"), m, n, k, mode, *warm_region(warm), _stream()), "gemv_bf16")
+                                          _dev(out, "out"), m, n, k, mode, *warm_region(warm),
+                                          *(handoff.producer_args() if handoff is not None else _NO_HANDOFF),
+                                          *(pre.reader_args() if pre is not None else _NO_PRE), _stream()), "gemv_bf16")
 
 
 KSPLIT_ROWS = 8          # rows the cluster split-K skinny product takes
@@ -383,7 +436,8 @@ def gemv_ksplit_supports(m: int, n: int, k: int) -> bool:
     return bool(load("gemv_ksplit").ni_gemv_ksplit_supports(m, n, k))
 
 
-def gemv_ksplit(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, warm=None) -> None:
+def gemv_ksplit(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, warm=None,
+                handoff: Optional["NormHandoff"] = None, pre=None) -> None:
     """x[M, K] . w[N, K]^T for M <= 8 and a long K, split over the blocks of a cluster (each keeps
     its slice of the activations in registers; the slices' sums are added in slice order).
     mode STORE_BF16 / STORE_F32 / ADD_F32 as gemv_bf16."""
@@ -394,8 +448,15 @@ def gemv_ksplit(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, 
     _gemv_check(m, n, k, w, out, mode, "gemv_ksplit")
     if not gemv_ksplit_supports(m, n, k):
         raise KernelError(f"gemv_ksplit: M={m}, N={n}, K={k} is not supported (up to 8 rows, K in 2 to 8 slices of 2,048)")
+    if pre is not None:
+        raise KernelError("gemv_ksplit: takes no prepared norm on its input")
+    if handoff is not None and (mode != ADD_F32 or handoff.x.shape != out.shape
+                                or handoff.tiles != int(load("gemv_ksplit").ni_gemv_ksplit_out_tiles(n, k))):
+        raise KernelError("gemv_ksplit: the handoff does not fit this product")
     _check(load("gemv_ksplit").ni_gemv_ksplit(_dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16),
-                                              _dev(out, "out"), m, n, k, mode, *warm_region(warm), _stream()), "gemv_ksplit")
+                                              _dev(out, "out"), m, n, k, mode, *warm_region(warm),
+                                              *(handoff.producer_args() if handoff is not None else _NO_HANDOFF),
+                                              _stream()), "gemv_ksplit")
 
 
 def gemv_norm_bf16(h: torch.Tensor, gain: torch.Tensor, eps: float, rows: Optional[torch.Tensor],
@@ -419,7 +480,7 @@ def gemv_qkv_rope(x: torch.Tensor, gain: Optional[torch.Tensor], eps: float, w: 
                   q_out: torch.Tensor, k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
                   positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
                   inv_freq: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int,
-                  page_size: int, warm=None) -> None:
+                  page_size: int, warm=None, pre: Optional["NormHandoff"] = None) -> None:
     """Fused QKV projection of at most 16 single tokens: optional RMSNorm in front (x float32
     residual stream and ``gain`` given) or bfloat16 activations (gain None); rotary encoding of
     adjacent pairs and the paged K/V write behind.  q -> q_out bf16 [M, Hq hd]."""
@@ -441,11 +502,12 @@ def gemv_qkv_rope(x: torch.Tensor, gain: Optional[torch.Tensor], eps: float, w: 
         _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
         _dev(block_table, "block_table", torch.int32), block_table.shape[1],
         _dev(inv_freq, "inv_freq", torch.float32), m, k, n_q_heads, n_kv_heads, head_dim, rotary_dim,
-        page_size, 1 if write else 0, *warm_region(warm), _stream()), "gemv_qkv_rope")
+        page_size, 1 if write else 0, *warm_region(warm), *(pre.reader_args() if pre is not None else _NO_PRE),
+        _stream()), "gemv_qkv_rope")
 
 
 def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
-                residual: Optional[torch.Tensor] = None, warm=None) -> Optional[torch.Tensor]:
+                residual: Optional[torch.Tensor] = None, warm=None, handoff: Optional["NormHandoff"] = None) -> Optional[torch.Tensor]:
     """y = x . w^T for bfloat16 operands with FP32 accumulation.
 
     Up to SKINNY_ROWS rows (decode): the package's own bandwidth kernel; with ``residual`` (float32
@@ -463,11 +525,13 @@ def linear_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype,
         product = gemv_ksplit if (m <= KSPLIT_ROWS and KSPLIT_MIN_K <= k <= KSPLIT_MAX_K
                                   and gemv_ksplit_supports(m, w.shape[0], k)) else gemv_bf16
         if residual is not None:
-            product(x, w, residual, ADD_F32, warm)
+            product(x, w, residual, ADD_F32, warm, handoff=handoff)
             return None
         out = torch.empty(m, w.shape[0], dtype=out_dtype, device=x.device)
         product(x, w, out, STORE_BF16 if out_dtype == torch.bfloat16 else STORE_F32, warm)
         return out
+    if handoff is not None:
+        raise KernelError("linear_bf16: a norm can only be handed over by the skinny product (up to 8 rows)")
     if out_dtype == torch.bfloat16:
         return torch.matmul(x, w.t())
     return torch.mm(x, w.t(), out_dtype=torch.float32)

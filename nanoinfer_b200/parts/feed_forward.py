@@ -42,8 +42,9 @@ class SwiGLU(Part):
         return (self.w_gate_up, self.w_down)
 
     def can_fuse_norm(self, norm, n_rows: int) -> bool:
-        return (self.blocked and self.rt.skinny(n_rows, self.hidden_size) and hasattr(norm, "gain")
-                and hasattr(norm, "eps"))
+        return self.blocked and self.rt.skinny(n_rows, self.hidden_size) and self.rt.fuses_norm(norm)
+
+    hands_off_norm = True       # forward_fused_norm / forward_prenormed accept then_norm= and may return its NormHandoff
 
     def forward(self, x: torch.Tensor, ctx, residual=None):
         rt = self.rt
@@ -64,13 +65,28 @@ class SwiGLU(Part):
             return None
         return rt.linear(act, self.w_down, residual=residual, warm=rt.warm_after(ctx, which=4))
 
-    def forward_fused_norm(self, h: torch.Tensor, norm, ctx, residual=None):
-        """As forward, with x = norm(h): norm, projection and activation in one launch."""
+    def forward_fused_norm(self, h: torch.Tensor, norm, ctx, residual=None, then_norm=None):
+        """As forward, with x = norm(h): norm, projection and activation in one launch.  ``then_norm``:
+        the norm that reads the stream next; where the down projection can prepare it, its
+        NormHandoff is returned instead of None."""
         rt = self.rt
         act = rt.empty(h.shape[0], self.inter)
         ops.gemv_norm_bf16(h, norm.gain, norm.eps, None, self.w_gate_up, act, ops.SWIGLU_BF16,
                            warm=rt.warm(self.w_down, 0, which=2))
-        return rt.linear(act, self.w_down, residual=residual, warm=rt.warm_after(ctx, which=4))
+        return self._down(act, ctx, residual, then_norm)
+
+    def forward_prenormed(self, pre, ctx, residual=None, then_norm=None):
+        """As forward_fused_norm, with the norm prepared by the kernel that last added into the stream."""
+        rt = self.rt
+        act = rt.empty(pre.x.shape[0], self.inter)
+        ops.gemv_bf16(pre.x, self.w_gate_up, act, ops.SWIGLU_BF16, warm=rt.warm(self.w_down, 0, which=2), pre=pre)
+        return self._down(act, ctx, residual, then_norm)
+
+    def _down(self, act, ctx, residual, then_norm):
+        rt = self.rt
+        handoff = rt.handoff(then_norm, act.shape[0], self.hidden_size, self.inter) if residual is not None else None
+        out = rt.linear(act, self.w_down, residual=residual, warm=rt.warm_after(ctx, which=4), handoff=handoff)
+        return handoff if handoff is not None else out
 
 
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)

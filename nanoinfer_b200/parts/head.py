@@ -34,8 +34,7 @@ class LinearHead(Part):
         rt = self.rt
         if ctx.n_logit_rows == 0:
             return rt.empty(0, self.vocab_size, dtype=torch.float32)
-        if (delta is None and rt.skinny(ctx.n_logit_rows, self.hidden_size) and hasattr(norm, "gain")
-                and hasattr(norm, "eps")):
+        if delta is None and rt.skinny(ctx.n_logit_rows, self.hidden_size) and rt.fuses_norm(norm):
             # few rows: final norm, row selection and output projection in one launch
             logits = rt.empty(ctx.n_logit_rows, self.vocab_size, dtype=torch.float32)
             ops.gemv_norm_bf16(h, norm.gain, norm.eps, ctx.logit_rows, self.weight, logits, ops.STORE_F32)

@@ -98,16 +98,24 @@ class PagedAttention(Part):
 
     def can_fuse_norm(self, norm, n_rows: int) -> bool:
         """True if forward_fused_norm can take the residual stream itself (few rows, bfloat16)."""
-        return self.rt.skinny(n_rows, self.hidden_size) and hasattr(norm, "gain") and hasattr(norm, "eps")
+        return self.rt.skinny(n_rows, self.hidden_size) and self.rt.fuses_norm(norm)
+
+    hands_off_norm = True       # forward_fused_norm / forward_prenormed accept then_norm= and may return its NormHandoff
 
     def forward(self, x: torch.Tensor, ctx, cache, residual=None):
         return self._forward(x, None, 0.0, ctx, cache, residual)
 
-    def forward_fused_norm(self, h: torch.Tensor, norm, ctx, cache, residual=None):
-        """As forward, with x = norm(h): the norm runs inside the projection kernel."""
-        return self._forward(h, norm.gain, norm.eps, ctx, cache, residual)
+    def forward_fused_norm(self, h: torch.Tensor, norm, ctx, cache, residual=None, then_norm=None):
+        """As forward, with x = norm(h): the norm runs inside the projection kernel.  ``then_norm``:
+        the norm that reads the stream next; where the output projection can prepare it, its
+        NormHandoff is returned instead of None."""
+        return self._forward(h, norm.gain, norm.eps, ctx, cache, residual, then_norm=then_norm)
 
-    def _forward(self, x, gain, eps, ctx, cache, residual):
+    def forward_prenormed(self, pre, ctx, cache, residual=None, then_norm=None):
+        """As forward_fused_norm, with the norm prepared by the kernel that last added into the stream."""
+        return self._forward(pre.x, None, 0.0, ctx, cache, residual, then_norm=then_norm, pre=pre)
+
+    def _forward(self, x, gain, eps, ctx, cache, residual, then_norm=None, pre=None):
         rt = self.rt
         n = x.shape[0]
         table = ctx.block_tables[cache.group]
@@ -119,7 +127,7 @@ class PagedAttention(Part):
             # decode: projection, rotation and cache write in one launch
             ops.gemv_qkv_rope(x, gain, eps, self.w_qkv, q, k_pages, v_pages, ctx.positions, ctx.seq_of_token,
                               table, pos.inv_freq, self.n_heads, self.n_kv, self.head_dim, pos.rotary_dim,
-                              rt.page_size)
+                              rt.page_size, pre=pre)
         elif rt.mid_batch(n, self.hidden_size, rt.MID_QKV) and self.head_dim % 2 == 0:
             # a middle batch: projection on the tensor cores with the weights on the tile's lanes,
             # rotation and cache write in its epilogue
@@ -136,7 +144,10 @@ class PagedAttention(Part):
             ops.gemm_swap_tc(att, self.w_o, residual, ops.ADD_F32)       # added into the residual stream in the epilogue
             return None
         # the attention kernel asked for the head of the next matrix; this one goes on from there
-        return rt.linear(att, self.w_o, residual=residual, warm=rt.warm_after(ctx, skip=rt.attention_share(ctx), which=1) if ctx.decode_only else None)
+        handoff = rt.handoff(then_norm, n, self.hidden_size, self.n_heads * self.head_dim) if residual is not None else None
+        out = rt.linear(att, self.w_o, residual=residual, handoff=handoff,
+                        warm=rt.warm_after(ctx, skip=rt.attention_share(ctx), which=1) if ctx.decode_only else None)
+        return handoff if handoff is not None else out
 
     def _attend(self, q, cache, att, ctx, table) -> None:
         """Attention of every token of the step over its own request's pages.

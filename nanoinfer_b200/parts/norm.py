@@ -14,6 +14,10 @@ class RMSNorm(Part):
     """y = x * rsqrt(mean(x^2) + eps) * gain, statistics in FP32
     (src/op/kernels/cuda/rmsnorm_kernel.cu:49-104; eps inside the root, :79)."""
 
+    # What a kernel that runs this norm inside itself computes (with ``gain`` and ``eps``): the
+    # skinny products fuse norms of this kind only.
+    fused_kind = "rmsnorm"
+
     @staticmethod
     def weight_slots(spec, hidden_size: int) -> Dict[str, WeightSlot]:
         return {"weight": WeightSlot((hidden_size,), init="ones")}

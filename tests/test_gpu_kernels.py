@@ -327,6 +327,76 @@ def test_gemv_k_split_refuses_what_it_cannot_take():
         torch.testing.assert_close(out.cpu().double(), x.cpu().double() @ w.cpu().double().t(), rtol=1e-5, atol=1e-3)
 
 
+@pytest.mark.parametrize("m,d,k_in", [(8, 2048, 8192), (3, 264, 2048), (1, 2048, 2048), (5, 520, 4104), (8, 3072, 3072)])
+def test_a_norm_handed_from_the_adding_product_to_its_reader(m, d, k_in):
+    """The product that adds into the residual stream (either skinny kernel) also stores
+    bfloat16(h * gain) and partial sums of h^2; the reader scales its products by 1/rms.  Compared
+    with the plain formulas, and with the reader that runs the norm inside itself."""
+    from nanoinfer_b200.kernels import ops
+    eps, inter = 1e-5, 400
+    act = _randn(m, k_in, dtype=torch.bfloat16, seed=1)
+    w_add = _randn(d, k_in, dtype=torch.bfloat16, seed=2, scale=0.03)
+    h0 = _randn(m, d, seed=3, scale=1.5)
+    gain = _randn(d, seed=4, scale=0.2) + 1.0
+
+    class Norm:                                                   # what a norm part shows of itself
+        fused_kind = "rmsnorm"
+    norm = Norm()
+    norm.gain, norm.eps = gain, eps
+    tiles = ops.gemv_out_tiles(m, d, k_in)
+    hand = ops.NormHandoff(norm, gain, eps, m, d, tiles, DEV)
+    hand.ssq.fill_(float("nan"))
+    h = h0.clone()
+    assert ops.linear_bf16(act, w_add, torch.float32, residual=h, handoff=hand) is None
+    want_h = h0.cpu().double() + act.cpu().double() @ w_add.cpu().double().t()
+    torch.testing.assert_close(h.cpu().double(), want_h, rtol=1e-5, atol=1e-5 * math.sqrt(k_in))
+    # the prepared input is bfloat16(h * gain) of the very h that was stored, and the partial sums add up to sum(h^2)
+    assert torch.equal(hand.x, (h * gain).to(torch.bfloat16))
+    torch.testing.assert_close(hand.ssq[:, :m].sum(0).cpu(), (h.cpu() ** 2).sum(-1), rtol=1e-5, atol=0)
+    # readers: gate/up with SwiGLU, and a plain store
+    gate = _randn(inter, d, dtype=torch.bfloat16, seed=5, scale=0.05)
+    up = _randn(inter, d, dtype=torch.bfloat16, seed=6, scale=0.05)
+    w13 = torch.stack([gate.view(inter // 8, 8, d), up.view(inter // 8, 8, d)], dim=1).reshape(2 * inter, d).contiguous()
+    got = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
+    ops.gemv_bf16(hand.x, w13, got, ops.SWIGLU_BF16, pre=hand)
+    fused = torch.empty_like(got)
+    ops.gemv_norm_bf16(h, gain, eps, None, w13, fused, ops.SWIGLU_BF16)
+    x = plain.rms_norm(h.cpu(), gain.cpu(), eps)
+    want = plain.swiglu_ffn(x, gate.cpu(), up.cpu(), torch.eye(inter))       # the activation alone (identity down projection)
+    scale = want.abs().max().item()
+    assert (got.cpu().float() - want).abs().max().item() <= 1e-2 * scale
+    assert (got.float() - fused.float()).abs().max().item() <= 4e-3 * scale       # the same roundings, another order of sums
+    # the fused QKV projection as a reader (rotation and cache write behind it), against itself with the norm inside
+    n_q, n_kv, hd, page = 4, 2, 32, 8
+    if True:
+        w_qkv = _randn((n_q + 2 * n_kv) * hd, d, dtype=torch.bfloat16, seed=7, scale=0.05)
+        positions = torch.arange(3, 3 + m, dtype=torch.int32, device=DEV)
+        seq_of = torch.arange(m, dtype=torch.int32, device=DEV)
+        table = torch.arange(m * 2, dtype=torch.int32, device=DEV).view(m, 2)
+        inv_freq = plain.rope_inv_freq(hd, 10000.0, None).to(DEV)
+        outs = []
+        for pre in (hand, None):
+            q_out = torch.zeros(m, n_q * hd, dtype=torch.bfloat16, device=DEV)
+            kp = torch.zeros(m * 2, n_kv, page, hd, dtype=torch.bfloat16, device=DEV)
+            vp = torch.zeros_like(kp)
+            if pre is not None:
+                ops.gemv_qkv_rope(hand.x, None, 0.0, w_qkv, q_out, kp, vp, positions, seq_of, table, inv_freq, n_q, n_kv, hd, hd, page, pre=hand)
+            else:
+                ops.gemv_qkv_rope(h, gain, eps, w_qkv, q_out, kp, vp, positions, seq_of, table, inv_freq, n_q, n_kv, hd, hd, page)
+            outs.append((q_out, kp, vp))
+        for a, b in zip(*outs):
+            assert (a.float() - b.float()).abs().max().item() <= 1e-2 * b.float().abs().max().item()
+    # a reader without 16-row tiles (a plain store of few columns) has no such variant: refused, not wrong
+    with pytest.raises(ops.KernelError, match="not supported"):
+        ops.gemv_bf16(hand.x, w13, torch.empty(m, 2 * inter, dtype=torch.float32, device=DEV), ops.STORE_F32, pre=hand)
+    # what cannot be handed over is refused
+    with pytest.raises(ops.KernelError, match="at most 8 rows"):
+        ops.gemv_bf16(_randn(9, d, dtype=torch.bfloat16), w13, torch.empty(9, 2 * inter, dtype=torch.float32, device=DEV),
+                      ops.STORE_F32, pre=hand)
+    with pytest.raises(ops.KernelError, match="does not fit"):
+        ops.gemv_bf16(act, w_add, torch.empty(m, d, dtype=torch.float32, device=DEV), ops.STORE_F32, handoff=hand)
+
+
 def test_a_request_to_warm_l2_changes_no_result():
     """The skinny products and the decode attention may be handed a stretch of memory to ask into
     L2 on their way (weights that later kernels read).  Results are the same bit for bit, for

@@ -148,6 +148,34 @@ def test_wide_decode_batches_with_the_balanced_attention(model_dirs, monkeypatch
     assert all(n * raw["num_key_value_heads"] <= 2 for n in split_rows.seen)     # only the smallest steps took the split kernel
 
 
+@pytest.mark.parametrize("key", ["ds", "e"])
+def test_single_token_steps_hand_their_norms_from_kernel_to_kernel(model_dirs, plain_cache, monkeypatch, key):
+    """In steps of up to 8 rows the product that adds into the residual stream prepares the norm that
+    follows, and gate/up and the QKV projection read it prepared: only the output projection over the
+    vocabulary still runs a norm inside itself.  Logits against the plain implementation, and - to
+    rounding - against the same run with the hand-over switched off."""
+    from nanoinfer_b200.kernels import ops
+    raw, reqs, want = _plain(plain_cache, key, model_dirs[key])
+    page = SETUP[key][0]
+    steps = ru.tail_by_token(reqs)
+    readers = _Spy(monkeypatch, "gemv_bf16", lambda x, w, out, mode, *a, **k: k.get("pre") is not None)
+    qkv_readers = _Spy(monkeypatch, "gemv_qkv_rope", lambda *a, **k: k.get("pre") is not None)
+    inside = _Spy(monkeypatch, "gemv_norm_bf16", lambda h, gain, eps, rows, w, *a, **k: w.shape[0])
+    runner = _runner(model_dirs[key], "bfloat16", page, steps)
+    got = ru.run_trace(runner, steps)
+    ru.compare(got, want, "bfloat16", label=f"handoff/{key}")
+    assert sum(readers.seen) > 0 and sum(qkv_readers.seen) > 0
+    n_layers = raw["num_hidden_layers"]
+    # per single-token step: every gate/up reads a prepared norm, and every QKV projection but the first layer's
+    assert sum(readers.seen) * (n_layers - 1) == sum(qkv_readers.seen) * n_layers
+    assert set(inside.seen) <= {raw["vocab_size"], 2 * raw["intermediate_size"]}      # (gate/up of the prompt's last portion may be skinny too)
+    runner2 = _runner(model_dirs[key], "bfloat16", page, steps)
+    runner2.rt.norm_handoff = False
+    got2 = ru.run_trace(runner2, steps)
+    worst = max((got[k] - got2[k]).abs().max().item() / max(got2[k].abs().max().item(), 1e-6) for k in got)
+    assert worst <= 0.02, f"with and without the hand-over the logits differ by {worst:.3g} of their size"
+
+
 @pytest.mark.parametrize("every_projection", [False, True])
 def test_wide_outputs_take_the_swapped_operand_product(model_dirs, monkeypatch, every_projection):
     """A vocabulary wide enough that, at 9 to 128 rows, the output projection goes to the
