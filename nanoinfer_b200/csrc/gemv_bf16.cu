@@ -54,14 +54,15 @@ struct GemvParams {
     int bt_stride, n_q_heads, n_kv_heads, head_dim, rotary_dim, page_size, write_cache;
     // A norm handed from kernel to kernel (up to 8 rows; template parameter HAND).  Producer (HAND 2,
     // mode GV_ADD_F32): after out += product it also stores next_x = bf16(out * next_gain) and, per
-    // tile of output columns and row, the sum of out^2 over the tile (next_ssq[tile][8]).  Consumer
+    // tile of output columns and row, the sum of out^2 over the tile (next_ssq[row][tile]).  Consumer
     // (HAND 1; its bfloat16 input is such a next_x): 1/rms of each row from the pre_parts partial
     // sums, applied to the finished products (a per-row scalar commutes with the product).  Together
     // they are RMSNorm without a kernel of its own and without the consumer reading the FP32 stream.
     const float* next_gain;
     __nv_bfloat16* next_x;
-    float* next_ssq;
-    const float* pre_ssq;
+    float* next_ssq;          // [8 rows][next_parts]: a row's partial sums lie together (parts: a multiple of 4; what no tile writes stays 0)
+    int next_parts;
+    const float* pre_ssq;     // [8 rows][pre_parts]
     int pre_parts;
     float pre_eps;
     // optional: bytes that kernels after this one read (weights), asked into L2 once this block has
@@ -100,6 +101,16 @@ __device__ __forceinline__ void gv_warm(const GemvParams& p) {
         const unsigned int sz = p.warm_bytes - off < PIECE ? (unsigned int)(p.warm_bytes - off) : PIECE;
         asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(p.warm + off), "r"(sz) : "memory");
     }
+}
+
+// One lane's share of the sum of a row of n floats (n a multiple of 4, the row 16-byte aligned).
+__device__ __forceinline__ float gv_row_sum(const float* row, int n, int lane) {
+    float q = 0.f;
+    for (int i = 4 * lane; i < n; i += 128) {
+        const float4 v = *reinterpret_cast<const float4*>(row + i);
+        q += (v.x + v.y) + (v.z + v.w);
+    }
+    return q;
 }
 
 // Builds the B fragment (8 activations of one batch row at k .. k+7) and, with the norm fused,
@@ -228,7 +239,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32, (NT == 1 && U <= 4) ? 2 : 1) ge
                 // a norm prepared by that kernel: this warp's share of its row's partial sums, requested
                 // together with the activations below (its latency hides behind theirs)
                 if (HAND == 1)
-                    for (int i = lane; i < p.pre_parts; i += 32) pre_q += p.pre_ssq[(size_t)i * 8 + warp];
+                    pre_q += gv_row_sum(p.pre_ssq + (size_t)warp * p.pre_parts, p.pre_parts, lane);
             }
             if (!KEEP || first_tile) {
 #pragma unroll
@@ -268,7 +279,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32, (NT == 1 && U <= 4) ? 2 : 1) ge
             pdl_wait();
             waited = true;
             if (HAND == 1)
-                for (int i = lane; i < p.pre_parts; i += 32) pre_q += p.pre_ssq[(size_t)i * 8 + warp];
+                pre_q += gv_row_sum(p.pre_ssq + (size_t)warp * p.pre_parts, p.pre_parts, lane);
         }
         // partial sums of the 8 warps -> shared memory -> summed in warp order
 #pragma unroll
@@ -284,6 +295,14 @@ __global__ void __launch_bounds__(GV_WARPS * 32, (NT == 1 && U <= 4) ? 2 : 1) ge
                 if (t == 0) ss_red[warp][nt * 8 + g] = s;
             }
         }
+        if (HAND == 1 && first_tile) {
+            // warp w holds row w's partial sums (lanes took them in turn): a fixed shuffle tree adds them
+            // up, in time for the barrier that the warps' partial products need anyway
+            float q = pre_q;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) q += __shfl_xor_sync(0xffffffffu, q, off);
+            if (lane == 0) inv_rms[warp] = 1.0f / sqrtf(q / (float)K + p.pre_eps);
+        }
         __syncthreads();
         if (NORM && first_tile) {
             if (threadIdx.x < NT * 8) {
@@ -292,14 +311,6 @@ __global__ void __launch_bounds__(GV_WARPS * 32, (NT == 1 && U <= 4) ? 2 : 1) ge
                 for (int wi = 0; wi < GV_WARPS; ++wi) q += ss_red[wi][threadIdx.x];
                 inv_rms[threadIdx.x] = 1.0f / sqrtf(q / (float)K + p.eps);
             }
-            __syncthreads();
-        }
-        if (HAND == 1 && first_tile) {
-            // warp w holds row w's partial sums (lanes took them in turn): a fixed shuffle tree adds them up
-            float q = pre_q;
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) q += __shfl_xor_sync(0xffffffffu, q, off);
-            if (lane == 0) inv_rms[warp] = 1.0f / sqrtf(q / (float)K + p.pre_eps);
             __syncthreads();
         }
         for (int idx = threadIdx.x; idx < NT * 8 * RN; idx += blockDim.x) {
@@ -329,7 +340,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32, (NT == 1 && U <= 4) ? 2 : 1) ge
                 float sq = v * v;
 #pragma unroll
                 for (int off = RN / 2; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
-                if (row == 0) p.next_ssq[(size_t)(n0 / RN) * 8 + m] = sq;
+                if (row == 0) p.next_ssq[(size_t)m * p.next_parts + n0 / RN] = sq;
             }
         } else if (mode <= GV_ADD_F32) {
             for (int idx = threadIdx.x; idx < NT * 8 * RN; idx += blockDim.x) {
@@ -504,13 +515,16 @@ NI_EXPORT int ni_gemv_bf16_reads_handoff(int M, int K) { return M >= 1 && M <= 8
 // which the variant does not exist are refused (-2).
 NI_EXPORT int ni_gemv_bf16(const void* x, const void* w, void* out, int M, int N, int K, int mode,
                            const void* warm, long long warm_bytes, const float* next_gain, void* next_x,
-                           float* next_ssq, const float* pre_ssq, int pre_parts, float pre_eps, cudaStream_t stream) {
+                           float* next_ssq, int next_parts, const float* pre_ssq, int pre_parts, float pre_eps,
+                           cudaStream_t stream) {
     if (mode == GV_ROPE_KV || !gv_warm_ok(warm, warm_bytes)) return NI_ERR_BAD_ARGUMENT;
-    if (next_gain && (mode != GV_ADD_F32 || !next_x || !next_ssq || pre_ssq)) return NI_ERR_BAD_ARGUMENT;
-    if (pre_ssq && pre_parts <= 0) return NI_ERR_BAD_ARGUMENT;
+    if (next_gain && (mode != GV_ADD_F32 || !next_x || !next_ssq || pre_ssq || next_parts % 4 ||
+                      next_parts < ni_gemv_bf16_out_tiles(N, mode)))
+        return NI_ERR_BAD_ARGUMENT;
+    if (pre_ssq && (pre_parts <= 0 || pre_parts % 4 || ((uintptr_t)pre_ssq & 15))) return NI_ERR_BAD_ARGUMENT;
     if (pre_ssq && mode != GV_SWIGLU && (N + 15) / 16 < 2 * ni_sm_count()) return NI_ERR_UNSUPPORTED_SIZE;   // (the reader has 16-row tiles)
     GemvParams p = {};
-    p.next_gain = next_gain; p.next_x = (__nv_bfloat16*)next_x; p.next_ssq = next_ssq;
+    p.next_gain = next_gain; p.next_x = (__nv_bfloat16*)next_x; p.next_ssq = next_ssq; p.next_parts = next_parts;
     p.pre_ssq = pre_ssq; p.pre_parts = pre_parts; p.pre_eps = pre_eps;
     p.warm = (const unsigned char*)warm; p.warm_bytes = (unsigned long long)warm_bytes;
     p.x = x; p.w = (const __nv_bfloat16*)w; p.out = out; p.M = M; p.N = N; p.K = K; p.mode = mode;
@@ -540,7 +554,7 @@ NI_EXPORT int ni_gemv_qkv_rope(const void* x, const float* gain, float eps, cons
                                int write_cache, const void* warm, long long warm_bytes, const float* pre_ssq,
                                int pre_parts, float pre_eps, cudaStream_t stream) {
     if (!gv_warm_ok(warm, warm_bytes)) return NI_ERR_BAD_ARGUMENT;
-    if (pre_ssq && (gain != nullptr || pre_parts <= 0)) return NI_ERR_BAD_ARGUMENT;
+    if (pre_ssq && (gain != nullptr || pre_parts <= 0 || pre_parts % 4 || ((uintptr_t)pre_ssq & 15))) return NI_ERR_BAD_ARGUMENT;
     GemvParams p = {};
     p.pre_ssq = pre_ssq; p.pre_parts = pre_parts; p.pre_eps = pre_eps;
     p.warm = (const unsigned char*)warm; p.warm_bytes = (unsigned long long)warm_bytes;

@@ -44,10 +44,11 @@ struct KsParams {
     const unsigned char* warm;
     unsigned long long warm_bytes;
     // with mode KS_ADD_F32: also prepare the norm that follows - next_x = bf16(out * next_gain) and per row
-    // tile and row the sum of out^2 (next_ssq[tile][8]); see gemv_bf16.cu
+    // tile and row the sum of out^2 (next_ssq[row][tile]); see gemv_bf16.cu
     const float* next_gain;
     __nv_bfloat16* next_x;
-    float* next_ssq;
+    float* next_ssq;          // [8 rows][next_parts]
+    int next_parts;
 };
 
 __device__ __forceinline__ void ks_mma(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -204,7 +205,7 @@ __global__ void __launch_bounds__(KS_WARPS * 32, 2) gemv_ksplit_kernel(const KsP
             float sq = v * v;
 #pragma unroll
             for (int off = RN / 2; off > 0; off >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, off);
-            if (row == 0 && tile0 + ti < n_tiles) p.next_ssq[(size_t)(tile0 + ti) * 8 + m] = sq;
+            if (row == 0 && tile0 + ti < n_tiles) p.next_ssq[(size_t)m * p.next_parts + tile0 + ti] = sq;
         }
         return;
     }
@@ -287,7 +288,7 @@ NI_EXPORT int ni_gemv_ksplit_out_tiles(int N, int K) {
 // next_gain / next_x / next_ssq: with mode 2, also prepare the norm that follows (null: off).
 NI_EXPORT int ni_gemv_ksplit(const void* x, const void* w, void* out, int M, int N, int K, int mode,
                              const void* warm, long long warm_bytes, const float* next_gain, void* next_x,
-                             float* next_ssq, cudaStream_t stream) {
+                             float* next_ssq, int next_parts, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return NI_OK;
     if (mode < KS_STORE_BF16 || mode > KS_ADD_F32) return NI_ERR_BAD_ARGUMENT;
     if (next_gain && (mode != KS_ADD_F32 || !next_x || !next_ssq)) return NI_ERR_BAD_ARGUMENT;
@@ -299,7 +300,8 @@ NI_EXPORT int ni_gemv_ksplit(const void* x, const void* w, void* out, int M, int
     p.M = M; p.N = N; p.K = K; p.mode = mode;
     p.splits = plan.splits; p.slice_blocks = plan.slice_blocks; p.tiles_per_cluster = plan.tiles_per_cluster;
     p.warm = (const unsigned char*)warm; p.warm_bytes = (unsigned long long)warm_bytes;
-    p.next_gain = next_gain; p.next_x = (__nv_bfloat16*)next_x; p.next_ssq = next_ssq;
+    p.next_gain = next_gain; p.next_x = (__nv_bfloat16*)next_x; p.next_ssq = next_ssq; p.next_parts = next_parts;
+    if (next_gain && (next_parts % 4 || next_parts < (N + plan.rn - 1) / plan.rn)) return NI_ERR_BAD_ARGUMENT;
 #define KS_GO(RN)                                                                       \
     do {                                                                                \
         if (next_gain) {                                                                \

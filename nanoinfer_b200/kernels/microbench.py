@@ -60,12 +60,20 @@ def gemv(args) -> None:
         out = torch.zeros(m, n, dtype=torch.bfloat16 if mode == ops.STORE_BF16 else torch.float32, device=DEV)
     if args.norm:
         fns = [lambda w=w: ops.gemv_norm_bf16(h, gain, 1e-5, None, w, out, mode) for w in ws]
+    elif args.prepared:
+        # the reader of a handed-over norm: bfloat16 input, 1/rms from partial sums (here: of a stand-in producer)
+        class _Norm:
+            fused_kind = "rmsnorm"
+        hand = ops.NormHandoff(_Norm(), gain, 1e-5, m, k, args.parts, DEV)
+        hand.x.copy_(x)
+        hand.ssq.fill_(float(k) / hand.parts)
+        fns = [lambda w=w: ops.gemv_bf16(hand.x, w, out, mode, pre=hand) for w in ws]
     elif args.ksplit:
         fns = [lambda w=w: ops.gemv_ksplit(x, w, out, mode) for w in ws]
     else:
         fns = [lambda w=w: ops.gemv_bf16(x, w, out, mode) for w in ws]
     us = _time(fns, args.iters)
-    print(f"gemv{' (K split over a cluster)' if args.ksplit else ''} m={m} n={n} k={k} mode={args.mode} norm={args.norm}: {us:.2f} us, "
+    print(f"gemv{' (K split over a cluster)' if args.ksplit else ''}{' (norm prepared by the kernel before)' if args.prepared else ''} m={m} n={n} k={k} mode={args.mode} norm={args.norm}: {us:.2f} us, "
           f"{w_bytes / us / 1e3:.0f} GB/s of weights ({copies} weight copies in turn)")
 
 
@@ -275,6 +283,8 @@ def main() -> None:
     p.add_argument("--mode", default="bf16", choices=["bf16", "f32", "add", "swiglu"])
     p.add_argument("--norm", action="store_true")
     p.add_argument("--ksplit", action="store_true", help="the cluster split-K kernel (gemv_ksplit.cu) instead of gemv_bf16.cu")
+    p.add_argument("--prepared", action="store_true", help="the reader of a norm handed over by the kernel before (bfloat16 input + partial sums)")
+    p.add_argument("--parts", type=int, default=256, help="--prepared: partial sums per row")
     p.set_defaults(fn=gemv)
     p = sub.add_parser("add_rmsnorm")
     p.add_argument("--rows", type=int, default=2048)

@@ -40,7 +40,7 @@ _SIGNATURES = {
         "ni_gemm_f32": [_P, _P, _P, _I, _I, _I, _P],
     },
     "gemv_bf16": {
-        "ni_gemv_bf16": [_P, _P, _P, _I, _I, _I, _I, _P, _LL, _P, _P, _P, _P, _I, _F, _P],
+        "ni_gemv_bf16": [_P, _P, _P, _I, _I, _I, _I, _P, _LL, _P, _P, _P, _I, _P, _I, _F, _P],
         "ni_gemv_bf16_out_tiles": [_I, _I],
         "ni_gemv_bf16_writes_handoff": [_I, _I, _I],
         "ni_gemv_bf16_reads_handoff": [_I, _I],
@@ -48,7 +48,7 @@ _SIGNATURES = {
         "ni_gemv_qkv_rope": [_P, _P, _F, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _LL, _P, _I, _F, _P],
     },
     "gemv_ksplit": {
-        "ni_gemv_ksplit": [_P, _P, _P, _I, _I, _I, _I, _P, _LL, _P, _P, _P, _P],
+        "ni_gemv_ksplit": [_P, _P, _P, _I, _I, _I, _I, _P, _LL, _P, _P, _P, _I, _P],
         "ni_gemv_ksplit_out_tiles": [_I, _I],
         "ni_gemv_ksplit_supports": [_I, _I, _I],
     },
@@ -369,23 +369,27 @@ HANDOFF_ROWS = 8      # rows up to which a norm can be handed from the kernel th
 class NormHandoff:
     """A norm prepared by the kernel that last added into the residual stream, for the kernel that
     reads it (up to HANDOFF_ROWS rows): ``x`` = bfloat16(h * gain) [M, d], ``ssq`` float32
-    [tiles, 8] = per tile of columns and row the sum of h^2, ``eps``.  The reader multiplies its
+    [8, parts] = per row and tile of columns the sum of h^2 (parts: the tiles rounded up to a multiple
+    of 4, the rest zero), ``eps``.  The reader multiplies its
     finished products by 1 / sqrt(sum(ssq) / d + eps) per row: together RMSNorm(h) * gain without a
     kernel of its own.  ``norm`` is the part it stands for."""
 
     def __init__(self, norm, gain: torch.Tensor, eps: float, rows: int, width: int, tiles: int, device) -> None:
         self.norm, self.gain, self.eps, self.tiles = norm, gain, float(eps), int(tiles)
+        self.parts = -(-self.tiles // 4) * 4
         self.x = torch.empty(rows, width, dtype=torch.bfloat16, device=device)
-        self.ssq = torch.empty(tiles, 8, dtype=torch.float32, device=device)
+        self.ssq = torch.empty(8, self.parts, dtype=torch.float32, device=device)
+        if self.parts != self.tiles:
+            self.ssq[:, self.tiles:].zero_()        # what no tile writes must add nothing
 
     def producer_args(self):
-        return _dev(self.gain, "gain", torch.float32), self.x.data_ptr(), self.ssq.data_ptr()
+        return _dev(self.gain, "gain", torch.float32), self.x.data_ptr(), self.ssq.data_ptr(), self.parts
 
     def reader_args(self):
-        return self.ssq.data_ptr(), self.tiles, self.eps
+        return self.ssq.data_ptr(), self.parts, self.eps
 
 
-_NO_HANDOFF = (None, None, None)
+_NO_HANDOFF = (None, None, None, 0)
 _NO_PRE = (None, 0, 0.0)
 
 

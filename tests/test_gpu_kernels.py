@@ -345,14 +345,13 @@ def test_a_norm_handed_from_the_adding_product_to_its_reader(m, d, k_in):
     norm.gain, norm.eps = gain, eps
     tiles = ops.gemv_out_tiles(m, d, k_in)
     hand = ops.NormHandoff(norm, gain, eps, m, d, tiles, DEV)
-    hand.ssq.fill_(float("nan"))
     h = h0.clone()
     assert ops.linear_bf16(act, w_add, torch.float32, residual=h, handoff=hand) is None
     want_h = h0.cpu().double() + act.cpu().double() @ w_add.cpu().double().t()
     torch.testing.assert_close(h.cpu().double(), want_h, rtol=1e-5, atol=1e-5 * math.sqrt(k_in))
     # the prepared input is bfloat16(h * gain) of the very h that was stored, and the partial sums add up to sum(h^2)
     assert torch.equal(hand.x, (h * gain).to(torch.bfloat16))
-    torch.testing.assert_close(hand.ssq[:, :m].sum(0).cpu(), (h.cpu() ** 2).sum(-1), rtol=1e-5, atol=0)
+    torch.testing.assert_close(hand.ssq[:m].sum(1).cpu(), (h.cpu() ** 2).sum(-1), rtol=1e-5, atol=0)
     # readers: gate/up with SwiGLU, and a plain store
     gate = _randn(inter, d, dtype=torch.bfloat16, seed=5, scale=0.05)
     up = _randn(inter, d, dtype=torch.bfloat16, seed=6, scale=0.05)
