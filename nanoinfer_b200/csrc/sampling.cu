@@ -50,6 +50,17 @@ __device__ __forceinline__ uint32_t philox_first_word(unsigned long long seed, u
     return c0;
 }
 
+// Adds `val` of every active lane to bin `bin` of this warp's own histogram.  (All threads of a block
+// adding to one shared histogram serialise on the few bins that the leading byte of similar numbers
+// falls into: the first radix pass over 128 K logits took over a millisecond that way.  With a
+// histogram per warp only a warp's own lanes can meet in a bin.  Taking the bins that occur in the
+// warp one after the other and adding their lanes up by shuffles - no atomics at all - was slower
+// again in the later passes, where every lane has a bin of its own: 94 us against 76 us for top-k; a
+// fast path for warps whose lanes all agree on the bin changed nothing.)
+__device__ __forceinline__ void warp_hist_add(unsigned long long* hist, uint32_t bin, unsigned long long val, bool active) {
+    if (active) atomicAdd(&hist[bin], val);
+}
+
 struct BlockScratch {
     unsigned long long hist[256];
     unsigned long long red[32];
@@ -173,8 +184,12 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out,
               const float* __restrict__ top_ps, const unsigned long long* __restrict__ seeds,
               const unsigned long long* __restrict__ counters, int vocab) {
     __shared__ BlockScratch s;
+    extern __shared__ unsigned long long warp_hists[];      // [warps][256]: one histogram per warp
     const int r = blockIdx.x;
     const int tid = threadIdx.x;
+    const int n_warps = blockDim.x >> 5;
+    unsigned long long* my_hist = warp_hists + (size_t)(tid >> 5) * 256;
+    const int vocab_up = (vocab + 31) & ~31;                // whole warps walk the vocabulary
     const float* row = logits + (size_t)r * vocab;
     const float temp = temperatures[r];
 
@@ -216,11 +231,17 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out,
         uint32_t prefix = 0u, mask = 0u;
         unsigned long long remaining = (unsigned long long)k;
         for (int shift = 24; shift >= 0; shift -= 8) {
-            for (int b = tid; b < 256; b += blockDim.x) s.hist[b] = 0ull;
+            for (int b = tid; b < 256 * n_warps; b += blockDim.x) warp_hists[b] = 0ull;
             __syncthreads();
-            for (int i = tid; i < vocab; i += blockDim.x) {
-                const uint32_t key = ordered_key(row[i] * inv_t);
-                if ((key & mask) == prefix) atomicAdd(&s.hist[(key >> shift) & 255u], 1ull);
+            for (int i = tid; i < vocab_up; i += blockDim.x) {
+                const uint32_t key = i < vocab ? ordered_key(row[i] * inv_t) : 0u;
+                warp_hist_add(my_hist, (key >> shift) & 255u, 1ull, i < vocab && (key & mask) == prefix);
+            }
+            __syncthreads();
+            for (int b = tid; b < 256; b += blockDim.x) {
+                unsigned long long t = 0ull;
+                for (int w = 0; w < n_warps; ++w) t += warp_hists[w * 256 + b];
+                s.hist[b] = t;
             }
             __syncthreads();
             if (tid == 0) {
@@ -257,14 +278,20 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out,
         unsigned long long remaining = (unsigned long long)((double)p * (double)total);
         uint32_t prefix = 0u, mask = 0u;
         for (int shift = 24; shift >= 0; shift -= 8) {
-            for (int b = tid; b < 256; b += blockDim.x) s.hist[b] = 0ull;
+            for (int b = tid; b < 256 * n_warps; b += blockDim.x) warp_hists[b] = 0ull;
             __syncthreads();
-            for (int i = tid; i < vocab; i += blockDim.x) {
-                const float z = row[i] * inv_t;
-                if (ordered_key(z) < key_floor) continue;
+            for (int i = tid; i < vocab_up; i += blockDim.x) {
+                const float z = i < vocab ? row[i] * inv_t : 0.f;
                 const float e = expf(z - m);
                 const uint32_t bits = __float_as_uint(e);
-                if ((bits & mask) == prefix) atomicAdd(&s.hist[(bits >> shift) & 255u], mass_of(e));
+                const bool in = i < vocab && ordered_key(z) >= key_floor && (bits & mask) == prefix;
+                warp_hist_add(my_hist, (bits >> shift) & 255u, mass_of(e), in);
+            }
+            __syncthreads();
+            for (int b = tid; b < 256; b += blockDim.x) {
+                unsigned long long t = 0ull;
+                for (int w = 0; w < n_warps; ++w) t += warp_hists[w * 256 + b];
+                s.hist[b] = t;
             }
             __syncthreads();
             if (tid == 0) {
@@ -300,39 +327,45 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out,
     unsigned long long target = (unsigned long long)(u * (double)total);
     if (total > 0ull && target >= total) target = total - 1ull;
 
-    const int chunk = (vocab + blockDim.x - 1) / blockDim.x;
-    const int lo = tid * chunk;
-    const int hi = min(vocab, lo + chunk);
-    local = 0ull;
-    for (int i = lo; i < hi; ++i) {
+    // every warp owns a stretch of the vocabulary (a multiple of 32 ids) and reads it lane by lane;
+    // the warp whose stretch holds the target then walks it 32 ids at a time
+    const int lane = tid & 31, warp = tid >> 5;
+    const int stretch = ((vocab + n_warps - 1) / n_warps + 31) & ~31;
+    const int lo = warp * stretch;
+    const int hi = min(vocab, lo + stretch);
+    auto kept_mass = [&](int i) -> unsigned long long {
+        if (i >= hi) return 0ull;
         const float z = row[i] * inv_t;
-        if (ordered_key(z) < key_floor) continue;
+        if (ordered_key(z) < key_floor) return 0ull;
         const float e = expf(z - m);
-        if (__float_as_uint(e) >= e_floor) local += mass_of(e);
-    }
-    // exclusive scan of the chunk sums over the block (warp scan, then warp totals)
-    unsigned long long incl = local;
+        return __float_as_uint(e) >= e_floor ? mass_of(e) : 0ull;
+    };
+    local = 0ull;
+    for (int i = lo + lane; i < hi; i += 32) local += kept_mass(i);
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const unsigned long long n = __shfl_up_sync(0xffffffffu, incl, o);
-        if ((tid & 31) >= o) incl += n;
-    }
+    for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
     __syncthreads();
-    if ((tid & 31) == 31) s.red[tid >> 5] = incl;
+    if (lane == 0) s.red[warp] = local;
     if (tid == 0) s.chosen_int = vocab;  // "not found"
     __syncthreads();
     unsigned long long before = 0ull;
-    for (int w = 0; w < (tid >> 5); ++w) before += s.red[w];
-    const unsigned long long excl = before + incl - local;
-    if (local > 0ull && excl <= target && target < excl + local) {
-        unsigned long long acc = excl;
-        for (int i = lo; i < hi; ++i) {
-            const float z = row[i] * inv_t;
-            if (ordered_key(z) < key_floor) continue;
-            const float e = expf(z - m);
-            if (__float_as_uint(e) < e_floor) continue;
-            acc += mass_of(e);
-            if (acc > target) { s.chosen_int = i; break; }
+    for (int w = 0; w < warp; ++w) before += s.red[w];
+    if (local > 0ull && before <= target && target < before + local) {      // (warp-uniform)
+        unsigned long long acc = before;
+        for (int i0 = lo; i0 < hi; i0 += 32) {
+            const unsigned long long mine = kept_mass(i0 + lane);
+            unsigned long long incl = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned long long n = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += n;
+            }
+            const unsigned hit = __ballot_sync(0xffffffffu, acc + incl > target);
+            if (hit) {
+                if (lane == 0) s.chosen_int = i0 + __ffs(hit) - 1;
+                break;
+            }
+            acc += __shfl_sync(0xffffffffu, incl, 31);
         }
     }
     __syncthreads();
@@ -343,15 +376,312 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out,
     }
 }
 
+// ---- the same selection by a thread-block cluster per row -----------------------------------------
+//
+// One block per row walks 128 K logits several times from L2 with one SM's load rate: 92 us for a plain
+// temperature draw, 0.5-0.7 ms with top-k or top-p - as long as a whole decode step of a small batch,
+// while the other SMs idle.  Here a row belongs to a cluster of SC_RANKS blocks.  Each block keeps its
+// eighth of the scaled logits in shared memory, so every pass after the first reads shared memory;
+// what the passes reduce (the maximum, the 256-bin histograms of the radix selects, the kept mass)
+// every block sends to all blocks of the cluster through distributed shared memory (an all-gather,
+// one cluster barrier per pass), and every block draws the same conclusion from the same numbers.
+// Sums are the same 64-bit fixed-point sums, the draw the same walk in id order: the result is bit
+// for bit that of the one-block kernel.
+#define SC_RANKS 8
+#define SC_THREADS 512
+#define SC_WARPS (SC_THREADS / 32)
+#define SC_MAX_SLICE 40960      // floats of a block's slice (160 KB): vocabularies up to 327,680
+
+__device__ __forceinline__ uint32_t sc_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void sc_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void sc_st_remote(const unsigned long long* local_addr, uint32_t rank, unsigned long long v) {
+    uint32_t a = (uint32_t)__cvta_generic_to_shared(local_addr), remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(a), "r"(rank));
+    asm volatile("st.shared::cluster.u64 [%0], %1;\n" ::"r"(remote), "l"(v) : "memory");
+}
+// Every block's `count` values (src) end up in every block's buf[rank][0..count): buf is [SC_RANKS][256].
+__device__ __forceinline__ void sc_all_gather(unsigned long long* buf, const unsigned long long* src, int count, uint32_t my_rank) {
+    for (int idx = threadIdx.x; idx < count * SC_RANKS; idx += blockDim.x) {
+        const int dst = idx / count, j = idx - dst * count;
+        sc_st_remote(buf + my_rank * 256 + j, (uint32_t)dst, src[j]);
+    }
+    sc_cluster_sync();
+}
+
+struct ScScratch {
+    unsigned long long hist[256];        // this block's histogram of a pass / values to send
+    unsigned long long red[SC_WARPS];
+    unsigned long long digit_rest[2];    // the chosen digit and what is left of the count or mass
+    int chosen;
+};
+
+__global__ void __launch_bounds__(SC_THREADS, 1)
+sample_cluster_kernel(const float* __restrict__ logits, int* __restrict__ out,
+                      const float* __restrict__ temperatures, const int* __restrict__ top_ks,
+                      const float* __restrict__ top_ps, const unsigned long long* __restrict__ seeds,
+                      const unsigned long long* __restrict__ counters, int vocab, int slice) {
+    extern __shared__ __align__(16) unsigned char sc_smem[];
+    float* z = reinterpret_cast<float*>(sc_smem);                                              // [slice]
+    unsigned long long* warp_hists = reinterpret_cast<unsigned long long*>(z + slice);       // [SC_WARPS][256]
+    unsigned long long* gather = warp_hists + SC_WARPS * 256;                                 // [2][SC_RANKS][256]
+    __shared__ ScScratch s;
+    const int r = blockIdx.x / SC_RANKS;
+    const uint32_t rank = sc_rank();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    unsigned long long* my_hist = warp_hists + (size_t)warp * 256;
+    const float* row = logits + (size_t)r * vocab;
+    const int lo = (int)rank * slice;
+    const int n = max(0, min(vocab, lo + slice) - lo);       // this block's ids: lo .. lo + n
+    const int n_up = (n + 31) & ~31;
+    const float temp = temperatures[r];
+    const bool greedy = temp <= 0.f;
+    const float inv_t = greedy ? 1.0f : 1.0f / temp;
+    sc_cluster_sync();                                       // every block of the cluster runs: its shared memory may be written
+    int pass = 0;                                            // which of the two gather buffers is next
+    auto next_buf = [&]() { unsigned long long* b = gather + (size_t)(pass & 1) * SC_RANKS * 256; ++pass; return b; };
+
+    // ---- the slice into shared memory; its maximum (with the lowest id that has it) ----
+    unsigned long long best = 0ull;                          // (ordered key << 32) | (0xffffffff - id): larger is better
+    for (int i = tid; i < n; i += blockDim.x) {
+        const float v = row[lo + i] * inv_t;
+        z[i] = v;
+        // (-0 and +0 are one value to a comparison, but not to the ordered key)
+        const unsigned long long cand = ((unsigned long long)ordered_key(v == 0.f ? 0.f : v) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)(lo + i));
+        best = cand > best ? cand : best;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
+    }
+    if (lane == 0) s.red[warp] = best;
+    __syncthreads();
+    if (tid == 0) {
+        for (int w = 1; w < SC_WARPS; ++w) best = s.red[w] > best ? s.red[w] : best;
+        s.hist[0] = best;
+    }
+    __syncthreads();
+    unsigned long long* g = next_buf();
+    sc_all_gather(g, s.hist, 1, rank);
+    best = g[0];
+    for (int c = 1; c < SC_RANKS; ++c) best = g[c * 256] > best ? g[c * 256] : best;
+    if (greedy) {
+        if (rank == 0 && tid == 0) out[r] = (best >> 32) == 0ull ? 0 : (int)(0xffffffffu - (uint32_t)best);
+        return;
+    }
+    const uint32_t max_key = (uint32_t)(best >> 32);
+    const float m = __uint_as_float((max_key & 0x80000000u) ? (max_key & 0x7fffffffu) : ~max_key);
+
+    // One radix select over this cluster's kept tokens: `by_mass` false counts tokens by the ordered
+    // key of z (top-k), true sums masses by the bits of exp(z - m) (top-p).  Returns the 32-bit floor.
+    auto radix_select = [&](bool by_mass, uint32_t key_floor, unsigned long long remaining, bool strict) -> uint32_t {
+        uint32_t prefix = 0u, mask = 0u;
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            for (int b = tid; b < 256 * SC_WARPS; b += blockDim.x) warp_hists[b] = 0ull;
+            __syncthreads();
+            for (int i = tid; i < n_up; i += blockDim.x) {
+                const float v = i < n ? z[i] : 0.f;
+                uint32_t bits;
+                unsigned long long val;
+                bool in = i < n;
+                if (by_mass) {
+                    const float e = expf(v - m);
+                    bits = __float_as_uint(e);
+                    val = mass_of(e);
+                    in = in && ordered_key(v) >= key_floor;
+                } else {
+                    bits = ordered_key(v);
+                    val = 1ull;
+                }
+                warp_hist_add(my_hist, (bits >> shift) & 255u, val, in && (bits & mask) == prefix);
+            }
+            __syncthreads();
+            for (int b = tid; b < 256; b += blockDim.x) {
+                unsigned long long t = 0ull;
+                for (int w = 0; w < SC_WARPS; ++w) t += warp_hists[w * 256 + b];
+                s.hist[b] = t;
+            }
+            __syncthreads();
+            unsigned long long* gb = next_buf();
+            sc_all_gather(gb, s.hist, 256, rank);
+            for (int b = tid; b < 256; b += blockDim.x) {
+                unsigned long long t = 0ull;
+                for (int c = 0; c < SC_RANKS; ++c) t += gb[c * 256 + b];
+                s.hist[b] = t;
+            }
+            __syncthreads();
+            // the digit: the largest d >= 1 whose bin, with all bins above it, reaches what is left (else 0).
+            // Thread b holds bin b and the sum of the bins above it (a suffix scan over the 256 bins).
+            if (tid < 256) {
+                const unsigned long long mine = s.hist[tid];
+                unsigned long long incl = mine;                       // inclusive suffix sum inside the warp
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const unsigned long long nb = __shfl_down_sync(0xffffffffu, incl, o);
+                    if (lane + o < 32) incl += nb;
+                }
+                if (lane == 0) s.red[warp] = incl;                    // the warp's total (8 warps hold the 256 bins)
+                asm volatile("bar.sync 1, 256;\n" ::: "memory");
+                unsigned long long above = incl - mine;
+                for (int w = warp + 1; w < 8; ++w) above += s.red[w];
+                const bool reach = strict ? above + mine > remaining : above + mine >= remaining;
+                const bool reached_above = strict ? above > remaining : above >= remaining;
+                if (tid == 0) { s.digit_rest[0] = 0ull; s.digit_rest[1] = remaining - (above + mine - s.hist[0]); }
+                asm volatile("bar.sync 1, 256;\n" ::: "memory");
+                if (tid >= 1 && reach && !reached_above) {
+                    s.digit_rest[0] = (unsigned long long)tid;
+                    s.digit_rest[1] = remaining - above;
+                }
+            }
+            __syncthreads();
+            prefix |= (uint32_t)s.digit_rest[0] << shift;
+            mask |= 255u << shift;
+            remaining = s.digit_rest[1];
+            __syncthreads();
+        }
+        return prefix;
+    };
+    // The kept mass of this block's slice, every block's share of it (shares[c]) and the total.
+    unsigned long long shares[SC_RANKS];
+    auto kept_total = [&](uint32_t key_floor, uint32_t e_floor) -> unsigned long long {
+        unsigned long long local = 0ull;
+        for (int i = tid; i < n; i += blockDim.x) {
+            const float v = z[i];
+            if (ordered_key(v) < key_floor) continue;
+            const float e = expf(v - m);
+            if (__float_as_uint(e) >= e_floor) local += mass_of(e);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+        __syncthreads();
+        if (lane == 0) s.red[warp] = local;
+        __syncthreads();
+        if (tid == 0) {
+            unsigned long long t = 0ull;
+            for (int w = 0; w < SC_WARPS; ++w) t += s.red[w];
+            s.hist[0] = t;
+        }
+        __syncthreads();
+        unsigned long long* gb = next_buf();
+        sc_all_gather(gb, s.hist, 1, rank);
+        unsigned long long total = 0ull;
+        for (int c = 0; c < SC_RANKS; ++c) { shares[c] = gb[c * 256]; total += shares[c]; }
+        return total;
+    };
+
+    uint32_t key_floor = 0u, e_floor = 0u;
+    const int k = top_ks[r];
+    if (k > 0 && k < vocab) key_floor = radix_select(false, 0u, (unsigned long long)k, false);
+    unsigned long long total = kept_total(key_floor, 0u);
+    const float p = top_ps[r];
+    if (p > 0.f && p < 1.f) {
+        e_floor = radix_select(true, key_floor, (unsigned long long)((double)p * (double)total), true);
+        total = kept_total(key_floor, e_floor);
+    }
+
+    // ---- draw: first id (in id order) whose inclusive mass exceeds u * total ----
+    const uint32_t word = philox_first_word(seeds[r], counters[r]);
+    const double u = ((double)(word >> 8) + 0.5) * (1.0 / 16777216.0);
+    unsigned long long target = (unsigned long long)(u * (double)total);
+    if (total > 0ull && target >= total) target = total - 1ull;
+    if (total == 0ull) {                                     // only if every mass rounded to zero
+        if (rank == 0 && tid == 0) out[r] = 0;
+        return;
+    }
+    unsigned long long before_me = 0ull;
+    for (int c = 0; c < (int)rank; ++c) before_me += shares[c];
+    if (!(before_me <= target && target < before_me + shares[rank])) return;     // (block-uniform) another block's ids
+    // this block holds the id: every warp sums a stretch of the slice, the warp with the target walks it
+    auto kept_mass = [&](int i, int end) -> unsigned long long {
+        if (i >= end) return 0ull;
+        const float v = z[i];
+        if (ordered_key(v) < key_floor) return 0ull;
+        const float e = expf(v - m);
+        return __float_as_uint(e) >= e_floor ? mass_of(e) : 0ull;
+    };
+    const int stretch = ((n + SC_WARPS - 1) / SC_WARPS + 31) & ~31;
+    const int w_lo = min(n, warp * stretch), w_hi = min(n, w_lo + stretch);
+    unsigned long long local = 0ull;
+    for (int i = w_lo + lane; i < w_hi; i += 32) local += kept_mass(i, w_hi);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+    __syncthreads();
+    if (lane == 0) s.red[warp] = local;
+    __syncthreads();
+    unsigned long long before = before_me;
+    for (int w = 0; w < warp; ++w) before += s.red[w];
+    if (local > 0ull && before <= target && target < before + local) {           // (warp-uniform)
+        unsigned long long acc = before;
+        for (int i0 = w_lo; i0 < w_hi; i0 += 32) {
+            unsigned long long incl = kept_mass(i0 + lane, w_hi);
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned long long nb = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += nb;
+            }
+            const unsigned hit = __ballot_sync(0xffffffffu, acc + incl > target);
+            if (hit) {
+                if (lane == 0) out[r] = lo + i0 + __ffs(hit) - 1;
+                break;
+            }
+            acc += __shfl_sync(0xffffffffu, incl, 31);
+        }
+    }
+}
+
 // One launch for a batch with per-row parameters.  temperatures[r] <= 0 selects arg-max.
 // top_ks[r] <= 0 or >= vocab: no top-k; top_ps[r] outside (0, 1): no top-p.
+static int sample_by_cluster = 1;
+// 0: always the one-block-per-row kernel (for comparisons); 1: a cluster per row where it fits (the default).
+NI_EXPORT int ni_sample_set_cluster(int on) { sample_by_cluster = on; return NI_OK; }
+
 NI_EXPORT int ni_sample(const float* logits, int* out, const float* temperatures, const int* top_ks,
                         const float* top_ps, const unsigned long long* seeds,
                         const unsigned long long* counters, int n_rows, int vocab, cudaStream_t stream) {
     if (n_rows <= 0) return NI_OK;
     if (vocab <= 0) return NI_ERR_BAD_ARGUMENT;
     if (vocab > (1 << 25)) return NI_ERR_UNSUPPORTED_SIZE;  // fixed-point mass would overflow
-    sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, out, temperatures, top_ks, top_ps,
-                                                        seeds, counters, vocab);
+    // a cluster per row while a block's slice of the vocabulary fits its shared memory
+    const int slice = (((vocab + SC_RANKS - 1) / SC_RANKS) + 31) & ~31;
+    if (sample_by_cluster && vocab >= 4096 && slice <= SC_MAX_SLICE) {
+        const size_t sc_smem = (size_t)slice * sizeof(float) + (size_t)(SC_WARPS + 2 * SC_RANKS) * 256 * sizeof(unsigned long long);
+        static size_t sc_configured = 0;
+        if (sc_configured < sc_smem) {
+            cudaError_t e = cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sc_smem);
+            if (e != cudaSuccess) return (int)e;
+            sc_configured = sc_smem;
+        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)n_rows * SC_RANKS);
+        cfg.blockDim = dim3(SC_THREADS);
+        cfg.dynamicSmemBytes = sc_smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = SC_RANKS;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, sample_cluster_kernel, logits, out, temperatures, top_ks, top_ps, seeds,
+                                           counters, vocab, slice);
+        return e == cudaSuccess ? NI_OK : (int)e;
+    }
+    const size_t smem = (size_t)(SAMPLE_THREADS / 32) * 256 * sizeof(unsigned long long);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    sample_kernel<<<n_rows, SAMPLE_THREADS, smem, stream>>>(logits, out, temperatures, top_ks, top_ps,
+                                                           seeds, counters, vocab);
     NI_RETURN_LAUNCH_STATUS();
 }

@@ -93,6 +93,7 @@ _SIGNATURES = {
         "ni_argmax": [_P, _P, _I, _I, _P, _P],
         "ni_repetition_penalty": [_P, _P, _P, _I, _I, _I, _P],
         "ni_sample": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P],
+        "ni_sample_set_cluster": [_I],
     },
 }
 
@@ -119,6 +120,8 @@ def load(module: str) -> ctypes.CDLL:
             f.argtypes = argtypes
             f.restype = _I
         import os
+        if module == "sampling" and os.environ.get("NANOINFER_B200_SAMPLE_ONE_BLOCK"):      # for comparisons
+            lib.ni_sample_set_cluster(0)
         if module == "attention_decode" and os.environ.get("NANOINFER_B200_SCRATCH_MERGE"):
             lib.ni_attention_decode_set_cluster_merge(0)
         if module == "attention_decode" and lib.ni_attention_decode_fresh_keys() != DECODE_FRESH_KEYS:
@@ -867,6 +870,12 @@ def repetition_penalty(logits: torch.Tensor, ids: torch.Tensor, penalties: torch
     _check(load("sampling").ni_repetition_penalty(
         _dev(logits, "logits", torch.float32), _dev(ids, "ids", torch.int32),
         _dev(penalties, "penalties", torch.float32), n, v, ids.shape[1], _stream()), "repetition_penalty")
+
+
+def sample_by_cluster(on: bool) -> None:
+    """Whether ``sample`` gives every row a thread-block cluster where the vocabulary allows it (the
+    default) or always one block (the two give the same tokens; for comparisons)."""
+    _check_plain(load("sampling").ni_sample_set_cluster(1 if on else 0), "sample")
 
 
 def sample(logits, out, temperatures, top_ks, top_ps, seeds, counters) -> None:

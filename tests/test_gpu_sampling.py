@@ -32,6 +32,46 @@ CASES = [dict(temperature=1.0), dict(temperature=0.7), dict(temperature=1.5, top
          dict(temperature=0.9, repetition_penalty=1.3), dict(temperature=0.0, repetition_penalty=2.0)]
 
 
+@pytest.mark.parametrize("vocab", [4096, 5001, 33007, 128256, 262145])
+def test_a_cluster_per_row_selects_the_same_tokens_as_one_block(vocab):
+    """Rows of every kind of parameters, at vocabularies that do and do not divide by the cluster's
+    eight blocks: the cluster kernel and the one-block kernel agree on every token, bit for bit."""
+    from nanoinfer_b200.kernels import ops
+    rows = 40
+    g = torch.Generator().manual_seed(vocab)
+    l = (torch.randn(rows, vocab, generator=g) * 3.0).to(DEV)
+    l[3] = 0.25                                                     # all equal: every id as likely
+    l[4, :] = -0.0
+    l[4, 17] = 0.0                                                  # +0 and -0 tie: the lowest id wins a greedy row
+    temps = torch.tensor([[0.0, 0.7, 1.0, 1.5][i % 4] for i in range(rows)], device=DEV)
+    temps[4] = 0.0
+    ks = torch.tensor([[0, 1, 40, 5000, vocab, 0][i % 6] for i in range(rows)], dtype=torch.int32, device=DEV)
+    ps_ = torch.tensor([[1.0, 0.9, 0.5, 0.05, 0.999][i % 5] for i in range(rows)], device=DEV)
+    seeds = torch.arange(rows, dtype=torch.int64, device=DEV) * 7919
+    counters = torch.arange(rows, dtype=torch.int64, device=DEV) % 5
+    outs = []
+    for cluster in (True, False):
+        ops.sample_by_cluster(cluster)
+        out = torch.full((rows,), -1, dtype=torch.int32, device=DEV)
+        ops.sample(l, out, temps, ks, ps_, seeds, counters)
+        outs.append(out.cpu())
+    ops.sample_by_cluster(True)
+    assert torch.equal(outs[0], outs[1]), f"rows {torch.nonzero(outs[0] != outs[1]).flatten().tolist()} differ"
+    assert int(outs[0].min()) >= 0 and int(outs[0].max()) < vocab and int(outs[0][4]) == 0
+    # many draws of one row: different counters give different tokens, the same counter the same token
+    many = 64
+    rep = l[1:2].expand(many, vocab).contiguous()
+    out_a = torch.empty(many, dtype=torch.int32, device=DEV)
+    t1 = torch.ones(many, device=DEV)
+    z0 = torch.zeros(many, dtype=torch.int32, device=DEV)
+    sd = torch.full((many,), 5, dtype=torch.int64, device=DEV)
+    ops.sample(rep, out_a, t1, z0, t1, sd, torch.arange(many, dtype=torch.int64, device=DEV))
+    assert len(set(out_a.tolist())) > many // 2
+    out_b = torch.empty_like(out_a)
+    ops.sample(rep, out_b, t1, z0, t1, sd, torch.zeros(many, dtype=torch.int64, device=DEV))
+    assert len(set(out_b.tolist())) == 1 and out_b[0] == out_a[0]
+
+
 @pytest.mark.parametrize("vocab", [384, 1000, 128256])
 def test_sampler_matches_plain_selection(vocab):
     from nanoinfer_b200.sampling import Sampler, SamplingParams
