@@ -390,6 +390,7 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out,
 #define SC_RANKS 8
 #define SC_THREADS 512
 #define SC_WARPS (SC_THREADS / 32)
+#define SC_HISTS (SC_WARPS / 2)  // histograms per block: one per pair of warps (16 KB; with one per warp a second block would not fit an SM)
 #define SC_MAX_SLICE 40960      // floats of a block's slice (160 KB): vocabularies up to 327,680
 
 __device__ __forceinline__ uint32_t sc_rank() {
@@ -422,20 +423,20 @@ struct ScScratch {
     int chosen;
 };
 
-__global__ void __launch_bounds__(SC_THREADS, 1)
+__global__ void __launch_bounds__(SC_THREADS, 2)
 sample_cluster_kernel(const float* __restrict__ logits, int* __restrict__ out,
                       const float* __restrict__ temperatures, const int* __restrict__ top_ks,
                       const float* __restrict__ top_ps, const unsigned long long* __restrict__ seeds,
                       const unsigned long long* __restrict__ counters, int vocab, int slice) {
     extern __shared__ __align__(16) unsigned char sc_smem[];
     float* z = reinterpret_cast<float*>(sc_smem);                                              // [slice]
-    unsigned long long* warp_hists = reinterpret_cast<unsigned long long*>(z + slice);       // [SC_WARPS][256]
-    unsigned long long* gather = warp_hists + SC_WARPS * 256;                                 // [2][SC_RANKS][256]
+    unsigned long long* warp_hists = reinterpret_cast<unsigned long long*>(z + slice);       // [SC_HISTS][256]
+    unsigned long long* gather = warp_hists + SC_HISTS * 256;                                 // [2][SC_RANKS][256]
     __shared__ ScScratch s;
     const int r = blockIdx.x / SC_RANKS;
     const uint32_t rank = sc_rank();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    unsigned long long* my_hist = warp_hists + (size_t)warp * 256;
+    unsigned long long* my_hist = warp_hists + (size_t)(warp >> 1) * 256;
     const float* row = logits + (size_t)r * vocab;
     const int lo = (int)rank * slice;
     const int n = max(0, min(vocab, lo + slice) - lo);       // this block's ids: lo .. lo + n
@@ -484,7 +485,7 @@ sample_cluster_kernel(const float* __restrict__ logits, int* __restrict__ out,
     auto radix_select = [&](bool by_mass, uint32_t key_floor, unsigned long long remaining, bool strict) -> uint32_t {
         uint32_t prefix = 0u, mask = 0u;
         for (int shift = 24; shift >= 0; shift -= 8) {
-            for (int b = tid; b < 256 * SC_WARPS; b += blockDim.x) warp_hists[b] = 0ull;
+            for (int b = tid; b < 256 * SC_HISTS; b += blockDim.x) warp_hists[b] = 0ull;
             __syncthreads();
             for (int i = tid; i < n_up; i += blockDim.x) {
                 const float v = i < n ? z[i] : 0.f;
@@ -505,7 +506,7 @@ sample_cluster_kernel(const float* __restrict__ logits, int* __restrict__ out,
             __syncthreads();
             for (int b = tid; b < 256; b += blockDim.x) {
                 unsigned long long t = 0ull;
-                for (int w = 0; w < SC_WARPS; ++w) t += warp_hists[w * 256 + b];
+                for (int w = 0; w < SC_HISTS; ++w) t += warp_hists[w * 256 + b];
                 s.hist[b] = t;
             }
             __syncthreads();
@@ -651,7 +652,7 @@ NI_EXPORT int ni_sample(const float* logits, int* out, const float* temperatures
     // a cluster per row while a block's slice of the vocabulary fits its shared memory
     const int slice = (((vocab + SC_RANKS - 1) / SC_RANKS) + 31) & ~31;
     if (sample_by_cluster && vocab >= 4096 && slice <= SC_MAX_SLICE) {
-        const size_t sc_smem = (size_t)slice * sizeof(float) + (size_t)(SC_WARPS + 2 * SC_RANKS) * 256 * sizeof(unsigned long long);
+        const size_t sc_smem = (size_t)slice * sizeof(float) + (size_t)(SC_HISTS + 2 * SC_RANKS) * 256 * sizeof(unsigned long long);
         static size_t sc_configured = 0;
         if (sc_configured < sc_smem) {
             cudaError_t e = cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sc_smem);
