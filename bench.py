@@ -290,6 +290,9 @@ WORKLOADS = {
     # long prompts and long greedy decoding at a large batch
     "long": {"shape": "llama-3.1-8b", "requests": 64, "prompt": (6144, 6144), "new_tokens": 2048,
              "temperature": 0.0, "chunk": 2048, "budget": 8192},
+    # a small batch of the 1B shape that samples with temperature, top-k and top-p: what the sampler costs
+    "sampled": {"shape": "llama-3.2-1b", "requests": 8, "prompt": (1024, 2048), "new_tokens": 512,
+                "temperature": 0.8, "top_k": 50, "top_p": 0.9, "chunk": 2048, "budget": 2048},
 }
 
 
@@ -322,7 +325,8 @@ def run_serving(args):
     engine.stop_token_ids = ()
 
     def one_pass(new_tokens):
-        sp = SamplingParams(temperature=w["temperature"], seed=1) if w["temperature"] > 0 else SamplingParams.greedy()
+        sp = (SamplingParams(temperature=w["temperature"], top_k=w.get("top_k", -1), top_p=w.get("top_p", 1.0), seed=1)
+              if w["temperature"] > 0 else SamplingParams.greedy())
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         ids = [engine.add_request(p, new_tokens, sp) for p in prompts]
@@ -357,7 +361,8 @@ def run_serving(args):
         "config": {"workload": args.workload, "model": shape + "-shape", "requests": n_req, "layers": layers,
                    "layers_full_model": full_layers, "prompt_tokens_min": min(lengths),
                    "prompt_tokens_max": max(lengths), "prompt_tokens_total": sum(lengths),
-                   "new_tokens": w["new_tokens"], "temperature": w["temperature"], "prefill_chunk": w["chunk"],
+                   "new_tokens": w["new_tokens"], "temperature": w["temperature"], "top_k": w.get("top_k", -1),
+                   "top_p": w.get("top_p", 1.0), "prefill_chunk": w["chunk"],
                    "token_budget": w["budget"], "kv_page_size": page, "kv_pages": pages},
         "clocks": clk,
     }
