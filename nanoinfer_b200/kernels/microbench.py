@@ -92,6 +92,25 @@ def add_rmsnorm(args) -> None:
           f"(h read and written, delta read, activations written)")
 
 
+def sample(args) -> None:
+    """One token per row from FP32 logits by temperature, top-k, top-p: the cluster-per-row kernel, or
+    with --one-block the kernel that gives a row one block."""
+    n, v = args.rows, args.vocab
+    g = torch.Generator(device=DEV).manual_seed(0)
+    sets = [torch.randn(n, v, device=DEV, generator=g) * 3.0 for _ in range(max(2, min(8, (2 * L2_BYTES) // (n * v * 4) + 1)))]
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    temps = torch.full((n,), args.temperature, device=DEV)
+    ks = torch.full((n,), args.top_k, dtype=torch.int32, device=DEV)
+    ps = torch.full((n,), args.top_p, device=DEV)
+    seeds = torch.arange(n, dtype=torch.int64, device=DEV)
+    counters = torch.zeros(n, dtype=torch.int64, device=DEV)
+    ops.sample_by_cluster(not args.one_block)
+    us = _time([lambda l=l: ops.sample(l, out, temps, ks, ps, seeds, counters) for l in sets], args.iters)
+    ops.sample_by_cluster(True)
+    print(f"sample{' (one block per row)' if args.one_block else ' (a cluster per row)'} rows={n} vocab={v} temperature={args.temperature} "
+          f"top_k={args.top_k} top_p={args.top_p}: {us:.1f} us")
+
+
 def gemm(args) -> None:
     """The tcgen05 product against the library product on the same operands."""
     m, n, k = args.m, args.n, args.k
@@ -286,6 +305,14 @@ def main() -> None:
     p.add_argument("--prepared", action="store_true", help="the reader of a norm handed over by the kernel before (bfloat16 input + partial sums)")
     p.add_argument("--parts", type=int, default=256, help="--prepared: partial sums per row")
     p.set_defaults(fn=gemv)
+    p = sub.add_parser("sample")
+    p.add_argument("--rows", type=int, default=8)
+    p.add_argument("--vocab", type=int, default=128256)
+    p.add_argument("--temperature", type=float, default=0.8)
+    p.add_argument("--top-k", type=int, default=0)
+    p.add_argument("--top-p", type=float, default=1.0)
+    p.add_argument("--one-block", action="store_true")
+    p.set_defaults(fn=sample)
     p = sub.add_parser("add_rmsnorm")
     p.add_argument("--rows", type=int, default=2048)
     p.add_argument("--width", type=int, default=2048)
