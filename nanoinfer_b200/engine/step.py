@@ -266,6 +266,11 @@ class ModelRunner:
         self._portion_graphs: Dict[tuple, "_PortionGraph"] = {}       # by step shape, least recently used first
         self._portion_seen: Dict[tuple, int] = {}
         self.max_portion_graphs = 8
+        # A captured shape gives its place to a new one only after it has not come for this many steps:
+        # with more recurring shapes than places, taking turns would capture every step anew (a serving
+        # workload with 20 prompt-step shapes per round, repeated: 50 ms of capture for each 11 ms step).
+        self.portion_graph_idle = 512
+        self._step_no = 0
         # A capture costs about three runs of the step (an eager run that sizes the workspaces, the
         # capture, the first replay) and a replay saves only the launch overhead, so a shape must
         # have come back a few times before it is worth one.
@@ -421,6 +426,7 @@ class ModelRunner:
         ``device_tokens`` (int32 on the device, one per entry): the tokens of a step of single
         tokens that the host has not read yet (entries then carry PENDING_TOKEN)."""
         self._validate(entries, pending_ok=device_tokens is not None)
+        self._step_no += 1
         if device_tokens is not None and not (self._graphable(entries) and device_tokens.numel() == len(entries)):
             raise StepError("tokens can be fed from the device only to a replayed step of single tokens")
         if self._graphable(entries) and (device_tokens is not None or self._decode_graph_due(len(entries), count=True)):
@@ -459,7 +465,13 @@ class ModelRunner:
         self._portion_seen[sig] = seen
         if len(self._portion_seen) > 4096:
             self._portion_seen.clear()
-        return seen >= self.portion_graph_after
+        if seen < self.portion_graph_after:
+            return False
+        if len(self._portion_graphs) >= self.max_portion_graphs:
+            oldest = next(iter(self._portion_graphs.values()))                # least recently used
+            if self._step_no - oldest.last_used < self.portion_graph_idle:
+                return False                                                  # every place is in use: this shape runs without a graph
+        return True
 
     def _portion_graph(self, entries: Sequence[StepEntry]) -> "_PortionGraph":
         sig = tuple((len(e.tokens), len(e.want)) for e in entries)
@@ -546,9 +558,11 @@ class _PortionGraph:
         self.host = self.host_np = self.dev = None
         self.copied = torch.cuda.Event()
         self.copy_pending = False
+        self.last_used = runner._step_no
 
     def run(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> torch.Tensor:
         runner = self.runner
+        self.last_used = runner._step_no
         parts, offsets, total, q_lens, kv_lens, slots, width, plans = runner._layout(entries, starts, full_width=True)
         if self.host is None:
             self.host = torch.zeros(total, dtype=torch.int32, pin_memory=True)

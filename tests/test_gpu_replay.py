@@ -246,6 +246,43 @@ def test_repeated_portion_shapes_are_replayed_from_a_graph(model_dirs, plain_cac
     assert runner.cache.num_free_pages(0) == runner.cache.pools[0].num_pages
 
 
+def test_more_recurring_step_shapes_than_graph_places_do_not_take_turns(model_dirs, plain_cache, monkeypatch):
+    """Four portion sizes come round and round while the runner keeps two captured shapes: the first
+    two are captured and replayed, the others run without a graph - no capture per step.  Once a
+    captured shape has stayed away long enough, a new one takes its place.  The logits do not notice."""
+    from nanoinfer_b200.engine import step as step_module
+    key = "d"
+    raw, reqs, want = _plain(plain_cache, key, model_dirs[key])
+    page = SETUP[key][0]
+    rid, toks = max(reqs.items(), key=lambda kv: len(kv[1]))          # the longest request, in portions of 5, 6, 7, 8, 5, ...
+    steps, at, s = [], 0, 0
+    while at < len(toks):
+        n = min(5 + s % 4, len(toks) - at)
+        steps.append({"step": s, "entries": [{"id": rid, "tokens": toks[at:at + n], "want": list(range(n))}],
+                      "end": [rid] if at + n == len(toks) else []})
+        at, s = at + n, s + 1
+    assert len(steps) > 40
+    captured = []
+    init = step_module._PortionGraph.__init__
+
+    def counting_init(self, runner):
+        captured.append(runner._step_no)
+        init(self, runner)
+    monkeypatch.setattr(step_module._PortionGraph, "__init__", counting_init)
+    runner = _runner(model_dirs[key], "bfloat16", page, steps)
+    runner.portion_graph_after, runner.max_portion_graphs = 2, 2
+    got = ru.run_trace(runner, steps)
+    ru.compare(got, {rid: want[rid]}, "bfloat16", label="graph places")
+    assert len(captured) == 2 and len(runner._portion_graphs) == 2, f"captures at steps {captured}"
+    # a shape that has stayed away for portion_graph_idle steps gives way
+    runner2 = _runner(model_dirs[key], "bfloat16", page, steps)
+    runner2.portion_graph_after, runner2.max_portion_graphs, runner2.portion_graph_idle = 2, 2, 3
+    captured.clear()
+    got2 = ru.run_trace(runner2, steps)
+    ru.compare(got2, {rid: want[rid]}, "bfloat16", label="graph places, short idle time")
+    assert len(captured) > 2
+
+
 @pytest.mark.parametrize("key", ["a", "b", "e"])
 def test_cuts_agree_bitwise_in_float32(model_dirs, plain_cache, key):
     """The 32-bit path fixes the order of every sum, so the cut cannot change a single bit."""
