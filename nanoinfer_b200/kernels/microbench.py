@@ -230,6 +230,62 @@ def attention_prefill(args) -> None:
           f"{flops / us / 1e6:.0f} TFLOP/s (causal)")
 
 
+def decode_step(args) -> None:
+    """One decode step of the whole model as the engine runs it (a replayed graph with arg-max and token
+    feedback on the device), optionally with one kind of kernel left out: the difference is what that
+    kind costs inside the chain of dependent launches.  With --without the results are WRONG (the
+    kernel's output is whatever was in its buffer); only the time means something."""
+    from ..config import config_from_dict, preset
+    from ..engine import ModelRunner, StepEntry
+    from ..weights import tensor_plan
+    raw = dict(preset(args.shape))
+    if args.layers:
+        raw["num_hidden_layers"] = args.layers
+    config = config_from_dict(raw)
+    g = torch.Generator(device=DEV).manual_seed(0)
+    weights = {p.name: (torch.ones(p.shape, dtype=torch.bfloat16, device=DEV) if p.init == "ones" else
+                        (torch.randn(p.shape, generator=g, device=DEV, dtype=torch.float32) * 0.02).to(torch.bfloat16))
+               for p in tensor_plan(config)}
+    batch, ctx_len, page = args.batch, args.context, 16
+    cpu = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, raw["vocab_size"], (ctx_len,), generator=cpu).tolist() for _ in range(batch)]
+    runner = ModelRunner(config, weights, dtype="bfloat16", page_size=page, num_pages=batch * (ctx_len // page + 8) + 8 + args.iters,
+                         max_requests=batch, max_tokens_per_request=ctx_len + 64 + args.iters)
+    last = [int(torch.argmax(runner.step([StepEntry(r, toks, [ctx_len - 1])])[0])) for r, toks in enumerate(prompts)]
+    keep = {name: getattr(ops, name) for name in ("attention_decode", "attention_decode_balanced", "gemv_qkv_rope",
+                                                  "gemv_ksplit", "gemv_bf16", "gemv_norm_bf16")}
+    nothing = lambda *a, **k: None
+    if args.without == "attention":
+        ops.attention_decode = ops.attention_decode_balanced = nothing
+    elif args.without == "qkv":
+        ops.gemv_qkv_rope = nothing
+    elif args.without == "down":
+        ops.gemv_ksplit = nothing
+    elif args.without in ("gate_up", "output", "vocabulary"):
+        def some(x, w, out, mode, *a, **k):
+            if (args.without == "gate_up" and mode == ops.SWIGLU_BF16) or (args.without == "output" and mode == ops.ADD_F32):
+                return
+            keep["gemv_bf16"](x, w, out, mode, *a, **k)
+
+        def some_norm(h, gain, eps, rows, w, out, mode, *a, **k):
+            if (args.without == "gate_up" and mode == ops.SWIGLU_BF16) or (args.without == "vocabulary" and mode == ops.STORE_F32):
+                return
+            keep["gemv_norm_bf16"](h, gain, eps, rows, w, out, mode, *a, **k)
+        ops.gemv_bf16, ops.gemv_norm_bf16 = some, some_norm
+    toks = runner.greedy_decode_on_device(list(range(batch)), last, 4)           # captures the step
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    runner.greedy_decode_on_device(list(range(batch)), toks[-1].tolist(), args.iters)
+    b.record()
+    torch.cuda.synchronize()
+    for name, fn in keep.items():
+        setattr(ops, name, fn)
+    ops.check_device_errors()
+    print(f"decode step, batch {batch}, context {ctx_len}, {raw['num_hidden_layers']} layers of {args.shape}"
+          f"{', WITHOUT ' + args.without + ' (time only)' if args.without else ''}: {a.elapsed_time(b) / args.iters:.4f} ms")
+
+
 def decode_fused(args) -> None:
     """One decode step of the whole model as ONE persistent kernel (csrc/decode_fused.cu) against the
     same step as the chain of per-part kernels, and where the fused kernel's time goes: block 0 stamps
@@ -334,6 +390,14 @@ def main() -> None:
     p.add_argument("--mode", default="bf16", choices=["bf16", "f32", "add", "swiglu"])
     p.add_argument("--milestones", action="store_true", help="also print block 0's timeline of one launch")
     p.set_defaults(fn=gemm_swap)
+    p = sub.add_parser("decode_step")
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--context", type=int, default=2048)
+    p.add_argument("--shape", default="llama-3.2-1b")
+    p.add_argument("--layers", type=int, default=0)
+    p.add_argument("--without", default="", choices=["", "attention", "qkv", "output", "gate_up", "down", "vocabulary"],
+                   help="leave one kind of kernel out of the step (wrong results; what it costs inside the chain)")
+    p.set_defaults(fn=decode_step)
     p = sub.add_parser("decode_fused")
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=2048)
