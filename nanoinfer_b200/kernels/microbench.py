@@ -174,7 +174,7 @@ def attention_decode(args) -> None:
     b, ctx, hq, hkv, hd, page = args.batch, args.context, args.q_heads, args.kv_heads, args.head_dim, args.page
     pages_per_seq = -(-ctx // page)
     kv_bytes = 2 * b * ctx * hkv * hd * 2
-    copies = max(2, min(16, -(-2 * L2_BYTES // kv_bytes)))
+    copies = args.copies or max(2, min(16, -(-2 * L2_BYTES // kv_bytes)))
     g = torch.Generator(device=DEV).manual_seed(0)
     n_pages = b * pages_per_seq
     caches = [(torch.randn(n_pages, hkv, page, hd, device=DEV, generator=g).to(torch.bfloat16),
@@ -415,6 +415,7 @@ def main() -> None:
         p.add_argument("--page", type=int, default=16)
         p.add_argument("--splits", type=int, default=0)
         p.add_argument("--kernel", default=None, choices=["tc", "mma"], help="prefill: insist on one kernel")
+        p.add_argument("--copies", type=int, default=0, help="decode: cache copies used in turn (default: enough to exceed L2; 1: the cache stays in L2)")
         p.add_argument("--balanced", action="store_true", help="decode: the kernel that deals the keys evenly over a fixed grid")
         p.add_argument("--ragged", action="store_true", help="decode: contexts from a quarter of --context up to it")
         p.add_argument("--scratch-merge", action="store_true",
