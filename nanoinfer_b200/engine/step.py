@@ -184,7 +184,7 @@ class ModelRunner:
     def __init__(self, config: ModelConfig, weights: Dict[str, torch.Tensor], *, dtype,
                  page_size: int = 16, num_pages=1024, max_requests: int = 8,
                  max_tokens_per_request: Optional[int] = None, max_portion_tokens: Optional[int] = None,
-                 device: str = "cuda:0", fused_decode: bool = False) -> None:
+                 device: str = "cuda:0", fused_decode: bool = False, beyond_model_limit: bool = False) -> None:
         """``num_pages``: pages of every cache group's pool, or one count per group (in the order
         the groups first appear in the schedule).  With one count, a windowed group gets no more
         pages than its requests can ever hold at once, if ``max_portion_tokens`` (the most tokens
@@ -192,7 +192,10 @@ class ModelRunner:
         ``fused_decode``: run steps of up to 8 single tokens as one persistent kernel
         (csrc/decode_fused.cu) where the model is a plain stack of attention + SwiGLU blocks.  Off by
         default: measured slower than the chain of per-part kernels (1.68 ms against 0.86 ms per
-        step at batch 8 of the 1B sizes; five grid barriers per layer are what it cannot hide)."""
+        step at batch 8 of the 1B sizes; five grid barriers per layer are what it cannot hide).
+        ``beyond_model_limit``: let a request grow past the model's max_position_embeddings, up to
+        ``max_tokens_per_request`` (for replaying given tokens: positions are computed, not looked up,
+        so nothing breaks there; serving keeps the model's limit)."""
         from .runtime import parse_dtype
         self.config = config
         self.rt = Runtime(device=torch.device(device), dtype=parse_dtype(dtype), page_size=page_size,
@@ -230,7 +233,8 @@ class ModelRunner:
         if max_tokens_per_request is None:
             full = [n for n, g in zip(pages_per_group, group_specs) if g.window is None] or pages_per_group
             max_tokens_per_request = min(config.max_position_embeddings, min(full) * page_size)
-        self.max_tokens_per_request = min(max_tokens_per_request, config.max_position_embeddings)
+        self.max_tokens_per_request = max_tokens_per_request if beyond_model_limit else \
+            min(max_tokens_per_request, config.max_position_embeddings)
         self.cache = CacheManager(group_specs, pages_per_group, page_size, max_requests, self.max_tokens_per_request)
         rt = self.rt
         for r, need in enumerate(needs):

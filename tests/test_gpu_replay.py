@@ -354,6 +354,44 @@ def test_trace_run_program(model_dirs, tmp_path):
             fed[e["id"]] = base + len(e["tokens"])
 
 
+def test_replay_goes_past_the_models_position_limit_and_serving_does_not(model_dirs, tmp_path):
+    """Tiny A says max_position_embeddings 128.  Replay feeds the tokens it is given all the same (positions are
+    computed, no table ends at the limit) and says so once on standard error; the logits past the limit
+    are the plain implementation's.  A runner built for serving refuses the step that would pass the limit."""
+    from nanoinfer_b200.engine import StepEntry, StepError
+    raw, w = load_plain(model_dirs["a"])
+    assert raw["max_position_embeddings"] == 128
+    reqs = _requests(raw, [150, 40], seed=8)
+    steps = ru.ragged(reqs)
+    out = tmp_path / "out"
+    proc = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dirs["a"], "--dtype",
+         "float32", "--out", str(out), "--max-tokens", str(ru.max_live_tokens(steps, 64))],
+        input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stderr.count("max_position_embeddings") == 1
+    want = ru.plain_logits(raw, w, reqs)
+    fed, checked_past = {}, 0
+    for s in steps:
+        n_want = sum(len(e["want"]) for e in s["entries"])
+        if n_want == 0:
+            continue
+        logits = torch.from_numpy(np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(n_want, raw["vocab_size"]))
+        r = 0
+        for e in s["entries"]:
+            base = fed.get(e["id"], 0)
+            for wpos in e["want"]:
+                torch.testing.assert_close(logits[r], want[e["id"]][base + wpos], rtol=ru.F32_RTOL, atol=ru.F32_ATOL)
+                checked_past += base + wpos >= 128
+                r += 1
+            fed[e["id"]] = base + len(e["tokens"])
+    assert checked_past == 150 - 128
+    runner = _runner(model_dirs["a"], "float32", 16, steps)
+    runner.step([StepEntry("x", reqs["r0"][:128], [127])])
+    with pytest.raises(StepError, match="limit of 128"):
+        runner.step([StepEntry("x", reqs["r0"][128:130], [1])])
+
+
 _LAYER_SIZES = {
     # width, q heads, kv heads, head size, feed-forward, vocabulary, rope factor, tied output
     "1b": (2048, 32, 8, 64, 8192, 128256, 32.0, True),
